@@ -1,0 +1,209 @@
+/*
+ * tensor_ops_b200.h -- C ABI of the B200 (sm_100a) operator library.
+ *
+ * The first block re-declares, with identical names, argument order, struct layouts and enum
+ * values, the entry points of the reference operator library that its Python operator classes
+ * bind through ctypes (tensor_ops/tensor_ops.h in Sakauma/onnx_translator).  A process that
+ * loads this library instead of the reference's tensor_ops.so gets the same functions; the one
+ * difference is WHERE Tensor.data lives: it is a CUDA device pointer (or managed memory, see
+ * tops_set_memory_mode), and every operator runs asynchronously on the library's stream.
+ *
+ * The second block (tops_*) is additive: transfers, streams, errors, zero-copy views and
+ * fused operators that the reference has no counterpart for.
+ *
+ * There is no CPU fallback anywhere: without a usable CUDA device every call records an error
+ * (tops_last_error) and create_tensor returns NULL.
+ */
+#ifndef TENSOR_OPS_B200_H
+#define TENSOR_OPS_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* ---- types: tensor_ops/tensor_ops.h:10-54 ------------------------------------------------ */
+
+/* tensor_ops/tensor_ops.h:10-23 (same numeric codes; Python mirrors them in nn/__init__.py:20-34) */
+typedef enum {
+    DTYPE_FLOAT8_E4M3 = 0,
+    DTYPE_FLOAT8_E5M2 = 1,
+    DTYPE_FLOAT16     = 2,
+    DTYPE_BFLOAT16    = 3,
+    DTYPE_FLOAT32     = 4,
+    DTYPE_FLOAT64     = 5,
+    DTYPE_INT4        = 6,   /* one value per byte, low nibble, sign-extended on read */
+    DTYPE_INT8        = 7,
+    DTYPE_UINT8       = 8,
+    DTYPE_INT16       = 9,
+    DTYPE_INT32       = 10,
+    DTYPE_INT64       = 11
+} DataType;
+
+/* tensor_ops/tensor_ops.h:28-34.  Dense, row-major, no strides.  `data` is device memory;
+   shape/ndim/size/dtype are host-readable. */
+typedef struct {
+    void*    data;
+    int*     shape;
+    int      ndim;
+    size_t   size;
+    DataType dtype;
+} Tensor;
+
+/* tensor_ops/tensor_ops.h:39-44.  Host arrays borrowed for the duration of the call.
+   pads = [top, left, bottom, right] (only top and left are read, as in the reference),
+   strides = [h, w], dilations = [h, w]. */
+typedef struct {
+    int* pads;
+    int* strides;
+    int* dilations;
+    int  group;
+} ConvParams;
+
+/* tensor_ops/tensor_ops.h:49-54 */
+typedef struct {
+    int* pads;
+    int* strides;
+    int* dilations;
+    int* kernel_shape;
+} PoolParams;
+
+/* ---- reference entry points ------------------------------------------------------------------ */
+
+/* tensor_ops/tensor_ops.h:70 (tensor_ops.c:357-433).  Allocates from the current device's
+   stream-ordered pool and zero-fills, like the reference's calloc.  NULL on failure. */
+Tensor* create_tensor(int* shape, int ndim, DataType dtype);
+
+/* tensor_ops/tensor_ops.h:77 (tensor_ops.c:440-450).  Drops one reference; the memory returns to
+   the pool when the last reference (views included) is gone.  NULL is ignored. */
+void free_tensor(Tensor* tensor);
+
+/* tensor_ops/tensor_ops.h:91 (tensor_ops.c:763-807).  Builds the 4097-entry cosine table on the
+   host and uploads it to the current device once.  cos_forward calls it on demand. */
+void init_cos_lut(void);
+
+/* tensor_ops/tensor_ops.h:85, 99, 107 (tensor_ops.c:708-757, 840-854).  input->size must equal
+   output->size; otherwise nothing is computed, the output is zero-filled and an error recorded. */
+void relu_forward(const Tensor* input, Tensor* output);
+void cos_forward(const Tensor* input, Tensor* output);
+void abs_forward(const Tensor* input, Tensor* output);
+
+/* tensor_ops/tensor_ops.h:116-143 (tensor_ops.c:864-997).  The output dtype selects the
+   arithmetic: integer outputs use saturating int64 arithmetic on round-to-nearest-even inputs,
+   float64 outputs use double, other float outputs round the double result once more.
+   Superset of the reference: an operand whose size differs from the output's is broadcast
+   against the output shape (numpy rules, trailing dimensions aligned) instead of being rejected. */
+void add_forward(const Tensor* A, const Tensor* B, Tensor* O);
+void sub_forward(const Tensor* A, const Tensor* B, Tensor* O);
+void mul_forward(const Tensor* A, const Tensor* B, Tensor* O);
+void div_forward(const Tensor* A, const Tensor* B, Tensor* O);
+
+/* tensor_ops/tensor_ops.h:149, 155 (tensor_ops.c:999-1034).
+   Quantize:   y = saturate(rint(x / scale) + zero_point), scale == 0 -> zero_point; fp8 outputs
+               encode that integer-valued result.
+   Dequantize: y = (x - zero_point) * scale.
+   Scale / ZeroPoint may be full-size (reference behaviour) or any shape that broadcasts against
+   Y (e.g. [1], or [1,C,1,1] for per-axis). */
+void quantize_linear_forward(const Tensor* X, const Tensor* Scale, const Tensor* ZeroPoint, Tensor* Y);
+void dequantize_linear_forward(const Tensor* X, const Tensor* Scale, const Tensor* ZeroPoint, Tensor* Y);
+
+/* tensor_ops/tensor_ops.h:161 (tensor_ops.c:1036-1114).  NCHW input, weights [M, C/group, KH, KW],
+   optional bias [M] (NULL or NULL data = none), Y pre-shaped by the caller. */
+void conv2d_forward(const Tensor* X, const Tensor* W, const Tensor* B, Tensor* Y, ConvParams* params);
+
+/* tensor_ops/tensor_ops.h:166 (tensor_ops.c:1116-1165).  NCHW; padding taps are skipped. */
+void max_pool_forward(const Tensor* X, Tensor* Y, PoolParams* params);
+
+/* tensor_ops/tensor_ops.h:173 (tensor_ops.c:1167-1228).  Y = alpha * op(A) * op(B) + beta * C,
+   C optional: scalar, 1-D of length N (per column) or M (per row), or >= 2-D with size-1
+   broadcast on either of its last two dimensions. */
+void gemm_forward(const Tensor* A, const Tensor* B, const Tensor* C, Tensor* Y,
+                  float alpha, float beta, int transA, int transB);
+
+/* tensor_ops/tensor_ops.h:179 (tensor_ops.c:1231-1270).  Softmax along `axis` (negative counts
+   from the end). */
+void softmax_forward(const Tensor* input, Tensor* output, int axis);
+
+/* tensor_ops/tensor_ops.h:210, 216 (tensor_ops.c:1289-1299).  Byte copy between equal-size
+   tensors (device to device). */
+void flatten_forward(const Tensor* input, Tensor* output);
+void reshape_forward(const Tensor* input, Tensor* output);
+
+/* ---- additive interface (no counterpart in the reference) -------------------------------------- */
+
+/* Error codes kept by the library (sticky until cleared; the first error wins). */
+enum {
+    TOPS_OK = 0,
+    TOPS_ERR_INVALID = 1,      /* null tensor, size/shape mismatch, unsupported attribute */
+    TOPS_ERR_CUDA = 2,         /* a CUDA runtime call failed (message holds its text)     */
+    TOPS_ERR_NO_DEVICE = 3,    /* no usable CUDA device                                   */
+    TOPS_ERR_OOM = 4,
+    TOPS_ERR_UNSUPPORTED = 5,
+    TOPS_ERR_DEVICE_TIMEOUT = 6 /* a bounded device-side wait expired                     */
+};
+int         tops_last_error(void);
+const char* tops_last_error_message(void);
+void        tops_clear_error(void);
+
+/* Device and stream of the calling thread.  Default device: $TOPS_DEVICE, else $LOCAL_RANK,
+   else 0.  Each device has one library-owned non-blocking stream; tops_set_stream substitutes
+   a caller stream (cudaStream_t passed as void*), NULL restores the library's own. */
+int   tops_set_device(int device);
+int   tops_get_device(void);
+int   tops_device_count(void);
+void* tops_get_stream(void);
+int   tops_set_stream(void* cuda_stream);
+int   tops_sync(void);
+
+/* 0 (default): cudaMallocAsync device memory.  1: CUDA managed memory plus a stream
+   synchronise at the end of every operator, so that an unmodified host-side caller which
+   memmove()s into Tensor.data and reads results back through the pointer keeps working. */
+int tops_set_memory_mode(int managed);
+
+/* Like create_tensor without the zero fill (operators overwrite the whole output). */
+Tensor* tops_create_uninit(const int* shape, int ndim, DataType dtype);
+/* Describe device memory owned by someone else (e.g. a framework tensor); never freed here. */
+Tensor* tops_wrap(void* device_ptr, const int* shape, int ndim, DataType dtype);
+/* Zero-copy reshape: a new Tensor header sharing base's memory and keeping it alive.
+   The element count must match.  This is Flatten / Reshape without the copy. */
+Tensor* tops_view(Tensor* base, const int* shape, int ndim);
+/* Sub-range along dimension 0: rows [row_begin, row_begin + row_count) as a view (shards). */
+Tensor* tops_slice_rows(Tensor* base, int row_begin, int row_count);
+void    tops_retain(Tensor* tensor);
+
+/* Host <-> device transfers on the current stream.  Upload returns after enqueueing when `host`
+   is pinned (tops_host_alloc); download synchronises the stream before returning. */
+int   tops_upload(Tensor* dst, const void* host, size_t nbytes);
+int   tops_download(const Tensor* src, void* host, size_t nbytes);
+int   tops_download_async(const Tensor* src, void* host, size_t nbytes);
+void* tops_host_alloc(size_t nbytes);
+void  tops_host_free(void* host);
+size_t tops_dtype_size(DataType dtype);
+
+/* Per-axis Q/DQ with 1-D scale / zero point of length shape[axis] (what the reference's Python
+   class builds by reshaping, nn/Operators.py:439-445). */
+void tops_quantize_linear_axis_forward(const Tensor* X, const Tensor* Scale, const Tensor* ZeroPoint,
+                                       Tensor* Y, int axis);
+void tops_dequantize_linear_axis_forward(const Tensor* X, const Tensor* Scale, const Tensor* ZeroPoint,
+                                         Tensor* Y, int axis);
+
+/* Device-side exhaustive codec self-check: encodes every float32 bit pattern with the fast
+   (hardware-convert) encoder and with the bit-level restatement of the reference encoder and
+   returns the number of disagreements (NaN inputs excluded), or -1 on error. */
+long long tops_selftest_encoder(DataType dtype);
+
+/* Host-only (no CUDA call): the collapsed broadcast plan of one operand against an output shape:
+   nd collapsed dimensions with their sizes and the operand's element strides (0 = broadcast);
+   flat = 1 when the operand has the output's element count and is read at the output index.
+   Returns 0 when the shapes do not broadcast.  Used by the CPU-side tests. */
+int tops_debug_plan_broadcast(const int* out_shape, int out_ndim, const int* in_shape, int in_ndim,
+                              int* nd, unsigned* sizes, int* strides, int* flat);
+
+const char* tops_version(void);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* TENSOR_OPS_B200_H */

@@ -1,0 +1,138 @@
+// Gemm: Y = alpha * op(A) * op(B) + beta * C (tensor_ops.c:1167-1228).
+//
+// This file holds the entry point, the bias-broadcast rules and the exact path: a shared-memory
+// tiled kernel that accumulates in double in increasing-k order, i.e. the reference's own
+// summation order, for every dtype combination.  Its results are bit-identical to the reference.
+// Tensor-core paths (gemm_tc.cu) take over for the 16-bit and 8-bit float inputs they support.
+#include "common.cuh"
+#include "gemm_common.cuh"
+
+namespace tops {
+
+constexpr int kTile = 64;      // output tile edge
+constexpr int kTileK = 16;
+constexpr int kPerThread = 4;  // 16 x 16 threads, 4 x 4 outputs each
+
+template <bool EXACT_PRODUCTS>
+__global__ void __launch_bounds__(256) gemm_exact_kernel(const void* __restrict__ A, const void* __restrict__ B,
+                                                          void* __restrict__ Y, int da, int db, int dy,
+                                                          GemmShape g, BiasView bias, double alpha, double beta) {
+    __shared__ double sa[kTileK][kTile + 1];
+    __shared__ double sb[kTileK][kTile + 1];
+    const int tx = threadIdx.x & 15, ty = threadIdx.x >> 4;
+    const int m0 = blockIdx.y * kTile, n0 = blockIdx.x * kTile;
+    double acc[kPerThread][kPerThread] = {};
+
+    for (int k0 = 0; k0 < g.K; k0 += kTileK) {
+        // stage a kTileK x kTile slab of op(A) and op(B), zero beyond the edges
+        for (int e = threadIdx.x; e < kTileK * kTile; e += 256) {
+            int kk, mm;
+            if (g.transA) { mm = e % kTile; kk = e / kTile; } else { kk = e % kTileK; mm = e / kTileK; }
+            const int m = m0 + mm, k = k0 + kk;
+            double v = 0.0;
+            if (m < g.M && k < g.K) v = load_f64_rt(A, da, g.transA ? (size_t)k * g.lda + m : (size_t)m * g.lda + k);
+            sa[kk][mm] = v;
+        }
+        for (int e = threadIdx.x; e < kTileK * kTile; e += 256) {
+            int kk, nn;
+            if (g.transB) { kk = e % kTileK; nn = e / kTileK; } else { nn = e % kTile; kk = e / kTile; }
+            const int n = n0 + nn, k = k0 + kk;
+            double v = 0.0;
+            if (n < g.N && k < g.K) v = load_f64_rt(B, db, g.transB ? (size_t)n * g.ldb + k : (size_t)k * g.ldb + n);
+            sb[kk][nn] = v;
+        }
+        __syncthreads();
+        #pragma unroll
+        for (int kk = 0; kk < kTileK; kk++) {
+            double av[kPerThread], bv[kPerThread];
+            #pragma unroll
+            for (int i = 0; i < kPerThread; i++) { av[i] = sa[kk][ty * kPerThread + i]; bv[i] = sb[kk][tx * kPerThread + i]; }
+            #pragma unroll
+            for (int i = 0; i < kPerThread; i++)
+                #pragma unroll
+                for (int j = 0; j < kPerThread; j++) {
+                    // products of float32-exact inputs are exact in double, so the fused form
+                    // rounds exactly like "multiply, then add"; otherwise keep two roundings
+                    if (EXACT_PRODUCTS) acc[i][j] = fma(av[i], bv[j], acc[i][j]);
+                    else acc[i][j] = __dadd_rn(acc[i][j], __dmul_rn(av[i], bv[j]));
+                }
+        }
+        __syncthreads();
+    }
+    #pragma unroll
+    for (int i = 0; i < kPerThread; i++)
+        #pragma unroll
+        for (int j = 0; j < kPerThread; j++) {
+            const int m = m0 + ty * kPerThread + i, n = n0 + tx * kPerThread + j;
+            if (m >= g.M || n >= g.N) continue;
+            double r = __dmul_rn(alpha, acc[i][j]);
+            if (bias.mode != kBiasNone) {
+                const long long ci = bias_index(bias, m, n);
+                const double cv = ci >= 0 ? load_f64_rt(bias.ptr, bias.dtype, (size_t)ci) : 0.0;
+                r = __dadd_rn(r, __dmul_rn(beta, cv));
+            }
+            store_f64_rt(Y, dy, (size_t)m * g.N + n, r);
+        }
+}
+
+BiasView make_bias_view(const Tensor* C, int M, int N) {
+    BiasView b;
+    b.ptr = nullptr; b.dtype = DTYPE_FLOAT32; b.mode = kBiasNone; b.rows = 1; b.cols = 1;
+    if (!C || !C->data) return b;
+    b.ptr = C->data;
+    b.dtype = (int)C->dtype;
+    if (C->size == 1) { b.mode = kBiasScalar; return b; }
+    if (C->ndim == 1) {
+        if (C->shape[0] == N) b.mode = kBiasPerColumn;        // tested first: wins when M == N
+        else if (C->shape[0] == M) b.mode = kBiasPerRow;
+        else b.mode = kBiasZero;                               // the reference adds beta * 0
+        return b;
+    }
+    b.mode = kBiasMatrix;
+    b.rows = C->shape[C->ndim - 2];
+    b.cols = C->shape[C->ndim - 1];
+    return b;
+}
+
+bool gemm_exact(const Tensor* A, const Tensor* B, Tensor* Y, const GemmShape& g, const BiasView& bias,
+                float alpha, float beta) {
+    DeviceState* st = acquire_device();
+    if (!st) return false;
+    dim3 grid((g.N + kTile - 1) / kTile, (g.M + kTile - 1) / kTile);
+    const bool exact = dtype_exact_in_f32((int)A->dtype) && dtype_exact_in_f32((int)B->dtype);
+    if (exact) gemm_exact_kernel<true><<<grid, 256, 0, current_stream()>>>(A->data, B->data, Y->data, (int)A->dtype, (int)B->dtype,
+                                                                           (int)Y->dtype, g, bias, (double)alpha, (double)beta);
+    else gemm_exact_kernel<false><<<grid, 256, 0, current_stream()>>>(A->data, B->data, Y->data, (int)A->dtype, (int)B->dtype,
+                                                                      (int)Y->dtype, g, bias, (double)alpha, (double)beta);
+    return TOPS_CHECK_LAUNCH("gemm_forward");
+}
+
+}  // namespace tops
+
+using namespace tops;
+
+TOPS_API void gemm_forward(const Tensor* A, const Tensor* B, const Tensor* C, Tensor* Y,
+                           float alpha, float beta, int transA, int transB) {
+    if (!A || !B || !Y || !A->data || !B->data || !Y->data || A->ndim != 2 || B->ndim != 2) {
+        set_error(TOPS_ERR_INVALID, "gemm_forward: null tensor or operands that are not 2-D");
+        zero_fill(Y);
+        return;
+    }
+    GemmShape g;
+    g.transA = transA ? 1 : 0; g.transB = transB ? 1 : 0;
+    g.M = transA ? A->shape[1] : A->shape[0];
+    g.K = transA ? A->shape[0] : A->shape[1];
+    g.N = transB ? B->shape[0] : B->shape[1];
+    g.lda = A->shape[1]; g.ldb = B->shape[1];
+    const int kb = transB ? B->shape[1] : B->shape[0];
+    if (kb != g.K || Y->size != (size_t)g.M * (size_t)g.N) {
+        set_error(TOPS_ERR_INVALID, "gemm_forward: inner dimensions differ or Y is not M x N");
+        zero_fill(Y);
+        return;
+    }
+    if (Y->size == 0) return;
+    const BiasView bias = make_bias_view(C, g.M, g.N);
+    if (!gemm_tensor_core(A, B, Y, g, bias, alpha, beta))       // false: not a case it covers
+        gemm_exact(A, B, Y, g, bias, alpha, beta);
+    finish_op();
+}

@@ -1,0 +1,49 @@
+// Types shared by the Gemm / Conv entry points and their tensor-core kernels.
+#pragma once
+
+#include "common.cuh"
+
+namespace tops {
+
+struct GemmShape {
+    int M, N, K;
+    int lda, ldb;          // row lengths of A and B as stored
+    int transA, transB;
+};
+
+// How C is broadcast over Y (tensor_ops.c:1194-1222).
+enum BiasMode { kBiasNone = 0, kBiasScalar = 1, kBiasPerColumn = 2, kBiasPerRow = 3, kBiasMatrix = 4, kBiasZero = 5 };
+
+struct BiasView {
+    const void* ptr;
+    int dtype;
+    int mode;
+    int rows, cols;        // last two dims of C for kBiasMatrix
+};
+
+// Element index of C for output (m, n); -1 when the reference would add zero.
+__host__ __device__ inline long long bias_index(const BiasView& b, int m, int n) {
+    switch (b.mode) {
+        case kBiasScalar:    return 0;
+        case kBiasPerColumn: return n;
+        case kBiasPerRow:    return m;
+        case kBiasMatrix: {
+            const int r = b.rows == 1 ? 0 : m, c = b.cols == 1 ? 0 : n;
+            return (r < b.rows && c < b.cols) ? (long long)r * b.cols + c : -1;
+        }
+        default:             return -1;
+    }
+}
+
+BiasView make_bias_view(const Tensor* C, int M, int N);
+
+// Exact double-accumulating path (any dtypes).
+bool gemm_exact(const Tensor* A, const Tensor* B, Tensor* Y, const GemmShape& g, const BiasView& bias,
+                float alpha, float beta);
+
+// Tensor-core path.  Returns false when the case is outside what it covers (caller falls back
+// to the exact kernel, which is still a GPU kernel of this library).
+bool gemm_tensor_core(const Tensor* A, const Tensor* B, Tensor* Y, const GemmShape& g, const BiasView& bias,
+                      float alpha, float beta);
+
+}  // namespace tops

@@ -1,0 +1,234 @@
+// QuantizeLinear / DequantizeLinear (tensor_ops.c:999-1034), per tensor and per axis.
+//
+// The reference reads X, scale and zero point at the same flat index, so its caller materialises
+// scale and zero point at full size.  Here they are broadcast operands: a scalar, a [1,C,1,1]
+// tensor or a full-size tensor all take the same kernel, and only X and Y stream through HBM.
+#include "elementwise.cuh"
+
+namespace tops {
+
+// ---- Quantize ------------------------------------------------------------------------------------------
+// Reference arithmetic: r = (s != 0) ? rint(x / s) + z : z, all in double, then the generic store
+// (integers: rint again + saturate; fp8: encode the integer-valued r).
+//
+// Fast path (x, s exact in float32; z a small integer): rint of the DOUBLE quotient equals rintf of
+// the correctly rounded FLOAT quotient unless a half-integer lies within one float ulp of it; only
+// those rare elements (and |q| >= 2^22) take the double division.
+template <int DO>
+__device__ __forceinline__ typename Storage<DO>::type quantize_fast(float x, float s, float z) {
+    if (s == 0.0f) return from_f32<DO>(z);
+    const float q = __fdiv_rn(x, s);
+    const float r = rintf(q);
+    const float aq = fabsf(q);
+    const float gap = 0.5f - fabsf(__fsub_rn(q, r));          // distance of q to the nearest tie
+    if (!(aq < 4194304.0f) || gap <= aq * 4.76837158e-7f) {   // 2^-21: two ulps of margin
+        const double rd = __dadd_rn(rint(__ddiv_rn((double)x, (double)s)), (double)z);
+        return from_f64<DO>(rd);
+    }
+    const float res = __fadd_rn(r, z);                          // exact: both are small integers
+    if constexpr (DO == DTYPE_INT8)       return (int8_t)min(max(__float2int_rn(res), -128), 127);
+    else if constexpr (DO == DTYPE_UINT8) return (uint8_t)min(max(__float2int_rn(res), 0), 255);
+    else return from_f32<DO>(res);
+}
+
+template <int DX, int DS, int DZ, int DO>
+struct QuantizeBody {
+    static constexpr int kV = vec_width(dtype_bytes(DX), dtype_bytes(DO), 1);
+    Geometry g;
+    Operand x, s, z;
+    void* out;
+    bool x_vec, s_vec, z_vec, o_vec;
+    __device__ __forceinline__ void operator()(uint32_t i0, uint32_t nv) const {
+        Run<typename Storage<DX>::type, kV> rx;
+        Run<typename Storage<DS>::type, kV> rs;
+        Run<typename Storage<DZ>::type, kV> rz;
+        Run<typename Storage<DO>::type, kV> ro;
+        fetch<DX, kV>(g, x, i0, nv, x_vec, rx);
+        fetch<DS, kV>(g, s, i0, nv, s_vec, rs);
+        fetch<DZ, kV>(g, z, i0, nv, z_vec, rz);
+        #pragma unroll
+        for (int j = 0; j < kV; j++) {
+            if constexpr (dtype_exact_in_f32(DX) && dtype_exact_in_f32(DS) && dtype_is_narrow_int(DZ)) {
+                ro.v[j] = quantize_fast<DO>(to_f32<DX>(rx.v[j]), to_f32<DS>(rs.v[j]), to_f32<DZ>(rz.v[j]));
+            } else {
+                const double sv = to_f64<DS>(rs.v[j]), zv = to_f64<DZ>(rz.v[j]);
+                double r = zv;
+                if (sv != 0.0) r = __dadd_rn(rint(__ddiv_rn(to_f64<DX>(rx.v[j]), sv)), zv);
+                ro.v[j] = from_f64<DO>(r);
+            }
+        }
+        put<DO, kV>(out, i0, nv, o_vec, ro);
+    }
+};
+
+// ---- Dequantize ----------------------------------------------------------------------------------------
+// Reference arithmetic: (x - z) * s in double, rounded once on store.  In float32 the same bits
+// come out whenever x - z is exact in float32 (8-bit integers, e4m3 codes, any x with z == 0):
+// the double product of a <= 24-bit difference and a 24-bit scale is exact, so a single
+// correctly rounded float multiply reproduces "exact product, one rounding".
+template <int DX, int DS, int DZ, int DO>
+struct DequantizeBody {
+    static constexpr int kV = vec_width(dtype_bytes(DX), dtype_bytes(DO), 1);
+    static constexpr bool kDiffExact = dtype_exact_in_f32(DX) && dtype_exact_in_f32(DZ) && dtype_exact_in_f32(DS) &&
+        DX != DTYPE_FLOAT8_E5M2 && DZ != DTYPE_FLOAT8_E5M2 && DX != DTYPE_FLOAT16 && DZ != DTYPE_FLOAT16 &&
+        DX != DTYPE_BFLOAT16 && DZ != DTYPE_BFLOAT16 && DX != DTYPE_FLOAT32 && DZ != DTYPE_FLOAT32 &&
+        DO != DTYPE_FLOAT64 && !dtype_is_int(DO);
+    Geometry g;
+    Operand x, s, z;
+    void* out;
+    bool x_vec, s_vec, z_vec, o_vec;
+    __device__ __forceinline__ void operator()(uint32_t i0, uint32_t nv) const {
+        Run<typename Storage<DX>::type, kV> rx;
+        Run<typename Storage<DS>::type, kV> rs;
+        Run<typename Storage<DZ>::type, kV> rz;
+        Run<typename Storage<DO>::type, kV> ro;
+        fetch<DX, kV>(g, x, i0, nv, x_vec, rx);
+        fetch<DS, kV>(g, s, i0, nv, s_vec, rs);
+        fetch<DZ, kV>(g, z, i0, nv, z_vec, rz);
+        #pragma unroll
+        for (int j = 0; j < kV; j++) {
+            if constexpr (kDiffExact) {
+                const float d = __fsub_rn(to_f32<DX>(rx.v[j]), to_f32<DZ>(rz.v[j]));
+                ro.v[j] = from_f32<DO>(__fmul_rn(d, to_f32<DS>(rs.v[j])));
+            } else if constexpr (dtype_exact_in_f32(DX) && dtype_exact_in_f32(DS) && dtype_exact_in_f32(DZ) &&
+                                 DO != DTYPE_FLOAT64 && !dtype_is_int(DO)) {
+                const float zv = to_f32<DZ>(rz.v[j]);
+                if (zv == 0.0f) {
+                    ro.v[j] = from_f32<DO>(__fmul_rn(to_f32<DX>(rx.v[j]), to_f32<DS>(rs.v[j])));
+                } else {
+                    const double d = __dsub_rn(to_f64<DX>(rx.v[j]), (double)zv);
+                    ro.v[j] = from_f64<DO>(__dmul_rn(d, to_f64<DS>(rs.v[j])));
+                }
+            } else {
+                const double d = __dsub_rn(to_f64<DX>(rx.v[j]), to_f64<DZ>(rz.v[j]));
+                ro.v[j] = from_f64<DO>(__dmul_rn(d, to_f64<DS>(rs.v[j])));
+            }
+        }
+        put<DO, kV>(out, i0, nv, o_vec, ro);
+    }
+};
+
+// ---- any dtype combination -------------------------------------------------------------------------------
+template <bool QUANTIZE>
+struct QdqGenericBody {
+    static constexpr int kV = 1;
+    Geometry g;
+    Operand x, s, z;
+    void* out;
+    int dx, ds, dz, dout;
+    __device__ __forceinline__ void operator()(uint32_t i, uint32_t) const {
+        uint32_t p;
+        const double xv = load_f64_rt(x.ptr, dx, x.flat ? i : operand_offset(g, x, i, p));
+        const double sv = load_f64_rt(s.ptr, ds, s.flat ? i : operand_offset(g, s, i, p));
+        const double zv = load_f64_rt(z.ptr, dz, z.flat ? i : operand_offset(g, z, i, p));
+        double r;
+        if constexpr (QUANTIZE) { r = zv; if (sv != 0.0) r = __dadd_rn(rint(__ddiv_rn(xv, sv)), zv); }
+        else r = __dmul_rn(__dsub_rn(xv, zv), sv);
+        store_f64_rt(out, dout, i, r);
+    }
+};
+
+template <template <int, int, int, int> class Body, int DX, int DS, int DZ, int DO>
+static bool qdq_typed(const char* name, const Geometry& geom, Operand* ops, Tensor* y) {
+    const int bytes[3] = {dtype_bytes(DX), dtype_bytes(DS), dtype_bytes(DZ)};
+    return launch_elementwise(name, geom, ops, bytes, 3, y->data, dtype_bytes(DO), y->size,
+        [&](const Geometry& g, const Operand* l, void* out_ptr) {
+            Body<DX, DS, DZ, DO> b;
+            b.g = g; b.x = l[0]; b.s = l[1]; b.z = l[2]; b.out = out_ptr;
+            b.x_vec = aligned_to(l[0].ptr, (size_t)dtype_bytes(DX) * b.kV);
+            b.s_vec = aligned_to(l[1].ptr, (size_t)dtype_bytes(DS) * b.kV);
+            b.z_vec = aligned_to(l[2].ptr, (size_t)dtype_bytes(DZ) * b.kV);
+            b.o_vec = aligned_to(out_ptr, (size_t)dtype_bytes(DO) * b.kV);
+            return b;
+        });
+}
+
+// axis >= 0: Scale / ZeroPoint are 1-D of length Y.shape[axis]; axis < -64: plain broadcasting.
+constexpr int kNoAxis = -1000;
+
+template <bool QUANTIZE>
+static void qdq_forward(const char* name, const Tensor* x, const Tensor* s, const Tensor* z, Tensor* y, int axis) {
+    if (!x || !s || !z || !y || !x->data || !s->data || !z->data || !y->data) {
+        set_error(TOPS_ERR_INVALID, "%s: null tensor", name);
+        zero_fill(y);
+        return;
+    }
+    const int dx = (int)x->dtype, ds = (int)s->dtype, dz = (int)z->dtype, dout = (int)y->dtype;
+    if (!dtype_valid(dx) || !dtype_valid(ds) || !dtype_valid(dz) || !dtype_valid(dout)) { set_error(TOPS_ERR_INVALID, "%s: bad dtype", name); return; }
+
+    int axis_shape[16];
+    ShapeView sv{s->shape, s->ndim, s->size}, zv{z->shape, z->ndim, z->size};
+    if (axis != kNoAxis) {
+        const int nd = y->ndim;
+        if (axis < 0) axis += nd;
+        if (nd > 16 || axis < 0 || axis >= nd || s->size != (size_t)y->shape[axis] || (z->size != s->size && z->size != 1)) {
+            set_error(TOPS_ERR_INVALID, "%s: scale length does not match the axis", name);
+            zero_fill(y);
+            return;
+        }
+        for (int d = 0; d < nd; d++) axis_shape[d] = 1;
+        axis_shape[axis] = y->shape[axis];
+        sv = ShapeView{axis_shape, nd, s->size};
+        if (z->size == s->size) zv = ShapeView{axis_shape, nd, z->size};
+    }
+    Geometry geom;
+    Operand ops[3];
+    const ShapeView out{y->shape, y->ndim, y->size};
+    const ShapeView ins[3] = {{x->shape, x->ndim, x->size}, sv, zv};
+    if (!plan_broadcast(out, ins, 3, &geom, ops)) {
+        set_error(TOPS_ERR_INVALID, "%s: operand shapes do not broadcast to the output shape", name);
+        zero_fill(y);
+        return;
+    }
+    ops[0].ptr = x->data; ops[1].ptr = s->data; ops[2].ptr = z->data;
+
+    bool done = false;
+#define TOPS_Q(X, Z, O) if (!done && dx == X && ds == DTYPE_FLOAT32 && dz == Z && dout == O) { \
+        qdq_typed<QuantizeBody, X, DTYPE_FLOAT32, Z, O>(name, geom, ops, y); done = true; }
+#define TOPS_DQ(X, Z, O) if (!done && dx == X && ds == DTYPE_FLOAT32 && dz == Z && dout == O) { \
+        qdq_typed<DequantizeBody, X, DTYPE_FLOAT32, Z, O>(name, geom, ops, y); done = true; }
+    if (QUANTIZE) {
+#define TOPS_Q_SOURCES(Z, O) TOPS_Q(DTYPE_FLOAT32, Z, O) TOPS_Q(DTYPE_FLOAT16, Z, O) TOPS_Q(DTYPE_BFLOAT16, Z, O)
+        TOPS_Q_SOURCES(DTYPE_INT8, DTYPE_INT8) TOPS_Q_SOURCES(DTYPE_UINT8, DTYPE_UINT8)
+        TOPS_Q_SOURCES(DTYPE_FLOAT8_E4M3, DTYPE_FLOAT8_E4M3) TOPS_Q_SOURCES(DTYPE_FLOAT8_E5M2, DTYPE_FLOAT8_E5M2)
+        TOPS_Q_SOURCES(DTYPE_INT8, DTYPE_FLOAT8_E4M3) TOPS_Q_SOURCES(DTYPE_INT8, DTYPE_FLOAT8_E5M2)
+#undef TOPS_Q_SOURCES
+    } else {
+#define TOPS_DQ_TARGETS(X, Z) TOPS_DQ(X, Z, DTYPE_FLOAT32) TOPS_DQ(X, Z, DTYPE_FLOAT16) TOPS_DQ(X, Z, DTYPE_BFLOAT16)
+        TOPS_DQ_TARGETS(DTYPE_INT8, DTYPE_INT8) TOPS_DQ_TARGETS(DTYPE_UINT8, DTYPE_UINT8)
+        TOPS_DQ_TARGETS(DTYPE_FLOAT8_E4M3, DTYPE_FLOAT8_E4M3) TOPS_DQ_TARGETS(DTYPE_FLOAT8_E5M2, DTYPE_FLOAT8_E5M2)
+        TOPS_DQ_TARGETS(DTYPE_FLOAT8_E4M3, DTYPE_INT8) TOPS_DQ_TARGETS(DTYPE_FLOAT8_E5M2, DTYPE_INT8)
+        TOPS_DQ_TARGETS(DTYPE_INT32, DTYPE_INT32)
+#undef TOPS_DQ_TARGETS
+    }
+#undef TOPS_Q
+#undef TOPS_DQ
+    if (!done) {
+        const int bytes[3] = {dtype_bytes(dx), dtype_bytes(ds), dtype_bytes(dz)};
+        launch_elementwise(name, geom, ops, bytes, 3, y->data, dtype_bytes(dout), y->size,
+            [&](const Geometry& g, const Operand* l, void* out_ptr) {
+                QdqGenericBody<QUANTIZE> b;
+                b.g = g; b.x = l[0]; b.s = l[1]; b.z = l[2]; b.out = out_ptr;
+                b.dx = dx; b.ds = ds; b.dz = dz; b.dout = dout;
+                return b;
+            });
+    }
+    finish_op();
+}
+
+}  // namespace tops
+
+using namespace tops;
+
+TOPS_API void quantize_linear_forward(const Tensor* X, const Tensor* Scale, const Tensor* ZeroPoint, Tensor* Y) {
+    qdq_forward<true>("quantize_linear_forward", X, Scale, ZeroPoint, Y, kNoAxis);
+}
+TOPS_API void dequantize_linear_forward(const Tensor* X, const Tensor* Scale, const Tensor* ZeroPoint, Tensor* Y) {
+    qdq_forward<false>("dequantize_linear_forward", X, Scale, ZeroPoint, Y, kNoAxis);
+}
+TOPS_API void tops_quantize_linear_axis_forward(const Tensor* X, const Tensor* Scale, const Tensor* ZeroPoint, Tensor* Y, int axis) {
+    qdq_forward<true>("tops_quantize_linear_axis_forward", X, Scale, ZeroPoint, Y, axis);
+}
+TOPS_API void tops_dequantize_linear_axis_forward(const Tensor* X, const Tensor* Scale, const Tensor* ZeroPoint, Tensor* Y, int axis) {
+    qdq_forward<false>("tops_dequantize_linear_axis_forward", X, Scale, ZeroPoint, Y, axis);
+}

@@ -1,0 +1,164 @@
+// Relu, Abs and Cos (tensor_ops.c:708-757, 815-854).
+#include "elementwise.cuh"
+
+namespace tops {
+
+enum UnaryOp { kRelu = 0, kAbs = 1, kCos = 2 };
+
+// Table cosine: fold |x| into [0, 2pi), scale to table cells, interpolate linearly -- every step
+// in double with separate roundings (no fused multiply-add), multiply before divide.
+__device__ __forceinline__ double cos_by_table(double x, const double* __restrict__ lut) {
+    constexpr double kPi = 3.141592653589793238462643383279502884197;
+    constexpr double kTwoPi = 2.0 * kPi;
+    if (!isfinite(x)) return __longlong_as_double(0x7FF8000000000000ll);   // undefined upstream
+    const double ax = fabs(x);
+    double r;
+    if (ax < kTwoPi) r = ax;                                   // fmod is the identity here
+    else if (ax < 2.0 * kTwoPi) r = __dsub_rn(ax, kTwoPi);     // exact (Sterbenz), equals fmod
+    else r = fmod(ax, kTwoPi);
+    const double pos = __ddiv_rn(__dmul_rn(r, 4096.0), kTwoPi);
+    int k = (int)pos;
+    double w = __dsub_rn(pos, (double)k);
+    if (k >= 4096) { k = 4095; w = 0.0; }
+    const double lo = __ldg(lut + k), hi = __ldg(lut + k + 1);
+    return __dadd_rn(__dmul_rn(lo, __dsub_rn(1.0, w)), __dmul_rn(hi, w));
+}
+
+template <int DX, int DO, int OP>
+__device__ __forceinline__ typename Storage<DO>::type unary_elem(typename Storage<DX>::type s, const double* lut) {
+    if constexpr (OP == kCos) {
+        return from_f64<DO>(cos_by_table(to_f64<DX>(s), lut));
+    } else if constexpr (dtype_is_int(DX)) {                   // branch on the INPUT dtype
+        if constexpr (dtype_is_narrow_int(DX) && DO != DTYPE_INT64) {
+            const int v = to_i32_narrow<DX>(s);
+            const int r = (OP == kRelu) ? max(v, 0) : abs(v);
+            return from_i32<DO>(r);
+        } else {
+            const long long v = to_i64<DX>(s);
+            long long r;
+            if constexpr (OP == kRelu) r = v > 0 ? v : 0;
+            else r = (v == (long long)0x8000000000000000ull) ? 0x7FFFFFFFFFFFFFFFll : (v < 0 ? -v : v);
+            return from_i64<DO>(r);
+        }
+    } else if constexpr (DX == DTYPE_FLOAT64) {
+        const double v = s;
+        const double r = (OP == kRelu) ? (v > 0 ? v : 0.0) : fabs(v);
+        return from_f64<DO>(r);
+    } else {
+        const float v = to_f32<DX>(s);
+        const float r = (OP == kRelu) ? (v > 0 ? v : 0.0f) : fabsf(v);
+        if constexpr (dtype_is_int(DO) || DO == DTYPE_FLOAT64) return from_f64<DO>((double)r);
+        else return from_f32<DO>(r);
+    }
+}
+
+template <int DX, int DO, int OP>
+struct UnaryBody {
+    static constexpr int kV = vec_width(dtype_bytes(DX), dtype_bytes(DO), 1);
+    Geometry g;
+    Operand x;
+    void* out;
+    const double* lut;
+    bool x_vec, o_vec;
+    __device__ __forceinline__ void operator()(uint32_t i0, uint32_t nv) const {
+        Run<typename Storage<DX>::type, kV> in;
+        Run<typename Storage<DO>::type, kV> res;
+        fetch<DX, kV>(g, x, i0, nv, x_vec, in);
+        #pragma unroll
+        for (int j = 0; j < kV; j++) res.v[j] = unary_elem<DX, DO, OP>(in.v[j], lut);
+        put<DO, kV>(out, i0, nv, o_vec, res);
+    }
+};
+
+// Any dtype pair, one element per run, dtype switches at run time (uniform across the grid).
+template <int OP>
+struct UnaryGenericBody {
+    static constexpr int kV = 1;
+    const void* x;
+    void* out;
+    int dx, dout;
+    const double* lut;
+    __device__ __forceinline__ void operator()(uint32_t i, uint32_t) const {
+        if constexpr (OP == kCos) {
+            store_f64_rt(out, dout, i, cos_by_table(load_f64_rt(x, dx, i), lut));
+        } else if (dtype_is_int(dx)) {
+            const long long v = load_i64_rt(x, dx, i);
+            long long r;
+            if constexpr (OP == kRelu) r = v > 0 ? v : 0;
+            else r = (v == (long long)0x8000000000000000ull) ? 0x7FFFFFFFFFFFFFFFll : (v < 0 ? -v : v);
+            store_i64_rt(out, dout, i, r);
+        } else {
+            const double v = load_f64_rt(x, dx, i);
+            store_f64_rt(out, dout, i, (OP == kRelu) ? (v > 0 ? v : 0.0) : fabs(v));
+        }
+    }
+};
+
+template <int DX, int DO, int OP>
+static bool run_typed(const char* name, const Tensor* x, Tensor* y, const double* lut) {
+    Geometry geom;
+    Operand op;
+    ShapeView out{y->shape, y->ndim, y->size}, in{x->shape, x->ndim, x->size};
+    plan_broadcast(out, &in, 1, &geom, &op);
+    op.ptr = x->data;
+    const int bytes[1] = {dtype_bytes(DX)};
+    return launch_elementwise(name, geom, &op, bytes, 1, y->data, dtype_bytes(DO), y->size,
+        [&](const Geometry& g, const Operand* o, void* out_ptr) {
+            UnaryBody<DX, DO, OP> b;
+            b.g = g; b.x = o[0]; b.out = out_ptr; b.lut = lut;
+            b.x_vec = aligned_to(o[0].ptr, (size_t)dtype_bytes(DX) * b.kV);
+            b.o_vec = aligned_to(out_ptr, (size_t)dtype_bytes(DO) * b.kV);
+            return b;
+        });
+}
+
+template <int OP>
+static bool run_generic(const char* name, const Tensor* x, Tensor* y, const double* lut) {
+    Geometry geom;
+    Operand op;
+    ShapeView out{y->shape, y->ndim, y->size}, in{x->shape, x->ndim, x->size};
+    plan_broadcast(out, &in, 1, &geom, &op);
+    op.ptr = x->data;
+    const int bytes[1] = {dtype_bytes((int)x->dtype)};
+    const int dx = (int)x->dtype, dout = (int)y->dtype;
+    return launch_elementwise(name, geom, &op, bytes, 1, y->data, dtype_bytes(dout), y->size,
+        [&](const Geometry&, const Operand* o, void* out_ptr) {
+            UnaryGenericBody<OP> b;
+            b.x = o[0].ptr; b.out = out_ptr; b.dx = dx; b.dout = dout; b.lut = lut;
+            return b;
+        });
+}
+
+template <int OP>
+static void unary_forward(const char* name, const Tensor* x, Tensor* y) {
+    if (!x || !y || !x->data || !y->data || x->size != y->size) {
+        set_error(TOPS_ERR_INVALID, "%s: null tensor or size mismatch", name);
+        zero_fill(y);
+        return;
+    }
+    if (!dtype_valid((int)x->dtype) || !dtype_valid((int)y->dtype)) { set_error(TOPS_ERR_INVALID, "%s: bad dtype", name); return; }
+    const double* lut = nullptr;
+    if (OP == kCos) { lut = cos_lut_device(); if (!lut) return; }
+    const int dx = (int)x->dtype, dout = (int)y->dtype;
+    bool done = false, ok = true;
+#define TOPS_SAME(DT) if (!done && dx == DT && dout == DT) { ok = run_typed<DT, DT, OP>(name, x, y, lut); done = true; }
+    if (OP == kCos) {
+        TOPS_SAME(DTYPE_FLOAT32) TOPS_SAME(DTYPE_FLOAT16) TOPS_SAME(DTYPE_BFLOAT16) TOPS_SAME(DTYPE_FLOAT64)
+    } else {
+        TOPS_SAME(DTYPE_FLOAT8_E4M3) TOPS_SAME(DTYPE_FLOAT8_E5M2) TOPS_SAME(DTYPE_FLOAT16) TOPS_SAME(DTYPE_BFLOAT16)
+        TOPS_SAME(DTYPE_FLOAT32) TOPS_SAME(DTYPE_FLOAT64) TOPS_SAME(DTYPE_INT4) TOPS_SAME(DTYPE_INT8)
+        TOPS_SAME(DTYPE_UINT8) TOPS_SAME(DTYPE_INT16) TOPS_SAME(DTYPE_INT32) TOPS_SAME(DTYPE_INT64)
+    }
+#undef TOPS_SAME
+    if (!done) ok = run_generic<OP>(name, x, y, lut);
+    (void)ok;
+    finish_op();
+}
+
+}  // namespace tops
+
+using namespace tops;
+
+TOPS_API void relu_forward(const Tensor* input, Tensor* output) { unary_forward<kRelu>("relu_forward", input, output); }
+TOPS_API void abs_forward(const Tensor* input, Tensor* output)  { unary_forward<kAbs>("abs_forward", input, output); }
+TOPS_API void cos_forward(const Tensor* input, Tensor* output)  { unary_forward<kCos>("cos_forward", input, output); }

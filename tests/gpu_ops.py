@@ -1,0 +1,62 @@
+"""Runs operators on the GPU through the package's operator classes (which call the C ABI) and
+returns host arrays, with the same call shapes as ``oracle.HostOracle`` so a parity test is
+``assert_same_codes(gpu.op(...), port.op(...))``."""
+from __future__ import annotations
+
+import numpy as np
+
+from onnx_translator_b200 import nn
+from onnx_translator_b200.nn import Operators as ops
+
+_UNARY = {"relu": ops.RELU, "abs": ops.ABS, "cos": ops.COS}
+_BINARY = {"add": ops.ADD, "sub": ops.SUB, "mul": ops.MUL, "div": ops.DIV}
+
+
+def _t(arr, dt):
+    arr = np.asarray(arr)
+    return nn.Tensor(*arr.shape, dtype=dt, data=arr)
+
+
+def unary(op, x, x_dt, out_dt):
+    return _UNARY[op]([], [], dtype=out_dt).forward(_t(x, x_dt))["tensor"].numpy()
+
+
+def binary(op, a, a_dt, b, b_dt, out_dt):
+    return _BINARY[op]([], [], dtype=out_dt).forward(_t(a, a_dt), _t(b, b_dt))["tensor"].numpy()
+
+
+def quantize(x, x_dt, s, s_dt, z, z_dt, out_dt, axis=None):
+    node = ops.QuantizeLinear([], [], axis=1 if axis is None else axis, dtype=out_dt)
+    return node.forward(_t(x, x_dt), _t(s, s_dt), _t(z, z_dt))["tensor"].numpy()
+
+
+def dequantize(x, x_dt, s, s_dt, z, z_dt, out_dt):
+    return ops.DequantizeLinear([], [], dtype=out_dt).forward(_t(x, x_dt), _t(s, s_dt), _t(z, z_dt))["tensor"].numpy()
+
+
+def conv2d(x, x_dt, w, w_dt, b, b_dt, out_dt, pads, strides, dilations, group):
+    node = ops.Conv([], [], pads=list(pads), strides=list(strides), dilations=list(dilations), group=group, dtype=out_dt)
+    bias = None if b is None else _t(b, b_dt)
+    return node.forward(_t(x, x_dt), _t(w, w_dt), bias)["tensor"].numpy()
+
+
+def max_pool(x, x_dt, out_dt, kernel, pads, strides, dilations=(1, 1)):
+    node = ops.MaxPool([], [], kernel_shape=list(kernel), pads=list(pads), strides=list(strides), dtype=out_dt,
+                       dilations=list(dilations))
+    return node.forward(_t(x, x_dt))["tensor"].numpy()
+
+
+def gemm(a, a_dt, b, b_dt, c, c_dt, out_dt, alpha=1.0, beta=1.0, transA=0, transB=0):
+    node = ops.Gemm([], [], alpha=alpha, beta=beta, transA=transA, transB=transB, dtype=out_dt)
+    cc = None if c is None else _t(c, c_dt)
+    return node.forward(_t(a, a_dt), _t(b, b_dt), cc)["tensor"].numpy()
+
+
+def softmax(x, x_dt, out_dt, axis=-1):
+    return ops.Softmax([], [], axis=axis, dtype=out_dt).forward(_t(x, x_dt))["tensor"].numpy()
+
+
+def flatten(x, x_dt, out_shape, copy=True):
+    node = ops.Flatten([], [], axis=1, dtype=x_dt, copy=copy)
+    out = node.forward(_t(x, x_dt))["tensor"].numpy()
+    return out.reshape(out_shape)
