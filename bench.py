@@ -1,0 +1,436 @@
+#!/usr/bin/env python
+"""Benchmark of the tensor_ops hot path on B200.
+
+Workload (N = 1): the broadcast elementwise sweep -- Add/Sub/Mul/Div of A[64,512,1024] with B of
+shape [1,512,1], [1024] and [64,512,1024] over seven dtype pairs, Relu/Abs on the same shape over
+the five A dtypes, Cos on float32.  One "step" is one pass over all 95 operator calls.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+
+Prints ONE JSON line.  `value` is algorithmic GB/s of the whole job with inputs resident in HBM,
+`e2e` the same metric through the C ABI with pinned HOST buffers (H2D of both operands and D2H of
+the result inside the timed region), `roofline` the achieved bandwidth of the dominant kernel
+family against the measured HBM copy peak, `cpu_baseline` the reference C library timed on this
+machine's cores on a bounded slab of the same sweep.
+
+Under torchrun every rank runs the same sweep on its own GPU (weak scaling, no data-path
+collective); times are device-measured and the maximum over ranks is used.
+"""
+from __future__ import annotations
+
+import argparse
+import ctypes
+import json
+import os
+import sys
+import threading
+import time
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+FULL_ROWS = 64
+MID, INNER = 512, 1024
+BINARY_OPS = ("add", "sub", "mul", "div")
+# (A dtype, B dtype, output dtype): the reference's promotion gives float64 for int32 + float16
+DTYPE_PAIRS = (("float32", "float32", "float32"), ("float16", "float16", "float16"),
+               ("bfloat16", "bfloat16", "bfloat16"), ("int32", "int32", "int32"), ("int8", "int8", "int8"),
+               ("int8", "float32", "float32"), ("int32", "float16", "float64"))
+UNARY_DTYPES = ("float32", "float16", "bfloat16", "int32", "int8")
+ITEM = {"float32": 4, "float16": 2, "bfloat16": 2, "int32": 4, "int8": 1, "float64": 8}
+STORAGE = {"float32": np.float32, "float16": np.float16, "bfloat16": np.uint16, "int32": np.int32,
+           "int8": np.int8, "float64": np.float64}
+
+
+def b_shapes(rows):
+    return {"row": (1, MID, 1), "vec": (INNER,), "full": (rows, MID, INNER)}
+
+
+# ---- synthetic data (seeded; value distributions of the benchmark configuration) ---------------------
+def _bf16(x):
+    u = np.ascontiguousarray(x, dtype=np.float32).view(np.uint32).astype(np.uint64)
+    return ((u + 0x7FFF + ((u >> 16) & 1)) >> 16).astype(np.uint16)
+
+
+def make_a(rng, rows, dtype):
+    shape = (rows, MID, INNER)
+    if dtype == "int8":
+        return rng.integers(-11, 12, shape).astype(np.int8)           # products stay inside int8
+    if dtype == "int32":
+        return rng.integers(-1000, 1001, shape).astype(np.int32)
+    v = rng.uniform(-100, 100, shape).astype(np.float32)
+    return v if dtype == "float32" else (v.astype(np.float16) if dtype == "float16" else _bf16(v))
+
+
+def make_b(rng, shape, dtype, divisor):
+    if dtype in ("int8", "int32"):
+        hi = 11 if dtype == "int8" else 1000
+        v = rng.integers(1 if divisor else -hi, hi + 1, shape)
+        if divisor:
+            v = v * rng.choice([-1, 1], shape)
+        return v.astype(STORAGE[dtype])
+    v = rng.uniform(0.5, 100, shape) * rng.choice([-1, 1], shape) if divisor else rng.uniform(-100, 100, shape)
+    v = v.astype(np.float32)
+    return v if dtype == "float32" else (v.astype(np.float16) if dtype == "float16" else _bf16(v))
+
+
+def sweep_plan(rows):
+    """List of launches in an order that never uses the same big tensor twice in a row."""
+    n = rows * MID * INNER
+    plan = []
+    for op in BINARY_OPS:
+        for bname, bshape in b_shapes(rows).items():
+            for a_dt, b_dt, o_dt in DTYPE_PAIRS:
+                nbytes = n * (ITEM[a_dt] + ITEM[o_dt]) + (n * ITEM[b_dt] if bname == "full" else int(np.prod(bshape)) * ITEM[b_dt])
+                plan.append(dict(kind="binary", op=op, a=a_dt, b=b_dt, o=o_dt, bname=bname, divisor=(op == "div"), bytes=nbytes,
+                                 label=f"{op}[{bname}] {a_dt},{b_dt}->{o_dt}"))
+    for op in ("relu", "abs"):
+        for dt in UNARY_DTYPES:
+            plan.append(dict(kind="unary", op=op, a=dt, o=dt, bytes=n * 2 * ITEM[dt], label=f"{op} {dt}"))
+    plan.append(dict(kind="unary", op="cos", a="float32", o="float32", bytes=n * 8, label="cos float32"))
+    return plan
+
+
+def host_inputs(rows, seed=0):
+    rng = np.random.default_rng(seed)
+    a = {dt: make_a(rng, rows, dt) for dt in UNARY_DTYPES}
+    a_cos = rng.uniform(-10, 10, (rows, MID, INNER)).astype(np.float32)
+    b = {}
+    for bname, bshape in b_shapes(rows).items():
+        for dt in ("float32", "float16", "bfloat16", "int32", "int8"):
+            for divisor in (False, True):
+                b[(bname, dt, divisor)] = make_b(rng, bshape, dt, divisor)
+    return a, a_cos, b
+
+
+# ---- clocks -----------------------------------------------------------------------------------------
+class ClockSampler:
+    """Samples SM clock and throttle reasons of one GPU through NVML (read-only) while running."""
+
+    def __init__(self, index):
+        self.samples, self.reasons, self.max_mhz, self.ok = [], set(), None, False
+        self._stop = threading.Event()
+        try:
+            import pynvml
+            pynvml.nvmlInit()
+            self.nv = pynvml
+            self.h = pynvml.nvmlDeviceGetHandleByIndex(index)
+            self.max_mhz = int(pynvml.nvmlDeviceGetMaxClockInfo(self.h, pynvml.NVML_CLOCK_SM))
+            self.ok = True
+        except Exception:
+            self.ok = False
+        self.thread = threading.Thread(target=self._run, daemon=True)
+
+    def _run(self):
+        nv = self.nv
+        names = {0x2: "applications_clocks_setting", 0x4: "sw_power_cap", 0x8: "hw_slowdown", 0x10: "sync_boost",
+                 0x20: "sw_thermal_slowdown", 0x40: "hw_thermal_slowdown", 0x80: "hw_power_brake_slowdown",
+                 0x100: "display_clock_setting"}
+        while not self._stop.is_set():
+            try:
+                self.samples.append(int(nv.nvmlDeviceGetClockInfo(self.h, nv.NVML_CLOCK_SM)))
+                mask = int(nv.nvmlDeviceGetCurrentClocksThrottleReasons(self.h))
+                for bit, name in names.items():
+                    if mask & bit:
+                        self.reasons.add(name)
+            except Exception:
+                pass
+            self._stop.wait(0.1)
+
+    def __enter__(self):
+        if self.ok:
+            self.thread.start()
+        return self
+
+    def __exit__(self, *exc):
+        self._stop.set()
+        if self.ok:
+            self.thread.join(timeout=2)
+
+    def summary(self):
+        if not self.ok or not self.samples:
+            return {"sm_mhz": None, "sm_max_mhz": self.max_mhz, "reasons": ["nvml unavailable"]}
+        return {"sm_mhz": int(np.median(self.samples)), "sm_max_mhz": self.max_mhz, "reasons": sorted(self.reasons)}
+
+
+# ---- our arm ------------------------------------------------------------------------------------------
+def peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        with open(path) as f:
+            p = json.load(f)
+        return float(p["hbm_gbs"]), "measured"
+    return 6650.0, "fallback"
+
+
+def run_ours(args):
+    import torch
+    from onnx_translator_b200 import capi
+    from onnx_translator_b200.device import DeviceArray
+
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py: no CUDA device (there is no CPU fallback; use --impl reference for the CPU baseline)")
+    torch.cuda.set_device(local)
+    if world > 1:
+        import torch.distributed as dist
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    lib = capi.load()
+    if lib.tops_set_device(local):
+        capi.check(lib)
+    lib.init_cos_lut()
+    stream = torch.cuda.ExternalStream(lib.tops_get_stream(), device=local)
+
+    rows = FULL_ROWS
+    plan = sweep_plan(rows)
+    a_host, a_cos_host, b_host = host_inputs(rows, seed=rank)
+    dev_a = {dt: DeviceArray.from_numpy(v, dt) for dt, v in a_host.items()}
+    dev_cos = DeviceArray.from_numpy(a_cos_host, "float32")
+    dev_b = {k: DeviceArray.from_numpy(v, k[1]) for k, v in b_host.items()}
+    dev_out = {dt: DeviceArray.empty((rows, MID, INNER), dt) for dt in ("float32", "float16", "bfloat16", "int32", "int8", "float64")}
+    capi.check(lib)
+
+    def fn_of(item):
+        return getattr(lib, item["op"] + "_forward")
+
+    def launch(item):
+        out = dev_out[item["o"]].handle
+        if item["kind"] == "binary":
+            fn_of(item)(dev_a[item["a"]].handle, dev_b[(item["bname"], item["b"], item["divisor"])].handle, out)
+        else:
+            src = dev_cos if item["op"] == "cos" else dev_a[item["a"]]
+            fn_of(item)(src.handle, out)
+
+    def barrier():
+        if world > 1:
+            import torch.distributed as dist
+            dist.barrier()
+        lib.tops_sync()
+        torch.cuda.synchronize()
+
+    # -- device-resident timing ------------------------------------------------------------------
+    for _ in range(max(args.warmup, 3)):
+        for item in plan:
+            launch(item)
+    capi.check(lib)
+    n_launch = len(plan)
+    marks = [[torch.cuda.Event(enable_timing=True) for _ in range(n_launch + 1)] for _ in range(args.steps)]
+    barrier()
+    with ClockSampler(local) as clocks:
+        with torch.cuda.stream(stream):
+            for s in range(args.steps):
+                marks[s][0].record(stream)
+                for i, item in enumerate(plan):
+                    launch(item)
+                    marks[s][i + 1].record(stream)
+        barrier()
+    capi.check(lib)
+    per_launch_ms = np.zeros(n_launch)
+    for s in range(args.steps):
+        for i in range(n_launch):
+            per_launch_ms[i] += marks[s][i].elapsed_time(marks[s][i + 1])
+    per_launch_ms /= args.steps
+    total_ms = sum(marks[s][0].elapsed_time(marks[s][-1]) for s in range(args.steps))
+    step_ms = total_ms / args.steps
+    bytes_step = sum(item["bytes"] for item in plan)
+
+    # -- end to end through the C ABI with pinned host buffers --------------------------------------
+    pinned = {}
+
+    def pin(arr):
+        key = id(arr)
+        if key not in pinned:
+            ptr = lib.tops_host_alloc(arr.nbytes)
+            if not ptr:
+                capi.check(lib)
+            ctypes.memmove(ptr, arr.ctypes.data, arr.nbytes)
+            pinned[key] = ptr
+        return pinned[key]
+
+    out_pinned = lib.tops_host_alloc(rows * MID * INNER * 8)
+    h2d = d2h = 0
+    e2e_items = []
+    for item in plan:
+        a_arr = a_cos_host if item["op"] == "cos" else a_host[item["a"]]
+        ent = dict(item=item, a_ptr=pin(a_arr), a_bytes=a_arr.nbytes)
+        if item["kind"] == "binary":
+            b_arr = b_host[(item["bname"], item["b"], item["divisor"])]
+            ent.update(b_ptr=pin(b_arr), b_bytes=b_arr.nbytes)
+            h2d += b_arr.nbytes
+        h2d += a_arr.nbytes
+        ent["o_bytes"] = rows * MID * INNER * ITEM[item["o"]]
+        d2h += ent["o_bytes"]
+        e2e_items.append(ent)
+
+    def e2e_step():
+        for ent in e2e_items:
+            item = ent["item"]
+            out = dev_out[item["o"]].handle
+            src = dev_cos if item["op"] == "cos" else dev_a[item["a"]]
+            lib.tops_upload(src.handle, ent["a_ptr"], ent["a_bytes"])
+            if item["kind"] == "binary":
+                bdev = dev_b[(item["bname"], item["b"], item["divisor"])]
+                lib.tops_upload(bdev.handle, ent["b_ptr"], ent["b_bytes"])
+                fn_of(item)(src.handle, bdev.handle, out)
+            else:
+                fn_of(item)(src.handle, out)
+            lib.tops_download_async(out, out_pinned, ent["o_bytes"])
+
+    e2e_steps = max(1, min(args.steps, 3))
+    e2e_step()
+    barrier()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    with torch.cuda.stream(stream):
+        e0.record(stream)
+        for _ in range(e2e_steps):
+            e2e_step()
+        e1.record(stream)
+    barrier()
+    capi.check(lib)
+    e2e_ms = e0.elapsed_time(e1) / e2e_steps
+
+    # -- max over ranks -----------------------------------------------------------------------------
+    times = torch.tensor([step_ms, e2e_ms], dtype=torch.float64, device=f"cuda:{local}")
+    if world > 1:
+        import torch.distributed as dist
+        dist.all_reduce(times, op=dist.ReduceOp.MAX)
+    step_ms_max, e2e_ms_max = (float(t) for t in times.cpu())
+
+    if rank == 0:
+        peak, peak_kind = peaks()
+        binary_idx = [i for i, it in enumerate(plan) if it["kind"] == "binary"]
+        fam_bytes = sum(plan[i]["bytes"] for i in binary_idx)
+        fam_ms = float(sum(per_launch_ms[i] for i in binary_idx))
+        achieved = fam_bytes / 1e9 / (fam_ms / 1e3)
+        per_op = {}
+        for i, it in enumerate(plan):
+            per_op[it["label"]] = round(it["bytes"] / 1e9 / (per_launch_ms[i] / 1e3), 1)
+        worst = sorted(per_op.items(), key=lambda kv: kv[1])[:5]
+        line = {
+            "metric": "per-op GB/s (aggregate over the broadcast elementwise sweep)",
+            "value": round(world * bytes_step / 1e9 / (step_ms_max / 1e3), 2),
+            "unit": "GB/s",
+            "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3),
+            "ms_per_step": round(step_ms_max, 4),
+            "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+            "dtype": "f32/f16/bf16/i32/i8 elementwise (f64 where the output is float64)",
+            "data": "synthetic",
+            "config": {"workload": "config 2: broadcast elementwise sweep, A[64,512,1024] x B{[1,512,1],[1024],full} x 7 dtype pairs x Add/Sub/Mul/Div + Relu/Abs x 5 dtypes + Cos f32 (95 launches per step, per GPU)",
+                       "l2": "inputs larger than L2 in aggregate: 1.9 GB of distinct tensors cycle between reuses of any one",
+                       "parallelism": f"replicated sweep per GPU x{world}, no data-path collective"},
+            "roofline": {"bound": "hbm", "kernel": "ew_kernel<BinaryBody> (84 launches per step)",
+                         "achieved": round(achieved, 1), "peak": peak, "unit": "GB/s",
+                         "frac": round(achieved / peak, 4), "peak_kind": peak_kind, "traffic": None},
+            "e2e": {"value": round(world * bytes_step / 1e9 / (e2e_ms_max / 1e3), 2), "unit": "GB/s",
+                    "h2d_bytes_per_step": int(h2d), "d2h_bytes_per_step": int(d2h), "ms_per_step": round(e2e_ms_max, 3)},
+            "gpu_launches": n_launch * args.steps,
+            "clocks": clocks.summary(),
+            "slowest_ops_GBps": dict(worst),
+        }
+        line["cpu_baseline"] = cpu_baseline(budget_s=20.0) if world == 1 else None
+        details = os.path.join(ROOT, "gpurun_out")
+        try:
+            os.makedirs(details, exist_ok=True)
+            with open(os.path.join(details, "bench_per_op.json"), "w") as f:
+                json.dump({"per_op_GBps": per_op, "per_launch_ms": [round(float(x), 5) for x in per_launch_ms]}, f, indent=1)
+        except OSError:
+            pass
+        print(json.dumps(line), flush=True)
+    for ptr in list(pinned.values()) + [out_pinned]:
+        lib.tops_host_free(ptr)
+    if world > 1:
+        import torch.distributed as dist
+        dist.destroy_process_group()
+
+
+# ---- the reference's CPU implementation ------------------------------------------------------------------
+def cpu_sweep(rows, steps, warmup):
+    """Times the reference C library (or, if no compiled copy is present, the oracle port) on the
+    sweep at `rows` rows of A, operands pre-broadcast to full size as its ABI requires.
+    Returns (GB/s, seconds per step, kind, cores)."""
+    import oracle
+    kind = "reference" if oracle.available("ref") else "port"
+    host = oracle.HostOracle("ref" if kind == "reference" else "port")
+    a_host, a_cos_host, b_host = host_inputs(rows, seed=0)
+    plan = sweep_plan(rows)
+    full = (rows, MID, INNER)
+    prepared = []
+    for item in plan:
+        a = a_cos_host if item["op"] == "cos" else a_host[item["a"]]
+        wa = oracle._Wrapped(a, item["a"])
+        wo = oracle._out(full, item["o"])
+        if item["kind"] == "binary":
+            b = np.ascontiguousarray(np.broadcast_to(b_host[(item["bname"], item["b"], item["divisor"])], full))
+            prepared.append((host._fn[item["op"]], (wa.ref, oracle._Wrapped(b, item["b"]).ref, wo.ref), (wa, b, wo)))
+        else:
+            prepared.append((host._fn[item["op"]], (wa.ref, wo.ref), (wa, wo)))
+    bytes_step = sum(item["bytes"] for item in plan)
+
+    def one_step():
+        for fn, fargs, _keep in prepared:
+            fn(*fargs)
+
+    for _ in range(warmup):
+        one_step()
+    t0 = time.perf_counter()
+    for _ in range(steps):
+        one_step()
+    dt = (time.perf_counter() - t0) / steps
+    cores = int(os.environ.get("OMP_NUM_THREADS", os.cpu_count() or 1))
+    return bytes_step / 1e9 / dt, dt, kind, cores
+
+
+def cpu_baseline(budget_s=20.0):
+    rows = 4
+    gbs, dt, kind, cores = cpu_sweep(rows, steps=1, warmup=0)
+    if dt * 4 < budget_s:                       # a 4x larger slab still fits the budget
+        rows = 16
+        gbs, dt, kind, cores = cpu_sweep(rows, steps=1, warmup=0)
+    return {"value": round(gbs, 3), "unit": "GB/s", "cores": cores, "kind": kind,
+            "sample": f"one pass of the 95-call sweep on A[{rows},512,1024] ({rows}/{FULL_ROWS} of the rows), C functions only, "
+                      f"operands pre-broadcast on the host outside the timed region, {dt:.2f} s"}
+
+
+def run_reference(args):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    rows = 8
+    steps, warmup = max(1, args.steps), max(0, min(args.warmup, 1))
+    gbs, dt, kind, cores = cpu_sweep(rows, steps, warmup)
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    line = {
+        "impl": "reference",
+        "metric": "per-op GB/s (aggregate over the broadcast elementwise sweep)",
+        "value": round(gbs, 3), "unit": "GB/s", "n_gpus": world, "steps": steps, "warmup": warmup,
+        "ms_per_step": round(dt * 1e3, 2), "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": "f64 arithmetic over f32/f16/bf16/i32/i8 storage", "data": "synthetic",
+        "config": {"workload": f"config 2 sweep, bounded sample: A[{rows},512,1024] ({rows}/{FULL_ROWS} of the rows), 95 calls per step",
+                   "parallelism": f"OpenMP, {cores} host threads"},
+        "cpu_baseline": {"value": round(gbs, 3), "unit": "GB/s", "cores": cores, "kind": kind,
+                         "sample": f"{steps} timed passes of the sweep on A[{rows},512,1024], C functions only, operands pre-broadcast"},
+        "e2e": {"value": round(gbs, 3), "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+    }
+    print(json.dumps(line), flush=True)
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=10)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", choices=("ours", "reference"), default="ours")
+    args = ap.parse_args()
+    if args.impl == "reference":
+        run_reference(args)
+    else:
+        run_ours(args)
+
+
+if __name__ == "__main__":
+    main()
