@@ -9,7 +9,7 @@ the five A dtypes, Cos on float32.  One "step" is one pass over all 95 operator 
 
 Prints ONE JSON line.  `value` is algorithmic GB/s of the whole job with inputs resident in HBM,
 `e2e` the same metric through the C ABI with pinned HOST buffers (H2D of both operands and D2H of
-the result inside the timed region), `roofline` the achieved bandwidth of the dominant kernel
+the result inside the timed region; two streams so uploads overlap downloads), `roofline` the achieved bandwidth of the dominant kernel
 family against the measured HBM copy peak, `cpu_baseline` the reference C library timed on this
 machine's cores on a bounded slab of the same sweep.
 
@@ -252,7 +252,18 @@ def run_ours(args):
             pinned[key] = ptr
         return pinned[key]
 
-    out_pinned = lib.tops_host_alloc(rows * MID * INNER * 8)
+    # Two lanes, each with its own stream, device operands and pinned result buffer: the upload of
+    # one call overlaps the download of the previous one (PCIe is full duplex).
+    n_lanes = 2
+    lane_streams = [torch.cuda.Stream(device=local) for _ in range(n_lanes)]
+    out_pinned = [lib.tops_host_alloc(rows * MID * INNER * 8) for _ in range(n_lanes)]
+    lanes = [dict(a=dev_a, cos=dev_cos, b=dev_b, out=dev_out)]
+    for _ in range(1, n_lanes):
+        lanes.append(dict(a={dt: DeviceArray.empty(v.shape, dt) for dt, v in a_host.items()},
+                          cos=DeviceArray.empty(a_cos_host.shape, "float32"),
+                          b={k: DeviceArray.empty(v.shape, k[1]) for k, v in b_host.items()},
+                          out={dt: DeviceArray.empty((rows, MID, INNER), dt) for dt in dev_out}))
+    capi.check(lib)
     h2d = d2h = 0
     e2e_items = []
     for item in plan:
@@ -268,28 +279,39 @@ def run_ours(args):
         e2e_items.append(ent)
 
     def e2e_step():
-        for ent in e2e_items:
+        for i, ent in enumerate(e2e_items):
+            k = i % n_lanes
+            lane = lanes[k]
+            lib.tops_set_stream(lane_streams[k].cuda_stream)
             item = ent["item"]
-            out = dev_out[item["o"]].handle
-            src = dev_cos if item["op"] == "cos" else dev_a[item["a"]]
+            out = lane["out"][item["o"]].handle
+            src = lane["cos"] if item["op"] == "cos" else lane["a"][item["a"]]
             lib.tops_upload(src.handle, ent["a_ptr"], ent["a_bytes"])
             if item["kind"] == "binary":
-                bdev = dev_b[(item["bname"], item["b"], item["divisor"])]
+                bdev = lane["b"][(item["bname"], item["b"], item["divisor"])]
                 lib.tops_upload(bdev.handle, ent["b_ptr"], ent["b_bytes"])
                 fn_of(item)(src.handle, bdev.handle, out)
             else:
                 fn_of(item)(src.handle, out)
-            lib.tops_download_async(out, out_pinned, ent["o_bytes"])
+            lib.tops_download_async(out, out_pinned[k], ent["o_bytes"])
+
+    def e2e_sync():
+        for st in lane_streams:
+            st.synchronize()
 
     e2e_steps = max(1, min(args.steps, 3))
     e2e_step()
+    e2e_sync()
     barrier()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    with torch.cuda.stream(stream):
-        e0.record(stream)
-        for _ in range(e2e_steps):
-            e2e_step()
-        e1.record(stream)
+    e0.record(lane_streams[0])
+    lane_streams[1].wait_event(e0)
+    for _ in range(e2e_steps):
+        e2e_step()
+    lane_streams[0].wait_stream(lane_streams[1])
+    e1.record(lane_streams[0])
+    e2e_sync()
+    lib.tops_set_stream(None)
     barrier()
     capi.check(lib)
     e2e_ms = e0.elapsed_time(e1) / e2e_steps
@@ -341,7 +363,7 @@ def run_ours(args):
         except OSError:
             pass
         print(json.dumps(line), flush=True)
-    for ptr in list(pinned.values()) + [out_pinned]:
+    for ptr in list(pinned.values()) + out_pinned:
         lib.tops_host_free(ptr)
     if world > 1:
         import torch.distributed as dist

@@ -64,26 +64,43 @@ binary_elem(typename Storage<DA>::type sa, typename Storage<DB>::type sb) {
     }
 }
 
-template <int DA, int DB, int DO, int OP>
+template <int DA, int DB, int DO, int OP, bool ALIGNED>
 struct BinaryBody {
     static constexpr int kV = vec_width(dtype_bytes(DA), dtype_bytes(DB), dtype_bytes(DO));
-    Geometry g;
-    Operand a, b;
+    Geo3 g;
+    Op3 a, b;
     void* out;
-    bool a_vec, b_vec, o_vec;
     __device__ __forceinline__ void operator()(uint32_t i0, uint32_t nv) const {
         Run<typename Storage<DA>::type, kV> ra;
         Run<typename Storage<DB>::type, kV> rb;
         Run<typename Storage<DO>::type, kV> ro;
-        fetch<DA, kV>(g, a, i0, nv, a_vec, ra);
-        fetch<DB, kV>(g, b, i0, nv, b_vec, rb);
-        #pragma unroll
-        for (int j = 0; j < kV; j++) ro.v[j] = binary_elem<DA, DB, DO, OP>(ra.v[j], rb.v[j]);
-        put<DO, kV>(out, i0, nv, o_vec, ro);
+        const Coord3 c = g.simple ? Coord3{0, 0, 0} : coords_of(g, i0);
+        fetch3<DA, kV, ALIGNED>(g, a, i0, nv, c, ra);
+        fetch3<DB, kV, ALIGNED>(g, b, i0, nv, c, rb);
+        constexpr bool int_lane = dtype_is_int(DO) && DO != DTYPE_INT64 && dtype_is_narrow_int(DA) && dtype_is_narrow_int(DB) &&
+                                  dtype_is_narrow_int(DO);
+        constexpr bool float_lane = !dtype_is_int(DO) && DO != DTYPE_FLOAT64 && dtype_exact_in_f32(DA) && dtype_exact_in_f32(DB);
+        if constexpr (int_lane) {
+            int v[kV];
+            #pragma unroll
+            for (int j = 0; j < kV; j++) v[j] = int_op32<OP>(to_i32_narrow<DA>(ra.v[j]), to_i32_narrow<DB>(rb.v[j]));
+            encode_ints<DO, kV>(v, ro);
+        } else if constexpr (float_lane) {
+            float fa[kV], fb[kV];
+            decode_floats<DA, kV>(ra, fa);
+            decode_floats<DB, kV>(rb, fb);
+            #pragma unroll
+            for (int j = 0; j < kV; j++) fa[j] = float_op32<OP>(fa[j], fb[j]);
+            encode_floats<DO, kV>(fa, ro);
+        } else {
+            #pragma unroll
+            for (int j = 0; j < kV; j++) ro.v[j] = binary_elem<DA, DB, DO, OP>(ra.v[j], rb.v[j]);
+        }
+        put3<DO, kV, ALIGNED>(out, i0, nv, ro);
     }
 };
 
-// Any dtype triple: one element per run, dtypes switched at run time.
+// Any dtype triple and any rank: one element per run, dtypes switched at run time.
 template <int OP>
 struct BinaryGenericBody {
     static constexpr int kV = 1;
@@ -103,18 +120,25 @@ struct BinaryGenericBody {
     }
 };
 
+template <int OP>
+static bool binary_generic_slab(const char* name, const Slab& s, int da, int db, int dout) {
+    BinaryGenericBody<OP> body{s.geom, s.ops[0], s.ops[1], s.out, da, db, dout};
+    return launch_body(name, body, s.n);
+}
+
 template <int DA, int DB, int DO, int OP>
 static bool binary_typed(const char* name, const Geometry& geom, Operand* ops, Tensor* o) {
     const int bytes[2] = {dtype_bytes(DA), dtype_bytes(DB)};
-    return launch_elementwise(name, geom, ops, bytes, 2, o->data, dtype_bytes(DO), o->size,
-        [&](const Geometry& g, const Operand* l, void* out_ptr) {
-            BinaryBody<DA, DB, DO, OP> body;
-            body.g = g; body.a = l[0]; body.b = l[1]; body.out = out_ptr;
-            body.a_vec = aligned_to(l[0].ptr, (size_t)dtype_bytes(DA) * body.kV);
-            body.b_vec = aligned_to(l[1].ptr, (size_t)dtype_bytes(DB) * body.kV);
-            body.o_vec = aligned_to(out_ptr, (size_t)dtype_bytes(DO) * body.kV);
-            return body;
-        });
+    return for_each_slab(name, geom, ops, bytes, 2, o->data, dtype_bytes(DO), o->size, [&](const Slab& s) {
+        if (!s.fits3) return binary_generic_slab<OP>(name, s, DA, DB, DO);
+        constexpr int V = vec_width(dtype_bytes(DA), dtype_bytes(DB), dtype_bytes(DO));
+        if (slab_aligned(s, 2, bytes, dtype_bytes(DO), V)) {
+            BinaryBody<DA, DB, DO, OP, true> body{s.geo3, s.ops3[0], s.ops3[1], s.out};
+            return launch_body(name, body, s.n);
+        }
+        BinaryBody<DA, DB, DO, OP, false> body{s.geo3, s.ops3[0], s.ops3[1], s.out};
+        return launch_body(name, body, s.n);
+    });
 }
 
 template <int OP>
@@ -152,13 +176,8 @@ static void binary_forward(const char* name, const Tensor* a, const Tensor* b, T
 #undef TOPS_COMBO
     if (!done) {
         const int bytes[2] = {dtype_bytes(da), dtype_bytes(db)};
-        launch_elementwise(name, geom, ops, bytes, 2, o->data, dtype_bytes(dout), o->size,
-            [&](const Geometry& g, const Operand* l, void* out_ptr) {
-                BinaryGenericBody<OP> body;
-                body.g = g; body.a = l[0]; body.b = l[1]; body.out = out_ptr;
-                body.da = da; body.db = db; body.dout = dout;
-                return body;
-            });
+        for_each_slab(name, geom, ops, bytes, 2, o->data, dtype_bytes(dout), o->size,
+                      [&](const Slab& s) { return binary_generic_slab<OP>(name, s, da, db, dout); });
     }
     finish_op();
 }

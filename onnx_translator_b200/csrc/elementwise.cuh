@@ -1,8 +1,13 @@
 // Elementwise engine: every unary / binary / Q / DQ kernel is one instantiation of ew_kernel
 // around a small "body" functor.  A thread owns runs of V consecutive output elements (V chosen
-// so the widest stream moves 16 bytes per access), walks them grid-stride, and fetches each
-// operand either as one vector (flat operands, or broadcast operands whose run stays inside the
-// innermost collapsed dimension) or element by element at run boundaries.
+// so the widest stream moves 16 bytes per access) and walks them grid-stride.
+//
+// Typed bodies see the output through a fixed three-level geometry [c0][c1][c2] (collapsed
+// dimensions, outermost first, padded in front).  An operand is three element strides: a dense
+// operand has (s1*s2, s2, 1) so its offset IS the output index, a broadcast operand has zeros.
+// Coordinates are computed once per run with two multiply-high divisions and shared by all
+// operands.  Shapes that do not collapse to three dimensions, and dtype combinations without a
+// typed body, take the generic bodies (any rank up to 16, one element per run).
 #pragma once
 
 #include "common.cuh"
@@ -10,6 +15,7 @@
 namespace tops {
 
 constexpr int kEwThreads = 256;
+constexpr int kEwCtasPerSm = 8;
 
 // ---- raw vector moves ---------------------------------------------------------------------------------
 template <int BYTES> __device__ __forceinline__ void load_bytes(const void* src, void* dst) {
@@ -23,11 +29,12 @@ template <int BYTES> __device__ __forceinline__ void load_bytes(const void* src,
         for (int k = 0; k < BYTES / 16; k++) ((uint4*)dst)[k] = ((const uint4*)src)[k];
     }
 }
-// Streaming variants for data touched exactly once (evict-first in L2, no L1 allocation).
+// Streaming variants for data touched exactly once (evict-first).
 template <int BYTES> __device__ __forceinline__ void load_bytes_stream(const void* src, void* dst) {
     if constexpr (BYTES == 4)       *(uint32_t*)dst = __ldcs((const uint32_t*)src);
     else if constexpr (BYTES == 8)  *(uint2*)dst    = __ldcs((const uint2*)src);
     else if constexpr (BYTES >= 16) {
+        static_assert(BYTES % 16 == 0, "vector width");
         #pragma unroll
         for (int k = 0; k < BYTES / 16; k++) ((uint4*)dst)[k] = __ldcs(((const uint4*)src) + k);
     } else load_bytes<BYTES>(src, dst);
@@ -38,6 +45,7 @@ template <int BYTES> __device__ __forceinline__ void store_bytes_stream(void* ds
     else if constexpr (BYTES == 4)  __stcs((uint32_t*)dst, *(const uint32_t*)src);
     else if constexpr (BYTES == 8)  __stcs((uint2*)dst, *(const uint2*)src);
     else {
+        static_assert(BYTES % 16 == 0, "vector width");
         #pragma unroll
         for (int k = 0; k < BYTES / 16; k++) __stcs(((uint4*)dst) + k, ((const uint4*)src)[k]);
     }
@@ -45,50 +53,141 @@ template <int BYTES> __device__ __forceinline__ void store_bytes_stream(void* ds
 
 template <typename S, int V> struct alignas(sizeof(S) * V >= 16 ? 16 : sizeof(S) * V) Run { S v[V]; };
 
-// Fetch V elements of an operand for output indices [i0, i0 + nv).
-// `vec_ok`: the operand's base pointer is aligned to V elements.
-template <int DT, int V>
-__device__ __forceinline__ void fetch(const Geometry& g, const Operand& op, uint32_t i0, uint32_t nv, bool vec_ok,
-                                      Run<typename Storage<DT>::type, V>& out) {
+// ---- three-level geometry ---------------------------------------------------------------------------------
+struct Geo3 {
+    uint32_t s1 = 0x80000000u, s2 = 0x80000000u;   // sizes of the two inner levels (padding: 2^31)
+    FastDiv d1, d2;
+    int simple = 1;                                // every operand dense: offsets equal the index
+};
+struct Op3 {
+    const void* ptr = nullptr;
+    uint32_t st0 = 0, st1 = 0, st2 = 1;
+};
+struct Coord3 { uint32_t c0, c1, c2; };
+
+__device__ __forceinline__ Coord3 coords_of(const Geo3& g, uint32_t i) {
+    Coord3 c;
+    const uint32_t t = g.d2.div(i);
+    c.c2 = i - t * g.s2;
+    c.c0 = g.d1.div(t);
+    c.c1 = t - c.c0 * g.s1;
+    return c;
+}
+__device__ __forceinline__ uint32_t offset_of(const Op3& op, const Coord3& c) {
+    return c.c0 * op.st0 + c.c1 * op.st1 + c.c2 * op.st2;
+}
+
+// Fetch a whole run.  ALIGNED: the run lies inside one innermost row and vector accesses are
+// aligned (checked on the host).  Otherwise each element is addressed on its own.
+template <int DT, int V, bool ALIGNED>
+__device__ __forceinline__ void fetch3(const Geo3& g, const Op3& op, uint32_t i0, uint32_t nv, const Coord3& c,
+                                       Run<typename Storage<DT>::type, V>& out) {
     using S = typename Storage<DT>::type;
     const S* base = (const S*)op.ptr;
-    if (op.flat) {
-        if (nv == V && vec_ok) { load_bytes_stream<sizeof(S) * V>(base + i0, &out); return; }
-        #pragma unroll
-        for (int j = 0; j < V; j++) out.v[j] = (uint32_t)j < nv ? base[i0 + j] : S(0);
-        return;
-    }
-    uint32_t pos;
-    const uint32_t off = operand_offset(g, op, i0, pos);
-    const int inner = op.stride[g.nd - 1];
-    if (pos + V <= g.size[g.nd - 1]) {               // the whole run sits in the innermost dimension
-        if (inner == 0) {
+    if (ALIGNED && nv == V) {
+        if (g.simple) { load_bytes_stream<sizeof(S) * V>(base + i0, &out); return; }
+        const uint32_t off = offset_of(op, c);
+        if (op.st2 == 0) {
             const S s = base[off];
             #pragma unroll
             for (int j = 0; j < V; j++) out.v[j] = s;
-        } else if (vec_ok && (off % V) == 0) {
-            load_bytes<sizeof(S) * V>(base + off, &out);
+        } else if (op.st0 | op.st1) {
+            load_bytes_stream<sizeof(S) * V>(base + off, &out);      // a big operand: touched once
         } else {
-            #pragma unroll
-            for (int j = 0; j < V; j++) out.v[j] = base[off + j];
+            load_bytes<sizeof(S) * V>(base + off, &out);             // a small vector: keep it cached
         }
         return;
     }
     #pragma unroll
     for (int j = 0; j < V; j++) {
-        uint32_t p;
-        out.v[j] = (uint32_t)j < nv ? base[operand_offset(g, op, i0 + j, p)] : S(0);
+        S s = S(0);
+        if ((uint32_t)j < nv) s = g.simple ? base[i0 + j] : base[offset_of(op, coords_of(g, i0 + j))];
+        out.v[j] = s;
     }
 }
 
-template <int DT, int V>
-__device__ __forceinline__ void put(void* out_ptr, uint32_t i0, uint32_t nv, bool vec_ok,
-                                    const Run<typename Storage<DT>::type, V>& r) {
+template <int DT, int V, bool ALIGNED>
+__device__ __forceinline__ void put3(void* out_ptr, uint32_t i0, uint32_t nv, const Run<typename Storage<DT>::type, V>& r) {
     using S = typename Storage<DT>::type;
     S* base = (S*)out_ptr;
-    if (nv == V && vec_ok) { store_bytes_stream<sizeof(S) * V>(base + i0, &r); return; }
+    if (ALIGNED && nv == V) { store_bytes_stream<sizeof(S) * V>(base + i0, &r); return; }
     #pragma unroll
     for (int j = 0; j < V; j++) if ((uint32_t)j < nv) base[i0 + j] = r.v[j];
+}
+
+// ---- packed decode / encode of whole runs --------------------------------------------------------------------
+template <int DT, int V>
+__device__ __forceinline__ void decode_floats(const Run<typename Storage<DT>::type, V>& r, float (&f)[V]) {
+    if constexpr (DT == DTYPE_FLOAT16 && V % 2 == 0) {
+        #pragma unroll
+        for (int j = 0; j < V; j += 2) {
+            const float2 p = __half22float2(*reinterpret_cast<const __half2*>(&r.v[j]));
+            f[j] = p.x; f[j + 1] = p.y;
+        }
+    } else {
+        #pragma unroll
+        for (int j = 0; j < V; j++) f[j] = to_f32<DT>(r.v[j]);
+    }
+}
+
+// Pairs of float32 -> packed 16-bit codes: one hardware convert for both lanes, then the
+// reference's deviations (NaN codes, fp16 flush below 2^-24) on the rare lanes that need them.
+__device__ __forceinline__ uint32_t encode_f16x2(float lo, float hi) {
+    const __half2 h = __floats2half2_rn(lo, hi);
+    uint32_t packed = *reinterpret_cast<const uint32_t*>(&h);
+    const uint32_t ml = f32_bits(lo) & 0x7FFFFFFFu, mh = f32_bits(hi) & 0x7FFFFFFFu;
+    // lanes that need the fix-up: NaN, or non-zero below 2^-24 ((m - 1) < 0x337FFFFF skips m == 0)
+    if ((ml > 0x7F800000u) | (mh > 0x7F800000u) | ((ml - 1u) < 0x337FFFFFu) | ((mh - 1u) < 0x337FFFFFu))
+        packed = (uint32_t)encode_f16(lo) | ((uint32_t)encode_f16(hi) << 16);
+    return packed;
+}
+__device__ __forceinline__ uint32_t encode_bf16x2(float lo, float hi) {
+    const __nv_bfloat162 b = __floats2bfloat162_rn(lo, hi);
+    uint32_t packed = *reinterpret_cast<const uint32_t*>(&b);
+    if ((lo != lo) | (hi != hi)) packed = (uint32_t)encode_bf16(lo) | ((uint32_t)encode_bf16(hi) << 16);
+    return packed;
+}
+
+template <int DT, int V>
+__device__ __forceinline__ void encode_floats(const float (&f)[V], Run<typename Storage<DT>::type, V>& r) {
+    if constexpr (DT == DTYPE_FLOAT16 && V % 2 == 0) {
+        #pragma unroll
+        for (int j = 0; j < V; j += 2) *reinterpret_cast<uint32_t*>(&r.v[j]) = encode_f16x2(f[j], f[j + 1]);
+    } else if constexpr (DT == DTYPE_BFLOAT16 && V % 2 == 0) {
+        #pragma unroll
+        for (int j = 0; j < V; j += 2) *reinterpret_cast<uint32_t*>(&r.v[j]) = encode_bf16x2(f[j], f[j + 1]);
+    } else {
+        #pragma unroll
+        for (int j = 0; j < V; j++) r.v[j] = from_f32<DT>(f[j]);
+    }
+}
+
+// Four int32 -> four saturated 8-bit codes in one word (two cvt.pack instructions).
+__device__ __forceinline__ uint32_t pack_sat_s8x4(int a0, int a1, int a2, int a3) {
+    uint32_t hi, out;
+    asm("cvt.pack.sat.s8.s32.b32 %0, %1, %2, %3;" : "=r"(hi) : "r"(a3), "r"(a2), "r"(0));
+    asm("cvt.pack.sat.s8.s32.b32 %0, %1, %2, %3;" : "=r"(out) : "r"(a1), "r"(a0), "r"(hi));
+    return out;
+}
+__device__ __forceinline__ uint32_t pack_sat_u8x4(int a0, int a1, int a2, int a3) {
+    uint32_t hi, out;
+    asm("cvt.pack.sat.u8.s32.b32 %0, %1, %2, %3;" : "=r"(hi) : "r"(a3), "r"(a2), "r"(0));
+    asm("cvt.pack.sat.u8.s32.b32 %0, %1, %2, %3;" : "=r"(out) : "r"(a1), "r"(a0), "r"(hi));
+    return out;
+}
+
+template <int DT, int V>
+__device__ __forceinline__ void encode_ints(const int (&v)[V], Run<typename Storage<DT>::type, V>& r) {
+    if constexpr (DT == DTYPE_INT8 && V % 4 == 0) {
+        #pragma unroll
+        for (int j = 0; j < V; j += 4) *reinterpret_cast<uint32_t*>(&r.v[j]) = pack_sat_s8x4(v[j], v[j + 1], v[j + 2], v[j + 3]);
+    } else if constexpr (DT == DTYPE_UINT8 && V % 4 == 0) {
+        #pragma unroll
+        for (int j = 0; j < V; j += 4) *reinterpret_cast<uint32_t*>(&r.v[j]) = pack_sat_u8x4(v[j], v[j + 1], v[j + 2], v[j + 3]);
+    } else {
+        #pragma unroll
+        for (int j = 0; j < V; j++) r.v[j] = from_i32<DT>(v[j]);
+    }
 }
 
 // ---- the kernel ----------------------------------------------------------------------------------------
@@ -112,15 +211,22 @@ constexpr int vec_width(int bytes_a, int bytes_b, int bytes_c) {
 
 inline bool aligned_to(const void* p, size_t bytes) { return ((uintptr_t)p % bytes) == 0; }
 
-// Launches `make_body(geometry, operands, out_ptr)` over the output, in slabs of < 2^31 elements.
-// Slabs cut the outermost collapsed dimension, so operand offsets advance by stride[0].
-template <class MakeBody>
-bool launch_elementwise(const char* name, const Geometry& geom, Operand* ops, const int* op_bytes, int n_ops,
-                        void* out, int out_bytes, size_t total, MakeBody&& make_body) {
-    DeviceState* st = acquire_device();
-    if (!st) return false;
+// One slab (< 2^31 elements) of an elementwise launch.
+struct Slab {
+    Geometry geom;          // general geometry (generic bodies)
+    Operand ops[4];
+    Geo3 geo3;              // three-level geometry (typed bodies); valid when `fits3`
+    Op3 ops3[4];
+    bool fits3 = false;
+    void* out = nullptr;
+    size_t n = 0;
+};
+
+// Walks the output in slabs that cut the outermost collapsed dimension and calls `emit(slab)`.
+template <class Emit>
+bool for_each_slab(const char* name, const Geometry& geom, const Operand* ops, const int* op_bytes, int n_ops,
+                   void* out, int out_bytes, size_t total, Emit&& emit) {
     if (total == 0) return true;
-    cudaStream_t stream = current_stream();
     bool all_flat = true;
     for (int k = 0; k < n_ops; k++) all_flat = all_flat && ops[k].flat;
 
@@ -133,26 +239,66 @@ bool launch_elementwise(const char* name, const Geometry& geom, Operand* ops, co
 
     for (size_t row = 0; row < rows_total; row += rows_per_slab) {
         const size_t rows = (rows_total - row < rows_per_slab) ? rows_total - row : rows_per_slab;
-        const size_t n = all_flat ? rows : rows * inner;
+        Slab s;
+        s.n = all_flat ? rows : rows * inner;
         const size_t first = all_flat ? row : row * inner;
-        Geometry g = geom;
-        if (all_flat) { g.nd = 1; g.size[0] = (uint32_t)n; g.div[0].set((uint32_t)n); }
-        else          { g.size[0] = (uint32_t)rows; g.div[0].set((uint32_t)rows); }
-        Operand local[4];
+        s.geom = geom;
+        if (all_flat) { s.geom.nd = 1; s.geom.size[0] = (uint32_t)s.n; s.geom.div[0].set((uint32_t)s.n); }
+        else          { s.geom.size[0] = (uint32_t)rows; s.geom.div[0].set((uint32_t)rows); }
         for (int k = 0; k < n_ops; k++) {
-            local[k] = ops[k];
+            s.ops[k] = ops[k];
             const size_t off = ops[k].flat ? first : row * (size_t)ops[k].stride[0];
-            local[k].ptr = (const char*)ops[k].ptr + off * (size_t)op_bytes[k];
+            s.ops[k].ptr = (const char*)ops[k].ptr + off * (size_t)op_bytes[k];
         }
-        void* out_slab = (char*)out + first * (size_t)out_bytes;
-        auto body = make_body(g, local, out_slab);
-        using Body = decltype(body);
-        const size_t runs = (n + Body::kV - 1) / Body::kV;
-        const int grid = grid_for(runs, kEwThreads, st->sm_count, 8);
-        ew_kernel<Body><<<grid, kEwThreads, 0, stream>>>(body, (uint32_t)n);
-        if (!TOPS_CHECK_LAUNCH(name)) return false;
+        s.out = (char*)out + first * (size_t)out_bytes;
+
+        // three-level view: pad in front with 2^31-sized levels that no index reaches
+        const int nd = s.geom.nd;
+        s.fits3 = nd <= 3;
+        if (s.fits3) {
+            s.geo3.simple = all_flat ? 1 : 0;
+            s.geo3.s2 = s.geom.size[nd - 1];
+            s.geo3.s1 = nd >= 2 ? s.geom.size[nd - 2] : 0x80000000u;
+            s.geo3.d2.set(s.geo3.s2);
+            s.geo3.d1.set(s.geo3.s1);
+            for (int k = 0; k < n_ops; k++) {
+                Op3& o = s.ops3[k];
+                o.ptr = s.ops[k].ptr;
+                if (s.ops[k].flat) {
+                    o.st2 = 1; o.st1 = s.geo3.s2; o.st0 = nd >= 3 ? s.geo3.s2 * s.geo3.s1 : 0;
+                } else {
+                    o.st2 = (uint32_t)s.ops[k].stride[nd - 1];
+                    o.st1 = nd >= 2 ? (uint32_t)s.ops[k].stride[nd - 2] : 0;
+                    o.st0 = nd >= 3 ? (uint32_t)s.ops[k].stride[0] : 0;
+                }
+            }
+        }
+        if (!emit(s)) return false;
     }
     return true;
+}
+
+// True when runs of V elements never straddle an innermost row and every vector access of the
+// slab is aligned, so the typed kernel may use its vector path.
+inline bool slab_aligned(const Slab& s, int n_ops, const int* op_bytes, int out_bytes, int V) {
+    if (!aligned_to(s.out, (size_t)out_bytes * V)) return false;
+    for (int k = 0; k < n_ops; k++) if (!aligned_to(s.ops3[k].ptr, (size_t)op_bytes[k] * V)) return false;
+    if (s.geo3.simple) return true;
+    if (s.geo3.s2 % (uint32_t)V) return false;
+    for (int k = 0; k < n_ops; k++) if ((s.ops3[k].st0 % V) || (s.ops3[k].st1 % V)) {
+        if (s.ops3[k].st2 != 0) return false;           // a vector-loaded operand needs aligned rows
+    }
+    return true;
+}
+
+template <class Body>
+bool launch_body(const char* name, const Body& body, size_t n) {
+    DeviceState* st = acquire_device();
+    if (!st) return false;
+    const size_t runs = (n + Body::kV - 1) / Body::kV;
+    const int grid = grid_for(runs, kEwThreads, st->sm_count, kEwCtasPerSm);
+    ew_kernel<Body><<<grid, kEwThreads, 0, current_stream()>>>(body, (uint32_t)n);
+    return TOPS_CHECK_LAUNCH(name);
 }
 
 }  // namespace tops

@@ -31,21 +31,21 @@ __device__ __forceinline__ typename Storage<DO>::type quantize_fast(float x, flo
     else return from_f32<DO>(res);
 }
 
-template <int DX, int DS, int DZ, int DO>
+template <int DX, int DS, int DZ, int DO, bool ALIGNED>
 struct QuantizeBody {
     static constexpr int kV = vec_width(dtype_bytes(DX), dtype_bytes(DO), 1);
-    Geometry g;
-    Operand x, s, z;
+    Geo3 g;
+    Op3 x, s, z;
     void* out;
-    bool x_vec, s_vec, z_vec, o_vec;
     __device__ __forceinline__ void operator()(uint32_t i0, uint32_t nv) const {
         Run<typename Storage<DX>::type, kV> rx;
         Run<typename Storage<DS>::type, kV> rs;
         Run<typename Storage<DZ>::type, kV> rz;
         Run<typename Storage<DO>::type, kV> ro;
-        fetch<DX, kV>(g, x, i0, nv, x_vec, rx);
-        fetch<DS, kV>(g, s, i0, nv, s_vec, rs);
-        fetch<DZ, kV>(g, z, i0, nv, z_vec, rz);
+        const Coord3 c = g.simple ? Coord3{0, 0, 0} : coords_of(g, i0);
+        fetch3<DX, kV, ALIGNED>(g, x, i0, nv, c, rx);
+        fetch3<DS, kV, ALIGNED>(g, s, i0, nv, c, rs);
+        fetch3<DZ, kV, ALIGNED>(g, z, i0, nv, c, rz);
         #pragma unroll
         for (int j = 0; j < kV; j++) {
             if constexpr (dtype_exact_in_f32(DX) && dtype_exact_in_f32(DS) && dtype_is_narrow_int(DZ)) {
@@ -57,7 +57,7 @@ struct QuantizeBody {
                 ro.v[j] = from_f64<DO>(r);
             }
         }
-        put<DO, kV>(out, i0, nv, o_vec, ro);
+        put3<DO, kV, ALIGNED>(out, i0, nv, ro);
     }
 };
 
@@ -66,25 +66,25 @@ struct QuantizeBody {
 // come out whenever x - z is exact in float32 (8-bit integers, e4m3 codes, any x with z == 0):
 // the double product of a <= 24-bit difference and a 24-bit scale is exact, so a single
 // correctly rounded float multiply reproduces "exact product, one rounding".
-template <int DX, int DS, int DZ, int DO>
+template <int DX, int DS, int DZ, int DO, bool ALIGNED>
 struct DequantizeBody {
     static constexpr int kV = vec_width(dtype_bytes(DX), dtype_bytes(DO), 1);
     static constexpr bool kDiffExact = dtype_exact_in_f32(DX) && dtype_exact_in_f32(DZ) && dtype_exact_in_f32(DS) &&
         DX != DTYPE_FLOAT8_E5M2 && DZ != DTYPE_FLOAT8_E5M2 && DX != DTYPE_FLOAT16 && DZ != DTYPE_FLOAT16 &&
         DX != DTYPE_BFLOAT16 && DZ != DTYPE_BFLOAT16 && DX != DTYPE_FLOAT32 && DZ != DTYPE_FLOAT32 &&
         DO != DTYPE_FLOAT64 && !dtype_is_int(DO);
-    Geometry g;
-    Operand x, s, z;
+    Geo3 g;
+    Op3 x, s, z;
     void* out;
-    bool x_vec, s_vec, z_vec, o_vec;
     __device__ __forceinline__ void operator()(uint32_t i0, uint32_t nv) const {
         Run<typename Storage<DX>::type, kV> rx;
         Run<typename Storage<DS>::type, kV> rs;
         Run<typename Storage<DZ>::type, kV> rz;
         Run<typename Storage<DO>::type, kV> ro;
-        fetch<DX, kV>(g, x, i0, nv, x_vec, rx);
-        fetch<DS, kV>(g, s, i0, nv, s_vec, rs);
-        fetch<DZ, kV>(g, z, i0, nv, z_vec, rz);
+        const Coord3 c = g.simple ? Coord3{0, 0, 0} : coords_of(g, i0);
+        fetch3<DX, kV, ALIGNED>(g, x, i0, nv, c, rx);
+        fetch3<DS, kV, ALIGNED>(g, s, i0, nv, c, rs);
+        fetch3<DZ, kV, ALIGNED>(g, z, i0, nv, c, rz);
         #pragma unroll
         for (int j = 0; j < kV; j++) {
             if constexpr (kDiffExact) {
@@ -104,7 +104,7 @@ struct DequantizeBody {
                 ro.v[j] = from_f64<DO>(__dmul_rn(d, to_f64<DS>(rs.v[j])));
             }
         }
-        put<DO, kV>(out, i0, nv, o_vec, ro);
+        put3<DO, kV, ALIGNED>(out, i0, nv, ro);
     }
 };
 
@@ -128,19 +128,25 @@ struct QdqGenericBody {
     }
 };
 
-template <template <int, int, int, int> class Body, int DX, int DS, int DZ, int DO>
+template <bool QUANTIZE>
+static bool qdq_generic_slab(const char* name, const Slab& s, int dx, int ds, int dz, int dout) {
+    QdqGenericBody<QUANTIZE> b{s.geom, s.ops[0], s.ops[1], s.ops[2], s.out, dx, ds, dz, dout};
+    return launch_body(name, b, s.n);
+}
+
+template <template <int, int, int, int, bool> class Body, bool QUANTIZE, int DX, int DS, int DZ, int DO>
 static bool qdq_typed(const char* name, const Geometry& geom, Operand* ops, Tensor* y) {
     const int bytes[3] = {dtype_bytes(DX), dtype_bytes(DS), dtype_bytes(DZ)};
-    return launch_elementwise(name, geom, ops, bytes, 3, y->data, dtype_bytes(DO), y->size,
-        [&](const Geometry& g, const Operand* l, void* out_ptr) {
-            Body<DX, DS, DZ, DO> b;
-            b.g = g; b.x = l[0]; b.s = l[1]; b.z = l[2]; b.out = out_ptr;
-            b.x_vec = aligned_to(l[0].ptr, (size_t)dtype_bytes(DX) * b.kV);
-            b.s_vec = aligned_to(l[1].ptr, (size_t)dtype_bytes(DS) * b.kV);
-            b.z_vec = aligned_to(l[2].ptr, (size_t)dtype_bytes(DZ) * b.kV);
-            b.o_vec = aligned_to(out_ptr, (size_t)dtype_bytes(DO) * b.kV);
-            return b;
-        });
+    return for_each_slab(name, geom, ops, bytes, 3, y->data, dtype_bytes(DO), y->size, [&](const Slab& s) {
+        if (!s.fits3) return qdq_generic_slab<QUANTIZE>(name, s, DX, DS, DZ, DO);
+        constexpr int V = vec_width(dtype_bytes(DX), dtype_bytes(DO), 1);
+        if (slab_aligned(s, 3, bytes, dtype_bytes(DO), V)) {
+            Body<DX, DS, DZ, DO, true> b{s.geo3, s.ops3[0], s.ops3[1], s.ops3[2], s.out};
+            return launch_body(name, b, s.n);
+        }
+        Body<DX, DS, DZ, DO, false> b{s.geo3, s.ops3[0], s.ops3[1], s.ops3[2], s.out};
+        return launch_body(name, b, s.n);
+    });
 }
 
 // axis >= 0: Scale / ZeroPoint are 1-D of length Y.shape[axis]; axis < -64: plain broadcasting.
@@ -184,9 +190,9 @@ static void qdq_forward(const char* name, const Tensor* x, const Tensor* s, cons
 
     bool done = false;
 #define TOPS_Q(X, Z, O) if (!done && dx == X && ds == DTYPE_FLOAT32 && dz == Z && dout == O) { \
-        qdq_typed<QuantizeBody, X, DTYPE_FLOAT32, Z, O>(name, geom, ops, y); done = true; }
+        qdq_typed<QuantizeBody, true, X, DTYPE_FLOAT32, Z, O>(name, geom, ops, y); done = true; }
 #define TOPS_DQ(X, Z, O) if (!done && dx == X && ds == DTYPE_FLOAT32 && dz == Z && dout == O) { \
-        qdq_typed<DequantizeBody, X, DTYPE_FLOAT32, Z, O>(name, geom, ops, y); done = true; }
+        qdq_typed<DequantizeBody, false, X, DTYPE_FLOAT32, Z, O>(name, geom, ops, y); done = true; }
     if (QUANTIZE) {
 #define TOPS_Q_SOURCES(Z, O) TOPS_Q(DTYPE_FLOAT32, Z, O) TOPS_Q(DTYPE_FLOAT16, Z, O) TOPS_Q(DTYPE_BFLOAT16, Z, O)
         TOPS_Q_SOURCES(DTYPE_INT8, DTYPE_INT8) TOPS_Q_SOURCES(DTYPE_UINT8, DTYPE_UINT8)
@@ -205,13 +211,8 @@ static void qdq_forward(const char* name, const Tensor* x, const Tensor* s, cons
 #undef TOPS_DQ
     if (!done) {
         const int bytes[3] = {dtype_bytes(dx), dtype_bytes(ds), dtype_bytes(dz)};
-        launch_elementwise(name, geom, ops, bytes, 3, y->data, dtype_bytes(dout), y->size,
-            [&](const Geometry& g, const Operand* l, void* out_ptr) {
-                QdqGenericBody<QUANTIZE> b;
-                b.g = g; b.x = l[0]; b.s = l[1]; b.z = l[2]; b.out = out_ptr;
-                b.dx = dx; b.ds = ds; b.dz = dz; b.dout = dout;
-                return b;
-            });
+        for_each_slab(name, geom, ops, bytes, 3, y->data, dtype_bytes(dout), y->size,
+                      [&](const Slab& s) { return qdq_generic_slab<QUANTIZE>(name, s, dx, ds, dz, dout); });
     }
     finish_op();
 }

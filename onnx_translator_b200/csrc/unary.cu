@@ -52,21 +52,36 @@ __device__ __forceinline__ typename Storage<DO>::type unary_elem(typename Storag
     }
 }
 
-template <int DX, int DO, int OP>
+template <int DX, int DO, int OP, bool ALIGNED>
 struct UnaryBody {
     static constexpr int kV = vec_width(dtype_bytes(DX), dtype_bytes(DO), 1);
-    Geometry g;
-    Operand x;
+    Geo3 g;
+    Op3 x;
     void* out;
     const double* lut;
-    bool x_vec, o_vec;
     __device__ __forceinline__ void operator()(uint32_t i0, uint32_t nv) const {
         Run<typename Storage<DX>::type, kV> in;
         Run<typename Storage<DO>::type, kV> res;
-        fetch<DX, kV>(g, x, i0, nv, x_vec, in);
-        #pragma unroll
-        for (int j = 0; j < kV; j++) res.v[j] = unary_elem<DX, DO, OP>(in.v[j], lut);
-        put<DO, kV>(out, i0, nv, o_vec, res);
+        fetch3<DX, kV, ALIGNED>(g, x, i0, nv, Coord3{0, 0, 0}, in);          // unary inputs are always dense
+        constexpr bool float_lane = OP != kCos && dtype_exact_in_f32(DX) && !dtype_is_int(DX) &&
+                                    !dtype_is_int(DO) && DO != DTYPE_FLOAT64;
+        constexpr bool int_lane = OP != kCos && dtype_is_narrow_int(DX) && dtype_is_narrow_int(DO);
+        if constexpr (float_lane) {
+            float f[kV];
+            decode_floats<DX, kV>(in, f);
+            #pragma unroll
+            for (int j = 0; j < kV; j++) f[j] = (OP == kRelu) ? (f[j] > 0 ? f[j] : 0.0f) : fabsf(f[j]);
+            encode_floats<DO, kV>(f, res);
+        } else if constexpr (int_lane) {
+            int v[kV];
+            #pragma unroll
+            for (int j = 0; j < kV; j++) { const int t = to_i32_narrow<DX>(in.v[j]); v[j] = (OP == kRelu) ? max(t, 0) : abs(t); }
+            encode_ints<DO, kV>(v, res);
+        } else {
+            #pragma unroll
+            for (int j = 0; j < kV; j++) res.v[j] = unary_elem<DX, DO, OP>(in.v[j], lut);
+        }
+        put3<DO, kV, ALIGNED>(out, i0, nv, res);
     }
 };
 
@@ -94,39 +109,41 @@ struct UnaryGenericBody {
     }
 };
 
+static bool plan_unary(const Tensor* x, Tensor* y, Geometry* geom, Operand* op) {
+    const ShapeView out{y->shape, y->ndim, y->size}, in{x->shape, x->ndim, x->size};
+    if (!plan_broadcast(out, &in, 1, geom, op)) return false;
+    op->ptr = x->data;
+    return true;
+}
+
 template <int DX, int DO, int OP>
 static bool run_typed(const char* name, const Tensor* x, Tensor* y, const double* lut) {
     Geometry geom;
     Operand op;
-    ShapeView out{y->shape, y->ndim, y->size}, in{x->shape, x->ndim, x->size};
-    plan_broadcast(out, &in, 1, &geom, &op);
-    op.ptr = x->data;
+    if (!plan_unary(x, y, &geom, &op)) return false;
     const int bytes[1] = {dtype_bytes(DX)};
-    return launch_elementwise(name, geom, &op, bytes, 1, y->data, dtype_bytes(DO), y->size,
-        [&](const Geometry& g, const Operand* o, void* out_ptr) {
-            UnaryBody<DX, DO, OP> b;
-            b.g = g; b.x = o[0]; b.out = out_ptr; b.lut = lut;
-            b.x_vec = aligned_to(o[0].ptr, (size_t)dtype_bytes(DX) * b.kV);
-            b.o_vec = aligned_to(out_ptr, (size_t)dtype_bytes(DO) * b.kV);
-            return b;
-        });
+    return for_each_slab(name, geom, &op, bytes, 1, y->data, dtype_bytes(DO), y->size, [&](const Slab& s) {
+        constexpr int V = vec_width(dtype_bytes(DX), dtype_bytes(DO), 1);
+        if (slab_aligned(s, 1, bytes, dtype_bytes(DO), V)) {
+            UnaryBody<DX, DO, OP, true> b{s.geo3, s.ops3[0], s.out, lut};
+            return launch_body(name, b, s.n);
+        }
+        UnaryBody<DX, DO, OP, false> b{s.geo3, s.ops3[0], s.out, lut};
+        return launch_body(name, b, s.n);
+    });
 }
 
 template <int OP>
 static bool run_generic(const char* name, const Tensor* x, Tensor* y, const double* lut) {
     Geometry geom;
     Operand op;
-    ShapeView out{y->shape, y->ndim, y->size}, in{x->shape, x->ndim, x->size};
-    plan_broadcast(out, &in, 1, &geom, &op);
-    op.ptr = x->data;
-    const int bytes[1] = {dtype_bytes((int)x->dtype)};
+    if (!plan_unary(x, y, &geom, &op)) return false;
     const int dx = (int)x->dtype, dout = (int)y->dtype;
-    return launch_elementwise(name, geom, &op, bytes, 1, y->data, dtype_bytes(dout), y->size,
-        [&](const Geometry&, const Operand* o, void* out_ptr) {
-            UnaryGenericBody<OP> b;
-            b.x = o[0].ptr; b.out = out_ptr; b.dx = dx; b.dout = dout; b.lut = lut;
-            return b;
-        });
+    const int bytes[1] = {dtype_bytes(dx)};
+    return for_each_slab(name, geom, &op, bytes, 1, y->data, dtype_bytes(dout), y->size, [&](const Slab& s) {
+        UnaryGenericBody<OP> b{s.ops[0].ptr, s.out, dx, dout, lut};
+        return launch_body(name, b, s.n);
+    });
 }
 
 template <int OP>
