@@ -194,6 +194,10 @@ void tops_dequantize_linear_axis_forward(const Tensor* X, const Tensor* Scale, c
    returns the number of disagreements (NaN inputs excluded), or -1 on error. */
 long long tops_selftest_encoder(DataType dtype);
 
+/* Number of tensor-core (tcgen05) kernels launched so far by Gemm / Conv2d in this process: lets a
+   caller tell that a call took the tensor-core path rather than the exact double-accumulating one. */
+long long tops_tensor_core_launches(void);
+
 /* Host-only (no CUDA call): the collapsed broadcast plan of one operand against an output shape:
    nd collapsed dimensions with their sizes and the operand's element strides (0 = broadcast);
    flat = 1 when the operand has the output's element count and is read at the output index.

@@ -37,6 +37,8 @@ void         set_error(int code, const char* fmt, ...);
 bool         check_cuda(cudaError_t e, const char* what);
 void         zero_fill(Tensor* t);        // best effort, used on rejected calls
 const double* cos_lut_device();           // uploads on first use
+int*         device_status_word();        // device pointer to the host-visible status word (may be null)
+void         poll_device_status();        // host: turn a raised status word into an error
 
 #define TOPS_CUDA_OK(expr) ::tops::check_cuda((expr), #expr)
 #define TOPS_CHECK_LAUNCH(name) ::tops::check_cuda(cudaGetLastError(), name)

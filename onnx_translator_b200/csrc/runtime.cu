@@ -373,7 +373,9 @@ TOPS_API int tops_set_stream(void* cuda_stream) {
 }
 TOPS_API int tops_sync(void) {
     if (!acquire_device()) return tops_last_error();
-    return TOPS_CUDA_OK(cudaStreamSynchronize(current_stream())) ? TOPS_OK : tops_last_error();
+    const bool ok = TOPS_CUDA_OK(cudaStreamSynchronize(current_stream()));
+    poll_device_status();
+    return ok ? tops_last_error() : tops_last_error();
 }
 TOPS_API int tops_set_memory_mode(int managed) { g_managed.store(managed ? 1 : 0); return TOPS_OK; }
 
@@ -454,7 +456,9 @@ TOPS_API int tops_download_async(const Tensor* src, void* host, size_t nbytes) {
 TOPS_API int tops_download(const Tensor* src, void* host, size_t nbytes) {
     const int rc = tops_download_async(src, host, nbytes);
     if (rc != TOPS_OK) return rc;
-    return TOPS_CUDA_OK(cudaStreamSynchronize(current_stream())) ? TOPS_OK : tops_last_error();
+    const bool ok = TOPS_CUDA_OK(cudaStreamSynchronize(current_stream()));
+    poll_device_status();
+    return ok ? tops_last_error() : tops_last_error();
 }
 TOPS_API void* tops_host_alloc(size_t nbytes) {
     if (!acquire_device()) return nullptr;
@@ -482,3 +486,33 @@ TOPS_API int tops_debug_plan_broadcast(const int* out_shape, int out_ndim, const
     for (int d = 0; d < g.nd; d++) { sizes[d] = g.size[d]; strides[d] = op.flat ? 0 : op.stride[d]; }
     return 1;
 }
+
+// ---- device status word ------------------------------------------------------------------------------------
+// One int in pinned, device-mapped host memory.  Kernels with bounded waits set it when a wait
+// gives up; the host looks at it whenever it synchronises and turns it into TOPS_ERR_DEVICE_TIMEOUT.
+namespace tops {
+static int* g_status_host = nullptr;
+static std::once_flag g_status_once;
+
+int* device_status_word() {
+    std::call_once(g_status_once, [] {
+        if (cudaHostAlloc((void**)&g_status_host, sizeof(int), cudaHostAllocMapped | cudaHostAllocPortable) != cudaSuccess) {
+            g_status_host = nullptr;
+            cudaGetLastError();
+            return;
+        }
+        *g_status_host = 0;
+    });
+    if (!g_status_host) return nullptr;
+    int* dev = nullptr;
+    if (cudaHostGetDevicePointer((void**)&dev, g_status_host, 0) != cudaSuccess) { cudaGetLastError(); return nullptr; }
+    return dev;
+}
+
+void poll_device_status() {
+    if (g_status_host && *(volatile int*)g_status_host) {
+        *(volatile int*)g_status_host = 0;
+        set_error(TOPS_ERR_DEVICE_TIMEOUT, "a bounded device-side wait expired inside a tensor-core kernel");
+    }
+}
+}  // namespace tops
