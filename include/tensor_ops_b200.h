@@ -194,6 +194,11 @@ void tops_dequantize_linear_axis_forward(const Tensor* X, const Tensor* Scale, c
    returns the number of disagreements (NaN inputs excluded), or -1 on error. */
 long long tops_selftest_encoder(DataType dtype);
 
+/* Device-side exhaustive check of the fast table cosine: for every finite float32 input the
+   reciprocal-multiply formulation must give the same double as the divide-based formulation of
+   the reference.  Returns the number of disagreements, or -1 on error. */
+long long tops_selftest_cos(void);
+
 /* Number of tensor-core (tcgen05) kernels launched so far by Gemm / Conv2d in this process: lets a
    caller tell that a call took the tensor-core path rather than the exact double-accumulating one. */
 long long tops_tensor_core_launches(void);

@@ -118,6 +118,7 @@ SIGNATURES = {
     "tops_dequantize_linear_axis_forward": (None, [_P, _P, _P, _P, _I]),
     "tops_selftest_encoder": (ctypes.c_longlong, [_I]),
     "tops_tensor_core_launches": (ctypes.c_longlong, []),
+    "tops_selftest_cos": (ctypes.c_longlong, []),
     "tops_debug_plan_broadcast": (_I, [_IP, _I, _IP, _I, _IP, ctypes.POINTER(ctypes.c_uint), _IP, _IP]),
     "tops_version": (ctypes.c_char_p, []),
 }

@@ -14,6 +14,7 @@
 // No cluster, no multicast: every CTA loads its own operands.  All waits are bounded.
 #include "gemm_common.cuh"
 #include "umma.cuh"
+#include "elementwise.cuh"
 
 #include <atomic>
 #include <mutex>
@@ -64,7 +65,7 @@ constexpr int kTileABytes = kBM * kRowBytes;       // 16 KB
 constexpr int kTileBBytes = kBN * kRowBytes;       // 32 KB
 constexpr int kStageBytes = kTileABytes + kTileBBytes;
 constexpr int kTcThreads = 192;
-constexpr size_t kTcSmemBytes = (size_t)kStages * kStageBytes + 1024 /*alignment slack*/ + 256 /*barriers*/;
+constexpr size_t kTcSmemBytes = (size_t)kStages * kStageBytes + 1024 /*alignment slack*/ + 128 /*barriers*/ + 4 * kBN * 4 /*bias*/;
 
 struct TcParams {
     int M, N;
@@ -76,6 +77,7 @@ struct TcParams {
     float alpha, beta;
     BiasView bias;
     int* status;           // device-visible word, set non-zero when a wait gave up
+    int debug;             // experiments only: bit 0 skips the stores, bit 1 skips the whole accumulator read-out
 };
 
 __device__ __forceinline__ void tile_coords(int tile, int tiles_m, int tiles_n, int& tm, int& tn) {
@@ -101,6 +103,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     uint64_t* acc_empty = acc_full + 2;       // [2]        epilogue -> MMA
     uint32_t* tmem_slot = (uint32_t*)(acc_empty + 2);
     volatile int* abort_flag = (volatile int*)(tmem_slot + 1);
+    float* bias_stage = (float*)(bars + 16);           // 4 warps x kBN floats
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int total_tiles = p.tiles_m * p.tiles_n;
@@ -163,30 +166,53 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     } else {
         const int quarter = warp & 3;                               // TMEM lanes this warp may read
         uint32_t local = 0;
+        float* my_bias = bias_stage + quarter * kBN;                 // this warp's private copy: no cross-warp sync
         for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x, local++) {
             const uint32_t buf = local & 1u, use = (local >> 1) & 1u;
             int tm, tn;
             tile_coords(tile, p.tiles_m, p.tiles_n, tm, tn);
+            const int m = tm * kBM + quarter * 32 + lane;
+            // beta * C for this tile, fetched while the tensor core is still working on it
+            float row_bias = 0.0f;
+            if (p.bias.mode == kBiasPerColumn) {
+                __syncwarp();
+                #pragma unroll
+                for (int j = 0; j < kBN / 32; j++) {
+                    const int n = tn * kBN + j * 32 + lane;
+                    my_bias[j * 32 + lane] = n < p.N ? __fmul_rn(p.beta, (float)load_f64_rt(p.bias.ptr, p.bias.dtype, (size_t)n)) : 0.0f;
+                }
+                __syncwarp();
+            } else if (p.bias.mode == kBiasScalar) {
+                row_bias = __fmul_rn(p.beta, (float)load_f64_rt(p.bias.ptr, p.bias.dtype, 0));
+            } else if (p.bias.mode == kBiasPerRow && m < p.M) {
+                row_bias = __fmul_rn(p.beta, (float)load_f64_rt(p.bias.ptr, p.bias.dtype, (size_t)m));
+            }
             if (!umma::mbar_wait(&acc_full[buf], use, abort_flag)) break;
             umma::fence_after_sync();
-            const int m = tm * kBM + quarter * 32 + lane;
             const uint32_t t_row = tmem_base + ((uint32_t)(quarter * 32) << 16) + buf * kBN;
             #pragma unroll 1
-            for (int c = 0; c < kBN / 32; c++) {
+            for (int c = 0; c < ((p.debug & 2) ? 0 : kBN / 32); c++) {
                 uint32_t r[32];
                 umma::tmem_load_32x32(t_row + (uint32_t)(c * 32), r);
                 umma::tmem_load_wait();
                 const int n0 = tn * kBN + c * 32;
-                if (m < p.M && n0 < p.N) {
+                if (m < p.M && n0 < p.N && !(p.debug & 1)) {
                     float v[32];
                     #pragma unroll
-                    for (int j = 0; j < 32; j++) {
-                        float x = __fmul_rn(p.alpha, __uint_as_float(r[j]));
-                        if (p.bias.mode != kBiasNone && n0 + j < p.N) {
-                            const long long ci = bias_index(p.bias, m, n0 + j);
-                            if (ci >= 0) x = __fmaf_rn(p.beta, (float)load_f64_rt(p.bias.ptr, p.bias.dtype, (size_t)ci), x);
+                    for (int j = 0; j < 32; j++) v[j] = __fadd_rn(__fmul_rn(p.alpha, __uint_as_float(r[j])), row_bias);
+                    if (p.bias.mode == kBiasPerColumn) {
+                        #pragma unroll
+                        for (int j = 0; j < 32; j += 4) {
+                            const float4 b4 = *(const float4*)(my_bias + c * 32 + j);
+                            v[j] = __fadd_rn(v[j], b4.x); v[j + 1] = __fadd_rn(v[j + 1], b4.y);
+                            v[j + 2] = __fadd_rn(v[j + 2], b4.z); v[j + 3] = __fadd_rn(v[j + 3], b4.w);
                         }
-                        v[j] = x;
+                    } else if (p.bias.mode == kBiasMatrix) {
+                        #pragma unroll
+                        for (int j = 0; j < 32; j++) {
+                            const long long ci = (n0 + j < p.N) ? bias_index(p.bias, m, n0 + j) : -1;
+                            if (ci >= 0) v[j] = __fmaf_rn(p.beta, (float)load_f64_rt(p.bias.ptr, p.bias.dtype, (size_t)ci), v[j]);
+                        }
                     }
                     const size_t row_off = (size_t)m * p.N + n0;
                     const bool full_chunk = (n0 + 32 <= p.N);
@@ -194,24 +220,27 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                         float* dst = (float*)p.Y + row_off;
                         if (full_chunk && (((uintptr_t)dst & 15) == 0)) {
                             #pragma unroll
-                            for (int j = 0; j < 32; j += 4) *(float4*)(dst + j) = make_float4(v[j], v[j + 1], v[j + 2], v[j + 3]);
+                            for (int j = 0; j < 32; j += 4) __stcs((float4*)(dst + j), make_float4(v[j], v[j + 1], v[j + 2], v[j + 3]));
                         } else {
-                            for (int j = 0; j < 32 && n0 + j < p.N; j++) dst[j] = v[j];
+                            #pragma unroll
+                            for (int j = 0; j < 32; j++) if (n0 + j < p.N) dst[j] = v[j];
                         }
                     } else {
                         uint16_t* dst = (uint16_t*)p.Y + row_off;
                         uint32_t packed[16];
-                        #pragma unroll
-                        for (int j = 0; j < 32; j += 2) {
-                            const uint32_t lo = p.dy == DTYPE_BFLOAT16 ? encode_bf16(v[j]) : encode_f16(v[j]);
-                            const uint32_t hi = p.dy == DTYPE_BFLOAT16 ? encode_bf16(v[j + 1]) : encode_f16(v[j + 1]);
-                            packed[j >> 1] = lo | (hi << 16);
+                        if (p.dy == DTYPE_BFLOAT16) {
+                            #pragma unroll
+                            for (int j = 0; j < 32; j += 2) packed[j >> 1] = encode_bf16x2(v[j], v[j + 1]);
+                        } else {
+                            #pragma unroll
+                            for (int j = 0; j < 32; j += 2) packed[j >> 1] = encode_f16x2(v[j], v[j + 1]);
                         }
                         if (full_chunk && (((uintptr_t)dst & 15) == 0)) {
                             #pragma unroll
-                            for (int j = 0; j < 16; j += 4) *(uint4*)(dst + 2 * j) = make_uint4(packed[j], packed[j + 1], packed[j + 2], packed[j + 3]);
+                            for (int j = 0; j < 16; j += 4) __stcs((uint4*)(dst + 2 * j), make_uint4(packed[j], packed[j + 1], packed[j + 2], packed[j + 3]));
                         } else {
-                            for (int j = 0; j < 32 && n0 + j < p.N; j++) dst[j] = (uint16_t)(packed[j >> 1] >> ((j & 1) * 16));
+                            #pragma unroll
+                            for (int j = 0; j < 32; j++) if (n0 + j < p.N) dst[j] = (uint16_t)(packed[j >> 1] >> ((j & 1) * 16));
                         }
                     }
                 }
@@ -270,6 +299,7 @@ bool gemm_tensor_core(const Tensor* A, const Tensor* B, Tensor* Y, const GemmSha
     p.alpha = alpha; p.beta = beta;
     p.bias = bias;
     p.status = device_status_word();
+    p.debug = getenv("TOPS_TC_DEBUG") ? atoi(getenv("TOPS_TC_DEBUG")) : 0;
 
     const uint32_t fa = fp8 ? (da == DTYPE_FLOAT8_E5M2 ? 1u : 0u) : (da == DTYPE_BFLOAT16 ? 1u : 0u);
     const uint32_t fb = fp8 ? (db == DTYPE_FLOAT8_E5M2 ? 1u : 0u) : (db == DTYPE_BFLOAT16 ? 1u : 0u);

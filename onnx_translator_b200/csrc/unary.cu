@@ -5,6 +5,8 @@ namespace tops {
 
 enum UnaryOp { kRelu = 0, kAbs = 1, kCos = 2 };
 
+bool cos_fast(const Tensor* x, Tensor* y, const double* lut);     // cos_fast.cu
+
 // Table cosine: fold |x| into [0, 2pi), scale to table cells, interpolate linearly -- every step
 // in double with separate roundings (no fused multiply-add), multiply before divide.
 __device__ __forceinline__ double cos_by_table(double x, const double* __restrict__ lut) {
@@ -160,7 +162,8 @@ static void unary_forward(const char* name, const Tensor* x, Tensor* y) {
     bool done = false, ok = true;
 #define TOPS_SAME(DT) if (!done && dx == DT && dout == DT) { ok = run_typed<DT, DT, OP>(name, x, y, lut); done = true; }
     if (OP == kCos) {
-        TOPS_SAME(DTYPE_FLOAT32) TOPS_SAME(DTYPE_FLOAT16) TOPS_SAME(DTYPE_BFLOAT16) TOPS_SAME(DTYPE_FLOAT64)
+        if (cos_fast(x, y, lut)) done = true;          // float32 / float16 / bfloat16, same dtype out
+        TOPS_SAME(DTYPE_FLOAT64)
     } else {
         TOPS_SAME(DTYPE_FLOAT8_E4M3) TOPS_SAME(DTYPE_FLOAT8_E5M2) TOPS_SAME(DTYPE_FLOAT16) TOPS_SAME(DTYPE_BFLOAT16)
         TOPS_SAME(DTYPE_FLOAT32) TOPS_SAME(DTYPE_FLOAT64) TOPS_SAME(DTYPE_INT4) TOPS_SAME(DTYPE_INT8)

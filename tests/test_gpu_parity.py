@@ -386,3 +386,23 @@ def test_create_tensor_is_zero_filled_and_views_share_memory():
     assert np.array_equal(v.numpy(), np.arange(24, dtype=np.float32).reshape(2, 12))
     assert np.array_equal(rows.numpy(), np.arange(6, 18, dtype=np.float32).reshape(2, 6))
     capi.check()
+
+
+def test_fast_cosine_division_is_exact_for_every_float32():
+    """All finite float32 inputs: multiply-by-reciprocal plus one fused correction gives the same
+    double as the reference's multiply-then-divide."""
+    from onnx_translator_b200 import capi
+    lib = capi.load()
+    assert lib.tops_selftest_cos() == 0
+    capi.check(lib)
+
+
+def test_cos_subnormal_huge_and_unaligned_inputs(port):
+    x = np.array([1e-40, -1e-45, 1.1754944e-38, 0.0, 3.4e38, -3.4e38, 12.566371, 12.56637, 6.2831855, 6.283185,
+                  100.0, -1000.5, 65504.0], dtype=np.float32)
+    assert_same_codes(gpu.unary("cos", x, "float32", "float32"), port.unary("cos", x, "float32", "float32"), "float32")
+    rng = np.random.default_rng(41)
+    for n in (1, 3, 5, 7, 1023, 4097):
+        for dt in ("float32", "float16", "bfloat16"):
+            v = from_f64(rng.uniform(-20, 20, n), dt)
+            assert_same_codes(gpu.unary("cos", v, dt, dt), port.unary("cos", v, dt, dt), dt, f"{dt} n={n}")
