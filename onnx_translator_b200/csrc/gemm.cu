@@ -91,6 +91,12 @@ BiasView make_bias_view(const Tensor* C, int M, int N) {
     b.mode = kBiasMatrix;
     b.rows = C->shape[C->ndim - 2];
     b.cols = C->shape[C->ndim - 1];
+    // the shapes the Python layer produces for a 1-D C -- (1, N) and (M, 1) -- index exactly like
+    // the per-column / per-row cases (only when C holds nothing beyond those two dimensions)
+    if (C->size == (size_t)b.rows * (size_t)b.cols) {
+        if (b.rows == 1 && b.cols == N) b.mode = kBiasPerColumn;
+        else if (b.cols == 1 && b.rows == M) b.mode = kBiasPerRow;
+    }
     return b;
 }
 

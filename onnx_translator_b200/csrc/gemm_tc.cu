@@ -65,7 +65,9 @@ constexpr int kTileABytes = kBM * kRowBytes;       // 16 KB
 constexpr int kTileBBytes = kBN * kRowBytes;       // 32 KB
 constexpr int kStageBytes = kTileABytes + kTileBBytes;
 constexpr int kTcThreads = 192;
-constexpr size_t kTcSmemBytes = (size_t)kStages * kStageBytes + 1024 /*alignment slack*/ + 128 /*barriers*/ + 4 * kBN * 4 /*bias*/;
+constexpr int kStageRowWords = 36;                 // 32 words of payload + 4 of padding: conflict-free 16-byte accesses
+constexpr size_t kTcSmemBytes = (size_t)kStages * kStageBytes + 1024 /*alignment slack*/ + 128 /*barriers*/ + 4 * kBN * 4 /*bias*/ +
+                                4 * 32 * kStageRowWords * 4 /*output staging*/;
 
 struct TcParams {
     int M, N;
@@ -77,7 +79,7 @@ struct TcParams {
     float alpha, beta;
     BiasView bias;
     int* status;           // device-visible word, set non-zero when a wait gave up
-    int debug;             // experiments only: bit 0 skips the stores, bit 1 skips the whole accumulator read-out
+    int vec_store;         // Y base and row pitch are 16-byte aligned
 };
 
 __device__ __forceinline__ void tile_coords(int tile, int tiles_m, int tiles_n, int& tm, int& tn) {
@@ -104,6 +106,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     uint32_t* tmem_slot = (uint32_t*)(acc_empty + 2);
     volatile int* abort_flag = (volatile int*)(tmem_slot + 1);
     float* bias_stage = (float*)(bars + 16);           // 4 warps x kBN floats
+    uint32_t* out_stage = (uint32_t*)(bias_stage + 4 * kBN);   // 4 warps x 32 rows x kStageRowWords
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int total_tiles = p.tiles_m * p.tiles_n;
@@ -167,6 +170,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
         const int quarter = warp & 3;                               // TMEM lanes this warp may read
         uint32_t local = 0;
         float* my_bias = bias_stage + quarter * kBN;                 // this warp's private copy: no cross-warp sync
+        uint32_t* my_stage = out_stage + quarter * 32 * kStageRowWords;
         for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x, local++) {
             const uint32_t buf = local & 1u, use = (local >> 1) & 1u;
             int tm, tn;
@@ -191,12 +195,12 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
             umma::fence_after_sync();
             const uint32_t t_row = tmem_base + ((uint32_t)(quarter * 32) << 16) + buf * kBN;
             #pragma unroll 1
-            for (int c = 0; c < ((p.debug & 2) ? 0 : kBN / 32); c++) {
+            for (int c = 0; c < kBN / 32; c++) {
                 uint32_t r[32];
                 umma::tmem_load_32x32(t_row + (uint32_t)(c * 32), r);
                 umma::tmem_load_wait();
                 const int n0 = tn * kBN + c * 32;
-                if (m < p.M && n0 < p.N && !(p.debug & 1)) {
+                if (n0 < p.N) {                                    // warp-uniform
                     float v[32];
                     #pragma unroll
                     for (int j = 0; j < 32; j++) v[j] = __fadd_rn(__fmul_rn(p.alpha, __uint_as_float(r[j])), row_bias);
@@ -207,42 +211,68 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                             v[j] = __fadd_rn(v[j], b4.x); v[j + 1] = __fadd_rn(v[j + 1], b4.y);
                             v[j + 2] = __fadd_rn(v[j + 2], b4.z); v[j + 3] = __fadd_rn(v[j + 3], b4.w);
                         }
-                    } else if (p.bias.mode == kBiasMatrix) {
+                    } else if (p.bias.mode == kBiasMatrix && m < p.M) {
+                        float cv[32];
+                        if (p.bias.dtype == DTYPE_FLOAT32) {            // independent loads, issued back to back
+                            #pragma unroll
+                            for (int j = 0; j < 32; j++) {
+                                const long long ci = (n0 + j < p.N) ? bias_index(p.bias, m, n0 + j) : -1;
+                                cv[j] = ci >= 0 ? __ldg((const float*)p.bias.ptr + ci) : 0.0f;
+                            }
+                        } else {
+                            #pragma unroll
+                            for (int j = 0; j < 32; j++) {
+                                const long long ci = (n0 + j < p.N) ? bias_index(p.bias, m, n0 + j) : -1;
+                                cv[j] = ci >= 0 ? (float)load_f64_rt(p.bias.ptr, p.bias.dtype, (size_t)ci) : 0.0f;
+                            }
+                        }
                         #pragma unroll
-                        for (int j = 0; j < 32; j++) {
-                            const long long ci = (n0 + j < p.N) ? bias_index(p.bias, m, n0 + j) : -1;
-                            if (ci >= 0) v[j] = __fmaf_rn(p.beta, (float)load_f64_rt(p.bias.ptr, p.bias.dtype, (size_t)ci), v[j]);
-                        }
+                        for (int j = 0; j < 32; j++) v[j] = __fmaf_rn(p.beta, cv[j], v[j]);
                     }
-                    const size_t row_off = (size_t)m * p.N + n0;
-                    const bool full_chunk = (n0 + 32 <= p.N);
+                    // Stage this warp's 32 x 32 chunk (already in output format) in shared memory,
+                    // then write it out with every store instruction covering whole 128-byte lines.
+                    uint32_t* my_rows = my_stage + lane * kStageRowWords;
                     if (p.dy == DTYPE_FLOAT32) {
-                        float* dst = (float*)p.Y + row_off;
-                        if (full_chunk && (((uintptr_t)dst & 15) == 0)) {
-                            #pragma unroll
-                            for (int j = 0; j < 32; j += 4) __stcs((float4*)(dst + j), make_float4(v[j], v[j + 1], v[j + 2], v[j + 3]));
-                        } else {
-                            #pragma unroll
-                            for (int j = 0; j < 32; j++) if (n0 + j < p.N) dst[j] = v[j];
-                        }
+                        #pragma unroll
+                        for (int j = 0; j < 32; j += 4)
+                            *(uint4*)(my_rows + j) = make_uint4(__float_as_uint(v[j]), __float_as_uint(v[j + 1]),
+                                                                 __float_as_uint(v[j + 2]), __float_as_uint(v[j + 3]));
+                    } else if (p.dy == DTYPE_BFLOAT16) {
+                        #pragma unroll
+                        for (int j = 0; j < 32; j += 8)
+                            *(uint4*)(my_rows + (j >> 1)) = make_uint4(encode_bf16x2(v[j], v[j + 1]), encode_bf16x2(v[j + 2], v[j + 3]),
+                                                                        encode_bf16x2(v[j + 4], v[j + 5]), encode_bf16x2(v[j + 6], v[j + 7]));
                     } else {
-                        uint16_t* dst = (uint16_t*)p.Y + row_off;
-                        uint32_t packed[16];
-                        if (p.dy == DTYPE_BFLOAT16) {
-                            #pragma unroll
-                            for (int j = 0; j < 32; j += 2) packed[j >> 1] = encode_bf16x2(v[j], v[j + 1]);
+                        #pragma unroll
+                        for (int j = 0; j < 32; j += 8)
+                            *(uint4*)(my_rows + (j >> 1)) = make_uint4(encode_f16x2(v[j], v[j + 1]), encode_f16x2(v[j + 2], v[j + 3]),
+                                                                        encode_f16x2(v[j + 4], v[j + 5]), encode_f16x2(v[j + 6], v[j + 7]));
+                    }
+                    __syncwarp();
+                    const int esize = p.dy == DTYPE_FLOAT32 ? 4 : 2;
+                    const int lanes_per_row = esize * 2;                 // 16-byte pieces per 32-element row
+                    const int rows_per_pass = 32 / lanes_per_row;
+                    const int piece = lane % lanes_per_row;              // which 16 bytes of the row
+                    const int elems_per_piece = 16 / esize;
+                    const int n = n0 + piece * elems_per_piece;
+                    #pragma unroll 1
+                    for (int r0 = 0; r0 < 32; r0 += rows_per_pass) {
+                        const int row = r0 + lane / lanes_per_row;
+                        const int mr = tm * kBM + quarter * 32 + row;
+                        if (mr >= p.M || n >= p.N) continue;
+                        const uint4 val = *(const uint4*)(my_stage + row * kStageRowWords + piece * 4);
+                        char* dst = (char*)p.Y + ((size_t)mr * p.N + n) * esize;
+                        if (p.vec_store && n + elems_per_piece <= p.N) {
+                            __stcs((uint4*)dst, val);
                         } else {
-                            #pragma unroll
-                            for (int j = 0; j < 32; j += 2) packed[j >> 1] = encode_f16x2(v[j], v[j + 1]);
-                        }
-                        if (full_chunk && (((uintptr_t)dst & 15) == 0)) {
-                            #pragma unroll
-                            for (int j = 0; j < 16; j += 4) __stcs((uint4*)(dst + 2 * j), make_uint4(packed[j], packed[j + 1], packed[j + 2], packed[j + 3]));
-                        } else {
-                            #pragma unroll
-                            for (int j = 0; j < 32; j++) if (n0 + j < p.N) dst[j] = (uint16_t)(packed[j >> 1] >> ((j & 1) * 16));
+                            const uint32_t w[4] = {val.x, val.y, val.z, val.w};
+                            for (int e = 0; e < elems_per_piece && n + e < p.N; e++) {
+                                if (esize == 4) ((uint32_t*)dst)[e] = w[e];
+                                else ((uint16_t*)dst)[e] = (uint16_t)(w[e >> 1] >> ((e & 1) * 16));
+                            }
                         }
                     }
+                    __syncwarp();
                 }
             }
             umma::fence_before_sync();
@@ -299,7 +329,7 @@ bool gemm_tensor_core(const Tensor* A, const Tensor* B, Tensor* Y, const GemmSha
     p.alpha = alpha; p.beta = beta;
     p.bias = bias;
     p.status = device_status_word();
-    p.debug = getenv("TOPS_TC_DEBUG") ? atoi(getenv("TOPS_TC_DEBUG")) : 0;
+    p.vec_store = (((uintptr_t)Y->data & 15) == 0) && (((size_t)g.N * dtype_bytes(dy)) % 16 == 0);
 
     const uint32_t fa = fp8 ? (da == DTYPE_FLOAT8_E5M2 ? 1u : 0u) : (da == DTYPE_BFLOAT16 ? 1u : 0u);
     const uint32_t fb = fp8 ? (db == DTYPE_FLOAT8_E5M2 ? 1u : 0u) : (db == DTYPE_BFLOAT16 ? 1u : 0u);
