@@ -1,9 +1,156 @@
-// Implicit-GEMM Conv2d on tensor cores.  Placeholder until the kernel lands: reports that it
-// covers no case, so every convolution takes the exact double-accumulating kernel.
+// Conv2d on tensor cores: implicit GEMM as a sum of shifted GEMMs (tensor_ops.c:1036-1114).
+//
+// Covered: group 1, stride 1, any dilation and padding; X and W both fp16, both bf16, or both fp8;
+// output fp32 / bf16 / fp16; C a multiple of 16 bytes of elements.  Everything else takes the
+// exact kernel in conv.cu.
+//
+// 1. X (NCHW) is copied once into a zero-padded channels-last scratch tensor Xp[N][Hp][Wp][C]
+//    (top / left padding as given, enough rows / columns at the bottom / right for every tap).
+//    Seen as a matrix [N*Hp*Wp, C] its row q = (n, oh, ow) is the top-left input pixel of output
+//    (n, oh, ow), and the pixel under filter tap (kh, kw) is simply row q + kh*dil_h*Wp + kw*dil_w.
+// 2. W [M][C][KH][KW] is copied into tap-major scratch Wt[KH*KW][M][C].
+// 3. The persistent tcgen05 kernel (tc_kernel.cuh) runs one GEMM whose K loop walks the taps: for
+//    tap t and channel block cb it TMA-loads 128 rows of Xp starting at tile_row + shift(t) and 256
+//    rows of Wt[t], and accumulates into the same tensor-memory tile.  The epilogue adds the bias
+//    and scatters the valid rows (oh < OH, ow < OW) into the NCHW output.
+// Both scratch tensors come from the stream-ordered pool and go back to it right after the launch.
+// Algorithmic flops: 2 * N*OH*OW * M * C*KH*KW; the padded formulation computes (Hp*Wp)/(OH*OW)
+// times as many rows (1.07x for 56x56, k3, p1).
 #include "conv_common.cuh"
+#include "tc_kernel.cuh"
 
 namespace tops {
 
-bool conv_tensor_core(const Tensor*, const Tensor*, const Tensor*, Tensor*, const ConvGeom&) { return false; }
+// NCHW -> zero-padded NHWC.  One CTA handles 64 channels x 64 consecutive padded columns of one
+// padded row; elements move as raw bits (ES bytes each).
+template <typename E>
+__global__ void __launch_bounds__(256) nchw_to_padded_nhwc(const E* __restrict__ x, E* __restrict__ xp,
+                                                            int C, int H, int W, int Hp, int Wp, int pt, int pl) {
+    __shared__ E tile[64][64 + 2];
+    const int wp0 = blockIdx.x * 64, hp = blockIdx.y % Hp, n = blockIdx.y / Hp, c0 = blockIdx.z * 64;
+    const int h = hp - pt;
+    const bool row_inside = h >= 0 && h < H;
+    // read: 64 channels x 64 columns, consecutive threads along the row (contiguous in NCHW)
+    for (int e = threadIdx.x; e < 64 * 64; e += 256) {
+        const int cc = e >> 6, ww = e & 63;
+        const int c = c0 + cc, w = wp0 + ww - pl;
+        E v = E(0);
+        if (row_inside && c < C && w >= 0 && w < W) v = x[(((size_t)n * C + c) * H + h) * W + w];
+        tile[cc][ww] = v;
+    }
+    __syncthreads();
+    // write: consecutive threads along the channels (contiguous in NHWC)
+    for (int e = threadIdx.x; e < 64 * 64; e += 256) {
+        const int ww = e >> 6, cc = e & 63;
+        const int c = c0 + cc, wp = wp0 + ww;
+        if (c < C && wp < Wp) xp[(((size_t)n * Hp + hp) * Wp + wp) * C + c] = tile[cc][ww];
+    }
+}
+
+// [M][C][KH*KW] -> [KH*KW][M][C]
+template <typename E>
+__global__ void __launch_bounds__(256) filters_to_tap_major(const E* __restrict__ w, E* __restrict__ wt, int M, int C, int taps) {
+    const size_t total = (size_t)M * C * taps;
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
+        const int c = (int)(i % C);
+        const size_t r = i / C;
+        const int m = (int)(r % M), t = (int)(r / M);
+        wt[i] = w[((size_t)m * C + c) * taps + t];
+    }
+}
+
+static bool fp8_dtype(int dt) { return dt == DTYPE_FLOAT8_E4M3 || dt == DTYPE_FLOAT8_E5M2; }
+
+bool conv_tensor_core(const Tensor* X, const Tensor* W, const Tensor* B, Tensor* Y, const ConvGeom& c) {
+    const int dx = (int)X->dtype, dw = (int)W->dtype, dy = (int)Y->dtype;
+    const bool fp8 = fp8_dtype(dx) && fp8_dtype(dw);
+    const bool half16 = dx == dw && (dx == DTYPE_FLOAT16 || dx == DTYPE_BFLOAT16);
+    if (!fp8 && !half16) return false;
+    if (dy != DTYPE_FLOAT32 && dy != DTYPE_BFLOAT16 && dy != DTYPE_FLOAT16) return false;
+    if (c.G != 1 || c.sh != 1 || c.sw != 1 || c.dh < 1 || c.dw < 1 || c.pt < 0 || c.pl < 0) return false;
+    const int es = fp8 ? 1 : 2;
+    if (((size_t)c.C * es) % 16 != 0) return false;
+    if (getenv("TOPS_DISABLE_TC")) return false;
+    if ((size_t)c.N * c.OH * c.OW * c.M < (size_t)1 << 16) return false;     // tiny problems: not worth two copies
+
+    const int Hp = max(c.H + c.pt, c.OH + (c.KH - 1) * c.dh);
+    const int Wp = max(c.W + c.pl, c.OW + (c.KW - 1) * c.dw);
+    const size_t rows = (size_t)c.N * Hp * Wp;
+    if (rows >= 0x7FFFFF00ull) return false;
+    const int taps = c.KH * c.KW;
+
+    DeviceState* st = acquire_device();
+    if (!st) return true;
+    cudaStream_t s = current_stream();
+    void *xp = nullptr, *wt = nullptr;
+    const size_t xp_bytes = rows * c.C * es, wt_bytes = (size_t)taps * c.M * c.C * es;
+    if (cudaMallocAsync(&xp, xp_bytes, s) != cudaSuccess) { cudaGetLastError(); return false; }
+    if (cudaMallocAsync(&wt, wt_bytes, s) != cudaSuccess) { cudaGetLastError(); cudaFreeAsync(xp, s); return false; }
+
+    const dim3 tgrid((Wp + 63) / 64, c.N * Hp, (c.C + 63) / 64);
+    const int wgrid = grid_for((size_t)c.M * c.C * taps, 256, st->sm_count, 4);
+    if (es == 2) {
+        nchw_to_padded_nhwc<uint16_t><<<tgrid, 256, 0, s>>>((const uint16_t*)X->data, (uint16_t*)xp, c.C, c.H, c.W, Hp, Wp, c.pt, c.pl);
+        filters_to_tap_major<uint16_t><<<wgrid, 256, 0, s>>>((const uint16_t*)W->data, (uint16_t*)wt, c.M, c.C, taps);
+    } else {
+        nchw_to_padded_nhwc<uint8_t><<<tgrid, 256, 0, s>>>((const uint8_t*)X->data, (uint8_t*)xp, c.C, c.H, c.W, Hp, Wp, c.pt, c.pl);
+        filters_to_tap_major<uint8_t><<<wgrid, 256, 0, s>>>((const uint8_t*)W->data, (uint8_t*)wt, c.M, c.C, taps);
+    }
+    bool ok = TOPS_CHECK_LAUNCH("conv2d_forward (layout copies)");
+
+    const int k_step = kRowBytes / es;
+    CUtensorMap map_a, map_b;
+    const uint64_t dims_a[2] = {(uint64_t)c.C, (uint64_t)rows};
+    const uint64_t strides_a[1] = {(uint64_t)c.C * es};
+    const uint32_t box_a[2] = {(uint32_t)k_step, (uint32_t)kBM};
+    const uint64_t dims_b[3] = {(uint64_t)c.C, (uint64_t)c.M, (uint64_t)taps};
+    const uint64_t strides_b[2] = {(uint64_t)c.C * es, (uint64_t)c.M * c.C * es};
+    const uint32_t box_b[3] = {(uint32_t)k_step, (uint32_t)kBN, 1u};
+    const bool f16 = dx == DTYPE_FLOAT16;
+    ok = ok && make_tensor_map(&map_a, xp, es, fp8, f16, 2, dims_a, strides_a, box_a, nullptr) &&
+         make_tensor_map(&map_b, wt, es, fp8, f16, 3, dims_b, strides_b, box_b, nullptr);
+
+    if (ok) {
+        TcParams p;
+        // rows beyond the last valid output position of the last image need no tile
+        const size_t last_row = ((size_t)(c.N - 1) * Hp + (c.OH - 1)) * Wp + c.OW;
+        p.M = (int)rows; p.N = c.M;
+        p.cv.c_blocks = (c.C + k_step - 1) / k_step;
+        p.k_blocks = taps * p.cv.c_blocks;
+        p.k_step = k_step;
+        p.tiles_m = (int)((last_row + kBM - 1) / kBM);
+        p.tiles_n = (c.M + kBN - 1) / kBN;
+        p.Y = Y->data; p.dy = dy;
+        p.alpha = 1.0f; p.beta = 1.0f;
+        p.bias.ptr = (B && B->data) ? B->data : nullptr;
+        p.bias.dtype = p.bias.ptr ? (int)B->dtype : DTYPE_FLOAT32;
+        p.bias.mode = p.bias.ptr ? kBiasPerColumn : kBiasNone;
+        p.bias.rows = 1; p.bias.cols = c.M;
+        p.status = device_status_word();
+        p.vec_store = 0;
+        p.cv.Wp = Wp; p.cv.plane = Hp * Wp;
+        p.cv.images = c.N; p.cv.OH = c.OH; p.cv.OW = c.OW; p.cv.OC = c.M;
+        p.cv.KW = c.KW; p.cv.dil_h = c.dh; p.cv.dil_w = c.dw;
+        const uint32_t fa = fp8 ? (dx == DTYPE_FLOAT8_E5M2 ? 1u : 0u) : (dx == DTYPE_BFLOAT16 ? 1u : 0u);
+        const uint32_t fb = fp8 ? (dw == DTYPE_FLOAT8_E5M2 ? 1u : 0u) : (dw == DTYPE_BFLOAT16 ? 1u : 0u);
+        const uint32_t idesc = umma::instr_desc(fa, fb, kBM, kBN);
+        const int tiles = p.tiles_m * p.tiles_n;
+        const int grid = tiles < st->sm_count ? tiles : st->sm_count;
+        if (fp8) {
+            static bool attr = false;
+            if (!attr) { cudaFuncSetAttribute(tc_kernel<true, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kTcSmemBytes); attr = true; }
+            tc_kernel<true, true><<<grid, kTcThreads, kTcSmemBytes, s>>>(map_a, map_b, p, idesc);
+        } else {
+            static bool attr = false;
+            if (!attr) { cudaFuncSetAttribute(tc_kernel<false, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kTcSmemBytes); attr = true; }
+            tc_kernel<false, true><<<grid, kTcThreads, kTcSmemBytes, s>>>(map_a, map_b, p, idesc);
+        }
+        ok = TOPS_CHECK_LAUNCH("conv2d_forward (tensor cores)");
+        if (ok) count_tensor_core_launch();
+    }
+    cudaFreeAsync(xp, s);
+    cudaFreeAsync(wt, s);
+    return ok;            // false: the exact kernel computes the result instead
+}
 
 }  // namespace tops

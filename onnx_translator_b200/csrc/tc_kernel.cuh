@@ -1,0 +1,288 @@
+// The persistent tcgen05 kernel shared by Gemm and Conv2d (see gemm_tc.cu for the role layout).
+#pragma once
+
+#include "gemm_common.cuh"
+#include "umma.cuh"
+#include "elementwise.cuh"
+
+namespace tops {
+
+// ---- kernel --------------------------------------------------------------------------------------------------------
+constexpr int kBM = 128, kBN = 256, kRowBytes = 128, kStages = 4;
+constexpr int kTileABytes = kBM * kRowBytes;       // 16 KB
+constexpr int kTileBBytes = kBN * kRowBytes;       // 32 KB
+constexpr int kStageBytes = kTileABytes + kTileBBytes;
+constexpr int kTcThreads = 192;
+constexpr int kStageRowWords = 36;                 // 32 words of payload + 4 of padding: conflict-free 16-byte accesses
+constexpr size_t kTcSmemBytes = (size_t)kStages * kStageBytes + 1024 /*alignment slack*/ + 128 /*barriers*/ + 4 * kBN * 4 /*bias*/ +
+                                4 * 32 * kStageRowWords * 4 /*output staging*/;
+
+// Convolution as shifted GEMMs over a zero-padded channels-last copy of the input: row q of the
+// GEMM is the padded position (n, oh, ow) = (q / plane, (q % plane) / Wp, q % Wp); filter tap
+// (kh, kw) reads rows q + kh * dil_h * Wp + kw * dil_w.  Rows with oh >= OH or ow >= OW are
+// computed and dropped.
+struct ConvView {
+    int Wp, plane;         // padded width, padded plane size Hp * Wp
+    int images, OH, OW, OC;
+    int c_blocks;          // K blocks per filter tap
+    int KW, dil_h, dil_w;
+};
+
+struct TcParams {
+    int M, N;
+    int k_blocks;          // K blocks of 128 bytes
+    int k_step;            // elements per K block
+    int tiles_m, tiles_n;
+    void* Y;
+    int dy;
+    float alpha, beta;
+    BiasView bias;
+    int* status;           // device-visible word, set non-zero when a wait gave up
+    int vec_store;         // Y base and row pitch are 16-byte aligned
+    ConvView cv;           // convolution mode only
+};
+
+__device__ __forceinline__ void tile_coords(int tile, int tiles_m, int tiles_n, int& tm, int& tn) {
+    // groups of 16 row blocks sweep all column blocks: concurrently running CTAs share A and B tiles in L2
+    constexpr int kGroup = 16;
+    const int per_group = kGroup * tiles_n;
+    const int g = tile / per_group, r = tile - g * per_group;
+    const int rows = min(kGroup, tiles_m - g * kGroup);
+    tm = g * kGroup + r % rows;
+    tn = r / rows;
+}
+
+template <bool FP8, bool CONV>
+__global__ void __launch_bounds__(kTcThreads, 1)
+tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, const TcParams p,
+               const uint32_t idesc) {
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* tiles = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+    uint64_t* bars = (uint64_t*)(tiles + (size_t)kStages * kStageBytes);
+    uint64_t* full = bars;                    // [kStages]  TMA -> MMA
+    uint64_t* empty = bars + kStages;         // [kStages]  MMA -> TMA
+    uint64_t* acc_full = bars + 2 * kStages;  // [2]        MMA -> epilogue
+    uint64_t* acc_empty = acc_full + 2;       // [2]        epilogue -> MMA
+    uint32_t* tmem_slot = (uint32_t*)(acc_empty + 2);
+    volatile int* abort_flag = (volatile int*)(tmem_slot + 1);
+    float* bias_stage = (float*)(bars + 16);           // 4 warps x kBN floats
+    uint32_t* out_stage = (uint32_t*)(bias_stage + 4 * kBN);   // 4 warps x 32 rows x kStageRowWords
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int total_tiles = p.tiles_m * p.tiles_n;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < kStages; s++) { umma::mbar_init(&full[s], 1); umma::mbar_init(&empty[s], 1); }
+        for (int b = 0; b < 2; b++) { umma::mbar_init(&acc_full[b], 1); umma::mbar_init(&acc_empty[b], 4); }
+        *abort_flag = 0;
+        umma::mbar_fence_init();
+        umma::tma_prefetch_desc(&map_a);
+        umma::tma_prefetch_desc(&map_b);
+    }
+    if (warp == 1) umma::tmem_alloc(tmem_slot, 512);
+    umma::fence_before_sync();
+    __syncthreads();
+    umma::fence_after_sync();
+    const uint32_t tmem_base = *tmem_slot;
+
+    if (warp == 0) {
+        if (lane == 0) {
+            uint32_t it = 0;
+            for (int tile = blockIdx.x; tile < total_tiles && !*abort_flag; tile += gridDim.x) {
+                int tm, tn;
+                tile_coords(tile, p.tiles_m, p.tiles_n, tm, tn);
+                for (int kb = 0; kb < p.k_blocks; kb++, it++) {
+                    const uint32_t s = it % kStages, ph = (it / kStages) & 1u;
+                    if (!umma::mbar_wait(&empty[s], ph ^ 1u, abort_flag)) break;
+                    uint8_t* a_tile = tiles + (size_t)s * kStageBytes;
+                    umma::mbar_expect_tx(&full[s], kStageBytes);
+                    if constexpr (CONV) {
+                        const int tap = kb / p.cv.c_blocks, cb = kb - tap * p.cv.c_blocks;
+                        const int kh = tap / p.cv.KW, kw = tap - kh * p.cv.KW;
+                        const int shift = kh * p.cv.dil_h * p.cv.Wp + kw * p.cv.dil_w;
+                        umma::tma_load_2d(a_tile, &map_a, &full[s], cb * p.k_step, tm * kBM + shift);
+                        umma::tma_load_3d(a_tile + kTileABytes, &map_b, &full[s], cb * p.k_step, tn * kBN, tap);
+                    } else {
+                        umma::tma_load_2d(a_tile, &map_a, &full[s], kb * p.k_step, tm * kBM);
+                        umma::tma_load_2d(a_tile + kTileABytes, &map_b, &full[s], kb * p.k_step, tn * kBN);
+                    }
+                }
+            }
+        }
+    } else if (warp == 1) {
+        if (lane == 0) {
+            uint32_t it = 0, local = 0;
+            for (int tile = blockIdx.x; tile < total_tiles && !*abort_flag; tile += gridDim.x, local++) {
+                const uint32_t buf = local & 1u, use = (local >> 1) & 1u;
+                if (!umma::mbar_wait(&acc_empty[buf], use ^ 1u, abort_flag)) break;
+                umma::fence_after_sync();
+                const uint32_t d_tmem = tmem_base + buf * kBN;
+                bool ok = true;
+                for (int kb = 0; kb < p.k_blocks; kb++, it++) {
+                    const uint32_t s = it % kStages, ph = (it / kStages) & 1u;
+                    if (!umma::mbar_wait(&full[s], ph, abort_flag)) { ok = false; break; }
+                    umma::fence_after_sync();
+                    const uint8_t* a_tile = tiles + (size_t)s * kStageBytes;
+                    const uint64_t da = umma::smem_desc_k_major_sw128(a_tile);
+                    const uint64_t db = umma::smem_desc_k_major_sw128(a_tile + kTileABytes);
+                    #pragma unroll
+                    for (int k = 0; k < kRowBytes / 32; k++)      // 32 bytes of K per instruction
+                        umma::mma_ss<FP8>(d_tmem, da + (uint64_t)(k * 2), db + (uint64_t)(k * 2), idesc, (kb | k) != 0);
+                    umma::mma_commit(&empty[s]);                    // the stage is free once these MMAs retire
+                }
+                if (!ok) break;
+                umma::mma_commit(&acc_full[buf]);
+            }
+        }
+    } else {
+        const int quarter = warp & 3;                               // TMEM lanes this warp may read
+        uint32_t local = 0;
+        float* my_bias = bias_stage + quarter * kBN;                 // this warp's private copy: no cross-warp sync
+        uint32_t* my_stage = out_stage + quarter * 32 * kStageRowWords;
+        for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x, local++) {
+            const uint32_t buf = local & 1u, use = (local >> 1) & 1u;
+            int tm, tn;
+            tile_coords(tile, p.tiles_m, p.tiles_n, tm, tn);
+            const int m = tm * kBM + quarter * 32 + lane;
+            // beta * C for this tile, fetched while the tensor core is still working on it
+            float row_bias = 0.0f;
+            if (p.bias.mode == kBiasPerColumn) {
+                __syncwarp();
+                #pragma unroll
+                for (int j = 0; j < kBN / 32; j++) {
+                    const int n = tn * kBN + j * 32 + lane;
+                    my_bias[j * 32 + lane] = n < p.N ? __fmul_rn(p.beta, (float)load_f64_rt(p.bias.ptr, p.bias.dtype, (size_t)n)) : 0.0f;
+                }
+                __syncwarp();
+            } else if (p.bias.mode == kBiasScalar) {
+                row_bias = __fmul_rn(p.beta, (float)load_f64_rt(p.bias.ptr, p.bias.dtype, 0));
+            } else if (p.bias.mode == kBiasPerRow && m < p.M) {
+                row_bias = __fmul_rn(p.beta, (float)load_f64_rt(p.bias.ptr, p.bias.dtype, (size_t)m));
+            }
+            if (!umma::mbar_wait(&acc_full[buf], use, abort_flag)) break;
+            umma::fence_after_sync();
+            const uint32_t t_row = tmem_base + ((uint32_t)(quarter * 32) << 16) + buf * kBN;
+            #pragma unroll 1
+            for (int c = 0; c < kBN / 32; c++) {
+                uint32_t r[32];
+                umma::tmem_load_32x32(t_row + (uint32_t)(c * 32), r);
+                umma::tmem_load_wait();
+                const int n0 = tn * kBN + c * 32;
+                if (n0 < p.N) {                                    // warp-uniform
+                    float v[32];
+                    #pragma unroll
+                    for (int j = 0; j < 32; j++) v[j] = __fadd_rn(__fmul_rn(p.alpha, __uint_as_float(r[j])), row_bias);
+                    if (p.bias.mode == kBiasPerColumn) {
+                        #pragma unroll
+                        for (int j = 0; j < 32; j += 4) {
+                            const float4 b4 = *(const float4*)(my_bias + c * 32 + j);
+                            v[j] = __fadd_rn(v[j], b4.x); v[j + 1] = __fadd_rn(v[j + 1], b4.y);
+                            v[j + 2] = __fadd_rn(v[j + 2], b4.z); v[j + 3] = __fadd_rn(v[j + 3], b4.w);
+                        }
+                    } else if (p.bias.mode == kBiasMatrix && m < p.M) {
+                        float cv[32];
+                        if (p.bias.dtype == DTYPE_FLOAT32) {            // independent loads, issued back to back
+                            #pragma unroll
+                            for (int j = 0; j < 32; j++) {
+                                const long long ci = (n0 + j < p.N) ? bias_index(p.bias, m, n0 + j) : -1;
+                                cv[j] = ci >= 0 ? __ldg((const float*)p.bias.ptr + ci) : 0.0f;
+                            }
+                        } else {
+                            #pragma unroll
+                            for (int j = 0; j < 32; j++) {
+                                const long long ci = (n0 + j < p.N) ? bias_index(p.bias, m, n0 + j) : -1;
+                                cv[j] = ci >= 0 ? (float)load_f64_rt(p.bias.ptr, p.bias.dtype, (size_t)ci) : 0.0f;
+                            }
+                        }
+                        #pragma unroll
+                        for (int j = 0; j < 32; j++) v[j] = __fmaf_rn(p.beta, cv[j], v[j]);
+                    }
+                    if constexpr (CONV) {
+                        // NCHW output: for one output channel, consecutive lanes (consecutive padded
+                        // positions) are consecutive pixels, so each store instruction is contiguous.
+                        const int img = m / p.cv.plane, rem = m - img * p.cv.plane;
+                        const int oh = rem / p.cv.Wp, ow = rem - oh * p.cv.Wp;
+                        if (img < p.cv.images && oh < p.cv.OH && ow < p.cv.OW) {
+                            const size_t plane_out = (size_t)p.cv.OH * p.cv.OW;
+                            const size_t base = ((size_t)img * p.cv.OC + n0) * plane_out + (size_t)oh * p.cv.OW + ow;
+                            if (p.dy == DTYPE_FLOAT32) {
+                                float* dst = (float*)p.Y + base;
+                                #pragma unroll
+                                for (int j = 0; j < 32; j++) if (n0 + j < p.N) dst[(size_t)j * plane_out] = v[j];
+                            } else if (p.dy == DTYPE_BFLOAT16) {
+                                uint16_t* dst = (uint16_t*)p.Y + base;
+                                #pragma unroll
+                                for (int j = 0; j < 32; j++) if (n0 + j < p.N) dst[(size_t)j * plane_out] = encode_bf16(v[j]);
+                            } else {
+                                uint16_t* dst = (uint16_t*)p.Y + base;
+                                #pragma unroll
+                                for (int j = 0; j < 32; j++) if (n0 + j < p.N) dst[(size_t)j * plane_out] = encode_f16(v[j]);
+                            }
+                        }
+                        continue;
+                    }
+                    // Stage this warp's 32 x 32 chunk (already in output format) in shared memory,
+                    // then write it out with every store instruction covering whole 128-byte lines.
+                    uint32_t* my_rows = my_stage + lane * kStageRowWords;
+                    if (p.dy == DTYPE_FLOAT32) {
+                        #pragma unroll
+                        for (int j = 0; j < 32; j += 4)
+                            *(uint4*)(my_rows + j) = make_uint4(__float_as_uint(v[j]), __float_as_uint(v[j + 1]),
+                                                                 __float_as_uint(v[j + 2]), __float_as_uint(v[j + 3]));
+                    } else if (p.dy == DTYPE_BFLOAT16) {
+                        #pragma unroll
+                        for (int j = 0; j < 32; j += 8)
+                            *(uint4*)(my_rows + (j >> 1)) = make_uint4(encode_bf16x2(v[j], v[j + 1]), encode_bf16x2(v[j + 2], v[j + 3]),
+                                                                        encode_bf16x2(v[j + 4], v[j + 5]), encode_bf16x2(v[j + 6], v[j + 7]));
+                    } else {
+                        #pragma unroll
+                        for (int j = 0; j < 32; j += 8)
+                            *(uint4*)(my_rows + (j >> 1)) = make_uint4(encode_f16x2(v[j], v[j + 1]), encode_f16x2(v[j + 2], v[j + 3]),
+                                                                        encode_f16x2(v[j + 4], v[j + 5]), encode_f16x2(v[j + 6], v[j + 7]));
+                    }
+                    __syncwarp();
+                    const int esize = p.dy == DTYPE_FLOAT32 ? 4 : 2;
+                    const int lanes_per_row = esize * 2;                 // 16-byte pieces per 32-element row
+                    const int rows_per_pass = 32 / lanes_per_row;
+                    const int piece = lane % lanes_per_row;              // which 16 bytes of the row
+                    const int elems_per_piece = 16 / esize;
+                    const int n = n0 + piece * elems_per_piece;
+                    #pragma unroll 1
+                    for (int r0 = 0; r0 < 32; r0 += rows_per_pass) {
+                        const int row = r0 + lane / lanes_per_row;
+                        const int mr = tm * kBM + quarter * 32 + row;
+                        if (mr >= p.M || n >= p.N) continue;
+                        const uint4 val = *(const uint4*)(my_stage + row * kStageRowWords + piece * 4);
+                        char* dst = (char*)p.Y + ((size_t)mr * p.N + n) * esize;
+                        if (p.vec_store && n + elems_per_piece <= p.N) {
+                            __stcs((uint4*)dst, val);
+                        } else {
+                            const uint32_t w[4] = {val.x, val.y, val.z, val.w};
+                            for (int e = 0; e < elems_per_piece && n + e < p.N; e++) {
+                                if (esize == 4) ((uint32_t*)dst)[e] = w[e];
+                                else ((uint16_t*)dst)[e] = (uint16_t)(w[e >> 1] >> ((e & 1) * 16));
+                            }
+                        }
+                    }
+                    __syncwarp();
+                }
+            }
+            umma::fence_before_sync();
+            __syncwarp();
+            if (lane == 0) umma::mbar_arrive(&acc_empty[buf]);
+        }
+    }
+
+    umma::fence_before_sync();
+    __syncthreads();
+    if (threadIdx.x == 0 && *abort_flag && p.status) atomicExch(p.status, 1);
+    if (warp == 1) {
+        umma::fence_after_sync();
+        umma::tmem_dealloc(tmem_base, 512);
+    }
+}
+
+
+void count_tensor_core_launch();
+
+}  // namespace tops

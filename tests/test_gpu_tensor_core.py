@@ -96,3 +96,79 @@ def test_gemm_unsupported_layouts_fall_back_to_the_exact_kernel(port):
     assert _tc_count() == before
     want = port.gemm(a, "bfloat16", b, "bfloat16", None, "float32", "float32", 1.0, 1.0, 1, 1)
     assert np.array_equal(got, want)
+
+
+# ---- Conv2d ------------------------------------------------------------------------------------------------
+def _conv_f64(x, w, b, pads, dil, out_hw):
+    """Direct convolution in float64 (stride 1, group 1) and the accumulated magnitude."""
+    n, c, h, wd = x.shape
+    m, _, kh, kw = w.shape
+    oh, ow = out_hw
+    xp = np.zeros((n, c, h + pads[0] + pads[2] + kh * dil[0], wd + pads[1] + pads[3] + kw * dil[1]))
+    xp[:, :, pads[0]:pads[0] + h, pads[1]:pads[1] + wd] = x
+    y = np.zeros((n, m, oh, ow))
+    s = np.zeros((n, m, oh, ow))
+    for i in range(kh):
+        for j in range(kw):
+            patch = xp[:, :, i * dil[0]:i * dil[0] + oh, j * dil[1]:j * dil[1] + ow]
+            y += np.einsum("nchw,mc->nmhw", patch, w[:, :, i, j], optimize=True)
+            s += np.einsum("nchw,mc->nmhw", np.abs(patch), np.abs(w[:, :, i, j]), optimize=True)
+    if b is not None:
+        y += b.reshape(1, -1, 1, 1)
+        s += np.abs(b).reshape(1, -1, 1, 1)
+    return y, s
+
+
+CONV_CASES = [  # N, C, H, W, M, k, pads, dil, x_dt, out_dt, bias
+    (4, 64, 28, 28, 128, 3, (1, 1, 1, 1), (1, 1), "bfloat16", "float32", True),
+    (2, 256, 56, 56, 256, 3, (1, 1, 1, 1), (1, 1), "bfloat16", "bfloat16", False),     # a slab of the benchmark conv
+    (6, 32, 13, 17, 70, 3, (1, 1, 1, 1), (1, 1), "float16", "float16", True),            # odd sizes, ragged channels-out
+    (2, 128, 20, 20, 300, 1, (0, 0, 0, 0), (1, 1), "bfloat16", "float32", True),         # 1x1
+    (2, 48, 24, 24, 64, 3, (2, 2, 2, 2), (2, 2), "bfloat16", "float32", False),          # dilation 2
+    (1, 16, 30, 30, 256, 5, (2, 2, 2, 2), (1, 1), "float16", "float32", True),
+    (2, 64, 19, 23, 96, 3, (1, 0, 0, 1), (1, 1), "bfloat16", "float32", True),           # asymmetric padding
+    (2, 128, 16, 16, 256, 3, (1, 1, 1, 1), (1, 1), "float8_e4m3", "float32", True),
+]
+
+
+@pytest.mark.parametrize("case", CONV_CASES, ids=lambda c: f"n{c[0]}c{c[1]}h{c[2]}w{c[3]}m{c[4]}k{c[5]}-{c[8]}-{c[9]}")
+def test_conv_tensor_core(case):
+    n, c, h, wd, m, k, pads, dil, x_dt, out_dt, with_bias = case
+    rng = np.random.default_rng(n * 131 + c * 7 + m)
+    scale_w = 0.5 if "float8" in x_dt else 0.05
+    x = from_f64(rng.normal(0, 1, (n, c, h, wd)), x_dt)
+    w = from_f64(rng.normal(0, scale_w, (m, c, k, k)), x_dt)
+    b = rng.normal(0, 1, m).astype(np.float32) if with_bias else None
+    oh = h + pads[0] + pads[2] - dil[0] * (k - 1)
+    ow = wd + pads[1] + pads[3] - dil[1] * (k - 1)
+    before = _tc_count()
+    got = to_f64(gpu.conv2d(x, x_dt, w, x_dt, b, "float32", out_dt, pads, (1, 1), dil, 1), out_dt)
+    assert _tc_count() == before + 1, "the call did not take the tensor-core path"
+    want, s_mag = _conv_f64(to_f64(x, x_dt), to_f64(w, x_dt), None if b is None else b.astype(np.float64), pads, dil, (oh, ow))
+    assert got.shape == want.shape
+    _gate(got, want, s_mag, out_dt, "conv")
+
+
+def test_conv_tensor_core_against_the_oracle(port):
+    rng = np.random.default_rng(77)
+    x = from_f64(rng.normal(0, 1, (8, 32, 12, 12)), "bfloat16")
+    w = from_f64(rng.normal(0, 0.1, (64, 32, 3, 3)), "bfloat16")
+    b = rng.normal(0, 1, 64).astype(np.float32)
+    args = (x, "bfloat16", w, "bfloat16", b, "float32", "float32", (1, 1, 1, 1), (1, 1), (1, 1), 1)
+    before = _tc_count()
+    got = gpu.conv2d(*args).astype(np.float64)
+    assert _tc_count() == before + 1
+    want = port.conv2d(*args).astype(np.float64)
+    _, s_mag = _conv_f64(to_f64(x, "bfloat16"), to_f64(w, "bfloat16"), b.astype(np.float64), (1, 1, 1, 1), (1, 1), (12, 12))
+    _gate(got, want, s_mag, "float32", "conv vs oracle")
+
+
+def test_conv_strided_or_grouped_falls_back_to_the_exact_kernel(port):
+    rng = np.random.default_rng(78)
+    x = from_f64(rng.normal(0, 1, (2, 32, 16, 16)), "bfloat16")
+    w = from_f64(rng.normal(0, 0.1, (64, 32, 3, 3)), "bfloat16")
+    args = (x, "bfloat16", w, "bfloat16", None, "float32", "float32", (1, 1, 1, 1), (2, 2), (1, 1), 1)
+    before = _tc_count()
+    got = gpu.conv2d(*args)
+    assert _tc_count() == before
+    assert np.array_equal(got, port.conv2d(*args))
