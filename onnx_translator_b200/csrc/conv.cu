@@ -59,16 +59,12 @@ bool conv_exact(const Tensor* X, const Tensor* W, const Tensor* B, Tensor* Y, co
     return TOPS_CHECK_LAUNCH("conv2d_forward");
 }
 
-}  // namespace tops
-
-using namespace tops;
-
-TOPS_API void conv2d_forward(const Tensor* X, const Tensor* W, const Tensor* B, Tensor* Y, ConvParams* params) {
+bool conv_geometry(const char* name, const Tensor* X, const Tensor* W, const Tensor* B, Tensor* Y, const ConvParams* params, ConvGeom* out) {
     if (!X || !W || !Y || !params || !X->data || !W->data || !Y->data || X->ndim != 4 || W->ndim != 4 || Y->ndim != 4 ||
         !params->pads || !params->strides || !params->dilations) {
-        set_error(TOPS_ERR_INVALID, "conv2d_forward: null argument or tensors that are not 4-D");
+        set_error(TOPS_ERR_INVALID, "%s: null argument or tensors that are not 4-D", name);
         zero_fill(Y);
-        return;
+        return false;
     }
     ConvGeom c;
     c.N = X->shape[0]; c.C = X->shape[1]; c.H = X->shape[2]; c.W = X->shape[3];
@@ -80,10 +76,21 @@ TOPS_API void conv2d_forward(const Tensor* X, const Tensor* W, const Tensor* B, 
     c.G = params->group;
     if (c.G < 1 || c.C % c.G || c.M % c.G || W->shape[1] != c.C / c.G || Y->shape[0] != c.N || Y->shape[1] != c.M ||
         c.sh < 1 || c.sw < 1 || (B && B->data && B->size < (size_t)c.M)) {
-        set_error(TOPS_ERR_INVALID, "conv2d_forward: inconsistent shapes or attributes");
+        set_error(TOPS_ERR_INVALID, "%s: inconsistent shapes or attributes", name);
         zero_fill(Y);
-        return;
+        return false;
     }
+    *out = c;
+    return true;
+}
+
+}  // namespace tops
+
+using namespace tops;
+
+TOPS_API void conv2d_forward(const Tensor* X, const Tensor* W, const Tensor* B, Tensor* Y, ConvParams* params) {
+    ConvGeom c;
+    if (!conv_geometry("conv2d_forward", X, W, B, Y, params, &c)) return;
     if (Y->size == 0) return;
     if (!conv_tensor_core(X, W, B, Y, c)) conv_exact(X, W, B, Y, c);
     finish_op();

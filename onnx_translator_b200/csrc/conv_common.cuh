@@ -19,4 +19,18 @@ bool conv_exact(const Tensor* X, const Tensor* W, const Tensor* B, Tensor* Y, co
 // Implicit-GEMM tensor-core path; false when the case is outside what it covers.
 bool conv_tensor_core(const Tensor* X, const Tensor* W, const Tensor* B, Tensor* Y, const ConvGeom& c);
 
+// The same path in two steps: eligibility and scratch sizes (no CUDA call), then the launches
+// given two scratch buffers of at least xp_bytes / wt_bytes (16-byte aligned device memory).
+struct ConvTcPlan {
+    bool ok, fp8;
+    int es, Hp, Wp, taps;
+    size_t rows, xp_bytes, wt_bytes;
+};
+ConvTcPlan conv_tc_plan(const Tensor* X, const Tensor* W, const Tensor* Y, const ConvGeom& c);
+bool conv_tc_run(const Tensor* X, const Tensor* W, const Tensor* B, Tensor* Y, const ConvGeom& c, const ConvTcPlan& plan,
+                 void* xp, void* wt, int* status);
+
+// Fills a ConvGeom from the ABI arguments; false (with the error recorded) when they are inconsistent.
+bool conv_geometry(const char* name, const Tensor* X, const Tensor* W, const Tensor* B, Tensor* Y, const ConvParams* params, ConvGeom* c);
+
 }  // namespace tops

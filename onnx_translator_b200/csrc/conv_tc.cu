@@ -61,31 +61,36 @@ __global__ void __launch_bounds__(256) filters_to_tap_major(const E* __restrict_
 
 static bool fp8_dtype(int dt) { return dt == DTYPE_FLOAT8_E4M3 || dt == DTYPE_FLOAT8_E5M2; }
 
-bool conv_tensor_core(const Tensor* X, const Tensor* W, const Tensor* B, Tensor* Y, const ConvGeom& c) {
+ConvTcPlan conv_tc_plan(const Tensor* X, const Tensor* W, const Tensor* Y, const ConvGeom& c) {
+    ConvTcPlan plan{};
     const int dx = (int)X->dtype, dw = (int)W->dtype, dy = (int)Y->dtype;
-    const bool fp8 = fp8_dtype(dx) && fp8_dtype(dw);
+    plan.fp8 = fp8_dtype(dx) && fp8_dtype(dw);
     const bool half16 = dx == dw && (dx == DTYPE_FLOAT16 || dx == DTYPE_BFLOAT16);
-    if (!fp8 && !half16) return false;
-    if (dy != DTYPE_FLOAT32 && dy != DTYPE_BFLOAT16 && dy != DTYPE_FLOAT16) return false;
-    if (c.G != 1 || c.sh != 1 || c.sw != 1 || c.dh < 1 || c.dw < 1 || c.pt < 0 || c.pl < 0) return false;
-    const int es = fp8 ? 1 : 2;
-    if (((size_t)c.C * es) % 16 != 0) return false;
-    if (getenv("TOPS_DISABLE_TC")) return false;
-    if ((size_t)c.N * c.OH * c.OW * c.M < (size_t)1 << 16) return false;     // tiny problems: not worth two copies
+    if (!plan.fp8 && !half16) return plan;
+    if (dy != DTYPE_FLOAT32 && dy != DTYPE_BFLOAT16 && dy != DTYPE_FLOAT16) return plan;
+    if (c.G != 1 || c.sh != 1 || c.sw != 1 || c.dh < 1 || c.dw < 1 || c.pt < 0 || c.pl < 0) return plan;
+    plan.es = plan.fp8 ? 1 : 2;
+    if (((size_t)c.C * plan.es) % 16 != 0) return plan;
+    plan.Hp = max(c.H + c.pt, c.OH + (c.KH - 1) * c.dh);
+    plan.Wp = max(c.W + c.pl, c.OW + (c.KW - 1) * c.dw);
+    plan.rows = (size_t)c.N * plan.Hp * plan.Wp;
+    if (plan.rows >= 0x7FFFFF00ull) return plan;
+    plan.taps = c.KH * c.KW;
+    plan.xp_bytes = plan.rows * c.C * plan.es;
+    plan.wt_bytes = (size_t)plan.taps * c.M * c.C * plan.es;
+    plan.ok = true;
+    return plan;
+}
 
-    const int Hp = max(c.H + c.pt, c.OH + (c.KH - 1) * c.dh);
-    const int Wp = max(c.W + c.pl, c.OW + (c.KW - 1) * c.dw);
-    const size_t rows = (size_t)c.N * Hp * Wp;
-    if (rows >= 0x7FFFFF00ull) return false;
-    const int taps = c.KH * c.KW;
-
+bool conv_tc_run(const Tensor* X, const Tensor* W, const Tensor* B, Tensor* Y, const ConvGeom& c, const ConvTcPlan& plan,
+                 void* xp, void* wt, int* status) {
     DeviceState* st = acquire_device();
-    if (!st) return true;
+    if (!st) return false;
     cudaStream_t s = current_stream();
-    void *xp = nullptr, *wt = nullptr;
-    const size_t xp_bytes = rows * c.C * es, wt_bytes = (size_t)taps * c.M * c.C * es;
-    if (cudaMallocAsync(&xp, xp_bytes, s) != cudaSuccess) { cudaGetLastError(); return false; }
-    if (cudaMallocAsync(&wt, wt_bytes, s) != cudaSuccess) { cudaGetLastError(); cudaFreeAsync(xp, s); return false; }
+    const int dx = (int)X->dtype, dw = (int)W->dtype, dy = (int)Y->dtype;
+    const int es = plan.es, Hp = plan.Hp, Wp = plan.Wp, taps = plan.taps;
+    const bool fp8 = plan.fp8;
+    const size_t rows = plan.rows;
 
     const dim3 tgrid((Wp + 63) / 64, c.N * Hp, (c.C + 63) / 64);
     const int wgrid = grid_for((size_t)c.M * c.C * taps, 256, st->sm_count, 4);
@@ -96,7 +101,7 @@ bool conv_tensor_core(const Tensor* X, const Tensor* W, const Tensor* B, Tensor*
         nchw_to_padded_nhwc<uint8_t><<<tgrid, 256, 0, s>>>((const uint8_t*)X->data, (uint8_t*)xp, c.C, c.H, c.W, Hp, Wp, c.pt, c.pl);
         filters_to_tap_major<uint8_t><<<wgrid, 256, 0, s>>>((const uint8_t*)W->data, (uint8_t*)wt, c.M, c.C, taps);
     }
-    bool ok = TOPS_CHECK_LAUNCH("conv2d_forward (layout copies)");
+    if (!TOPS_CHECK_LAUNCH("conv2d_forward (layout copies)")) return false;
 
     const int k_step = kRowBytes / es;
     CUtensorMap map_a, map_b;
@@ -107,47 +112,60 @@ bool conv_tensor_core(const Tensor* X, const Tensor* W, const Tensor* B, Tensor*
     const uint64_t strides_b[2] = {(uint64_t)c.C * es, (uint64_t)c.M * c.C * es};
     const uint32_t box_b[3] = {(uint32_t)k_step, (uint32_t)kBN, 1u};
     const bool f16 = dx == DTYPE_FLOAT16;
-    ok = ok && make_tensor_map(&map_a, xp, es, fp8, f16, 2, dims_a, strides_a, box_a, nullptr) &&
-         make_tensor_map(&map_b, wt, es, fp8, f16, 3, dims_b, strides_b, box_b, nullptr);
+    if (!make_tensor_map(&map_a, xp, es, fp8, f16, 2, dims_a, strides_a, box_a, nullptr) ||
+        !make_tensor_map(&map_b, wt, es, fp8, f16, 3, dims_b, strides_b, box_b, nullptr))
+        return false;
 
-    if (ok) {
-        TcParams p;
-        // rows beyond the last valid output position of the last image need no tile
-        const size_t last_row = ((size_t)(c.N - 1) * Hp + (c.OH - 1)) * Wp + c.OW;
-        p.M = (int)rows; p.N = c.M;
-        p.cv.c_blocks = (c.C + k_step - 1) / k_step;
-        p.k_blocks = taps * p.cv.c_blocks;
-        p.k_step = k_step;
-        p.tiles_m = (int)((last_row + kBM - 1) / kBM);
-        p.tiles_n = (c.M + kBN - 1) / kBN;
-        p.Y = Y->data; p.dy = dy;
-        p.alpha = 1.0f; p.beta = 1.0f;
-        p.bias.ptr = (B && B->data) ? B->data : nullptr;
-        p.bias.dtype = p.bias.ptr ? (int)B->dtype : DTYPE_FLOAT32;
-        p.bias.mode = p.bias.ptr ? kBiasPerColumn : kBiasNone;
-        p.bias.rows = 1; p.bias.cols = c.M;
-        p.status = device_status_word();
-        p.vec_store = 0;
-        p.cv.Wp = Wp; p.cv.plane = Hp * Wp;
-        p.cv.images = c.N; p.cv.OH = c.OH; p.cv.OW = c.OW; p.cv.OC = c.M;
-        p.cv.KW = c.KW; p.cv.dil_h = c.dh; p.cv.dil_w = c.dw;
-        const uint32_t fa = fp8 ? (dx == DTYPE_FLOAT8_E5M2 ? 1u : 0u) : (dx == DTYPE_BFLOAT16 ? 1u : 0u);
-        const uint32_t fb = fp8 ? (dw == DTYPE_FLOAT8_E5M2 ? 1u : 0u) : (dw == DTYPE_BFLOAT16 ? 1u : 0u);
-        const uint32_t idesc = umma::instr_desc(fa, fb, kBM, kBN);
-        const int tiles = p.tiles_m * p.tiles_n;
-        const int grid = tiles < st->sm_count ? tiles : st->sm_count;
-        if (fp8) {
-            static bool attr = false;
-            if (!attr) { cudaFuncSetAttribute(tc_kernel<true, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kTcSmemBytes); attr = true; }
-            tc_kernel<true, true><<<grid, kTcThreads, kTcSmemBytes, s>>>(map_a, map_b, p, idesc);
-        } else {
-            static bool attr = false;
-            if (!attr) { cudaFuncSetAttribute(tc_kernel<false, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kTcSmemBytes); attr = true; }
-            tc_kernel<false, true><<<grid, kTcThreads, kTcSmemBytes, s>>>(map_a, map_b, p, idesc);
-        }
-        ok = TOPS_CHECK_LAUNCH("conv2d_forward (tensor cores)");
-        if (ok) count_tensor_core_launch();
+    TcParams p;
+    // rows beyond the last valid output position of the last image need no tile
+    const size_t last_row = ((size_t)(c.N - 1) * Hp + (c.OH - 1)) * Wp + c.OW;
+    p.M = (int)rows; p.N = c.M;
+    p.cv.c_blocks = (c.C + k_step - 1) / k_step;
+    p.k_blocks = taps * p.cv.c_blocks;
+    p.k_step = k_step;
+    p.tiles_m = (int)((last_row + kBM - 1) / kBM);
+    p.tiles_n = (c.M + kBN - 1) / kBN;
+    p.Y = Y->data; p.dy = dy;
+    p.alpha = 1.0f; p.beta = 1.0f;
+    p.bias.ptr = (B && B->data) ? B->data : nullptr;
+    p.bias.dtype = p.bias.ptr ? (int)B->dtype : DTYPE_FLOAT32;
+    p.bias.mode = p.bias.ptr ? kBiasPerColumn : kBiasNone;
+    p.bias.rows = 1; p.bias.cols = c.M;
+    p.status = status;
+    p.vec_store = 0;
+    p.cv.Wp = Wp; p.cv.plane = Hp * Wp;
+    p.cv.images = c.N; p.cv.OH = c.OH; p.cv.OW = c.OW; p.cv.OC = c.M;
+    p.cv.KW = c.KW; p.cv.dil_h = c.dh; p.cv.dil_w = c.dw;
+    const uint32_t fa = fp8 ? (dx == DTYPE_FLOAT8_E5M2 ? 1u : 0u) : (dx == DTYPE_BFLOAT16 ? 1u : 0u);
+    const uint32_t fb = fp8 ? (dw == DTYPE_FLOAT8_E5M2 ? 1u : 0u) : (dw == DTYPE_BFLOAT16 ? 1u : 0u);
+    const uint32_t idesc = umma::instr_desc(fa, fb, kBM, kBN);
+    const int tiles = p.tiles_m * p.tiles_n;
+    const int grid = tiles < st->sm_count ? tiles : st->sm_count;
+    if (fp8) {
+        static bool attr = false;
+        if (!attr) { cudaFuncSetAttribute(tc_kernel<true, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kTcSmemBytes); attr = true; }
+        tc_kernel<true, true><<<grid, kTcThreads, kTcSmemBytes, s>>>(map_a, map_b, p, idesc);
+    } else {
+        static bool attr = false;
+        if (!attr) { cudaFuncSetAttribute(tc_kernel<false, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kTcSmemBytes); attr = true; }
+        tc_kernel<false, true><<<grid, kTcThreads, kTcSmemBytes, s>>>(map_a, map_b, p, idesc);
     }
+    if (!TOPS_CHECK_LAUNCH("conv2d_forward (tensor cores)")) return false;
+    count_tensor_core_launch();
+    return true;
+}
+
+bool conv_tensor_core(const Tensor* X, const Tensor* W, const Tensor* B, Tensor* Y, const ConvGeom& c) {
+    if (getenv("TOPS_DISABLE_TC")) return false;
+    if ((size_t)c.N * c.OH * c.OW * c.M < (size_t)1 << 16) return false;     // tiny problems: not worth two copies
+    const ConvTcPlan plan = conv_tc_plan(X, W, Y, c);
+    if (!plan.ok) return false;
+    if (!acquire_device()) return true;
+    cudaStream_t s = current_stream();
+    void *xp = nullptr, *wt = nullptr;
+    if (cudaMallocAsync(&xp, plan.xp_bytes, s) != cudaSuccess) { cudaGetLastError(); return false; }
+    if (cudaMallocAsync(&wt, plan.wt_bytes, s) != cudaSuccess) { cudaGetLastError(); cudaFreeAsync(xp, s); return false; }
+    const bool ok = conv_tc_run(X, W, B, Y, c, plan, xp, wt, device_status_word());
     cudaFreeAsync(xp, s);
     cudaFreeAsync(wt, s);
     return ok;            // false: the exact kernel computes the result instead
