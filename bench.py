@@ -355,6 +355,11 @@ def run_ours(args):
             "slowest_ops_GBps": dict(worst),
         }
         line["cpu_baseline"] = cpu_baseline(budget_s=20.0) if world == 1 else None
+        if world == 1 and not args.no_extra:
+            try:
+                line["other_ops"] = other_ops(lib, stream, peak)
+            except Exception as exc:                      # the headline numbers stand on their own
+                line["other_ops"] = {"error": str(exc)[:200]}
         details = os.path.join(ROOT, "gpurun_out")
         try:
             os.makedirs(details, exist_ok=True)
@@ -368,6 +373,104 @@ def run_ours(args):
     if world > 1:
         import torch.distributed as dist
         dist.destroy_process_group()
+
+
+# ---- the other operators of the hot path (reported beside the headline, device-resident, event-timed) --------
+def other_ops(lib, stream, hbm_peak):
+    """QuantizeLinear / DequantizeLinear at 8192 x 8192, Softmax, MaxPool (GB/s and fraction of the HBM
+    peak) and Gemm 8192^3 / Conv 256x256x56x56 k3 (TFLOP/s) -- the sizes of benchmark configs 3 and 4."""
+    import torch
+    from onnx_translator_b200 import capi
+    from onnx_translator_b200.device import DeviceArray
+    from onnx_translator_b200.capi import CConvParams, CPoolParams
+    rng = np.random.default_rng(0)
+    out = {}
+
+    def timed(call, iters=5):
+        call()
+        lib.tops_sync()
+        ev = [torch.cuda.Event(enable_timing=True) for _ in range(iters + 1)]
+        ev[0].record(stream)
+        for i in range(iters):
+            call()
+            ev[i + 1].record(stream)
+        lib.tops_sync()
+        torch.cuda.synchronize()
+        capi.check(lib)
+        return float(np.median([ev[i].elapsed_time(ev[i + 1]) for i in range(iters)]))
+
+    def mem(label, nbytes, call):
+        ms = timed(call)
+        gbs = nbytes / 1e9 / (ms / 1e3)
+        out[label] = {"GBps": round(gbs, 1), "frac_hbm": round(gbs / hbm_peak, 3), "ms": round(ms, 4)}
+
+    def ints(vals):
+        arr = (ctypes.c_int * len(vals))(*vals)
+        return arr, ctypes.cast(arr, ctypes.POINTER(ctypes.c_int))
+
+    n = 8192 * 8192
+    x = DeviceArray.from_numpy(rng.standard_normal((8192, 8192)).astype(np.float32), "float32")
+    s1 = DeviceArray.from_numpy(np.array([0.02], np.float32), "float32")
+    s16 = DeviceArray.from_numpy(np.array([1 / 16], np.float32), "float32")
+    sax = DeviceArray.from_numpy(rng.uniform(0.01, 0.05, (1, 8192)).astype(np.float32), "float32")
+    z8 = DeviceArray.from_numpy(np.array([0], np.int8), "int8")
+    zu8 = DeviceArray.from_numpy(np.array([128], np.uint8), "uint8")
+    zax = DeviceArray.from_numpy(rng.integers(-8, 9, (1, 8192)).astype(np.int8), "int8")
+    back = DeviceArray.empty((8192, 8192), "float32")
+    for label, dt, sc, zp in (("int8", "int8", s1, z8), ("uint8", "uint8", s1, zu8), ("int8_per_axis", "int8", sax, zax),
+                              ("float8_e4m3", "float8_e4m3", s16, z8), ("float8_e5m2", "float8_e5m2", s16, z8)):
+        q = DeviceArray.empty((8192, 8192), dt)
+        mem(f"quantize_f32_to_{label}", n * 5, lambda: lib.quantize_linear_forward(x.handle, sc.handle, zp.handle, q.handle))
+        mem(f"dequantize_{label}_to_f32", n * 5, lambda: lib.dequantize_linear_forward(q.handle, sc.handle, zp.handle, back.handle))
+        del q
+    del x, back
+
+    sx = DeviceArray.from_numpy(rng.uniform(-10, 10, (65536, 1000)).astype(np.float32), "float32")
+    sy = DeviceArray.empty((65536, 1000), "float32")
+    mem("softmax_f32_65536x1000", sx.size * 8, lambda: lib.softmax_forward(sx.handle, sy.handle, 1))
+    del sx, sy
+    px = DeviceArray.from_numpy(rng.standard_normal((64, 64, 112, 112)).astype(np.float32), "float32")
+    py = DeviceArray.empty((64, 64, 56, 56), "float32")
+    keep = [ints([1, 1, 1, 1]), ints([2, 2]), ints([1, 1]), ints([3, 3])]
+    pool = CPoolParams(keep[0][1], keep[1][1], keep[2][1], keep[3][1])
+    mem("maxpool_f32_64x64x112x112_k3s2p1", (px.size + py.size) * 4, lambda: lib.max_pool_forward(px.handle, py.handle, ctypes.byref(pool)))
+    del px, py
+
+    def bf16(a):
+        u = np.ascontiguousarray(a, dtype=np.float32).view(np.uint32).astype(np.uint64)
+        return ((u + 0x7FFF + ((u >> 16) & 1)) >> 16).astype(np.uint16)
+
+    m = 8192
+    a32 = rng.normal(0, 0.02, (m, m)).astype(np.float32)
+    b32 = rng.normal(0, 0.02, (m, m)).astype(np.float32)
+    bias = DeviceArray.from_numpy(rng.standard_normal((1, m)).astype(np.float32), "float32")
+    flops = 2.0 * m * m * m
+    import ml_dtypes
+    variants = (("bf16_in_f32_out", "bfloat16", bf16, "float32"), ("bf16_in_bf16_out", "bfloat16", bf16, "bfloat16"),
+                ("fp16_in_fp16_out", "float16", lambda v: v.astype(np.float16), "float16"),
+                ("fp8_e4m3_in_bf16_out", "float8_e4m3", lambda v: (v * 16).astype(ml_dtypes.float8_e4m3fn).view(np.uint8), "bfloat16"))
+    for label, dt, conv, odt in variants:
+        a = DeviceArray.from_numpy(conv(a32), dt)
+        b = DeviceArray.from_numpy(conv(b32), dt)
+        y = DeviceArray.empty((m, m), odt)
+        before = lib.tops_tensor_core_launches()
+        ms = timed(lambda: lib.gemm_forward(a.handle, b.handle, bias.handle, y.handle, 1.0, 1.0, 0, 1))
+        out[f"gemm_8192_{label}"] = {"TFLOPs": round(flops / 1e12 / (ms / 1e3), 1), "ms": round(ms, 4),
+                                     "tensor_core_path": lib.tops_tensor_core_launches() > before}
+        del a, b, y
+    del a32, b32
+
+    cx = DeviceArray.from_numpy(bf16(rng.standard_normal((256, 256, 56, 56)).astype(np.float32)), "bfloat16")
+    cw = DeviceArray.from_numpy(bf16(rng.normal(0, 0.02, (256, 256, 3, 3)).astype(np.float32)), "bfloat16")
+    cy = DeviceArray.empty((256, 256, 56, 56), "bfloat16")
+    keep2 = [ints([1, 1, 1, 1]), ints([1, 1]), ints([1, 1])]
+    cprm = CConvParams(keep2[0][1], keep2[1][1], keep2[2][1], 1)
+    before = lib.tops_tensor_core_launches()
+    ms = timed(lambda: lib.conv2d_forward(cx.handle, cw.handle, None, cy.handle, ctypes.byref(cprm)), iters=3)
+    out["conv_256x256x56x56_k3_bf16"] = {"TFLOPs": round(2.0 * 256 * 56 * 56 * 256 * 2304 / 1e12 / (ms / 1e3), 1), "ms": round(ms, 4),
+                                         "tensor_core_path": lib.tops_tensor_core_launches() > before,
+                                         "includes": "NCHW -> padded NHWC copy of X and tap-major copy of W"}
+    return out
 
 
 # ---- the reference's CPU implementation ------------------------------------------------------------------
@@ -447,6 +550,7 @@ def main():
     ap.add_argument("--steps", type=int, default=10)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", choices=("ours", "reference"), default="ours")
+    ap.add_argument("--no-extra", action="store_true", help="skip the QDQ / Softmax / MaxPool / Gemm / Conv side measurements")
     args = ap.parse_args()
     if args.impl == "reference":
         run_reference(args)

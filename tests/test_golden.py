@@ -1,0 +1,68 @@
+"""Golden vectors generated from the reference's own compiled C library (tests/golden/make_golden.py):
+the CPU oracle must reproduce every one of them bit for bit (this is the oracle's pin on machines
+without the reference), and so must the CUDA library.  Softmax alone is compared to 1e-6 relative on
+the GPU (its parallel sum adds in a different order)."""
+import json
+import os
+
+import numpy as np
+import pytest
+
+from datagen import assert_same_codes, to_f64
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+with open(os.path.join(HERE, "golden", "hot_path.json")) as _f:
+    MANIFEST = json.load(_f)
+ARRAYS = np.load(os.path.join(HERE, "golden", "hot_path.npz"))
+CASES = MANIFEST["cases"]
+
+
+def _run(backend, case):
+    ins = [None if k is None else ARRAYS[k] for k in case["inputs"]]
+    p = case["params"]
+    op = case["op"]
+    if op in ("relu", "abs", "cos"):
+        return backend.unary(op, ins[0], p["x_dt"], p["out_dt"])
+    if op in ("add", "sub", "mul", "div"):
+        return backend.binary(op, ins[0], p["a_dt"], ins[1], p["b_dt"], p["out_dt"])
+    if op == "quantize":
+        return backend.quantize(ins[0], p["x_dt"], ins[1], p["s_dt"], ins[2], p["z_dt"], p["out_dt"], axis=p["axis"])
+    if op == "dequantize":
+        return backend.dequantize(ins[0], p["x_dt"], ins[1], p["s_dt"], ins[2], p["z_dt"], p["out_dt"])
+    if op == "conv2d":
+        return backend.conv2d(ins[0], p["x_dt"], ins[1], p["w_dt"], ins[2], p["b_dt"], p["out_dt"], tuple(p["pads"]),
+                              tuple(p["strides"]), tuple(p["dilations"]), p["group"])
+    if op == "max_pool":
+        return backend.max_pool(ins[0], p["x_dt"], p["out_dt"], tuple(p["kernel"]), tuple(p["pads"]), tuple(p["strides"]),
+                                tuple(p["dilations"]))
+    if op == "gemm":
+        return backend.gemm(ins[0], p["a_dt"], ins[1], p["b_dt"], ins[2], p["c_dt"], p["out_dt"], p["alpha"], p["beta"],
+                            p["transA"], p["transB"])
+    if op == "softmax":
+        return backend.softmax(ins[0], p["x_dt"], p["out_dt"], p["axis"])
+    raise AssertionError(op)
+
+
+def _ids(case):
+    return f"{case['id']}-{case['op']}"
+
+
+@pytest.mark.parametrize("case", CASES, ids=_ids)
+def test_oracle_reproduces_golden_vectors(port, case):
+    want = ARRAYS[f"c{case['id']}_out"]
+    assert_same_codes(_run(port, case), want, case["params"]["out_dt"], _ids(case))
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("case", CASES, ids=_ids)
+def test_cuda_library_reproduces_golden_vectors(case):
+    import gpu_ops
+    want = ARRAYS[f"c{case['id']}_out"]
+    got = _run(gpu_ops, case)
+    out_dt = case["params"]["out_dt"]
+    if case["op"] == "softmax":
+        g, w = to_f64(got, out_dt), to_f64(want, out_dt)
+        ulp = {"float32": 2.0 ** -23, "float16": 2.0 ** -10}[out_dt]
+        assert np.all(np.abs(g - w) <= (1e-6 + ulp) * np.abs(w) + 1e-45)
+    else:
+        assert_same_codes(got, want, out_dt, _ids(case))
