@@ -189,6 +189,23 @@ void tops_quantize_linear_axis_forward(const Tensor* X, const Tensor* Scale, con
 void tops_dequantize_linear_axis_forward(const Tensor* X, const Tensor* Scale, const Tensor* ZeroPoint,
                                          Tensor* Y, int axis);
 
+/* Convolution for callers that must not let this library allocate GPU memory (no counterpart in
+   the reference, whose library only ever uses the host heap).  conv2d_forward takes two scratch
+   tensors from the CUDA memory pool on each call; a process that has given the whole device to its
+   own allocator, runs under a fixed memory budget, or is in a phase where an allocation may block or
+   fail cannot accept that.  This variant computes the same result with scratch in a fixed 36 MiB
+   array inside the library image (reserved on every GPU that loads the library, until exit).
+   Limits: the padded channels-last copy of X (N*Hp*Wp*C elements) must fit 32 MiB and the filter copy
+   (KH*KW*M*C elements) 4 MiB; only what the tensor-core path covers is accepted (group 1, stride 1,
+   fp16 / bf16 / fp8 inputs of one kind, fp32 / bf16 / fp16 output, C a multiple of 16 bytes).
+   Anything else: output zero-filled, TOPS_ERR_UNSUPPORTED with the sizes in the message.
+   The first call on a device resolves the array's device address (and creates the library stream
+   if nothing ran there yet): make it before any stream capture.  All calls share the array, which
+   keeps the previous call's contents (each call overwrites all it reads); calls that overlap on the
+   GPU race, so keep them ordered on one stream.  tops_conv2d_noalloc_limits reports the limits. */
+void   tops_conv2d_forward_noalloc(const Tensor* X, const Tensor* W, const Tensor* B, Tensor* Y, ConvParams* params);
+size_t tops_conv2d_noalloc_limits(size_t* input_bytes, size_t* filter_bytes);
+
 /* Device-side exhaustive codec self-check: encodes every float32 bit pattern with the fast
    (hardware-convert) encoder and with the bit-level restatement of the reference encoder and
    returns the number of disagreements (NaN inputs excluded), or -1 on error. */

@@ -38,6 +38,7 @@ bool         check_cuda(cudaError_t e, const char* what);
 void         zero_fill(Tensor* t);        // best effort, used on rejected calls
 const double* cos_lut_device();           // uploads on first use
 int*         device_status_word();        // device pointer to the host-visible status word (may be null)
+int*         device_status_word_if_created();   // as above, but never allocates (null until first created)
 void         poll_device_status();        // host: turn a raised status word into an error
 
 #define TOPS_CUDA_OK(expr) ::tops::check_cuda((expr), #expr)

@@ -509,6 +509,14 @@ int* device_status_word() {
     return dev;
 }
 
+// The same pointer, but only if an earlier call already created the word: never allocates.
+int* device_status_word_if_created() {
+    if (!g_status_host) return nullptr;
+    int* dev = nullptr;
+    if (cudaHostGetDevicePointer((void**)&dev, g_status_host, 0) != cudaSuccess) { cudaGetLastError(); return nullptr; }
+    return dev;
+}
+
 void poll_device_status() {
     if (g_status_host && *(volatile int*)g_status_host) {
         *(volatile int*)g_status_host = 0;
