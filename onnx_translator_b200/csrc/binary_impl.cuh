@@ -66,7 +66,7 @@ binary_elem(typename Storage<DA>::type sa, typename Storage<DB>::type sb) {
 
 template <int DA, int DB, int DO, int OP, bool ALIGNED>
 struct BinaryBody {
-    static constexpr int kV = vec_width(dtype_bytes(DA), dtype_bytes(DB), dtype_bytes(DO));
+    static constexpr int kV = vec_width(dtype_bytes(DA), dtype_bytes(DB), dtype_bytes(DO), OP == kDiv ? kRunCapDivide : kRunCapDefault);
     Geo3 g;
     Op3 a, b;
     void* out;
@@ -131,7 +131,7 @@ static bool binary_typed(const char* name, const Geometry& geom, Operand* ops, T
     const int bytes[2] = {dtype_bytes(DA), dtype_bytes(DB)};
     return for_each_slab(name, geom, ops, bytes, 2, o->data, dtype_bytes(DO), o->size, [&](const Slab& s) {
         if (!s.fits3) return binary_generic_slab<OP>(name, s, DA, DB, DO);
-        constexpr int V = vec_width(dtype_bytes(DA), dtype_bytes(DB), dtype_bytes(DO));
+        constexpr int V = BinaryBody<DA, DB, DO, OP, true>::kV;
         if (slab_aligned(s, 2, bytes, dtype_bytes(DO), V)) {
             BinaryBody<DA, DB, DO, OP, true> body{s.geo3, s.ops3[0], s.ops3[1], s.out};
             return launch_body(name, body, s.n);

@@ -26,24 +26,44 @@ namespace tops {
 template <typename E>
 __global__ void __launch_bounds__(256) nchw_to_padded_nhwc(const E* __restrict__ x, E* __restrict__ xp,
                                                             int C, int H, int W, int Hp, int Wp, int pt, int pl) {
-    __shared__ E tile[64][64 + 2];
+    constexpr int kVec = 16 / (int)sizeof(E);               // channels per 16-byte store
+    constexpr int kPitch = 64 + kVec;                       // tile row pitch in elements (keeps rows 16-byte aligned)
+    __shared__ __align__(16) E tile[64][kPitch];            // [column][channel]
     const int wp0 = blockIdx.x * 64, hp = blockIdx.y % Hp, n = blockIdx.y / Hp, c0 = blockIdx.z * 64;
     const int h = hp - pt;
     const bool row_inside = h >= 0 && h < H;
-    // read: 64 channels x 64 columns, consecutive threads along the row (contiguous in NCHW)
-    for (int e = threadIdx.x; e < 64 * 64; e += 256) {
-        const int cc = e >> 6, ww = e & 63;
-        const int c = c0 + cc, w = wp0 + ww - pl;
-        E v = E(0);
-        if (row_inside && c < C && w >= 0 && w < W) v = x[(((size_t)n * C + c) * H + h) * W + w];
-        tile[cc][ww] = v;
+    // read: each thread owns one column and walks 16 channels; a warp reads 32 consecutive
+    // columns of one channel plane (contiguous in NCHW); the 16 loads are independent
+    {
+        const int ww = threadIdx.x & 63, cc0 = threadIdx.x >> 6;
+        const int w = wp0 + ww - pl;
+        const bool col_inside = row_inside && w >= 0 && w < W;
+        const size_t plane = (size_t)H * W;
+        const E* src = x + ((size_t)n * C + (size_t)(c0 + cc0)) * plane + (size_t)(row_inside ? h : 0) * W + (col_inside ? w : 0);
+        E v[16];
+        #pragma unroll
+        for (int i = 0; i < 16; i++) {
+            const int cc = cc0 + 4 * i;
+            v[i] = (col_inside && c0 + cc < C) ? src[(size_t)(4 * i) * plane] : E(0);
+        }
+        #pragma unroll
+        for (int i = 0; i < 16; i++) tile[ww][cc0 + 4 * i] = v[i];
     }
     __syncthreads();
-    // write: consecutive threads along the channels (contiguous in NHWC)
-    for (int e = threadIdx.x; e < 64 * 64; e += 256) {
-        const int ww = e >> 6, cc = e & 63;
-        const int c = c0 + cc, wp = wp0 + ww;
-        if (c < C && wp < Wp) xp[(((size_t)n * Hp + hp) * Wp + wp) * C + c] = tile[cc][ww];
+    // write: 16 bytes (kVec channels) per thread, consecutive threads along the channels of one
+    // padded position (contiguous in NHWC)
+    constexpr int kLanesPerPos = 64 / kVec, kPosPerPass = 256 / kLanesPerPos;
+    const int part = threadIdx.x % kLanesPerPos, pos0 = threadIdx.x / kLanesPerPos;
+    const int c = c0 + part * kVec;
+    if (c < C) {
+        #pragma unroll
+        for (int pass = 0; pass < 64 / kPosPerPass; pass++) {
+            const int ww = pos0 + pass * kPosPerPass, wp = wp0 + ww;
+            if (wp < Wp) {
+                const uint4 val = *reinterpret_cast<const uint4*>(&tile[ww][part * kVec]);
+                *reinterpret_cast<uint4*>(xp + (((size_t)n * Hp + hp) * Wp + wp) * C + c) = val;
+            }
+        }
     }
 }
 
@@ -143,12 +163,12 @@ bool conv_tc_run(const Tensor* X, const Tensor* W, const Tensor* B, Tensor* Y, c
     const int grid = tiles < st->sm_count ? tiles : st->sm_count;
     if (fp8) {
         static bool attr = false;
-        if (!attr) { cudaFuncSetAttribute(tc_kernel<true, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kTcSmemBytes); attr = true; }
-        tc_kernel<true, true><<<grid, kTcThreads, kTcSmemBytes, s>>>(map_a, map_b, p, idesc);
+        if (!attr) { cudaFuncSetAttribute(tc_kernel<true, kModeConv>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kTcSmemBytes); attr = true; }
+        tc_kernel<true, kModeConv><<<grid, kTcThreads, kTcSmemBytes, s>>>(map_a, map_b, p, idesc);
     } else {
         static bool attr = false;
-        if (!attr) { cudaFuncSetAttribute(tc_kernel<false, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kTcSmemBytes); attr = true; }
-        tc_kernel<false, true><<<grid, kTcThreads, kTcSmemBytes, s>>>(map_a, map_b, p, idesc);
+        if (!attr) { cudaFuncSetAttribute(tc_kernel<false, kModeConv>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kTcSmemBytes); attr = true; }
+        tc_kernel<false, kModeConv><<<grid, kTcThreads, kTcSmemBytes, s>>>(map_a, map_b, p, idesc);
     }
     if (!TOPS_CHECK_LAUNCH("conv2d_forward (tensor cores)")) return false;
     count_tensor_core_launch();

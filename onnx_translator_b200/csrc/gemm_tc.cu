@@ -59,11 +59,92 @@ bool make_tensor_map(CUtensorMap* out, const void* base, int elem_bytes, bool is
 // ---- host --------------------------------------------------------------------------------------------------------
 static bool is_fp8(int dt) { return dt == DTYPE_FLOAT8_E4M3 || dt == DTYPE_FLOAT8_E5M2; }
 
+
+// ---- float32 operands on the bfloat16 tensor cores -----------------------------------------------------------
+// A float32 value is the exact sum of three bfloat16 values (8 + 8 + 8 significand bits):
+// a = a1 + a2 + a3 with a1 = bf16(a), a2 = bf16(a - a1), a3 = bf16(a - a1 - a2).  The product a*b is
+// then sum_ij a_i b_j; the three smallest of the nine terms (a2 b3, a3 b2, a3 b3) are below 2^-23 |a b|
+// and are dropped, the other six are accumulated in float32 by one run of the tensor-core kernel whose
+// K loop walks the plane pairs (smallest products first).  Error against the double-accumulating
+// reference: about 3e-7 * sum_k |a_k b_k|, inside the 1e-6 gate used for every tensor-core result.
+// Inf / NaN operands give NaN (Inf - Inf appears in the split).
+__global__ void __launch_bounds__(256) split_f32_to_bf16x3(const float* __restrict__ src, uint16_t* __restrict__ planes,
+                                                            size_t n, size_t plane_stride) {
+    for (size_t i = ((size_t)blockIdx.x * blockDim.x + threadIdx.x) * 4; i < n; i += (size_t)gridDim.x * blockDim.x * 4) {
+        const float4 v = *reinterpret_cast<const float4*>(src + i);          // n is a multiple of 8, src 16-byte aligned
+        const float a[4] = {v.x, v.y, v.z, v.w};
+        uint16_t p1[4], p2[4], p3[4];
+        #pragma unroll
+        for (int j = 0; j < 4; j++) {
+            p1[j] = encode_bf16(a[j]);
+            const float r1 = __fsub_rn(a[j], decode_bf16(p1[j]));
+            p2[j] = encode_bf16(r1);
+            const float r2 = __fsub_rn(r1, decode_bf16(p2[j]));
+            p3[j] = encode_bf16(r2);
+        }
+        *reinterpret_cast<uint2*>(planes + i) = make_uint2(p1[0] | ((uint32_t)p1[1] << 16), p1[2] | ((uint32_t)p1[3] << 16));
+        *reinterpret_cast<uint2*>(planes + plane_stride + i) = make_uint2(p2[0] | ((uint32_t)p2[1] << 16), p2[2] | ((uint32_t)p2[3] << 16));
+        *reinterpret_cast<uint2*>(planes + 2 * plane_stride + i) = make_uint2(p3[0] | ((uint32_t)p3[1] << 16), p3[2] | ((uint32_t)p3[3] << 16));
+    }
+}
+
+static bool gemm_split_f32(const Tensor* A, const Tensor* B, Tensor* Y, const GemmShape& g, const BiasView& bias,
+                           float alpha, float beta) {
+    DeviceState* st = acquire_device();
+    if (!st) return true;
+    cudaStream_t s = current_stream();
+    const size_t a_elems = (size_t)g.M * g.K, b_elems = (size_t)g.N * g.K;
+    uint16_t *ap = nullptr, *bp = nullptr;
+    if (cudaMallocAsync((void**)&ap, a_elems * 6, s) != cudaSuccess) { cudaGetLastError(); return false; }
+    if (cudaMallocAsync((void**)&bp, b_elems * 6, s) != cudaSuccess) { cudaGetLastError(); cudaFreeAsync(ap, s); return false; }
+    split_f32_to_bf16x3<<<grid_for(a_elems / 4, 256, st->sm_count, 8), 256, 0, s>>>((const float*)A->data, ap, a_elems, a_elems);
+    split_f32_to_bf16x3<<<grid_for(b_elems / 4, 256, st->sm_count, 8), 256, 0, s>>>((const float*)B->data, bp, b_elems, b_elems);
+    bool ok = TOPS_CHECK_LAUNCH("gemm_forward (float32 split)");
+
+    const int k_step = kRowBytes / 2;
+    CUtensorMap map_a, map_b;
+    const uint64_t dims_a[3] = {(uint64_t)g.K, (uint64_t)g.M, 3}, dims_b[3] = {(uint64_t)g.K, (uint64_t)g.N, 3};
+    const uint64_t strides_a[2] = {(uint64_t)g.K * 2, a_elems * 2}, strides_b[2] = {(uint64_t)g.K * 2, b_elems * 2};
+    const uint32_t box_a[3] = {(uint32_t)k_step, (uint32_t)kBM, 1}, box_b[3] = {(uint32_t)k_step, (uint32_t)kBN, 1};
+    ok = ok && make_tensor_map(&map_a, ap, 2, false, false, 3, dims_a, strides_a, box_a, nullptr) &&
+         make_tensor_map(&map_b, bp, 2, false, false, 3, dims_b, strides_b, box_b, nullptr);
+    if (ok) {
+        TcParams p;
+        p.M = g.M; p.N = g.N;
+        p.cv.c_blocks = (g.K + k_step - 1) / k_step;
+        p.k_blocks = 6 * p.cv.c_blocks;
+        p.k_step = k_step;
+        p.tiles_m = (g.M + kBM - 1) / kBM;
+        p.tiles_n = (g.N + kBN - 1) / kBN;
+        p.Y = Y->data; p.dy = (int)Y->dtype;
+        p.alpha = alpha; p.beta = beta;
+        p.bias = bias;
+        p.status = device_status_word();
+        p.vec_store = (((uintptr_t)Y->data & 15) == 0) && (((size_t)g.N * dtype_bytes((int)Y->dtype)) % 16 == 0);
+        const uint32_t idesc = umma::instr_desc(1u, 1u, kBM, kBN);
+        const int tiles = p.tiles_m * p.tiles_n;
+        const int grid = tiles < st->sm_count ? tiles : st->sm_count;
+        static bool attr = false;
+        if (!attr) { cudaFuncSetAttribute(tc_kernel<false, kModeSplit>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kTcSmemBytes); attr = true; }
+        tc_kernel<false, kModeSplit><<<grid, kTcThreads, kTcSmemBytes, s>>>(map_a, map_b, p, idesc);
+        ok = TOPS_CHECK_LAUNCH("gemm_forward (tensor cores, float32 split)");
+        if (ok) count_tensor_core_launch();
+    }
+    cudaFreeAsync(ap, s);
+    cudaFreeAsync(bp, s);
+    return ok;
+}
+
 bool gemm_tensor_core(const Tensor* A, const Tensor* B, Tensor* Y, const GemmShape& g, const BiasView& bias,
                       float alpha, float beta) {
     const int da = (int)A->dtype, db = (int)B->dtype, dy = (int)Y->dtype;
     const bool fp8 = is_fp8(da) && is_fp8(db);
     const bool half16 = (da == db) && (da == DTYPE_FLOAT16 || da == DTYPE_BFLOAT16);
+    // large float32 problems: three-way bfloat16 split (small ones keep the exact, bit-identical kernel)
+    if (da == DTYPE_FLOAT32 && db == DTYPE_FLOAT32 && (dy == DTYPE_FLOAT32 || dy == DTYPE_BFLOAT16 || dy == DTYPE_FLOAT16) &&
+        g.transA == 0 && g.transB == 1 && g.K % 8 == 0 && g.lda == g.K && g.ldb == g.K && !getenv("TOPS_DISABLE_TC") &&
+        (((uintptr_t)A->data | (uintptr_t)B->data) & 15) == 0 && (double)g.M * g.N * g.K >= 134217728.0)
+        return gemm_split_f32(A, B, Y, g, bias, alpha, beta);
     if (!fp8 && !half16) return false;
     if (dy != DTYPE_FLOAT32 && dy != DTYPE_BFLOAT16 && dy != DTYPE_FLOAT16) return false;
     if (g.transA != 0 || g.transB != 1) return false;                 // both operands K-major
@@ -105,12 +186,12 @@ bool gemm_tensor_core(const Tensor* A, const Tensor* B, Tensor* Y, const GemmSha
     cudaStream_t s = current_stream();
     if (fp8) {
         static bool attr = false;
-        if (!attr) { cudaFuncSetAttribute(tc_kernel<true, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kTcSmemBytes); attr = true; }
-        tc_kernel<true, false><<<grid, kTcThreads, kTcSmemBytes, s>>>(map_a, map_b, p, idesc);
+        if (!attr) { cudaFuncSetAttribute(tc_kernel<true, kModeGemm>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kTcSmemBytes); attr = true; }
+        tc_kernel<true, kModeGemm><<<grid, kTcThreads, kTcSmemBytes, s>>>(map_a, map_b, p, idesc);
     } else {
         static bool attr = false;
-        if (!attr) { cudaFuncSetAttribute(tc_kernel<false, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kTcSmemBytes); attr = true; }
-        tc_kernel<false, false><<<grid, kTcThreads, kTcSmemBytes, s>>>(map_a, map_b, p, idesc);
+        if (!attr) { cudaFuncSetAttribute(tc_kernel<false, kModeGemm>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kTcSmemBytes); attr = true; }
+        tc_kernel<false, kModeGemm><<<grid, kTcThreads, kTcSmemBytes, s>>>(map_a, map_b, p, idesc);
     }
     TOPS_CHECK_LAUNCH("gemm_forward (tensor cores)");
     count_tensor_core_launch();

@@ -14,26 +14,33 @@ namespace tops {
 // Fast path (x, s exact in float32; z a small integer): rint of the DOUBLE quotient equals rintf of
 // the correctly rounded FLOAT quotient unless a half-integer lies within one float ulp of it; only
 // those rare elements (and |q| >= 2^22) take the double division.
-template <int DO>
-__device__ __forceinline__ typename Storage<DO>::type quantize_fast(float x, float s, float z) {
-    if (s == 0.0f) return from_f32<DO>(z);
-    const float q = __fdiv_rn(x, s);
-    const float r = rintf(q);
+//
+// The quotient itself is never needed, only its rounding, so the fast path does not divide at all:
+// q ~ x * (1/s) with an approximate reciprocal is within 2^-21 |q| of x / s; adding and subtracting
+// 1.5 * 2^23 rounds it to the nearest integer r (ties to even) and leaves r in the low mantissa
+// bits.  r equals rint(x / s) -- for the exact quotient and for its double rounding alike --
+// whenever q is further than 2^-19 |q| from a tie; the rest (about 1e-5 of the elements for
+// |q| ~ 50, plus s == 0, non-finite x and |q| >= 2^21) take the double division.
+// Returns rint(x / s) + z as an integer; `ok` tells whether the fast path was conclusive.
+__device__ __forceinline__ int quantize_round_fast(float x, float inv_s, int z, bool& ok) {
+    const float q = __fmul_rn(x, inv_s);
+    const float t = __fadd_rn(q, 12582912.0f);
+    const float r = __fsub_rn(t, 12582912.0f);
     const float aq = fabsf(q);
-    const float gap = 0.5f - fabsf(__fsub_rn(q, r));          // distance of q to the nearest tie
-    if (!(aq < 4194304.0f) || gap <= aq * 4.76837158e-7f) {   // 2^-21: two ulps of margin
-        const double rd = __dadd_rn(rint(__ddiv_rn((double)x, (double)s)), (double)z);
-        return from_f64<DO>(rd);
-    }
-    const float res = __fadd_rn(r, z);                          // exact: both are small integers
-    if constexpr (DO == DTYPE_INT8)       return (int8_t)min(max(__float2int_rn(res), -128), 127);
-    else if constexpr (DO == DTYPE_UINT8) return (uint8_t)min(max(__float2int_rn(res), 0), 255);
-    else return from_f32<DO>(res);
+    ok = (aq < 2097152.0f) && (__fsub_rn(0.5f, fabsf(__fsub_rn(q, r))) > aq * 1.9073486e-6f);
+    return (__float_as_int(t) - 0x4B400000) + z;
+}
+// The reference's arithmetic, element by element.
+template <int DO>
+__device__ __forceinline__ typename Storage<DO>::type quantize_exact(double x, double s, double z) {
+    double r = z;
+    if (s != 0.0) r = __dadd_rn(rint(__ddiv_rn(x, s)), z);
+    return from_f64<DO>(r);
 }
 
 template <int DX, int DS, int DZ, int DO, bool ALIGNED>
 struct QuantizeBody {
-    static constexpr int kV = vec_width(dtype_bytes(DX), dtype_bytes(DO), 1);
+    static constexpr int kV = vec_width(dtype_bytes(DX), dtype_bytes(DO), dtype_bytes(DO), kRunCapQuantize);
     Geo3 g;
     Op3 x, s, z;
     void* out;
@@ -46,16 +53,38 @@ struct QuantizeBody {
         fetch3<DX, kV, ALIGNED>(g, x, i0, nv, c, rx);
         fetch3<DS, kV, ALIGNED>(g, s, i0, nv, c, rs);
         fetch3<DZ, kV, ALIGNED>(g, z, i0, nv, c, rz);
-        #pragma unroll
-        for (int j = 0; j < kV; j++) {
-            if constexpr (dtype_exact_in_f32(DX) && dtype_exact_in_f32(DS) && dtype_is_narrow_int(DZ)) {
-                ro.v[j] = quantize_fast<DO>(to_f32<DX>(rx.v[j]), to_f32<DS>(rs.v[j]), to_f32<DZ>(rz.v[j]));
-            } else {
-                const double sv = to_f64<DS>(rs.v[j]), zv = to_f64<DZ>(rz.v[j]);
-                double r = zv;
-                if (sv != 0.0) r = __dadd_rn(rint(__ddiv_rn(to_f64<DX>(rx.v[j]), sv)), zv);
-                ro.v[j] = from_f64<DO>(r);
+        if constexpr (dtype_exact_in_f32(DX) && dtype_exact_in_f32(DS) && dtype_is_narrow_int(DZ)) {
+            float fx[kV];
+            decode_floats<DX, kV>(rx, fx);
+            int v[kV];
+            bool all_ok = true;
+            const bool uniform_scale = ALIGNED && !g.simple && s.st2 == 0;    // one scale for the whole run
+            float inv = uniform_scale ? __fdividef(1.0f, to_f32<DS>(rs.v[0])) : 0.0f;
+            #pragma unroll
+            for (int j = 0; j < kV; j++) {
+                if (!uniform_scale) inv = __fdividef(1.0f, to_f32<DS>(rs.v[j]));
+                bool ok;
+                v[j] = quantize_round_fast(fx[j], inv, to_i32_narrow<DZ>(rz.v[j]), ok);
+                all_ok = all_ok && ok;
             }
+            if (all_ok) {
+                if constexpr (DO == DTYPE_INT8 || DO == DTYPE_UINT8) {
+                    encode_ints<DO, kV>(v, ro);
+                } else {
+                    float fr[kV];
+                    #pragma unroll
+                    for (int j = 0; j < kV; j++) fr[j] = (float)v[j];       // |v| < 2^22: exact
+                    encode_floats<DO, kV>(fr, ro);
+                }
+            } else {
+                #pragma unroll
+                for (int j = 0; j < kV; j++)
+                    ro.v[j] = quantize_exact<DO>((double)fx[j], to_f64<DS>(rs.v[j]), to_f64<DZ>(rz.v[j]));
+            }
+        } else {
+            #pragma unroll
+            for (int j = 0; j < kV; j++)
+                ro.v[j] = quantize_exact<DO>(to_f64<DX>(rx.v[j]), to_f64<DS>(rs.v[j]), to_f64<DZ>(rz.v[j]));
         }
         put3<DO, kV, ALIGNED>(out, i0, nv, ro);
     }
@@ -68,7 +97,7 @@ struct QuantizeBody {
 // correctly rounded float multiply reproduces "exact product, one rounding".
 template <int DX, int DS, int DZ, int DO, bool ALIGNED>
 struct DequantizeBody {
-    static constexpr int kV = vec_width(dtype_bytes(DX), dtype_bytes(DO), 1);
+    static constexpr int kV = vec_width(dtype_bytes(DX), dtype_bytes(DO), dtype_bytes(DO), kRunCapDequantize);
     static constexpr bool kDiffExact = dtype_exact_in_f32(DX) && dtype_exact_in_f32(DZ) && dtype_exact_in_f32(DS) &&
         DX != DTYPE_FLOAT8_E5M2 && DZ != DTYPE_FLOAT8_E5M2 && DX != DTYPE_FLOAT16 && DZ != DTYPE_FLOAT16 &&
         DX != DTYPE_BFLOAT16 && DZ != DTYPE_BFLOAT16 && DX != DTYPE_FLOAT32 && DZ != DTYPE_FLOAT32 &&
@@ -85,11 +114,20 @@ struct DequantizeBody {
         fetch3<DX, kV, ALIGNED>(g, x, i0, nv, c, rx);
         fetch3<DS, kV, ALIGNED>(g, s, i0, nv, c, rs);
         fetch3<DZ, kV, ALIGNED>(g, z, i0, nv, c, rz);
+        if constexpr (kDiffExact) {
+            float fx[kV], fz[kV], f[kV];
+            decode_floats<DX, kV>(rx, fx);
+            decode_floats<DZ, kV>(rz, fz);
+            #pragma unroll
+            for (int j = 0; j < kV; j++) f[j] = __fmul_rn(__fsub_rn(fx[j], fz[j]), to_f32<DS>(rs.v[j]));
+            encode_floats<DO, kV>(f, ro);
+            put3<DO, kV, ALIGNED>(out, i0, nv, ro);
+            return;
+        }
         #pragma unroll
         for (int j = 0; j < kV; j++) {
             if constexpr (kDiffExact) {
-                const float d = __fsub_rn(to_f32<DX>(rx.v[j]), to_f32<DZ>(rz.v[j]));
-                ro.v[j] = from_f32<DO>(__fmul_rn(d, to_f32<DS>(rs.v[j])));
+                ro.v[j] = typename Storage<DO>::type(0);        // handled above
             } else if constexpr (dtype_exact_in_f32(DX) && dtype_exact_in_f32(DS) && dtype_exact_in_f32(DZ) &&
                                  DO != DTYPE_FLOAT64 && !dtype_is_int(DO)) {
                 const float zv = to_f32<DZ>(rz.v[j]);
@@ -139,7 +177,7 @@ static bool qdq_typed(const char* name, const Geometry& geom, Operand* ops, Tens
     const int bytes[3] = {dtype_bytes(DX), dtype_bytes(DS), dtype_bytes(DZ)};
     return for_each_slab(name, geom, ops, bytes, 3, y->data, dtype_bytes(DO), y->size, [&](const Slab& s) {
         if (!s.fits3) return qdq_generic_slab<QUANTIZE>(name, s, DX, DS, DZ, DO);
-        constexpr int V = vec_width(dtype_bytes(DX), dtype_bytes(DO), 1);
+        constexpr int V = Body<DX, DS, DZ, DO, true>::kV;
         if (slab_aligned(s, 3, bytes, dtype_bytes(DO), V)) {
             Body<DX, DS, DZ, DO, true> b{s.geo3, s.ops3[0], s.ops3[1], s.ops3[2], s.out};
             return launch_body(name, b, s.n);

@@ -52,7 +52,11 @@ __device__ __forceinline__ void tile_coords(int tile, int tiles_m, int tiles_n, 
     tn = r / rows;
 }
 
-template <bool FP8, bool CONV>
+// MODE 0: Gemm.  MODE 1: Conv2d as shifted GEMMs (ConvView).  MODE 2: Gemm on float32 operands that
+// were split into three bfloat16 planes each (see gemm_tc.cu); the K loop walks six plane pairs.
+constexpr int kModeGemm = 0, kModeConv = 1, kModeSplit = 2;
+
+template <bool FP8, int MODE>
 __global__ void __launch_bounds__(kTcThreads, 1)
 tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, const TcParams p,
                const uint32_t idesc) {
@@ -96,7 +100,13 @@ tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUt
                     if (!umma::mbar_wait(&empty[s], ph ^ 1u, abort_flag)) break;
                     uint8_t* a_tile = tiles + (size_t)s * kStageBytes;
                     umma::mbar_expect_tx(&full[s], kStageBytes);
-                    if constexpr (CONV) {
+                    if constexpr (MODE == kModeSplit) {
+                        // smallest products first: (a3 b1) (a2 b2) (a1 b3) (a2 b1) (a1 b2) (a1 b1)
+                        const int seg = kb / p.cv.c_blocks, cb = kb - seg * p.cv.c_blocks;
+                        const int plane_a = (0x001012 >> (4 * seg)) & 0xF, plane_b = (0x010210 >> (4 * seg)) & 0xF;
+                        umma::tma_load_3d(a_tile, &map_a, &full[s], cb * p.k_step, tm * kBM, plane_a);
+                        umma::tma_load_3d(a_tile + kTileABytes, &map_b, &full[s], cb * p.k_step, tn * kBN, plane_b);
+                    } else if constexpr (MODE == kModeConv) {
                         const int tap = kb / p.cv.c_blocks, cb = kb - tap * p.cv.c_blocks;
                         const int kh = tap / p.cv.KW, kw = tap - kh * p.cv.KW;
                         const int shift = kh * p.cv.dil_h * p.cv.Wp + kw * p.cv.dil_w;
@@ -197,7 +207,7 @@ tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUt
                         #pragma unroll
                         for (int j = 0; j < 32; j++) v[j] = __fmaf_rn(p.beta, cv[j], v[j]);
                     }
-                    if constexpr (CONV) {
+                    if constexpr (MODE == kModeConv) {
                         // NCHW output: for one output channel, consecutive lanes (consecutive padded
                         // positions) are consecutive pixels, so each store instruction is contiguous.
                         const int img = m / p.cv.plane, rem = m - img * p.cv.plane;

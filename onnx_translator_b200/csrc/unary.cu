@@ -56,7 +56,7 @@ __device__ __forceinline__ typename Storage<DO>::type unary_elem(typename Storag
 
 template <int DX, int DO, int OP, bool ALIGNED>
 struct UnaryBody {
-    static constexpr int kV = vec_width(dtype_bytes(DX), dtype_bytes(DO), 1);
+    static constexpr int kV = vec_width(dtype_bytes(DX), dtype_bytes(DO), dtype_bytes(DO));
     Geo3 g;
     Op3 x;
     void* out;
@@ -125,7 +125,7 @@ static bool run_typed(const char* name, const Tensor* x, Tensor* y, const double
     if (!plan_unary(x, y, &geom, &op)) return false;
     const int bytes[1] = {dtype_bytes(DX)};
     return for_each_slab(name, geom, &op, bytes, 1, y->data, dtype_bytes(DO), y->size, [&](const Slab& s) {
-        constexpr int V = vec_width(dtype_bytes(DX), dtype_bytes(DO), 1);
+        constexpr int V = vec_width(dtype_bytes(DX), dtype_bytes(DO), dtype_bytes(DO));
         if (slab_aligned(s, 1, bytes, dtype_bytes(DO), V)) {
             UnaryBody<DX, DO, OP, true> b{s.geo3, s.ops3[0], s.out, lut};
             return launch_body(name, b, s.n);

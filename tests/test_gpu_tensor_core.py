@@ -46,6 +46,9 @@ GEMM_CASES = [  # M, N, K, a_dt, b_dt, out_dt, bias
     (200, 260, 144, "float8_e5m2", "float8_e4m3", "bfloat16", "matrix"),
     (2048, 2048, 2048, "bfloat16", "bfloat16", "float32", "col"),
     (1024, 4096, 8192, "bfloat16", "bfloat16", "bfloat16", "col"),     # K of the 8192^3 benchmark case
+    (512, 768, 1024, "float32", "float32", "float32", "col"),           # float32 inputs: three-way bfloat16 split
+    (1024, 1024, 256, "float32", "float32", "float32", None),
+    (640, 520, 2048, "float32", "float32", "bfloat16", "row"),
 ]
 
 
