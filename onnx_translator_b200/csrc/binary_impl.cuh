@@ -29,11 +29,22 @@ template <int OP> __device__ __forceinline__ long long int_op64(long long a, lon
         return a / b;
     }
 }
+// Truncated quotient of two integers below 2^16 in magnitude (given as floats) without the integer
+// divider: a * (1/b) is within 2^-22 relative of the quotient; scaling by 1 + 2^-20 lifts an exact
+// quotient to at least itself, and never reaches the next integer, because a quotient that is not
+// an integer is at least |q| * 2^-16 away from one.  Truncation then gives a / b.  Division by
+// zero yields the extreme of the sign of a, as the reference does.
+__device__ __forceinline__ int narrow_int_quotient(float a, float b) {
+    float r;
+    asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(r) : "f"(b));
+    const int q = __float2int_rz(__fmul_rn(__fmul_rn(a, r), 1.00000095367431640625f));
+    return b == 0.0f ? (a >= 0.0f ? 0x7FFFFFFF : (int)0x80000000) : q;
+}
 template <int OP> __device__ __forceinline__ int int_op32(int a, int b) {      // inputs within 16 bits
     if constexpr (OP == kAdd) return a + b;
     else if constexpr (OP == kSub) return a - b;
     else if constexpr (OP == kMul) return a * b;
-    else return b == 0 ? (a >= 0 ? 0x7FFFFFFF : (int)0x80000000) : a / b;
+    else return narrow_int_quotient((float)a, (float)b);
 }
 template <int OP> __device__ __forceinline__ float float_op32(float a, float b) {
     if constexpr (OP == kAdd) return __fadd_rn(a, b);
@@ -82,8 +93,16 @@ struct BinaryBody {
         constexpr bool float_lane = !dtype_is_int(DO) && DO != DTYPE_FLOAT64 && dtype_exact_in_f32(DA) && dtype_exact_in_f32(DB);
         if constexpr (int_lane) {
             int v[kV];
-            #pragma unroll
-            for (int j = 0; j < kV; j++) v[j] = int_op32<OP>(to_i32_narrow<DA>(ra.v[j]), to_i32_narrow<DB>(rb.v[j]));
+            if constexpr (OP == kDiv && kV % 4 == 0 && (DA == DTYPE_INT8 || DA == DTYPE_UINT8) && (DB == DTYPE_INT8 || DB == DTYPE_UINT8)) {
+                float fa[kV], fb[kV];                     // bytes to float on the integer pipe, no conversion unit
+                decode_floats<DA, kV>(ra, fa);
+                decode_floats<DB, kV>(rb, fb);
+                #pragma unroll
+                for (int j = 0; j < kV; j++) v[j] = narrow_int_quotient(fa[j], fb[j]);
+            } else {
+                #pragma unroll
+                for (int j = 0; j < kV; j++) v[j] = int_op32<OP>(to_i32_narrow<DA>(ra.v[j]), to_i32_narrow<DB>(rb.v[j]));
+            }
             encode_ints<DO, kV>(v, ro);
         } else if constexpr (float_lane) {
             float fa[kV], fb[kV];

@@ -6,7 +6,7 @@
 // contiguous (stride-1 pools) or stride-s segments of the same input rows, and the kh/kw re-reads
 // of overlapping windows are served by L1.  max_pool_kernel is the general form (any dtype pair,
 // 64-bit indices); max_pool_win below is the fast form for same-dtype pools.
-#include "common.cuh"
+#include "elementwise.cuh"
 
 namespace tops {
 
@@ -93,9 +93,12 @@ __global__ void __launch_bounds__(256) max_pool_win(const typename Storage<DT>::
     }
 }
 
+template <int DT> static bool launch_stride2(const Tensor* X, Tensor* Y, const PoolGeom& p, DeviceState* st, cudaStream_t s);
+
 template <int DT>
 static void launch_win(const Tensor* X, Tensor* Y, const PoolGeom& p, DeviceState* st, cudaStream_t s) {
     using S = typename Storage<DT>::type;
+    if (launch_stride2<DT>(X, Y, p, st, s)) return;
     FastDiv by_ow, by_oh;
     by_ow.set((uint32_t)p.OW);
     by_oh.set((uint32_t)p.OH);
@@ -106,6 +109,113 @@ static void launch_win(const Tensor* X, Tensor* Y, const PoolGeom& p, DeviceStat
     if (p.KH == 2 && p.KW == 2)      max_pool_win<DT, 2, 2><<<grid, 256, 0, s>>>(x, y, p, by_ow, by_oh, total);
     else if (p.KH == 3 && p.KW == 3) max_pool_win<DT, 3, 3><<<grid, 256, 0, s>>>(x, y, p, by_ow, by_oh, total);
     else                             max_pool_win<DT, 0, 0><<<grid, 256, 0, s>>>(x, y, p, by_ow, by_oh, total);
+}
+
+// ---------------------------------------------------------------------------------------------
+// The two stride-2 pools of convolutional networks -- 2x2 without padding and 3x3 with one cell of
+// padding -- on planes whose width is a multiple of four.  A thread owns four input columns (one
+// 16-byte load for float32), hence two output columns, and walks down a strip of output rows:
+// every input row is loaded once, reduced along the row first (the left neighbour of the 3x3
+// window comes from the neighbouring lane by a shuffle), then combined down the column, with the
+// row shared by two vertically adjacent 3x3 windows carried in registers.  The tap order of the
+// reference (row by row, left to right, strict '>') is kept, so ties between +0 and -0 and the
+// NaN rule resolve identically.
+// ---------------------------------------------------------------------------------------------
+template <int DT> __device__ __forceinline__ void pool_load4(const typename Storage<DT>::type* p, bool on, float (&v)[4]) {
+    using S = typename Storage<DT>::type;
+    v[0] = v[1] = v[2] = v[3] = -INFINITY;
+    if (!on) return;
+    S raw[4];
+    load_bytes<4 * (int)sizeof(S)>(p, raw);
+    #pragma unroll
+    for (int j = 0; j < 4; j++) v[j] = to_f32<DT>(raw[j]);
+}
+
+template <int DT, int K>
+__global__ void __launch_bounds__(256) max_pool_stride2_strips(const typename Storage<DT>::type* __restrict__ x,
+                                                                typename Storage<DT>::type* __restrict__ y,
+                                                                int H, int W, int OH, int OW, int strip, uint32_t quads,
+                                                                uint32_t strips, FastDiv by_quads, FastDiv by_strips, uint32_t total) {
+    using S = typename Storage<DT>::type;
+    const uint32_t i = blockIdx.x * blockDim.x + threadIdx.x, lane = threadIdx.x & 31u;
+    const bool live = i < total;
+    const uint32_t t = by_quads.div(i), q = i - t * quads;
+    const uint32_t plane = by_strips.div(t), part = t - plane * strips;
+    const int oh0 = (int)part * strip;
+    const S* src = x + (size_t)plane * (size_t)(H * W) + 4u * q;
+    S* dst = y + (size_t)plane * (size_t)(OH * OW) + 2u * q;
+
+    // horizontal maxima of one input row for this thread's two output columns
+    auto row_maxima = [&](int ih, bool on, float& m0, float& m1) {
+        float v[4];
+        pool_load4<DT>(src + ih * W, on, v);
+        m0 = -INFINITY; m1 = -INFINITY;
+        if constexpr (K == 3) {
+            float left = __shfl_up_sync(0xFFFFFFFFu, v[3], 1);        // column 4q - 1 lives in the lane to the left
+            if (q == 0) left = -INFINITY;                             // padding column
+            else if (lane == 0 && on) left = to_f32<DT>(src[ih * W - 1]);
+            if (left > m0) m0 = left;
+            if (v[0] > m0) m0 = v[0];
+            if (v[1] > m0) m0 = v[1];
+            if (v[1] > m1) m1 = v[1];
+            if (v[2] > m1) m1 = v[2];
+            if (v[3] > m1) m1 = v[3];
+        } else {
+            if (v[0] > m0) m0 = v[0];
+            if (v[1] > m0) m0 = v[1];
+            if (v[2] > m1) m1 = v[2];
+            if (v[3] > m1) m1 = v[3];
+        }
+    };
+
+    float carry0 = -INFINITY, carry1 = -INFINITY;                     // the row above the strip (3x3 only)
+    if constexpr (K == 3) row_maxima(2 * oh0 - 1, live && oh0 > 0 && oh0 < OH, carry0, carry1);
+    for (int r = 0; r < strip; r++) {
+        const int oh = oh0 + r;
+        const bool on = live && oh < OH;
+        float a0, a1, b0, b1;
+        row_maxima(2 * oh, on, a0, a1);
+        row_maxima(2 * oh + 1, on, b0, b1);
+        float o0 = carry0, o1 = carry1;                               // -Inf for the 2x2 pool
+        if (a0 > o0) o0 = a0;
+        if (a1 > o1) o1 = a1;
+        if (b0 > o0) o0 = b0;
+        if (b1 > o1) o1 = b1;
+        if constexpr (K == 3) { carry0 = b0; carry1 = b1; }
+        if (on) {
+            S out[2];
+            if constexpr (dtype_is_int(DT)) { out[0] = from_f64<DT>((double)o0); out[1] = from_f64<DT>((double)o1); }
+            else { out[0] = from_f32<DT>(o0); out[1] = from_f32<DT>(o1); }
+            store_bytes_stream<2 * (int)sizeof(S)>(dst + oh * OW, out);
+        }
+    }
+}
+
+// false: the shape is not one of the two stride-2 pools this kernel covers
+template <int DT>
+static bool launch_stride2(const Tensor* X, Tensor* Y, const PoolGeom& p, DeviceState* st, cudaStream_t s) {
+    using S = typename Storage<DT>::type;
+    const int K = p.KH;
+    if (!(p.KH == p.KW && (K == 2 || K == 3) && p.sh == 2 && p.sw == 2 && p.dh == 1 && p.dw == 1 &&
+          p.pt == (K == 3) && p.pl == (K == 3) && p.W % 4 == 0 && p.H % 2 == 0 && p.OH == p.H / 2 && p.OW == p.W / 2))
+        return false;
+    if ((uintptr_t)X->data % (4 * sizeof(S)) || (uintptr_t)Y->data % (2 * sizeof(S))) return false;
+    const size_t planes = (size_t)X->shape[0] * X->shape[1];
+    const uint32_t quads = (uint32_t)(p.W / 4);
+    int strip = 8;                                                    // output rows per thread
+    while (strip > 1 && planes * quads * (size_t)((p.OH + strip - 1) / strip) < (size_t)st->sm_count * 4096) strip /= 2;
+    const uint32_t strips = (uint32_t)((p.OH + strip - 1) / strip);
+    const size_t total = planes * quads * strips;
+    if (total >= 0x7FFFFFFFull) return false;
+    FastDiv by_quads, by_strips;
+    by_quads.set(quads);
+    by_strips.set(strips);
+    const uint32_t grid = (uint32_t)((total + 255) / 256);
+    const S* x = (const S*)X->data;
+    S* y = (S*)Y->data;
+    if (K == 2) max_pool_stride2_strips<DT, 2><<<grid, 256, 0, s>>>(x, y, p.H, p.W, p.OH, p.OW, strip, quads, strips, by_quads, by_strips, (uint32_t)total);
+    else        max_pool_stride2_strips<DT, 3><<<grid, 256, 0, s>>>(x, y, p.H, p.W, p.OH, p.OW, strip, quads, strips, by_quads, by_strips, (uint32_t)total);
+    return true;
 }
 
 }  // namespace tops

@@ -112,6 +112,29 @@ def test_binary_saturation_and_wrap(port, op):
         assert_same_codes(gpu.binary(op, af, "float32", bf, "float32", out), port.binary(op, af, "float32", bf, "float32", out), out)
 
 
+def test_narrow_integer_division_is_exact(port):
+    """Division of 8- and 16-bit integers runs on a float reciprocal: every int8 and uint8 pair, and
+    for int16 the pairs that stress it (exact multiples and their neighbours, extremes, random)."""
+    a8, b8 = np.meshgrid(np.arange(-128, 128, dtype=np.int8), np.arange(-128, 128, dtype=np.int8), indexing="ij")
+    for out in ("int8", "int16", "int32"):
+        assert_same_codes(gpu.binary("div", a8.copy(), "int8", b8.copy(), "int8", out), port.binary("div", a8.copy(), "int8", b8.copy(), "int8", out), out)
+    au, bu = np.meshgrid(np.arange(256, dtype=np.uint8), np.arange(256, dtype=np.uint8), indexing="ij")
+    assert_same_codes(gpu.binary("div", au.copy(), "uint8", bu.copy(), "uint8", "uint8"), port.binary("div", au.copy(), "uint8", bu.copy(), "uint8", "uint8"), "uint8")
+    assert_same_codes(gpu.binary("div", a8.copy(), "int8", bu.copy(), "uint8", "int16"), port.binary("div", a8.copy(), "int8", bu.copy(), "uint8", "int16"), "int16")
+    rng = np.random.default_rng(41)
+    b = rng.integers(-32768, 32768, size=1 << 20, dtype=np.int64)
+    q = rng.integers(-40, 41, size=b.size, dtype=np.int64)
+    near = np.clip(q * b + rng.integers(-1, 2, size=b.size), -32768, 32767)        # multiples of b and their neighbours
+    rand = rng.integers(-32768, 32768, size=b.size, dtype=np.int64)
+    edge = rng.choice(np.array([-32768, -32767, -1, 0, 1, 32767]), size=b.size)
+    for a in (near, rand, edge):
+        a16, b16 = a.astype(np.int16), b.astype(np.int16)
+        for out in ("int16", "int32"):
+            assert_same_codes(gpu.binary("div", a16, "int16", b16, "int16", out), port.binary("div", a16, "int16", b16, "int16", out), out)
+    a16, b16 = edge.astype(np.int16), rng.choice(np.array([-32768, -1, 1, 2, 32767, 0]), size=b.size).astype(np.int16)
+    assert_same_codes(gpu.binary("div", a16, "int16", b16, "int16", "int16"), port.binary("div", a16, "int16", b16, "int16", "int16"), "int16")
+
+
 def test_binary_output_dtype_inference():
     """No explicit dtype: numpy promotion over the storage types (bfloat16 is stored as uint16)."""
     from onnx_translator_b200 import nn
@@ -267,6 +290,12 @@ def test_conv2d_exact_path(port, plan):
     ("float32", "float32", (1, 1, 3, 3), (2, 2), (2, 2, 2, 2), (3, 3), (1, 1)),
     ("float32", "float32", (4, 64, 112, 112), (3, 3), (1, 1, 1, 1), (2, 2), (1, 1)),      # the ResNet stem pool
     ("float32", "float32", (4, 256, 7, 7), (7, 7), (0, 0, 0, 0), (1, 1), (1, 1)),          # the final 7x7 pool
+    ("float16", "float16", (3, 5, 24, 40), (3, 3), (1, 1, 1, 1), (2, 2), (1, 1)),
+    ("bfloat16", "bfloat16", (2, 7, 34, 132), (3, 3), (1, 1, 1, 1), (2, 2), (1, 1)),
+    ("int8", "int8", (2, 3, 18, 20), (3, 3), (1, 1, 1, 1), (2, 2), (1, 1)),
+    ("float32", "float32", (3, 9, 6, 8), (2, 2), (0, 0, 0, 0), (2, 2), (1, 1)),
+    ("uint8", "uint8", (1, 130, 8, 136), (2, 2), (0, 0, 0, 0), (2, 2), (1, 1)),
+    ("float8_e5m2", "float8_e5m2", (2, 2, 10, 12), (3, 3), (1, 1, 1, 1), (2, 2), (1, 1)),
 ], ids=lambda p: f"{p[0]}-{p[2]}-k{p[3]}")
 def test_max_pool(port, plan):
     x_dt, out_dt, xs, kernel, pads, strides, dil = plan
@@ -275,6 +304,9 @@ def test_max_pool(port, plan):
     if x_dt == "float32":
         x.reshape(-1)[::7] = np.nan
         x.reshape(-1)[3::11] = -np.inf
+        x.reshape(-1)[1::5] = 0.0                  # ties between +0 and -0 go to the first tap scanned
+        x.reshape(-1)[2::5] = -0.0
+        x.reshape(-1)[4::10] = -1.0
     args = (x, x_dt, out_dt, kernel, pads, strides, dil)
     assert_same_codes(gpu.max_pool(*args), port.max_pool(*args), out_dt)
 
