@@ -347,7 +347,10 @@ def run_ours(args):
                        "parallelism": f"replicated sweep per GPU x{world}, no data-path collective"},
             "roofline": {"bound": "hbm", "kernel": "ew_kernel<BinaryBody> (84 launches per step)",
                          "achieved": round(achieved, 1), "peak": peak, "unit": "GB/s",
-                         "frac": round(achieved / peak, 4), "peak_kind": peak_kind, "traffic": None},
+                         "frac": round(achieved / peak, 4), "peak_kind": peak_kind,
+                         "algorithmic_bytes_per_launch": int(fam_bytes / len(binary_idx)),
+                         "launch_ms": round(fam_ms / len(binary_idx), 5),
+                         "traffic": BINARY_DRAM_BYTES_PER_LAUNCH},
             "e2e": {"value": round(world * bytes_step / 1e9 / (e2e_ms_max / 1e3), 2), "unit": "GB/s",
                     "h2d_bytes_per_step": int(h2d), "d2h_bytes_per_step": int(d2h), "ms_per_step": round(e2e_ms_max, 3)},
             "gpu_launches": n_launch * args.steps,
@@ -473,6 +476,14 @@ def other_ops(lib, stream, hbm_peak):
     return out
 
 
+# DRAM read + write bytes of one ew_kernel<BinaryBody> launch, averaged over the 84 launches of one
+# pass of this sweep at full size: dram__bytes_read.sum + dram__bytes_write.sum from an ncu launch
+# list of `bench.py --steps 1 --warmup 3 --no-extra` (15.860 GB over 84 launches; the summary is
+# profiles/bench_sweep_launch_list.md).  It is below the algorithmic bytes because part of each
+# output is still in the 126 MB L2 when its kernel ends.
+BINARY_DRAM_BYTES_PER_LAUNCH = 188_800_000
+
+
 # ---- the reference's CPU implementation ------------------------------------------------------------------
 def cpu_sweep(rows, steps, warmup):
     """Times the reference C library (or, if no compiled copy is present, the oracle port) on the
@@ -481,6 +492,7 @@ def cpu_sweep(rows, steps, warmup):
     import oracle
     kind = "reference" if oracle.available("ref") else "port"
     host = oracle.HostOracle("ref" if kind == "reference" else "port")
+    cores = oracle.use_all_host_threads()
     a_host, a_cos_host, b_host = host_inputs(rows, seed=0)
     plan = sweep_plan(rows)
     full = (rows, MID, INNER)
@@ -506,7 +518,6 @@ def cpu_sweep(rows, steps, warmup):
     for _ in range(steps):
         one_step()
     dt = (time.perf_counter() - t0) / steps
-    cores = int(os.environ.get("OMP_NUM_THREADS", os.cpu_count() or 1))
     return bytes_step / 1e9 / dt, dt, kind, cores
 
 

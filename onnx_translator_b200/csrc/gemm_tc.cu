@@ -11,7 +11,7 @@
 //   warps 2-5 epilogue: tcgen05.ld the accumulator (each warp its own 32-lane quarter), apply
 //             alpha / beta * C, convert and store; then hand the accumulator back.  Because there
 //             are two accumulators, the epilogue of tile i overlaps the main loop of tile i + 1.
-// No cluster, no multicast: every CTA loads its own operands.  All waits are bounded.
+// No cluster: every CTA loads its own operands.  All waits are bounded.
 #include "tc_kernel.cuh"
 
 #include <atomic>

@@ -131,17 +131,17 @@ template <int DT> __device__ __forceinline__ void pool_load4(const typename Stor
     for (int j = 0; j < 4; j++) v[j] = to_f32<DT>(raw[j]);
 }
 
-template <int DT, int K>
+template <int DT, int K, int STRIP>
 __global__ void __launch_bounds__(256) max_pool_stride2_strips(const typename Storage<DT>::type* __restrict__ x,
                                                                 typename Storage<DT>::type* __restrict__ y,
-                                                                int H, int W, int OH, int OW, int strip, uint32_t quads,
+                                                                int H, int W, int OH, int OW, uint32_t quads,
                                                                 uint32_t strips, FastDiv by_quads, FastDiv by_strips, uint32_t total) {
     using S = typename Storage<DT>::type;
     const uint32_t i = blockIdx.x * blockDim.x + threadIdx.x, lane = threadIdx.x & 31u;
     const bool live = i < total;
     const uint32_t t = by_quads.div(i), q = i - t * quads;
     const uint32_t plane = by_strips.div(t), part = t - plane * strips;
-    const int oh0 = (int)part * strip;
+    const int oh0 = (int)part * STRIP;
     const S* src = x + (size_t)plane * (size_t)(H * W) + 4u * q;
     S* dst = y + (size_t)plane * (size_t)(OH * OW) + 2u * q;
 
@@ -170,7 +170,8 @@ __global__ void __launch_bounds__(256) max_pool_stride2_strips(const typename St
 
     float carry0 = -INFINITY, carry1 = -INFINITY;                     // the row above the strip (3x3 only)
     if constexpr (K == 3) row_maxima(2 * oh0 - 1, live && oh0 > 0 && oh0 < OH, carry0, carry1);
-    for (int r = 0; r < strip; r++) {
+    #pragma unroll
+    for (int r = 0; r < STRIP; r++) {                                 // unrolled: the loads of the whole strip are in flight together
         const int oh = oh0 + r;
         const bool on = live && oh < OH;
         float a0, a1, b0, b1;
@@ -213,8 +214,10 @@ static bool launch_stride2(const Tensor* X, Tensor* Y, const PoolGeom& p, Device
     const uint32_t grid = (uint32_t)((total + 255) / 256);
     const S* x = (const S*)X->data;
     S* y = (S*)Y->data;
-    if (K == 2) max_pool_stride2_strips<DT, 2><<<grid, 256, 0, s>>>(x, y, p.H, p.W, p.OH, p.OW, strip, quads, strips, by_quads, by_strips, (uint32_t)total);
-    else        max_pool_stride2_strips<DT, 3><<<grid, 256, 0, s>>>(x, y, p.H, p.W, p.OH, p.OW, strip, quads, strips, by_quads, by_strips, (uint32_t)total);
+#define TOPS_STRIPS(KK, SS) max_pool_stride2_strips<DT, KK, SS><<<grid, 256, 0, s>>>(x, y, p.H, p.W, p.OH, p.OW, quads, strips, by_quads, by_strips, (uint32_t)total)
+    if (K == 2) { if (strip == 8) TOPS_STRIPS(2, 8); else if (strip == 4) TOPS_STRIPS(2, 4); else if (strip == 2) TOPS_STRIPS(2, 2); else TOPS_STRIPS(2, 1); }
+    else        { if (strip == 8) TOPS_STRIPS(3, 8); else if (strip == 4) TOPS_STRIPS(3, 4); else if (strip == 2) TOPS_STRIPS(3, 2); else TOPS_STRIPS(3, 1); }
+#undef TOPS_STRIPS
     return true;
 }
 

@@ -30,6 +30,18 @@ __device__ __forceinline__ int quantize_round_fast(float x, float inv_s, int z, 
     ok = (aq < 2097152.0f) && (__fsub_rn(0.5f, fabsf(__fsub_rn(q, r))) > aq * 1.9073486e-6f);
     return (__float_as_int(t) - 0x4B400000) + z;
 }
+// 8-bit outputs with an 8-bit zero point: the same rounding and the same tie margin (2^-19 |q|,
+// folded into one multiply-add).  For int8 / uint8, quotients of 4096 and more saturate whichever
+// way they round (|z| <= 255), so they stay on the fast path up to the limit of the magic-number
+// rounding; fp8 outputs take the double division from 2^21 on like every other type.
+// `z_minus_magic` = z - 0x4B400000, the same for every element of a run with one zero point.
+__device__ __forceinline__ int quantize_round_8bit(float x, float inv_s, int z_minus_magic, bool& ok) {
+    const float q = __fmul_rn(x, inv_s);
+    const float t = __fadd_rn(q, 12582912.0f);
+    const float d = __fsub_rn(q, __fsub_rn(t, 12582912.0f));
+    ok = (fmaf(fabsf(q), 1.9073486e-6f, fabsf(d)) < 0.5f) & (fabsf(q) < 2097152.0f);
+    return __float_as_int(t) + z_minus_magic;
+}
 // The reference's arithmetic, element by element.
 template <int DO>
 __device__ __forceinline__ typename Storage<DO>::type quantize_exact(double x, double s, double z) {
@@ -60,12 +72,24 @@ struct QuantizeBody {
             bool all_ok = true;
             const bool uniform_scale = ALIGNED && !g.simple && s.st2 == 0;    // one scale for the whole run
             float inv = uniform_scale ? __fdividef(1.0f, to_f32<DS>(rs.v[0])) : 0.0f;
-            #pragma unroll
-            for (int j = 0; j < kV; j++) {
-                if (!uniform_scale) inv = __fdividef(1.0f, to_f32<DS>(rs.v[j]));
-                bool ok;
-                v[j] = quantize_round_fast(fx[j], inv, to_i32_narrow<DZ>(rz.v[j]), ok);
-                all_ok = all_ok && ok;
+            constexpr bool kEightBit = (DO == DTYPE_INT8 || DO == DTYPE_UINT8 || DO == DTYPE_FLOAT8_E4M3 || DO == DTYPE_FLOAT8_E5M2) &&
+                                       (DZ == DTYPE_INT8 || DZ == DTYPE_UINT8);
+            if (kEightBit && uniform_scale && z.st2 == 0) {
+                const int zm = to_i32_narrow<DZ>(rz.v[0]) - 0x4B400000;
+                #pragma unroll
+                for (int j = 0; j < kV; j++) {
+                    bool ok;
+                    v[j] = quantize_round_8bit(fx[j], inv, zm, ok);
+                    all_ok = all_ok & ok;
+                }
+            } else {
+                #pragma unroll
+                for (int j = 0; j < kV; j++) {
+                    if (!uniform_scale) inv = __fdividef(1.0f, to_f32<DS>(rs.v[j]));
+                    bool ok;
+                    v[j] = quantize_round_fast(fx[j], inv, to_i32_narrow<DZ>(rz.v[j]), ok);
+                    all_ok = all_ok && ok;
+                }
             }
             if (all_ok) {
                 if constexpr (DO == DTYPE_INT8 || DO == DTYPE_UINT8) {
@@ -114,6 +138,27 @@ struct DequantizeBody {
         fetch3<DX, kV, ALIGNED>(g, x, i0, nv, c, rx);
         fetch3<DS, kV, ALIGNED>(g, s, i0, nv, c, rs);
         fetch3<DZ, kV, ALIGNED>(g, z, i0, nv, c, rz);
+        if constexpr (kDiffExact && (DX == DTYPE_INT8 || DX == DTYPE_UINT8) && kV % 4 == 0) {
+            // one scale and one zero point for the whole run: the byte is placed in the low mantissa
+            // byte of 2^23 and (2^23 + offset + z) is subtracted in one exact step
+            if (ALIGNED && nv == kV && !g.simple && s.st2 == 0 && z.st2 == 0) {
+                const float fs = to_f32<DS>(rs.v[0]);
+                const float base = __fadd_rn(DX == DTYPE_INT8 ? 8388736.0f : 8388608.0f, to_f32<DZ>(rz.v[0]));
+                float f[kV];
+                #pragma unroll
+                for (int j = 0; j < kV; j += 4) {
+                    uint32_t w = *reinterpret_cast<const uint32_t*>(&rx.v[j]);
+                    if (DX == DTYPE_INT8) w ^= 0x80808080u;
+                    f[j]     = __fmul_rn(__fsub_rn(__uint_as_float(__byte_perm(w, 0x4B000000u, 0x7540)), base), fs);
+                    f[j + 1] = __fmul_rn(__fsub_rn(__uint_as_float(__byte_perm(w, 0x4B000000u, 0x7541)), base), fs);
+                    f[j + 2] = __fmul_rn(__fsub_rn(__uint_as_float(__byte_perm(w, 0x4B000000u, 0x7542)), base), fs);
+                    f[j + 3] = __fmul_rn(__fsub_rn(__uint_as_float(__byte_perm(w, 0x4B000000u, 0x7543)), base), fs);
+                }
+                encode_floats<DO, kV>(f, ro);
+                put3<DO, kV, ALIGNED>(out, i0, nv, ro);
+                return;
+            }
+        }
         if constexpr (kDiffExact) {
             float fx[kV], fz[kV], f[kV];
             decode_floats<DX, kV>(rx, fx);

@@ -48,7 +48,7 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volati
     }
 }
 
-// ---- TMA (no cluster multicast anywhere: each CTA loads its own tiles) ------------------------------------------
+// ---- TMA (each CTA loads its own tiles) ------------------------------------------
 __device__ __forceinline__ void tma_prefetch_desc(const CUtensorMap* map) {
     asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(map)) : "memory");
 }

@@ -62,6 +62,17 @@ def available(kind: str) -> bool:
     return os.path.exists(PORT_SO if kind == "port" else REF_SO)
 
 
+def use_all_host_threads() -> int:
+    """Sets the OpenMP team of the libraries loaded from here to every core this process may run on
+    (a launcher may have exported OMP_NUM_THREADS=1) and returns that count."""
+    n = len(os.sched_getaffinity(0)) if hasattr(os, "sched_getaffinity") else (os.cpu_count() or 1)
+    try:
+        ctypes.CDLL("libgomp.so.1").omp_set_num_threads(ctypes.c_int(n))
+    except OSError:
+        return int(os.environ.get("OMP_NUM_THREADS", "1"))
+    return n
+
+
 def _ints(values: Sequence[int]):
     return (ctypes.c_int * len(values))(*[int(v) for v in values])
 
