@@ -77,17 +77,31 @@ binary_elem(typename Storage<DA>::type sa, typename Storage<DB>::type sb) {
 
 template <int DA, int DB, int DO, int OP, bool ALIGNED>
 struct BinaryBody {
-    static constexpr int kV = vec_width(dtype_bytes(DA), dtype_bytes(DB), dtype_bytes(DO), OP == kDiv ? kRunCapDivide : kRunCapDefault);
+    static constexpr int kV = vec_width(dtype_bytes(DA), dtype_bytes(DB), dtype_bytes(DO));
+    static constexpr bool kMixedWidths = dtype_bytes(DA) != dtype_bytes(DB) || dtype_bytes(DB) != dtype_bytes(DO);
+    static constexpr bool kWideDivide = OP == kDiv && (DO == DTYPE_FLOAT64 || (DO == DTYPE_FLOAT32 && DA == DTYPE_FLOAT32 && DB == DTYPE_FLOAT32));
+    static constexpr int kGroups = kWideDivide ? 4 : kMixedWidths ? 2 : 0;     // 0: run kernel
+    struct Regs {
+        Run<typename Storage<DA>::type, kV> ra;
+        Run<typename Storage<DB>::type, kV> rb;
+    };
     Geo3 g;
     Op3 a, b;
     void* out;
-    __device__ __forceinline__ void operator()(uint32_t i0, uint32_t nv) const {
-        Run<typename Storage<DA>::type, kV> ra;
-        Run<typename Storage<DB>::type, kV> rb;
-        Run<typename Storage<DO>::type, kV> ro;
+    __device__ __forceinline__ void load(uint32_t i0, uint32_t nv, Regs& r) const {
         const Coord3 c = g.simple ? Coord3{0, 0, 0} : coords_of(g, i0);
-        fetch3<DA, kV, ALIGNED>(g, a, i0, nv, c, ra);
-        fetch3<DB, kV, ALIGNED>(g, b, i0, nv, c, rb);
+        fetch3<DA, kV, ALIGNED>(g, a, i0, nv, c, r.ra);
+        fetch3<DB, kV, ALIGNED>(g, b, i0, nv, c, r.rb);
+    }
+    __device__ __forceinline__ void operator()(uint32_t i0, uint32_t nv) const {
+        Regs r;
+        load(i0, nv, r);
+        finish(i0, nv, r);
+    }
+    __device__ __forceinline__ void finish(uint32_t i0, uint32_t nv, const Regs& r) const {
+        const Run<typename Storage<DA>::type, kV>& ra = r.ra;
+        const Run<typename Storage<DB>::type, kV>& rb = r.rb;
+        Run<typename Storage<DO>::type, kV> ro;
         constexpr bool int_lane = dtype_is_int(DO) && DO != DTYPE_INT64 && dtype_is_narrow_int(DA) && dtype_is_narrow_int(DB) &&
                                   dtype_is_narrow_int(DO);
         constexpr bool float_lane = !dtype_is_int(DO) && DO != DTYPE_FLOAT64 && dtype_exact_in_f32(DA) && dtype_exact_in_f32(DB);
@@ -123,6 +137,7 @@ struct BinaryBody {
 template <int OP>
 struct BinaryGenericBody {
     static constexpr int kV = 1;
+    static constexpr int kGroups = 0;
     Geometry g;
     Operand a, b;
     void* out;

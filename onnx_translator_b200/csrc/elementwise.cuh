@@ -206,7 +206,8 @@ __device__ __forceinline__ void encode_ints(const int (&v)[V], Run<typename Stor
     }
 }
 
-// ---- the kernel ----------------------------------------------------------------------------------------
+// ---- the kernels ---------------------------------------------------------------------------------------
+// Run kernel: a thread owns one run of V consecutive outputs per step (generic bodies, V = 1).
 template <class Body>
 __global__ void __launch_bounds__(kEwThreads) ew_kernel(const Body body, const uint32_t n) {
     constexpr uint32_t V = Body::kV;
@@ -219,14 +220,42 @@ __global__ void __launch_bounds__(kEwThreads) ew_kernel(const Body body, const u
     }
 }
 
-// Elements per run.  The narrowest stream would like 16 bytes per access, which makes the widest
-// stream take several 16-byte accesses per run; `cap_bytes` bounds what the widest stream moves per
-// run.  Measured on B200 (4096 x 4096 operands): for add / sub / mul of mixed widths a cap of 16
-// bytes is fastest (int32 + float16 -> float64: 5.2 TB/s against 3.7 TB/s at 64), the division and
-// dequantize kernels gain from 32 (more independent divisions / decodes in flight), and quantize
-// (float32 -> 8 bit) from 64, where the 8-bit output is then stored 16 bytes at a time.
-constexpr int kRunCapDefault = 16, kRunCapDivide = 32, kRunCapDequantize = 32, kRunCapQuantize = 64;
-constexpr int vec_width(int bytes_a, int bytes_b, int bytes_c, int cap_bytes = kRunCapDefault) {
+// Tile kernel (typed bodies): a warp owns tiles of 32 * V * G consecutive outputs.  Within a tile
+// lane l takes the runs l, l + 32, ..., l + 32 (G - 1), so every access of the warp covers one
+// contiguous span (512 bytes for the widest stream, whose runs are 16 bytes) whatever the other
+// streams' widths, and the loads of all G runs are issued before the first result is needed.
+template <class Body>
+__global__ void __launch_bounds__(kEwThreads) ew_kernel_tiled(const Body body, const uint32_t n) {
+    constexpr uint32_t V = Body::kV, G = Body::kGroups, TILE = 32u * V * G;
+    const uint32_t lane = threadIdx.x & 31u;
+    const uint32_t warp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, warps = (gridDim.x * blockDim.x) >> 5;
+    for (uint32_t base = warp * TILE; base < n; base += warps * TILE) {          // n < 2^31 and warps * TILE < 2^30
+        typename Body::Regs regs[G];
+        #pragma unroll
+        for (uint32_t j = 0; j < G; j++) {
+            const uint32_t i0 = base + (j * 32u + lane) * V;
+            if (i0 < n) body.load(i0, n - i0 < V ? n - i0 : V, regs[j]);
+        }
+        #pragma unroll
+        for (uint32_t j = 0; j < G; j++) {
+            const uint32_t i0 = base + (j * 32u + lane) * V;
+            if (i0 < n) body.finish(i0, n - i0 < V ? n - i0 : V, regs[j]);
+        }
+    }
+}
+
+// Elements per run: the narrowest stream would like 16 bytes per access; `cap_bytes` bounds what the
+// widest stream then moves per run (16 = one vector access per lane for the widest stream).
+//
+// Which kernel and which widths a body uses is decided by measurement on B200 (A/B builds over the
+// 95-launch sweep and the 8192 x 8192 quantize cases):
+//   * same-width add / sub / mul, unary ops: run kernel, 16-byte runs (5.4-5.9 TB/s; the tile kernel
+//     costs registers, hence occupancy, and is 10-15 % slower for the 16-bit types);
+//   * operands of different widths (int8 + float32, int32 + float16 -> float64), dequantize: tile kernel
+//     with two runs per lane (+10-17 %: every access of the warp is one contiguous span);
+//   * float32 / float64 division: tile kernel with four runs per lane (+20 %: more divisions in flight);
+//   * quantize to 8 bits: run kernel with 64-byte runs of float32 (16-byte stores of the codes).
+constexpr int vec_width(int bytes_a, int bytes_b, int bytes_c, int cap_bytes = 16) {
     int lo = bytes_a < bytes_b ? bytes_a : bytes_b;
     lo = lo < bytes_c ? lo : bytes_c;
     int hi = bytes_a > bytes_b ? bytes_a : bytes_b;
@@ -324,9 +353,15 @@ template <class Body>
 bool launch_body(const char* name, const Body& body, size_t n) {
     DeviceState* st = acquire_device();
     if (!st) return false;
-    const size_t runs = (n + Body::kV - 1) / Body::kV;
-    const int grid = grid_for(runs, kEwThreads, st->sm_count, kEwCtasPerSm);
-    ew_kernel<Body><<<grid, kEwThreads, 0, current_stream()>>>(body, (uint32_t)n);
+    if constexpr (Body::kGroups > 0) {
+        const size_t tile = (size_t)32 * Body::kV * Body::kGroups;
+        const int grid = grid_for(((n + tile - 1) / tile) * 32, kEwThreads, st->sm_count, kEwCtasPerSm);
+        ew_kernel_tiled<Body><<<grid, kEwThreads, 0, current_stream()>>>(body, (uint32_t)n);
+    } else {
+        const size_t runs = (n + Body::kV - 1) / Body::kV;
+        const int grid = grid_for(runs, kEwThreads, st->sm_count, kEwCtasPerSm);
+        ew_kernel<Body><<<grid, kEwThreads, 0, current_stream()>>>(body, (uint32_t)n);
+    }
     return TOPS_CHECK_LAUNCH(name);
 }
 

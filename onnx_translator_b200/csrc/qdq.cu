@@ -52,19 +52,32 @@ __device__ __forceinline__ typename Storage<DO>::type quantize_exact(double x, d
 
 template <int DX, int DS, int DZ, int DO, bool ALIGNED>
 struct QuantizeBody {
-    static constexpr int kV = vec_width(dtype_bytes(DX), dtype_bytes(DO), dtype_bytes(DO), kRunCapQuantize);
-    Geo3 g;
-    Op3 x, s, z;
-    void* out;
-    __device__ __forceinline__ void operator()(uint32_t i0, uint32_t nv) const {
+    static constexpr int kV = vec_width(dtype_bytes(DX), dtype_bytes(DO), dtype_bytes(DO), 64);
+    static constexpr int kGroups = 0;
+    struct Regs {
         Run<typename Storage<DX>::type, kV> rx;
         Run<typename Storage<DS>::type, kV> rs;
         Run<typename Storage<DZ>::type, kV> rz;
-        Run<typename Storage<DO>::type, kV> ro;
+    };
+    Geo3 g;
+    Op3 x, s, z;
+    void* out;
+    __device__ __forceinline__ void load(uint32_t i0, uint32_t nv, Regs& r) const {
         const Coord3 c = g.simple ? Coord3{0, 0, 0} : coords_of(g, i0);
-        fetch3<DX, kV, ALIGNED>(g, x, i0, nv, c, rx);
-        fetch3<DS, kV, ALIGNED>(g, s, i0, nv, c, rs);
-        fetch3<DZ, kV, ALIGNED>(g, z, i0, nv, c, rz);
+        fetch3<DX, kV, ALIGNED>(g, x, i0, nv, c, r.rx);
+        fetch3<DS, kV, ALIGNED>(g, s, i0, nv, c, r.rs);
+        fetch3<DZ, kV, ALIGNED>(g, z, i0, nv, c, r.rz);
+    }
+    __device__ __forceinline__ void operator()(uint32_t i0, uint32_t nv) const {
+        Regs r;
+        load(i0, nv, r);
+        finish(i0, nv, r);
+    }
+    __device__ __forceinline__ void finish(uint32_t i0, uint32_t nv, const Regs& r) const {
+        const Run<typename Storage<DX>::type, kV>& rx = r.rx;
+        const Run<typename Storage<DS>::type, kV>& rs = r.rs;
+        const Run<typename Storage<DZ>::type, kV>& rz = r.rz;
+        Run<typename Storage<DO>::type, kV> ro;
         if constexpr (dtype_exact_in_f32(DX) && dtype_exact_in_f32(DS) && dtype_is_narrow_int(DZ)) {
             float fx[kV];
             decode_floats<DX, kV>(rx, fx);
@@ -121,23 +134,36 @@ struct QuantizeBody {
 // correctly rounded float multiply reproduces "exact product, one rounding".
 template <int DX, int DS, int DZ, int DO, bool ALIGNED>
 struct DequantizeBody {
-    static constexpr int kV = vec_width(dtype_bytes(DX), dtype_bytes(DO), dtype_bytes(DO), kRunCapDequantize);
     static constexpr bool kDiffExact = dtype_exact_in_f32(DX) && dtype_exact_in_f32(DZ) && dtype_exact_in_f32(DS) &&
         DX != DTYPE_FLOAT8_E5M2 && DZ != DTYPE_FLOAT8_E5M2 && DX != DTYPE_FLOAT16 && DZ != DTYPE_FLOAT16 &&
         DX != DTYPE_BFLOAT16 && DZ != DTYPE_BFLOAT16 && DX != DTYPE_FLOAT32 && DZ != DTYPE_FLOAT32 &&
         DO != DTYPE_FLOAT64 && !dtype_is_int(DO);
-    Geo3 g;
-    Op3 x, s, z;
-    void* out;
-    __device__ __forceinline__ void operator()(uint32_t i0, uint32_t nv) const {
+    static constexpr int kV = vec_width(dtype_bytes(DX), dtype_bytes(DO), dtype_bytes(DO));
+    static constexpr int kGroups = 2;
+    struct Regs {
         Run<typename Storage<DX>::type, kV> rx;
         Run<typename Storage<DS>::type, kV> rs;
         Run<typename Storage<DZ>::type, kV> rz;
-        Run<typename Storage<DO>::type, kV> ro;
+    };
+    Geo3 g;
+    Op3 x, s, z;
+    void* out;
+    __device__ __forceinline__ void load(uint32_t i0, uint32_t nv, Regs& r) const {
         const Coord3 c = g.simple ? Coord3{0, 0, 0} : coords_of(g, i0);
-        fetch3<DX, kV, ALIGNED>(g, x, i0, nv, c, rx);
-        fetch3<DS, kV, ALIGNED>(g, s, i0, nv, c, rs);
-        fetch3<DZ, kV, ALIGNED>(g, z, i0, nv, c, rz);
+        fetch3<DX, kV, ALIGNED>(g, x, i0, nv, c, r.rx);
+        fetch3<DS, kV, ALIGNED>(g, s, i0, nv, c, r.rs);
+        fetch3<DZ, kV, ALIGNED>(g, z, i0, nv, c, r.rz);
+    }
+    __device__ __forceinline__ void operator()(uint32_t i0, uint32_t nv) const {
+        Regs r;
+        load(i0, nv, r);
+        finish(i0, nv, r);
+    }
+    __device__ __forceinline__ void finish(uint32_t i0, uint32_t nv, const Regs& r) const {
+        const Run<typename Storage<DX>::type, kV>& rx = r.rx;
+        const Run<typename Storage<DS>::type, kV>& rs = r.rs;
+        const Run<typename Storage<DZ>::type, kV>& rz = r.rz;
+        Run<typename Storage<DO>::type, kV> ro;
         if constexpr (kDiffExact && (DX == DTYPE_INT8 || DX == DTYPE_UINT8) && kV % 4 == 0) {
             // one scale and one zero point for the whole run: the byte is placed in the low mantissa
             // byte of 2^23 and (2^23 + offset + z) is subtracted in one exact step
@@ -195,6 +221,7 @@ struct DequantizeBody {
 template <bool QUANTIZE>
 struct QdqGenericBody {
     static constexpr int kV = 1;
+    static constexpr int kGroups = 0;
     Geometry g;
     Operand x, s, z;
     void* out;

@@ -57,14 +57,23 @@ __device__ __forceinline__ typename Storage<DO>::type unary_elem(typename Storag
 template <int DX, int DO, int OP, bool ALIGNED>
 struct UnaryBody {
     static constexpr int kV = vec_width(dtype_bytes(DX), dtype_bytes(DO), dtype_bytes(DO));
+    static constexpr int kGroups = 0;
+    struct Regs { Run<typename Storage<DX>::type, kV> in; };
     Geo3 g;
     Op3 x;
     void* out;
     const double* lut;
+    __device__ __forceinline__ void load(uint32_t i0, uint32_t nv, Regs& r) const {
+        fetch3<DX, kV, ALIGNED>(g, x, i0, nv, Coord3{0, 0, 0}, r.in);        // unary inputs are always dense
+    }
     __device__ __forceinline__ void operator()(uint32_t i0, uint32_t nv) const {
-        Run<typename Storage<DX>::type, kV> in;
+        Regs r;
+        load(i0, nv, r);
+        finish(i0, nv, r);
+    }
+    __device__ __forceinline__ void finish(uint32_t i0, uint32_t nv, const Regs& r) const {
+        const Run<typename Storage<DX>::type, kV>& in = r.in;
         Run<typename Storage<DO>::type, kV> res;
-        fetch3<DX, kV, ALIGNED>(g, x, i0, nv, Coord3{0, 0, 0}, in);          // unary inputs are always dense
         constexpr bool float_lane = OP != kCos && dtype_exact_in_f32(DX) && !dtype_is_int(DX) &&
                                     !dtype_is_int(DO) && DO != DTYPE_FLOAT64;
         constexpr bool int_lane = OP != kCos && dtype_is_narrow_int(DX) && dtype_is_narrow_int(DO);
@@ -91,6 +100,7 @@ struct UnaryBody {
 template <int OP>
 struct UnaryGenericBody {
     static constexpr int kV = 1;
+    static constexpr int kGroups = 0;
     const void* x;
     void* out;
     int dx, dout;
