@@ -460,6 +460,17 @@ def other_ops(lib, stream, hbm_peak):
         ms = timed(lambda: lib.gemm_forward(a.handle, b.handle, bias.handle, y.handle, 1.0, 1.0, 0, 1))
         out[f"gemm_8192_{label}"] = {"TFLOPs": round(flops / 1e12 / (ms / 1e3), 1), "ms": round(ms, 4),
                                      "tensor_core_path": lib.tops_tensor_core_launches() > before}
+        if label == "fp8_e4m3_in_bf16_out":
+            # the DQ -> Gemm -> Q chain of config 4 in one call: per-tensor operand scales, e4m3 result
+            sa = DeviceArray.from_numpy(np.array([1 / 16], np.float32), "float32")
+            sy = DeviceArray.from_numpy(np.array([1 / 64], np.float32), "float32")
+            yq = DeviceArray.empty((m, m), "float8_e4m3")
+            before = lib.tops_tensor_core_launches()
+            ms = timed(lambda: lib.tops_gemm_qdq_forward(a.handle, sa.handle, b.handle, sa.handle, bias.handle, sy.handle, yq.handle,
+                                                         1.0, 1.0, 0, 1))
+            out["gemm_8192_fp8_e4m3_dq_gemm_q_fused"] = {"TFLOPs": round(flops / 1e12 / (ms / 1e3), 1), "ms": round(ms, 4),
+                                                         "tensor_core_path": lib.tops_tensor_core_launches() > before}
+            del yq
         del a, b, y
     del a32, b32
 
@@ -473,6 +484,13 @@ def other_ops(lib, stream, hbm_peak):
     out["conv_256x256x56x56_k3_bf16"] = {"TFLOPs": round(2.0 * 256 * 56 * 56 * 256 * 2304 / 1e12 / (ms / 1e3), 1), "ms": round(ms, 4),
                                          "tensor_core_path": lib.tops_tensor_core_launches() > before,
                                          "includes": "NCHW -> padded NHWC copy of X and tap-major copy of W"}
+    # the same convolution with int8 weight codes and per-output-channel scales (DequantizeLinear -> Conv in one call)
+    wq = DeviceArray.from_numpy(rng.integers(-127, 128, (256, 256, 3, 3)).astype(np.int8), "int8")
+    ws = DeviceArray.from_numpy(rng.uniform(0.005, 0.02, 256).astype(np.float32), "float32")
+    before = lib.tops_tensor_core_launches()
+    ms = timed(lambda: lib.tops_conv2d_dqw_forward(cx.handle, wq.handle, ws.handle, None, cy.handle, ctypes.byref(cprm)), iters=3)
+    out["conv_256x256x56x56_k3_bf16_int8_qdq_weights"] = {"TFLOPs": round(2.0 * 256 * 56 * 56 * 256 * 2304 / 1e12 / (ms / 1e3), 1),
+                                                          "ms": round(ms, 4), "tensor_core_path": lib.tops_tensor_core_launches() > before}
     return out
 
 

@@ -206,6 +206,27 @@ void tops_dequantize_linear_axis_forward(const Tensor* X, const Tensor* Scale, c
 void   tops_conv2d_forward_noalloc(const Tensor* X, const Tensor* W, const Tensor* B, Tensor* Y, ConvParams* params);
 size_t tops_conv2d_noalloc_limits(size_t* input_bytes, size_t* filter_bytes);
 
+/* Fused forms of the operator sequences of quantised graphs (no single counterpart in the
+   reference: each replaces a chain of its operators, nn/Operators.py:427-473 QuantizeLinear /
+   DequantizeLinear followed by :613-669 Gemm or :475-548 Conv).  Scales are float32 tensors in
+   device memory.  Return TOPS_OK or the recorded error; a case the tensor-core kernels do not
+   cover is refused with TOPS_ERR_UNSUPPORTED (output zero-filled) and the caller runs the unfused
+   chain instead.
+
+   tops_gemm_qdq_forward:  Y = [QuantizeLinear]( alpha * DQ(A, a_scale) * DQ(B, b_scale)^T + beta * C )
+     A, B fp8 codes (e4m3 / e5m2, zero point 0), one scale each; transA = 0, transB = 1.  With
+     y_scale (one value) Y is an 8-bit type and receives rint(y / y_scale) stored the way
+     quantize_linear_forward stores it; without it Y is float32 / bfloat16 / float16.
+
+   tops_conv2d_dqw_forward:  Y = Conv(X, DQ(Wq, w_scale), B)
+     Wq int8 codes with zero point 0 and one float32 scale per output channel; X float16 or
+     bfloat16; group 1, stride 1. */
+int tops_gemm_qdq_forward(const Tensor* A, const Tensor* a_scale, const Tensor* B, const Tensor* b_scale,
+                          const Tensor* C, const Tensor* y_scale, Tensor* Y,
+                          float alpha, float beta, int transA, int transB);
+int tops_conv2d_dqw_forward(const Tensor* X, const Tensor* Wq, const Tensor* w_scale, const Tensor* B, Tensor* Y,
+                            ConvParams* params);
+
 /* Device-side exhaustive codec self-check: encodes every float32 bit pattern with the fast
    (hardware-convert) encoder and with the bit-level restatement of the reference encoder and
    returns the number of disagreements (NaN inputs excluded), or -1 on error. */

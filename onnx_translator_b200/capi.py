@@ -118,6 +118,8 @@ SIGNATURES = {
     "tops_dequantize_linear_axis_forward": (None, [_P, _P, _P, _P, _I]),
     "tops_conv2d_forward_noalloc": (None, [_P, _P, _P, _P, ctypes.POINTER(CConvParams)]),
     "tops_conv2d_noalloc_limits": (_SZ, [ctypes.POINTER(_SZ), ctypes.POINTER(_SZ)]),
+    "tops_gemm_qdq_forward": (_I, [_P, _P, _P, _P, _P, _P, _P, ctypes.c_float, ctypes.c_float, _I, _I]),
+    "tops_conv2d_dqw_forward": (_I, [_P, _P, _P, _P, _P, ctypes.POINTER(CConvParams)]),
     "tops_selftest_encoder": (ctypes.c_longlong, [_I]),
     "tops_tensor_core_launches": (ctypes.c_longlong, []),
     "tops_selftest_cos": (ctypes.c_longlong, []),

@@ -26,9 +26,12 @@ struct ConvTcPlan {
     int es, Hp, Wp, taps;
     size_t rows, xp_bytes, wt_bytes;
 };
-ConvTcPlan conv_tc_plan(const Tensor* X, const Tensor* W, const Tensor* Y, const ConvGeom& c);
+// `w_scale` (float32, one value per output channel, device memory): W holds int8 codes of a
+// DequantizeLinear with zero point 0; the codes are widened exactly to X's 16-bit type while they
+// are reordered and the scales are applied to the accumulator.
+ConvTcPlan conv_tc_plan(const Tensor* X, const Tensor* W, const Tensor* Y, const ConvGeom& c, bool int8_weights = false);
 bool conv_tc_run(const Tensor* X, const Tensor* W, const Tensor* B, Tensor* Y, const ConvGeom& c, const ConvTcPlan& plan,
-                 void* xp, void* wt, int* status);
+                 void* xp, void* wt, int* status, const float* w_scale = nullptr);
 
 // Fills a ConvGeom from the ABI arguments; false (with the error recorded) when they are inconsistent.
 bool conv_geometry(const char* name, const Tensor* X, const Tensor* W, const Tensor* B, Tensor* Y, const ConvParams* params, ConvGeom* c);

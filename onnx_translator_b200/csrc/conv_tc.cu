@@ -79,13 +79,26 @@ __global__ void __launch_bounds__(256) filters_to_tap_major(const E* __restrict_
     }
 }
 
+// int8 codes [M][C][KH*KW] -> [KH*KW][M][C] as float16 / bfloat16 values (|code| <= 128 is exact in both)
+template <bool BF16>
+__global__ void __launch_bounds__(256) int8_filters_to_tap_major(const int8_t* __restrict__ w, uint16_t* __restrict__ wt, int M, int C, int taps) {
+    const size_t total = (size_t)M * C * taps;
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
+        const int c = (int)(i % C);
+        const size_t r = i / C;
+        const int m = (int)(r % M), t = (int)(r / M);
+        const float v = (float)w[((size_t)m * C + c) * taps + t];
+        wt[i] = BF16 ? encode_bf16(v) : encode_f16(v);
+    }
+}
+
 static bool fp8_dtype(int dt) { return dt == DTYPE_FLOAT8_E4M3 || dt == DTYPE_FLOAT8_E5M2; }
 
-ConvTcPlan conv_tc_plan(const Tensor* X, const Tensor* W, const Tensor* Y, const ConvGeom& c) {
+ConvTcPlan conv_tc_plan(const Tensor* X, const Tensor* W, const Tensor* Y, const ConvGeom& c, bool int8_weights) {
     ConvTcPlan plan{};
     const int dx = (int)X->dtype, dw = (int)W->dtype, dy = (int)Y->dtype;
-    plan.fp8 = fp8_dtype(dx) && fp8_dtype(dw);
-    const bool half16 = dx == dw && (dx == DTYPE_FLOAT16 || dx == DTYPE_BFLOAT16);
+    plan.fp8 = !int8_weights && fp8_dtype(dx) && fp8_dtype(dw);
+    const bool half16 = (dx == DTYPE_FLOAT16 || dx == DTYPE_BFLOAT16) && (int8_weights ? dw == DTYPE_INT8 : dx == dw);
     if (!plan.fp8 && !half16) return plan;
     if (dy != DTYPE_FLOAT32 && dy != DTYPE_BFLOAT16 && dy != DTYPE_FLOAT16) return plan;
     if (c.G != 1 || c.sh != 1 || c.sw != 1 || c.dh < 1 || c.dw < 1 || c.pt < 0 || c.pl < 0) return plan;
@@ -103,7 +116,7 @@ ConvTcPlan conv_tc_plan(const Tensor* X, const Tensor* W, const Tensor* Y, const
 }
 
 bool conv_tc_run(const Tensor* X, const Tensor* W, const Tensor* B, Tensor* Y, const ConvGeom& c, const ConvTcPlan& plan,
-                 void* xp, void* wt, int* status) {
+                 void* xp, void* wt, int* status, const float* w_scale) {
     DeviceState* st = acquire_device();
     if (!st) return false;
     cudaStream_t s = current_stream();
@@ -116,7 +129,12 @@ bool conv_tc_run(const Tensor* X, const Tensor* W, const Tensor* B, Tensor* Y, c
     const int wgrid = grid_for((size_t)c.M * c.C * taps, 256, st->sm_count, 4);
     if (es == 2) {
         nchw_to_padded_nhwc<uint16_t><<<tgrid, 256, 0, s>>>((const uint16_t*)X->data, (uint16_t*)xp, c.C, c.H, c.W, Hp, Wp, c.pt, c.pl);
-        filters_to_tap_major<uint16_t><<<wgrid, 256, 0, s>>>((const uint16_t*)W->data, (uint16_t*)wt, c.M, c.C, taps);
+        if (dw == DTYPE_INT8 && dx == DTYPE_BFLOAT16)
+            int8_filters_to_tap_major<true><<<wgrid, 256, 0, s>>>((const int8_t*)W->data, (uint16_t*)wt, c.M, c.C, taps);
+        else if (dw == DTYPE_INT8)
+            int8_filters_to_tap_major<false><<<wgrid, 256, 0, s>>>((const int8_t*)W->data, (uint16_t*)wt, c.M, c.C, taps);
+        else
+            filters_to_tap_major<uint16_t><<<wgrid, 256, 0, s>>>((const uint16_t*)W->data, (uint16_t*)wt, c.M, c.C, taps);
     } else {
         nchw_to_padded_nhwc<uint8_t><<<tgrid, 256, 0, s>>>((const uint8_t*)X->data, (uint8_t*)xp, c.C, c.H, c.W, Hp, Wp, c.pt, c.pl);
         filters_to_tap_major<uint8_t><<<wgrid, 256, 0, s>>>((const uint8_t*)W->data, (uint8_t*)wt, c.M, c.C, taps);
@@ -157,7 +175,8 @@ bool conv_tc_run(const Tensor* X, const Tensor* W, const Tensor* B, Tensor* Y, c
     p.cv.images = c.N; p.cv.OH = c.OH; p.cv.OW = c.OW; p.cv.OC = c.M;
     p.cv.KW = c.KW; p.cv.dil_h = c.dh; p.cv.dil_w = c.dw;
     const uint32_t fa = fp8 ? (dx == DTYPE_FLOAT8_E5M2 ? 1u : 0u) : (dx == DTYPE_BFLOAT16 ? 1u : 0u);
-    const uint32_t fb = fp8 ? (dw == DTYPE_FLOAT8_E5M2 ? 1u : 0u) : (dw == DTYPE_BFLOAT16 ? 1u : 0u);
+    const uint32_t fb = fp8 ? (dw == DTYPE_FLOAT8_E5M2 ? 1u : 0u) : (dw == DTYPE_INT8 ? fa : (dw == DTYPE_BFLOAT16 ? 1u : 0u));
+    if (w_scale) { p.fs.b_scale = w_scale; p.fs.b_per_column = 1; }
     const uint32_t idesc = umma::instr_desc(fa, fb, kBM, kBN);
     const int tiles = p.tiles_m * p.tiles_n;
     const int grid = tiles < st->sm_count ? tiles : st->sm_count;

@@ -35,6 +35,17 @@ __host__ __device__ inline long long bias_index(const BiasView& b, int m, int n)
     }
 }
 
+// Scales of a fused DequantizeLinear -> Gemm / Conv -> QuantizeLinear sequence, all float32 in device
+// memory so that nothing is read back to the host: the operand scales multiply the accumulator, the
+// result scale divides it before rounding to an integer value and encoding (the reference's
+// QuantizeLinear: rint(y / s), then the store of the output type).
+struct EpilogueScales {
+    const float* a_scale = nullptr;    // one value
+    const float* b_scale = nullptr;    // one value, or one per output column
+    int b_per_column = 0;
+    const float* y_scale = nullptr;    // one value; only with 8-bit output types
+};
+
 BiasView make_bias_view(const Tensor* C, int M, int N);
 
 // Exact double-accumulating path (any dtypes).
@@ -43,7 +54,8 @@ bool gemm_exact(const Tensor* A, const Tensor* B, Tensor* Y, const GemmShape& g,
 
 // Tensor-core path.  Returns false when the case is outside what it covers (caller falls back
 // to the exact kernel, which is still a GPU kernel of this library).
+// With `fused` (operand / result scales of a DQ -> Gemm -> Q sequence) 8-bit output types are accepted too.
 bool gemm_tensor_core(const Tensor* A, const Tensor* B, Tensor* Y, const GemmShape& g, const BiasView& bias,
-                      float alpha, float beta);
+                      float alpha, float beta, const EpilogueScales* fused = nullptr);
 
 }  // namespace tops

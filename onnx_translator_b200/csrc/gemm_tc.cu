@@ -136,17 +136,18 @@ static bool gemm_split_f32(const Tensor* A, const Tensor* B, Tensor* Y, const Ge
 }
 
 bool gemm_tensor_core(const Tensor* A, const Tensor* B, Tensor* Y, const GemmShape& g, const BiasView& bias,
-                      float alpha, float beta) {
+                      float alpha, float beta, const EpilogueScales* fused) {
     const int da = (int)A->dtype, db = (int)B->dtype, dy = (int)Y->dtype;
     const bool fp8 = is_fp8(da) && is_fp8(db);
     const bool half16 = (da == db) && (da == DTYPE_FLOAT16 || da == DTYPE_BFLOAT16);
     // large float32 problems: three-way bfloat16 split (small ones keep the exact, bit-identical kernel)
-    if (da == DTYPE_FLOAT32 && db == DTYPE_FLOAT32 && (dy == DTYPE_FLOAT32 || dy == DTYPE_BFLOAT16 || dy == DTYPE_FLOAT16) &&
+    if (!fused && da == DTYPE_FLOAT32 && db == DTYPE_FLOAT32 && (dy == DTYPE_FLOAT32 || dy == DTYPE_BFLOAT16 || dy == DTYPE_FLOAT16) &&
         g.transA == 0 && g.transB == 1 && g.K % 8 == 0 && g.lda == g.K && g.ldb == g.K && !getenv("TOPS_DISABLE_TC") &&
         (((uintptr_t)A->data | (uintptr_t)B->data) & 15) == 0 && (double)g.M * g.N * g.K >= 134217728.0)
         return gemm_split_f32(A, B, Y, g, bias, alpha, beta);
     if (!fp8 && !half16) return false;
-    if (dy != DTYPE_FLOAT32 && dy != DTYPE_BFLOAT16 && dy != DTYPE_FLOAT16) return false;
+    const bool eight_bit_out = fused && (dy == DTYPE_FLOAT8_E4M3 || dy == DTYPE_FLOAT8_E5M2 || dy == DTYPE_INT8 || dy == DTYPE_UINT8);
+    if (dy != DTYPE_FLOAT32 && dy != DTYPE_BFLOAT16 && dy != DTYPE_FLOAT16 && !eight_bit_out) return false;
     if (g.transA != 0 || g.transB != 1) return false;                 // both operands K-major
     const int eb = fp8 ? 1 : 2;
     if (((size_t)g.K * eb) % 16 != 0 || ((uintptr_t)A->data & 15) || ((uintptr_t)B->data & 15)) return false;
@@ -177,6 +178,7 @@ bool gemm_tensor_core(const Tensor* A, const Tensor* B, Tensor* Y, const GemmSha
     p.bias = bias;
     p.status = device_status_word();
     p.vec_store = (((uintptr_t)Y->data & 15) == 0) && (((size_t)g.N * dtype_bytes(dy)) % 16 == 0);
+    if (fused) p.fs = *fused;
 
     const uint32_t fa = fp8 ? (da == DTYPE_FLOAT8_E5M2 ? 1u : 0u) : (da == DTYPE_BFLOAT16 ? 1u : 0u);
     const uint32_t fb = fp8 ? (db == DTYPE_FLOAT8_E5M2 ? 1u : 0u) : (db == DTYPE_BFLOAT16 ? 1u : 0u);

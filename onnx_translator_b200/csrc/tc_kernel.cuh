@@ -15,7 +15,7 @@ constexpr int kStageBytes = kTileABytes + kTileBBytes;
 constexpr int kTcThreads = 192;
 constexpr int kStageRowWords = 36;                 // 32 words of payload + 4 of padding: conflict-free 16-byte accesses
 constexpr size_t kTcSmemBytes = (size_t)kStages * kStageBytes + 1024 /*alignment slack*/ + 128 /*barriers*/ + 4 * kBN * 4 /*bias*/ +
-                                4 * 32 * kStageRowWords * 4 /*output staging*/;
+                                4 * 32 * kStageRowWords * 4 /*output staging*/ + 4 * kBN * 4 /*column scales*/;
 
 // Convolution as shifted GEMMs over a zero-padded channels-last copy of the input: row q of the
 // GEMM is the padded position (n, oh, ow) = (q / plane, (q % plane) / Wp, q % Wp); filter tap
@@ -40,6 +40,7 @@ struct TcParams {
     int* status;           // device-visible word, set non-zero when a wait gave up
     int vec_store;         // Y base and row pitch are 16-byte aligned
     ConvView cv;           // convolution mode only
+    EpilogueScales fs;
 };
 
 __device__ __forceinline__ void tile_coords(int tile, int tiles_m, int tiles_n, int& tm, int& tn) {
@@ -71,6 +72,7 @@ tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUt
     volatile int* abort_flag = (volatile int*)(tmem_slot + 1);
     float* bias_stage = (float*)(bars + 16);           // 4 warps x kBN floats
     uint32_t* out_stage = (uint32_t*)(bias_stage + 4 * kBN);   // 4 warps x 32 rows x kStageRowWords
+    float* scale_stage = (float*)(out_stage + 4 * 32 * kStageRowWords);   // 4 warps x kBN floats
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int total_tiles = p.tiles_m * p.tiles_n;
@@ -149,6 +151,11 @@ tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUt
         uint32_t local = 0;
         float* my_bias = bias_stage + quarter * kBN;                 // this warp's private copy: no cross-warp sync
         uint32_t* my_stage = out_stage + quarter * 32 * kStageRowWords;
+        float* my_scale = scale_stage + quarter * kBN;
+        float alpha = p.alpha;
+        if (p.fs.a_scale) alpha = __fmul_rn(alpha, __ldg(p.fs.a_scale));
+        if (p.fs.b_scale && !p.fs.b_per_column) alpha = __fmul_rn(alpha, __ldg(p.fs.b_scale));
+        const float y_scale = p.fs.y_scale ? __ldg(p.fs.y_scale) : 0.0f;
         for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x, local++) {
             const uint32_t buf = local & 1u, use = (local >> 1) & 1u;
             int tm, tn;
@@ -169,6 +176,15 @@ tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUt
             } else if (p.bias.mode == kBiasPerRow && m < p.M) {
                 row_bias = __fmul_rn(p.beta, (float)load_f64_rt(p.bias.ptr, p.bias.dtype, (size_t)m));
             }
+            if (p.fs.b_per_column) {
+                __syncwarp();
+                #pragma unroll
+                for (int j = 0; j < kBN / 32; j++) {
+                    const int n = tn * kBN + j * 32 + lane;
+                    my_scale[j * 32 + lane] = n < p.N ? __fmul_rn(alpha, __ldg(p.fs.b_scale + n)) : 0.0f;
+                }
+                __syncwarp();
+            }
             if (!umma::mbar_wait(&acc_full[buf], use, abort_flag)) break;
             umma::fence_after_sync();
             const uint32_t t_row = tmem_base + ((uint32_t)(quarter * 32) << 16) + buf * kBN;
@@ -181,7 +197,10 @@ tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUt
                 if (n0 < p.N) {                                    // warp-uniform
                     float v[32];
                     #pragma unroll
-                    for (int j = 0; j < 32; j++) v[j] = __fadd_rn(__fmul_rn(p.alpha, __uint_as_float(r[j])), row_bias);
+                    for (int j = 0; j < 32; j++) {
+                        const float scale = p.fs.b_per_column ? my_scale[c * 32 + j] : alpha;
+                        v[j] = __fadd_rn(__fmul_rn(scale, __uint_as_float(r[j])), row_bias);
+                    }
                     if (p.bias.mode == kBiasPerColumn) {
                         #pragma unroll
                         for (int j = 0; j < 32; j += 4) {
@@ -244,6 +263,24 @@ tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUt
                         for (int j = 0; j < 32; j += 8)
                             *(uint4*)(my_rows + (j >> 1)) = make_uint4(encode_bf16x2(v[j], v[j + 1]), encode_bf16x2(v[j + 2], v[j + 3]),
                                                                         encode_bf16x2(v[j + 4], v[j + 5]), encode_bf16x2(v[j + 6], v[j + 7]));
+                    } else if (dtype_bytes(p.dy) == 1) {
+                        // 8-bit outputs: QuantizeLinear when a result scale was given, a plain store otherwise
+                        #pragma unroll
+                        for (int j = 0; j < 32; j += 4) {
+                            uint32_t word = 0;
+                            #pragma unroll
+                            for (int e = 0; e < 4; e++) {
+                                float q = v[j + e];
+                                if (p.fs.y_scale) q = y_scale != 0.0f ? rintf(__fdiv_rn(q, y_scale)) : 0.0f;
+                                uint32_t code;
+                                if (p.dy == DTYPE_FLOAT8_E4M3) code = encode_e4m3(q);
+                                else if (p.dy == DTYPE_FLOAT8_E5M2) code = encode_e5m2(q);
+                                else if (p.dy == DTYPE_INT8) code = (uint8_t)from_f64<DTYPE_INT8>((double)q);
+                                else code = from_f64<DTYPE_UINT8>((double)q);
+                                word |= code << (8 * e);
+                            }
+                            my_rows[j >> 2] = word;
+                        }
                     } else {
                         #pragma unroll
                         for (int j = 0; j < 32; j += 8)
@@ -251,7 +288,7 @@ tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUt
                                                                         encode_f16x2(v[j + 4], v[j + 5]), encode_f16x2(v[j + 6], v[j + 7]));
                     }
                     __syncwarp();
-                    const int esize = p.dy == DTYPE_FLOAT32 ? 4 : 2;
+                    const int esize = dtype_bytes(p.dy);
                     const int lanes_per_row = esize * 2;                 // 16-byte pieces per 32-element row
                     const int rows_per_pass = 32 / lanes_per_row;
                     const int piece = lane % lanes_per_row;              // which 16 bytes of the row
@@ -270,7 +307,8 @@ tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUt
                             const uint32_t w[4] = {val.x, val.y, val.z, val.w};
                             for (int e = 0; e < elems_per_piece && n + e < p.N; e++) {
                                 if (esize == 4) ((uint32_t*)dst)[e] = w[e];
-                                else ((uint16_t*)dst)[e] = (uint16_t)(w[e >> 1] >> ((e & 1) * 16));
+                                else if (esize == 2) ((uint16_t*)dst)[e] = (uint16_t)(w[e >> 1] >> ((e & 1) * 16));
+                                else ((uint8_t*)dst)[e] = (uint8_t)(w[e >> 2] >> ((e & 3) * 8));
                             }
                         }
                     }

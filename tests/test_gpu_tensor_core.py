@@ -175,3 +175,81 @@ def test_conv_strided_or_grouped_falls_back_to_the_exact_kernel(port):
     got = gpu.conv2d(*args)
     assert _tc_count() == before
     assert np.array_equal(got, port.conv2d(*args))
+
+
+# ---- fused DequantizeLinear -> Gemm / Conv -> QuantizeLinear ------------------------------------------------------
+@pytest.mark.parametrize("case", [(256, 512, 1024, "float32", "col"), (130, 272, 528, "bfloat16", None), (512, 1024, 2048, "float32", "col")],
+                         ids=lambda c: f"{c[0]}x{c[1]}x{c[2]}-{c[3]}")
+def test_fused_fp8_gemm_with_operand_scales(port, case):
+    """DQ(A), DQ(B) -> Gemm in one call against the same chain evaluated by the oracle in float64."""
+    from onnx_translator_b200 import fused
+    m, n, k, out_dt, bias_kind = case
+    rng = np.random.default_rng(m + n + k)
+    sa, sb = np.float32(0.02 / 64), np.float32(0.02 / 48)
+    a = from_f64(rng.normal(0, 64, (m, k)), "float8_e4m3")
+    b = from_f64(rng.normal(0, 48, (n, k)), "float8_e4m3")
+    bias = rng.normal(0, 1, n).astype(np.float32) if bias_kind else None
+    zero = np.zeros(1, np.uint8)
+    a_dq = port.dequantize(a, "float8_e4m3", np.array([sa]), "float32", zero, "float8_e4m3", "float32").astype(np.float64)
+    b_dq = port.dequantize(b, "float8_e4m3", np.array([sb]), "float32", zero, "float8_e4m3", "float32").astype(np.float64)
+    want = a_dq @ b_dq.T + (0 if bias is None else bias.astype(np.float64))
+    s_mag = np.abs(a_dq) @ np.abs(b_dq).T + (0 if bias is None else np.abs(bias.astype(np.float64)))
+    before = _tc_count()
+    got = fused.gemm_qdq(a, sa, b, sb, None if bias is None else bias.reshape(1, n), out_dtype=out_dt).numpy()
+    assert _tc_count() == before + 1
+    _gate(to_f64(got, out_dt), want, s_mag, out_dt, "fused fp8 gemm")
+
+
+def test_fused_fp8_gemm_quantised_result(port):
+    """DQ -> Gemm -> Q(e4m3): every code lies between the codes the oracle's QuantizeLinear gives
+    for the float64 result minus and plus the accumulation tolerance."""
+    from onnx_translator_b200 import fused
+    m, n, k = 384, 512, 1024
+    rng = np.random.default_rng(5)
+    sa, sb, sy = np.float32(1 / 1024), np.float32(1 / 2048), np.float32(1 / 16)
+    a = from_f64(rng.normal(0, 40, (m, k)), "float8_e4m3")
+    b = from_f64(rng.normal(0, 90, (n, k)), "float8_e4m3")
+    bias = rng.normal(0, 1, n).astype(np.float32)
+    zero = np.zeros(1, np.uint8)
+    a_dq = port.dequantize(a, "float8_e4m3", np.array([sa]), "float32", zero, "float8_e4m3", "float32").astype(np.float64)
+    b_dq = port.dequantize(b, "float8_e4m3", np.array([sb]), "float32", zero, "float8_e4m3", "float32").astype(np.float64)
+    y = a_dq @ b_dq.T + bias.astype(np.float64)
+    tol = 1e-6 * (np.abs(a_dq) @ np.abs(b_dq).T + np.abs(bias)) + 2.0 ** -23 * np.abs(y)
+    lo = np.nextafter((y - tol).astype(np.float32), np.float32(-np.inf))
+    hi = np.nextafter((y + tol).astype(np.float32), np.float32(np.inf))
+    q = lambda v: to_f64(port.quantize(v, "float32", np.array([sy]), "float32", zero, "float8_e4m3", "float8_e4m3"), "float8_e4m3")
+    q_lo, q_hi = q(lo), q(hi)
+    got = to_f64(fused.gemm_qdq(a, sa, b, sb, bias.reshape(1, n), y_scale=sy, out_dtype="float8_e4m3").numpy(), "float8_e4m3")
+    assert np.all((got >= q_lo) & (got <= q_hi)), int(((got < q_lo) | (got > q_hi)).sum())
+    assert np.mean(got == q(y.astype(np.float32))) > 0.999
+    assert np.unique(got).size > 20                                   # a real spread of codes, not a saturated output
+
+
+@pytest.mark.parametrize("x_dt", ["bfloat16", "float16"])
+def test_fused_conv_with_int8_weights(port, x_dt):
+    """DQ(W per output channel) -> Conv in one call against the chain in float64."""
+    from onnx_translator_b200 import fused
+    rng = np.random.default_rng(91)
+    n, c, h, wd, m = 4, 64, 28, 28, 96
+    x = from_f64(rng.normal(0, 1, (n, c, h, wd)), x_dt)
+    wq = rng.integers(-127, 128, (m, c, 3, 3)).astype(np.int8)
+    ws = rng.uniform(0.005, 0.02, m).astype(np.float32)
+    b = rng.normal(0, 1, m).astype(np.float32)
+    full_scale = np.ascontiguousarray(np.broadcast_to(ws.reshape(m, 1, 1, 1), wq.shape))
+    w_dq = port.dequantize(wq, "int8", full_scale, "float32", np.zeros(wq.shape, np.int8), "int8", "float32").astype(np.float64)
+    want, s_mag = _conv_f64(to_f64(x, x_dt), w_dq, b.astype(np.float64), (1, 1, 1, 1), (1, 1), (h, wd))
+    before = _tc_count()
+    got = fused.conv2d_dqw(x, wq, ws, b, out_dtype="float32", pads=(1, 1, 1, 1), x_dtype=x_dt).numpy().astype(np.float64)
+    assert _tc_count() == before + 1
+    _gate(got, want, s_mag, "float32", "fused conv with int8 weights")
+
+
+def test_fused_entry_points_refuse_what_they_do_not_cover():
+    from onnx_translator_b200 import capi, fused
+    rng = np.random.default_rng(3)
+    a = from_f64(rng.normal(0, 1, (64, 64)), "bfloat16")
+    with pytest.raises(capi.TensorOpsError):
+        fused.gemm_qdq(a, 1.0, a, 1.0, a_dtype="bfloat16", b_dtype="bfloat16")          # not fp8
+    x = rng.normal(0, 1, (1, 16, 8, 8)).astype(np.float32)
+    with pytest.raises(capi.TensorOpsError):
+        fused.conv2d_dqw(x, np.ones((16, 16, 3, 3), np.int8), np.ones(16, np.float32), x_dtype="float32")   # float32 activations
