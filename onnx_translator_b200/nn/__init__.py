@@ -169,3 +169,6 @@ def synchronize() -> None:
     lib = Ops._get_lib()
     lib.tops_sync()
     capi.check(lib)
+
+
+from .graph import Graph, qdq_resnet50, small_cnn  # noqa: E402  (the graph runner builds on the classes above)

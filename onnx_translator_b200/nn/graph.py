@@ -1,0 +1,234 @@
+"""Resident graph runner and the two graph-shaped benchmark workloads.
+
+``Graph`` mirrors the reference's graph object (nn/__init__.py:346-456: a list of operator nodes
+with named input and output edges, executed in list order) with the three things a resident runner
+needs and the reference lacks: initializers (weights, scales) are fed to the nodes and uploaded
+once, every edge stays on the device between nodes, and ``forward`` returns the graph outputs.
+
+The builders construct the graphs from operator constructor calls -- the same objects an ONNX import
+would create -- so no model file or ``onnx`` package is involved:
+
+* ``small_cnn``      the small CNN of the first benchmark configuration;
+* ``qdq_resnet50``   a ResNet-50-shaped network (stem 7x7/2, bottleneck stages [3, 4, 6, 3], widths
+                     64/128/256/512 with 4x expansion) in which every convolution reads its input
+                     through QuantizeLinear -> DequantizeLinear (int8, per tensor) and its weights
+                     through DequantizeLinear (int8, per output channel).  Weights are random
+                     (seeded); only the well-known layer shapes are taken from the architecture.
+"""
+from __future__ import annotations
+
+from collections import OrderedDict
+from typing import Dict, List, Optional, Sequence
+
+import numpy as np
+
+
+class Graph:
+    """Operator nodes with named edges, executed in list order (which must be topological)."""
+
+    def __init__(self, ops, input_name, output_name=None, model_name=None, initializers: Optional[Dict[str, object]] = None):
+        self.input_name = input_name if isinstance(input_name, list) else [input_name]
+        self.ops = OrderedDict()
+        self.model_name = model_name
+        self.initializers = dict(initializers or {})
+        self._resident = False
+        counts: Dict[str, int] = {}
+        produced = set(self.input_name) | set(self.initializers)
+        self.consumers: Dict[str, int] = {}
+        for op in ops:
+            kind = type(op).__name__
+            counts[kind] = counts.get(kind, -1) + 1
+            if not getattr(op, "name", None):
+                op.name = f"{kind}.{counts[kind]}"
+            if op.name in self.ops:
+                raise ValueError(f"node name {op.name} repeats")
+            for edge in op.inputs:
+                if edge and edge not in produced:
+                    raise ValueError(f"{op.name} reads edge {edge!r} before any node produces it")
+                if edge:
+                    self.consumers[edge] = self.consumers.get(edge, 0) + 1
+            for edge in op.outputs:
+                if edge in produced:
+                    raise ValueError(f"output edge name {edge} repeats")
+                produced.add(edge)
+            self.ops[op.name] = op
+        if output_name is None or output_name == [None]:
+            # edges nobody reads are the outputs (what the reference infers)
+            output_name = [e for op in self.ops.values() for e in op.outputs if self.consumers.get(e, 0) == 0]
+        self.output_name = output_name if isinstance(output_name, list) else [output_name]
+        for edge in self.output_name:
+            if edge not in produced:
+                raise ValueError(f"graph output {edge!r} is not produced by any node")
+
+    def make_resident(self) -> None:
+        """Upload every initializer once; later calls of ``forward`` reuse the device copies."""
+        if not self._resident:
+            for t in self.initializers.values():
+                t.to_device()
+            self._resident = True
+
+    def forward(self, *inputs):
+        """Runs the graph on device-resident edges and returns the output tensor (or a tuple of
+        them).  Intermediate edges are dropped as soon as their last consumer has run."""
+        if len(inputs) != len(self.input_name):
+            raise ValueError(f"graph takes {len(self.input_name)} inputs, got {len(inputs)}")
+        self.make_resident()
+        edges = dict(self.initializers)
+        for name, value in zip(self.input_name, inputs):
+            edges[name] = value.to_device() if hasattr(value, "to_device") else value
+        left = dict(self.consumers)
+        keep = set(self.output_name) | set(self.initializers)
+        for op in self.ops.values():
+            args = [edges[e] if e else None for e in op.inputs]
+            while args and args[-1] is None:
+                args.pop()
+            result = op.forward(*args)["tensor"]
+            if len(op.outputs) == 1:
+                edges[op.outputs[0]] = result
+            else:
+                for edge, value in zip(op.outputs, result):
+                    edges[edge] = value
+            for e in op.inputs:
+                if e and e not in keep:
+                    left[e] -= 1
+                    if left[e] == 0:
+                        edges.pop(e, None)
+        outs = tuple(edges[e] for e in self.output_name)
+        return outs[0] if len(outs) == 1 else outs
+
+
+# ---------------------------------------------------------------------------------------------------
+# builders
+# ---------------------------------------------------------------------------------------------------
+def _tensor(array, dtype):
+    from . import Tensor
+    array = np.ascontiguousarray(array)
+    return Tensor(*array.shape, dtype=dtype, data=array)
+
+
+def small_cnn(seed: int = 0):
+    """Conv 3->16 k3 p1 -> Relu -> MaxPool 2x2 -> Flatten -> Gemm 4096->10 -> Softmax, plus the side
+    branch Add/Sub/Mul with a [16,1,1] tensor, Div by a [16,1,1] tensor, Abs, Cos on the conv output.
+    Returns (graph, x) with x the seeded float32 [1,3,32,32] input; outputs: ("prob", "side")."""
+    from . import Operators as ops
+    rng = np.random.default_rng(seed)
+    f32 = "float32"
+    x = rng.standard_normal((1, 3, 32, 32)).astype(np.float32)
+    init = {
+        "conv.w": _tensor(rng.normal(0, 0.1, (16, 3, 3, 3)).astype(np.float32), f32),
+        "conv.b": _tensor(np.zeros(16, np.float32), f32),
+        "fc.w": _tensor(rng.normal(0, 0.02, (10, 4096)).astype(np.float32), f32),
+        "fc.b": _tensor(rng.normal(0, 1, 10).astype(np.float32), f32),
+        "t": _tensor(rng.uniform(-1, 1, (16, 1, 1)).astype(np.float32), f32),
+        "d": _tensor(rng.uniform(0.5, 2, (16, 1, 1)).astype(np.float32), f32),
+    }
+    nodes = [
+        ops.Conv(["x", "conv.w", "conv.b"], ["conv"], pads=[1, 1, 1, 1], strides=[1, 1], dilations=[1, 1], group=1, dtype=f32),
+        ops.RELU(["conv"], ["relu"], dtype=f32),
+        ops.MaxPool(["relu"], ["pool"], kernel_shape=[2, 2], pads=[0, 0, 0, 0], strides=[2, 2], dtype=f32),
+        ops.Flatten(["pool"], ["flat"], axis=1, dtype=f32),
+        ops.Gemm(["flat", "fc.w", "fc.b"], ["logits"], alpha=1.0, beta=1.0, transA=0, transB=1, dtype=f32),
+        ops.Softmax(["logits"], ["prob"], axis=1, dtype=f32),
+        ops.ADD(["conv", "t"], ["s1"], dtype=f32),
+        ops.SUB(["s1", "t"], ["s2"], dtype=f32),
+        ops.MUL(["s2", "t"], ["s3"], dtype=f32),
+        ops.DIV(["s3", "d"], ["s4"], dtype=f32),
+        ops.ABS(["s4"], ["s5"], dtype=f32),
+        ops.COS(["s5"], ["side"], dtype=f32),
+    ]
+    return Graph(nodes, "x", ["prob", "side"], "small_cnn", init), _tensor(x, f32)
+
+
+class _QdqBuilder:
+    """Accumulates nodes and initializers of a QDQ convolutional network.  Activation scales come
+    from a calibration run: the builder executes each new float32 edge eagerly on a small seeded
+    batch, so the scale of a convolution input is amax / 127 of the very tensor it will quantise."""
+
+    def __init__(self, rng, calibration):
+        from . import Operators as ops
+        self.ops_module = ops
+        self.rng = rng
+        self.nodes: List[object] = []
+        self.init: Dict[str, object] = {}
+        self.live = {"x": calibration}          # calibration values of the float32 edges
+        self.counter = 0
+
+    def _name(self, stem):
+        self.counter += 1
+        return f"{stem}{self.counter}"
+
+    def _run(self, node, *edge_names):
+        args = [self.live[e] if e in self.live else self.init[e] for e in edge_names]
+        return node.forward(*args)["tensor"]
+
+    def add(self, node, calibrate: bool = True):
+        self.nodes.append(node)
+        if calibrate:
+            self.live[node.outputs[0]] = self._run(node, *[e for e in node.inputs if e])
+        return node.outputs[0]
+
+    def qdq_conv(self, x_edge, c_in, c_out, k, stride, pad, relu=True):
+        """QuantizeLinear -> DequantizeLinear -> Conv (weights through DequantizeLinear) [-> Relu]."""
+        ops, f32 = self.ops_module, "float32"
+        tag = self._name("conv")
+        fan_in = c_in * k * k
+        w = self.rng.normal(0, np.sqrt(2.0 / fan_in), (c_out, c_in, k, k)).astype(np.float32)
+        w_scale = (np.abs(w).reshape(c_out, -1).max(axis=1) / 127.0).astype(np.float32)
+        w_q = np.clip(np.rint(w / w_scale.reshape(-1, 1, 1, 1)), -127, 127).astype(np.int8)
+        amax = float(np.abs(self.live[x_edge].numpy()).max())
+        x_scale = np.float32(max(amax, 1e-6) / 127.0)
+        self.init[f"{tag}.x_scale"] = _tensor(np.array([x_scale], np.float32), f32)
+        self.init[f"{tag}.x_zero"] = _tensor(np.zeros(1, np.int8), "int8")
+        self.init[f"{tag}.w_q"] = _tensor(w_q, "int8")
+        self.init[f"{tag}.w_scale"] = _tensor(w_scale.reshape(c_out, 1, 1, 1), f32)
+        self.init[f"{tag}.w_zero"] = _tensor(np.zeros((c_out, 1, 1, 1), np.int8), "int8")
+        self.init[f"{tag}.b"] = _tensor(self.rng.normal(0, 0.05, c_out).astype(np.float32), f32)
+        q = self.add(ops.QuantizeLinear([x_edge, f"{tag}.x_scale", f"{tag}.x_zero"], [f"{tag}.xq"], axis=1, dtype="int8"))
+        dq = self.add(ops.DequantizeLinear([q, f"{tag}.x_scale", f"{tag}.x_zero"], [f"{tag}.xdq"], dtype=f32))
+        wdq = self.add(ops.DequantizeLinear([f"{tag}.w_q", f"{tag}.w_scale", f"{tag}.w_zero"], [f"{tag}.wdq"], dtype=f32))
+        y = self.add(ops.Conv([dq, wdq, f"{tag}.b"], [f"{tag}.y"], pads=[pad] * 4, strides=[stride, stride], dilations=[1, 1],
+                              group=1, dtype=f32))
+        for edge in (q, dq, wdq):
+            self.live.pop(edge, None)
+        if relu:
+            y = self.add(ops.RELU([y], [f"{tag}.relu"], dtype=f32))
+        return y
+
+
+def qdq_resnet50(batch: int = 256, seed: int = 0, image: int = 224, stages: Sequence[int] = (3, 4, 6, 3),
+                 widths: Sequence[int] = (64, 128, 256, 512), classes: int = 1000, calibration_batch: int = 2):
+    """Builds the QDQ ResNet-50-shaped graph and its seeded input.  Returns (graph, x) with
+    x float32 [batch, 3, image, image] ~ N(0, 1); the graph output is the [batch, classes] softmax.
+    The stride of each stage sits on its 3x3 convolution; BatchNorm is folded (convolutions carry
+    a bias).  Smaller ``image`` / ``stages`` / ``widths`` give the same structure at test size."""
+    from . import Operators as ops
+    rng = np.random.default_rng(seed)
+    f32 = "float32"
+    x = rng.standard_normal((batch, 3, image, image)).astype(np.float32)
+    b = _QdqBuilder(rng, _tensor(x[:max(1, min(calibration_batch, batch))], f32).to_device())
+    stem = widths[0]
+    y = b.qdq_conv("x", 3, stem, 7, 2, 3)
+    y = b.add(ops.MaxPool([y], ["stem.pool"], kernel_shape=[3, 3], pads=[1, 1, 1, 1], strides=[2, 2], dtype=f32))
+    c_in = stem
+    for stage, (blocks, width) in enumerate(zip(stages, widths)):
+        for block in range(blocks):
+            stride = 2 if (block == 0 and stage > 0) else 1
+            c_out = width * 4
+            shortcut = y
+            if block == 0:
+                shortcut = b.qdq_conv(y, c_in, c_out, 1, stride, 0, relu=False)
+            z = b.qdq_conv(y, c_in, width, 1, 1, 0)
+            z = b.qdq_conv(z, width, width, 3, stride, 1)
+            z = b.qdq_conv(z, width, c_out, 1, 1, 0, relu=False)
+            tag = f"s{stage}b{block}"
+            z = b.add(ops.ADD([z, shortcut], [f"{tag}.sum"], dtype=f32))
+            y = b.add(ops.RELU([z], [f"{tag}.out"], dtype=f32))
+            c_in = c_out
+    side = b.live[y].data.shape[2]
+    y = b.add(ops.MaxPool([y], ["head.pool"], kernel_shape=[side, side], pads=[0, 0, 0, 0], strides=[1, 1], dtype=f32))
+    y = b.add(ops.Flatten([y], ["head.flat"], axis=1, dtype=f32))
+    b.init["fc.w"] = _tensor(rng.normal(0, 0.01, (classes, c_in)).astype(np.float32), f32)
+    b.init["fc.b"] = _tensor(np.zeros(classes, np.float32), f32)
+    y = b.add(ops.Gemm([y, "fc.w", "fc.b"], ["logits"], alpha=1.0, beta=1.0, transA=0, transB=1, dtype=f32))
+    b.add(ops.Softmax([y], ["prob"], axis=1, dtype=f32))
+    return Graph(b.nodes, "x", ["prob"], "qdq_resnet50", b.init), _tensor(x, f32)

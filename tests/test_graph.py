@@ -1,0 +1,103 @@
+"""The resident graph runner: topology rules on the CPU (with stand-in nodes), and on the GPU the
+two benchmark graphs against the oracle executing the same nodes."""
+import numpy as np
+import pytest
+
+from onnx_translator_b200.nn.graph import Graph
+
+
+class _Value:
+    def __init__(self, v):
+        self.v = v
+        self.uploads = 0
+
+    def to_device(self):
+        self.uploads += 1
+        return self
+
+
+class _Node:
+    """Stand-in operator: adds its inputs (no library, no GPU)."""
+    log = []
+
+    def __init__(self, inputs, outputs, name=None):
+        self.inputs, self.outputs, self.name = inputs, outputs, name
+
+    def forward(self, *args):
+        _Node.log.append((self.name, len(args)))
+        return {"tensor": _Value(sum(a.v for a in args))}
+
+
+class _Other(_Node):
+    pass
+
+
+def test_graph_runs_nodes_in_order_feeds_initializers_and_returns_outputs():
+    w = _Value(10)
+    g = Graph([_Node(["x", "w"], ["a"]), _Other(["a", "a"], ["b"]), _Node(["b", "x"], ["y"])], "x", initializers={"w": w})
+    assert list(g.ops) == ["_Node.0", "_Other.0", "_Node.1"]
+    assert g.output_name == ["y"]                       # inferred: the edge nobody reads
+    out = g.forward(_Value(1))
+    assert out.v == (1 + 10) * 2 + 1
+    g.forward(_Value(2))
+    assert w.uploads == 1                               # weights are made resident once
+
+
+def test_graph_returns_a_tuple_for_several_outputs_and_skips_absent_optional_inputs():
+    _Node.log = []
+    g = Graph([_Node(["x", ""], ["a"], name="first"), _Node(["a"], ["b"]), _Node(["a"], ["c"])], ["x"], ["b", "c"])
+    b, c = g.forward(_Value(3))
+    assert (b.v, c.v) == (3, 3)
+    assert _Node.log[0] == ("first", 1)                 # the empty optional input is not passed
+
+
+def test_graph_rejects_bad_topology():
+    with pytest.raises(ValueError):
+        Graph([_Node(["nowhere"], ["a"])], "x")
+    with pytest.raises(ValueError):
+        Graph([_Node(["x"], ["a"]), _Node(["x"], ["a"])], "x")
+    with pytest.raises(ValueError):
+        Graph([_Node(["x"], ["a"])], "x", ["missing"])
+    with pytest.raises(ValueError):
+        Graph([_Node(["x"], ["a"])], "x").forward()
+
+
+# ---- on the device --------------------------------------------------------------------------------------------
+def _bits_equal(got, want):
+    return got.shape == want.shape and np.array_equal(np.ascontiguousarray(got).view(np.uint8), np.ascontiguousarray(want).view(np.uint8))
+
+
+@pytest.mark.gpu
+def test_small_cnn_graph_matches_the_oracle(port):
+    import oracle_graph
+    from onnx_translator_b200 import nn
+    graph, x = nn.small_cnn(seed=0)
+    prob, side = graph.forward(x)
+    want_prob, want_side = oracle_graph.run(graph, port, x)
+    assert _bits_equal(side.numpy(), want_side)          # conv, add, sub, mul, div, abs, cos: bit for bit
+    assert np.allclose(prob.numpy(), want_prob, rtol=1e-6, atol=0)
+    again, _ = graph.forward(x)                          # a second run on resident weights gives the same bits
+    assert _bits_equal(again.numpy(), prob.numpy())
+
+
+@pytest.mark.gpu
+def test_qdq_resnet_shaped_graph_matches_the_oracle_node_for_node(port):
+    """A small instance of the QDQ ResNet-50-shaped graph (same node pattern, one block per stage).
+    With every convolution on the exact kernel the logits agree bit for bit; the softmax within 1e-6."""
+    import os
+    import oracle_graph
+    from onnx_translator_b200 import nn
+    os.environ["TOPS_DISABLE_TC"] = "1"
+    try:
+        graph, x = nn.qdq_resnet50(batch=2, seed=0, image=64, stages=(1, 1, 1, 1), widths=(8, 16, 24, 32), classes=20)
+        kinds = [type(op).__name__ for op in graph.ops.values()]
+        assert kinds.count("Conv") == 1 + 4 * 4 and kinds.count("QuantizeLinear") == kinds.count("Conv")
+        assert kinds.count("DequantizeLinear") == 2 * kinds.count("Conv") and kinds.count("ADD") == 4
+        graph.output_name = ["logits", "prob"]
+        logits, prob = graph.forward(x)
+        want_logits, want_prob = oracle_graph.run(graph, port, x)
+    finally:
+        del os.environ["TOPS_DISABLE_TC"]
+    assert _bits_equal(logits.numpy(), want_logits)
+    assert np.allclose(prob.numpy(), want_prob, rtol=1e-6, atol=1e-45)
+    assert np.allclose(prob.numpy().sum(axis=1), 1.0, atol=1e-5)
