@@ -2,6 +2,7 @@
 #pragma once
 
 #include "common.cuh"
+#include "gemm_common.cuh"
 
 namespace tops {
 
@@ -32,6 +33,22 @@ struct ConvTcPlan {
 ConvTcPlan conv_tc_plan(const Tensor* X, const Tensor* W, const Tensor* Y, const ConvGeom& c, bool int8_weights = false);
 bool conv_tc_run(const Tensor* X, const Tensor* W, const Tensor* B, Tensor* Y, const ConvGeom& c, const ConvTcPlan& plan,
                  void* xp, void* wt, int* status, const float* w_scale = nullptr);
+
+// The tensor-core step on operands that are already laid out: `xp` = activations [images][Hp][Wp][C]
+// channels-last with every padding cell present, `wt` = filters [KH*KW][M][C]; output (n, m, oh, ow)
+// for oh < OH, ow < OW reads rows (oh + kh*dil_h, ow + kw*dil_w).  C * es must be a multiple of 16.
+struct ShiftedGemm {
+    const void* xp = nullptr; const void* wt = nullptr;
+    int es = 2; bool fp8 = false;
+    unsigned a_format = 1, b_format = 1;      // tcgen05 operand formats (16-bit: 0 = float16, 1 = bfloat16; fp8: 0 = e4m3, 1 = e5m2)
+    int images = 0, Hp = 0, Wp = 0, C = 0, M = 0, KH = 1, KW = 1, dil_h = 1, dil_w = 1, OH = 0, OW = 0;
+    void* Y = nullptr; int dy = DTYPE_FLOAT32;
+    const void* bias = nullptr; int bias_dtype = DTYPE_FLOAT32;
+    int* status = nullptr;
+    EpilogueScales fs;
+    int relu = 0;
+};
+bool shifted_gemm_launch(const ShiftedGemm& g);
 
 // Fills a ConvGeom from the ABI arguments; false (with the error recorded) when they are inconsistent.
 bool conv_geometry(const char* name, const Tensor* X, const Tensor* W, const Tensor* B, Tensor* Y, const ConvParams* params, ConvGeom* c);

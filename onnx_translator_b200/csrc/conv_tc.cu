@@ -29,7 +29,7 @@ __global__ void __launch_bounds__(256) nchw_to_padded_nhwc(const E* __restrict__
     constexpr int kVec = 16 / (int)sizeof(E);               // channels per 16-byte store
     constexpr int kPitch = 64 + kVec;                       // tile row pitch in elements (keeps rows 16-byte aligned)
     __shared__ __align__(16) E tile[64][kPitch];            // [column][channel]
-    const int wp0 = blockIdx.x * 64, hp = blockIdx.y % Hp, n = blockIdx.y / Hp, c0 = blockIdx.z * 64;
+    const int wp0 = blockIdx.y * 64, hp = blockIdx.x % Hp, n = blockIdx.x / Hp, c0 = blockIdx.z * 64;
     const int h = hp - pt;
     const bool row_inside = h >= 0 && h < H;
     // read: each thread owns one column and walks 16 channels; a warp reads 32 consecutive
@@ -125,7 +125,7 @@ bool conv_tc_run(const Tensor* X, const Tensor* W, const Tensor* B, Tensor* Y, c
     const bool fp8 = plan.fp8;
     const size_t rows = plan.rows;
 
-    const dim3 tgrid((Wp + 63) / 64, c.N * Hp, (c.C + 63) / 64);
+    const dim3 tgrid(c.N * Hp, (Wp + 63) / 64, (c.C + 63) / 64);
     const int wgrid = grid_for((size_t)c.M * c.C * taps, 256, st->sm_count, 4);
     if (es == 2) {
         nchw_to_padded_nhwc<uint16_t><<<tgrid, 256, 0, s>>>((const uint16_t*)X->data, (uint16_t*)xp, c.C, c.H, c.W, Hp, Wp, c.pt, c.pl);
@@ -141,46 +141,67 @@ bool conv_tc_run(const Tensor* X, const Tensor* W, const Tensor* B, Tensor* Y, c
     }
     if (!TOPS_CHECK_LAUNCH("conv2d_forward (layout copies)")) return false;
 
+    ShiftedGemm sg;
+    sg.xp = xp; sg.wt = wt; sg.es = es; sg.fp8 = fp8;
+    sg.a_format = fp8 ? (dx == DTYPE_FLOAT8_E5M2 ? 1u : 0u) : (dx == DTYPE_BFLOAT16 ? 1u : 0u);
+    sg.b_format = fp8 ? (dw == DTYPE_FLOAT8_E5M2 ? 1u : 0u) : (dw == DTYPE_INT8 ? sg.a_format : (dw == DTYPE_BFLOAT16 ? 1u : 0u));
+    sg.images = c.N; sg.Hp = Hp; sg.Wp = Wp; sg.C = c.C; sg.M = c.M; sg.KH = c.KH; sg.KW = c.KW; sg.dil_h = c.dh; sg.dil_w = c.dw;
+    sg.OH = c.OH; sg.OW = c.OW;
+    sg.Y = Y->data; sg.dy = dy;
+    sg.bias = (B && B->data) ? B->data : nullptr;
+    sg.bias_dtype = sg.bias ? (int)B->dtype : DTYPE_FLOAT32;
+    sg.status = status;
+    if (w_scale) { sg.fs.b_scale = w_scale; sg.fs.b_per_column = 1; }
+    return shifted_gemm_launch(sg);
+}
+
+// The tensor-core part shared by every convolution path: KH * KW shifted GEMMs over a padded
+// channels-last activation tensor and tap-major filters that are already in place.
+bool shifted_gemm_launch(const ShiftedGemm& g) {
+    DeviceState* st = acquire_device();
+    if (!st) return false;
+    cudaStream_t s = current_stream();
+    const int es = g.es, taps = g.KH * g.KW;
+    const size_t rows = (size_t)g.images * g.Hp * g.Wp;
     const int k_step = kRowBytes / es;
     CUtensorMap map_a, map_b;
-    const uint64_t dims_a[2] = {(uint64_t)c.C, (uint64_t)rows};
-    const uint64_t strides_a[1] = {(uint64_t)c.C * es};
+    const uint64_t dims_a[2] = {(uint64_t)g.C, (uint64_t)rows};
+    const uint64_t strides_a[1] = {(uint64_t)g.C * es};
     const uint32_t box_a[2] = {(uint32_t)k_step, (uint32_t)kBM};
-    const uint64_t dims_b[3] = {(uint64_t)c.C, (uint64_t)c.M, (uint64_t)taps};
-    const uint64_t strides_b[2] = {(uint64_t)c.C * es, (uint64_t)c.M * c.C * es};
+    const uint64_t dims_b[3] = {(uint64_t)g.C, (uint64_t)g.M, (uint64_t)taps};
+    const uint64_t strides_b[2] = {(uint64_t)g.C * es, (uint64_t)g.M * g.C * es};
     const uint32_t box_b[3] = {(uint32_t)k_step, (uint32_t)kBN, 1u};
-    const bool f16 = dx == DTYPE_FLOAT16;
-    if (!make_tensor_map(&map_a, xp, es, fp8, f16, 2, dims_a, strides_a, box_a, nullptr) ||
-        !make_tensor_map(&map_b, wt, es, fp8, f16, 3, dims_b, strides_b, box_b, nullptr))
+    const bool f16 = !g.fp8 && g.a_format == 0u;
+    if (!make_tensor_map(&map_a, g.xp, es, g.fp8, f16, 2, dims_a, strides_a, box_a, nullptr) ||
+        !make_tensor_map(&map_b, g.wt, es, g.fp8, f16, 3, dims_b, strides_b, box_b, nullptr))
         return false;
 
     TcParams p;
     // rows beyond the last valid output position of the last image need no tile
-    const size_t last_row = ((size_t)(c.N - 1) * Hp + (c.OH - 1)) * Wp + c.OW;
-    p.M = (int)rows; p.N = c.M;
-    p.cv.c_blocks = (c.C + k_step - 1) / k_step;
+    const size_t last_row = ((size_t)(g.images - 1) * g.Hp + (g.OH - 1)) * g.Wp + g.OW;
+    p.M = (int)rows; p.N = g.M;
+    p.cv.c_blocks = (g.C + k_step - 1) / k_step;
     p.k_blocks = taps * p.cv.c_blocks;
     p.k_step = k_step;
     p.tiles_m = (int)((last_row + kBM - 1) / kBM);
-    p.tiles_n = (c.M + kBN - 1) / kBN;
-    p.Y = Y->data; p.dy = dy;
+    p.tiles_n = (g.M + kBN - 1) / kBN;
+    p.Y = g.Y; p.dy = g.dy;
     p.alpha = 1.0f; p.beta = 1.0f;
-    p.bias.ptr = (B && B->data) ? B->data : nullptr;
-    p.bias.dtype = p.bias.ptr ? (int)B->dtype : DTYPE_FLOAT32;
-    p.bias.mode = p.bias.ptr ? kBiasPerColumn : kBiasNone;
-    p.bias.rows = 1; p.bias.cols = c.M;
-    p.status = status;
+    p.bias.ptr = g.bias;
+    p.bias.dtype = g.bias_dtype;
+    p.bias.mode = g.bias ? kBiasPerColumn : kBiasNone;
+    p.bias.rows = 1; p.bias.cols = g.M;
+    p.status = g.status;
     p.vec_store = 0;
-    p.cv.Wp = Wp; p.cv.plane = Hp * Wp;
-    p.cv.images = c.N; p.cv.OH = c.OH; p.cv.OW = c.OW; p.cv.OC = c.M;
-    p.cv.KW = c.KW; p.cv.dil_h = c.dh; p.cv.dil_w = c.dw;
-    const uint32_t fa = fp8 ? (dx == DTYPE_FLOAT8_E5M2 ? 1u : 0u) : (dx == DTYPE_BFLOAT16 ? 1u : 0u);
-    const uint32_t fb = fp8 ? (dw == DTYPE_FLOAT8_E5M2 ? 1u : 0u) : (dw == DTYPE_INT8 ? fa : (dw == DTYPE_BFLOAT16 ? 1u : 0u));
-    if (w_scale) { p.fs.b_scale = w_scale; p.fs.b_per_column = 1; }
-    const uint32_t idesc = umma::instr_desc(fa, fb, kBM, kBN);
+    p.cv.Wp = g.Wp; p.cv.plane = g.Hp * g.Wp;
+    p.cv.images = g.images; p.cv.OH = g.OH; p.cv.OW = g.OW; p.cv.OC = g.M;
+    p.cv.KW = g.KW; p.cv.dil_h = g.dil_h; p.cv.dil_w = g.dil_w;
+    p.fs = g.fs;
+    p.relu = g.relu;
+    const uint32_t idesc = umma::instr_desc(g.a_format, g.b_format, kBM, kBN);
     const int tiles = p.tiles_m * p.tiles_n;
     const int grid = tiles < st->sm_count ? tiles : st->sm_count;
-    if (fp8) {
+    if (g.fp8) {
         static bool attr = false;
         if (!attr) { cudaFuncSetAttribute(tc_kernel<true, kModeConv>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kTcSmemBytes); attr = true; }
         tc_kernel<true, kModeConv><<<grid, kTcThreads, kTcSmemBytes, s>>>(map_a, map_b, p, idesc);

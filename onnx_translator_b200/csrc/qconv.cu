@@ -1,0 +1,185 @@
+// Convolution of a quantised graph in one call:
+//
+//     Y = [Relu]( Conv( DequantizeLinear(Xq, x_scale, x_zero), DequantizeLinear(Wq, w_scale, 0) ) + B )
+//
+// i.e. the chain QuantizeLinear -> DequantizeLinear -> Conv (weights through DequantizeLinear) [-> Relu]
+// that wraps every convolution of a QDQ network (reference operators: nn/Operators.py:427-473, 475-548,
+// C functions tensor_ops.c:999-1034, 1036-1114), starting from the activation CODES.
+//
+// The integer levels (code - zero point, |level| <= 255, and the weight codes, |code| <= 128) are
+// exact in bfloat16, so they go to the tensor cores as bfloat16 operands; every product is exact and
+// the fp32 accumulator only rounds once a partial sum exceeds 2^24.  The scales are applied to the
+// accumulator: x_scale * w_scale[m].  The reference multiplies each operand by its scale first
+// (rounding each to float32) and accumulates in double: the results differ by the accumulation
+// order and by those per-element roundings, the tolerance class of the tensor-core convolution.
+//
+// Layout work (one pass over the activations, one over the filters):
+//   * stride 1: codes NCHW -> levels, zero-padded channels-last [N][Hp][Wp][C8] (C8 = C rounded up to 8);
+//   * stride 2: the same with a space-to-depth step, Z[A][B][(r,s,c)] = Xpad[2A + r][2B + s][c], which
+//     turns the stride-2 KH x KW convolution into a stride-1 ceil(KH/2) x ceil(KW/2) convolution over
+//     4C channels (filter taps that fall outside the original window are zero);
+//   * filters [M][C][KH][KW] -> tap-major [taps][M][C8'] in the same channel order.
+// Then the shifted-GEMM tensor-core kernel (conv_tc.cu, tc_kernel.cuh) runs unchanged.
+#include "conv_common.cuh"
+
+namespace tops {
+
+struct QGeom {
+    int C, H, W;           // input
+    int S;                 // stride (1 or 2), the same in both directions
+    int pt, pl;
+    int Hz, Wz, Cz;        // levels tensor: rows, columns, channels (S*S*C rounded up to 8)
+    int KH, KW, KHz, KWz;  // original and space-to-depth filter extents
+    int M;
+};
+
+__device__ __forceinline__ uint16_t level_bits(int v) {        // small integer -> bfloat16 bits (exact for |v| <= 256)
+    return (uint16_t)(__float_as_uint((float)v) >> 16);
+}
+
+// One CTA: 64 channels x 64 columns of one row of the levels tensor (shared-memory transpose so that
+// reads run along W of the NCHW input and writes along the channels of the NHWC output).
+template <bool SIGNED>
+__global__ void __launch_bounds__(256) codes_to_levels(const uint8_t* __restrict__ x, uint16_t* __restrict__ z, QGeom g,
+                                                       const void* __restrict__ zero_ptr) {
+    __shared__ __align__(16) uint16_t tile[64][72];            // [column][channel]
+    const int b0 = blockIdx.y * 64, a = blockIdx.x % g.Hz, n = blockIdx.x / g.Hz, c0 = blockIdx.z * 64;
+    int zero = 0;
+    if (zero_ptr) zero = SIGNED ? (int)*(const int8_t*)zero_ptr : (int)*(const uint8_t*)zero_ptr;
+    {
+        const int bb = threadIdx.x & 63, cc0 = threadIdx.x >> 6;
+        const size_t plane = (size_t)g.H * g.W;
+        #pragma unroll 4
+        for (int i = 0; i < 16; i++) {
+            const int cz = c0 + cc0 + 4 * i;
+            int v = 0;
+            if (cz < g.S * g.S * g.C) {
+                const int rs = cz / g.C, c = cz - rs * g.C;
+                const int r = rs / g.S, s = rs - r * g.S;
+                const int h = g.S * a + r - g.pt, w = g.S * (b0 + bb) + s - g.pl;
+                if (h >= 0 && h < g.H && w >= 0 && w < g.W) {
+                    const uint8_t code = x[((size_t)n * g.C + c) * plane + (size_t)h * g.W + w];
+                    v = (SIGNED ? (int)(int8_t)code : (int)code) - zero;
+                }
+            }
+            tile[bb][cc0 + 4 * i] = level_bits(v);
+        }
+    }
+    __syncthreads();
+    const int part = threadIdx.x & 7, pos0 = threadIdx.x >> 3;     // 8 lanes x 8 channels (16 bytes) per position
+    const int c = c0 + part * 8;
+    if (c < g.Cz) {
+        #pragma unroll
+        for (int pass = 0; pass < 2; pass++) {
+            const int bb = pos0 + pass * 32, b = b0 + bb;
+            if (b < g.Wz) {
+                const uint4 val = *reinterpret_cast<const uint4*>(&tile[bb][part * 8]);
+                *reinterpret_cast<uint4*>(z + (((size_t)n * g.Hz + a) * g.Wz + b) * g.Cz + c) = val;
+            }
+        }
+    }
+}
+
+// int8 filter codes [M][C][KH][KW] -> bfloat16 levels [KHz*KWz][M][Cz] in the channel order of the activations
+__global__ void __launch_bounds__(256) filter_codes_to_levels(const int8_t* __restrict__ w, uint16_t* __restrict__ wt, QGeom g) {
+    const size_t total = (size_t)g.KHz * g.KWz * g.M * g.Cz;
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
+        const int cz = (int)(i % g.Cz);
+        const size_t t1 = i / g.Cz;
+        const int m = (int)(t1 % g.M), tap = (int)(t1 / g.M);
+        const int ta = tap / g.KWz, tb = tap - ta * g.KWz;
+        int v = 0;
+        if (cz < g.S * g.S * g.C) {
+            const int rs = cz / g.C, c = cz - rs * g.C;
+            const int r = rs / g.S, s = rs - r * g.S;
+            const int kh = g.S * ta + r, kw = g.S * tb + s;
+            if (kh < g.KH && kw < g.KW) v = w[(((size_t)m * g.C + c) * g.KH + kh) * g.KW + kw];
+        }
+        wt[i] = level_bits(v);
+    }
+}
+
+}  // namespace tops
+
+using namespace tops;
+
+TOPS_API int tops_qlinear_conv_forward(const Tensor* Xq, const Tensor* x_scale, const Tensor* x_zero, const Tensor* Wq,
+                                       const Tensor* w_scale, const Tensor* B, Tensor* Y, ConvParams* params, int relu) {
+    const char* name = "tops_qlinear_conv_forward";
+    ConvGeom c;
+    if (!conv_geometry(name, Xq, Wq, B, Y, params, &c)) return tops_last_error();
+    const bool x8 = Xq->dtype == DTYPE_INT8 || Xq->dtype == DTYPE_UINT8;
+    if (!x8 || Wq->dtype != DTYPE_INT8 || !x_scale || !x_scale->data || x_scale->dtype != DTYPE_FLOAT32 || x_scale->size != 1 ||
+        !w_scale || !w_scale->data || w_scale->dtype != DTYPE_FLOAT32 || w_scale->size != (size_t)c.M ||
+        (x_zero && x_zero->data && (x_zero->dtype != Xq->dtype || x_zero->size != 1)) ||
+        (B && B->data && B->dtype != DTYPE_FLOAT32)) {
+        set_error(TOPS_ERR_UNSUPPORTED, "%s: wants int8 / uint8 activation codes with one float32 scale (and one zero point of the same "
+                                        "type), int8 filter codes with one float32 scale per output channel, a float32 bias", name);
+        zero_fill(Y);
+        return tops_last_error();
+    }
+    const int dy = (int)Y->dtype;
+    const bool strided = c.sh == 2 && c.sw == 2 && c.dh == 1 && c.dw == 1;
+    if (c.G != 1 || !((c.sh == 1 && c.sw == 1) || strided) || c.dh < 1 || c.dw < 1 || c.pt < 0 || c.pl < 0 ||
+        (dy != DTYPE_FLOAT32 && dy != DTYPE_BFLOAT16 && dy != DTYPE_FLOAT16)) {
+        set_error(TOPS_ERR_UNSUPPORTED, "%s: covers group 1, stride 1 (any dilation) or stride 2 (dilation 1), float32 / bfloat16 / float16 output", name);
+        zero_fill(Y);
+        return tops_last_error();
+    }
+    if (Y->size == 0) return TOPS_OK;
+
+    QGeom g;
+    g.C = c.C; g.H = c.H; g.W = c.W; g.S = c.sh; g.pt = c.pt; g.pl = c.pl; g.M = c.M; g.KH = c.KH; g.KW = c.KW;
+    g.KHz = strided ? (c.KH + 1) / 2 : c.KH;
+    g.KWz = strided ? (c.KW + 1) / 2 : c.KW;
+    const int dil_h = strided ? 1 : c.dh, dil_w = strided ? 1 : c.dw;
+    const int need_h = c.OH + (g.KHz - 1) * dil_h, need_w = c.OW + (g.KWz - 1) * dil_w;       // rows / columns the taps reach
+    const int have_h = strided ? (c.H + c.pt + 1) / 2 : c.H + c.pt, have_w = strided ? (c.W + c.pl + 1) / 2 : c.W + c.pl;
+    g.Hz = need_h > have_h ? need_h : have_h;
+    g.Wz = need_w > have_w ? need_w : have_w;
+    g.Cz = (g.S * g.S * c.C + 7) & ~7;
+    const size_t rows = (size_t)c.N * g.Hz * g.Wz;
+    if (rows >= 0x7FFFFF00ull) {
+        set_error(TOPS_ERR_UNSUPPORTED, "%s: more than 2^31 padded positions", name);
+        zero_fill(Y);
+        return tops_last_error();
+    }
+    DeviceState* st = acquire_device();
+    if (!st) return tops_last_error();
+    cudaStream_t s = current_stream();
+    const size_t z_bytes = rows * g.Cz * 2, wt_bytes = (size_t)g.KHz * g.KWz * c.M * g.Cz * 2;
+    void *z = nullptr, *wt = nullptr;
+    if (cudaMallocAsync(&z, z_bytes, s) != cudaSuccess) { cudaGetLastError(); set_error(TOPS_ERR_OOM, "%s: scratch", name); return tops_last_error(); }
+    if (cudaMallocAsync(&wt, wt_bytes, s) != cudaSuccess) {
+        cudaGetLastError();
+        cudaFreeAsync(z, s);
+        set_error(TOPS_ERR_OOM, "%s: scratch", name);
+        return tops_last_error();
+    }
+    const dim3 grid(c.N * g.Hz, (g.Wz + 63) / 64, (g.Cz + 63) / 64);
+    const void* zero_ptr = (x_zero && x_zero->data) ? x_zero->data : nullptr;
+    if (Xq->dtype == DTYPE_INT8) codes_to_levels<true><<<grid, 256, 0, s>>>((const uint8_t*)Xq->data, (uint16_t*)z, g, zero_ptr);
+    else codes_to_levels<false><<<grid, 256, 0, s>>>((const uint8_t*)Xq->data, (uint16_t*)z, g, zero_ptr);
+    filter_codes_to_levels<<<grid_for(wt_bytes / 2, 256, st->sm_count, 4), 256, 0, s>>>((const int8_t*)Wq->data, (uint16_t*)wt, g);
+    bool ok = TOPS_CHECK_LAUNCH(name);
+    if (ok) {
+        ShiftedGemm sg;
+        sg.xp = z; sg.wt = wt; sg.es = 2; sg.fp8 = false; sg.a_format = 1u; sg.b_format = 1u;
+        sg.images = c.N; sg.Hp = g.Hz; sg.Wp = g.Wz; sg.C = g.Cz; sg.M = c.M;
+        sg.KH = g.KHz; sg.KW = g.KWz; sg.dil_h = dil_h; sg.dil_w = dil_w; sg.OH = c.OH; sg.OW = c.OW;
+        sg.Y = Y->data; sg.dy = dy;
+        sg.bias = (B && B->data) ? B->data : nullptr;
+        sg.bias_dtype = DTYPE_FLOAT32;
+        sg.status = device_status_word();
+        sg.fs.a_scale = (const float*)x_scale->data;
+        sg.fs.b_scale = (const float*)w_scale->data;
+        sg.fs.b_per_column = 1;
+        sg.relu = relu ? 1 : 0;
+        ok = shifted_gemm_launch(sg);
+    }
+    cudaFreeAsync(z, s);
+    cudaFreeAsync(wt, s);
+    if (!ok) return tops_last_error();
+    finish_op();
+    return TOPS_OK;
+}

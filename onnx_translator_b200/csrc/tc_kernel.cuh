@@ -41,6 +41,7 @@ struct TcParams {
     int vec_store;         // Y base and row pitch are 16-byte aligned
     ConvView cv;           // convolution mode only
     EpilogueScales fs;
+    int relu = 0;          // clamp the result at zero before it is stored (v > 0 ? v : 0)
 };
 
 __device__ __forceinline__ void tile_coords(int tile, int tiles_m, int tiles_n, int& tm, int& tn) {
@@ -225,6 +226,10 @@ tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUt
                         }
                         #pragma unroll
                         for (int j = 0; j < 32; j++) v[j] = __fmaf_rn(p.beta, cv[j], v[j]);
+                    }
+                    if (p.relu) {
+                        #pragma unroll
+                        for (int j = 0; j < 32; j++) v[j] = v[j] > 0.0f ? v[j] : 0.0f;
                     }
                     if constexpr (MODE == kModeConv) {
                         // NCHW output: for one output channel, consecutive lanes (consecutive padded

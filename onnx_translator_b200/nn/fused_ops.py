@@ -1,0 +1,42 @@
+"""Graph nodes that stand for a chain of reference operators executed by one fused library call.
+They are created by ``Graph.fused()``, never by a model import, and have the node interface of the
+operator classes in Operators.py (``inputs``, ``outputs``, ``forward`` returning the result dict)."""
+from __future__ import annotations
+
+import ctypes
+
+from . import Ops, Tensor
+from .. import capi
+from ..capi import CConvParams
+from .Operators import _int_ptr, _pooled_extent
+
+
+class QLinearConv(Ops):
+    """DequantizeLinear(activation codes) + DequantizeLinear(weight codes) + Conv [+ Relu] in one call
+    (replaces nn/Operators.py:452-473 twice, :475-548 and :170-200).
+    inputs: [x_codes, x_scale, x_zero, w_codes, w_scale, bias or ""]."""
+
+    def __init__(self, inputs, outputs, pads, strides, dilations, relu, dtype="float32"):
+        super().__init__(inputs, outputs)
+        self.pads, self.strides, self.dilations, self.relu, self.dtype = list(pads), list(strides), list(dilations), bool(relu), dtype
+
+    def forward(self, xq: Tensor, x_scale: Tensor, x_zero: Tensor, wq: Tensor, w_scale: Tensor, b: Tensor = None) -> dict:
+        n, _, h, w = xq.data.shape
+        m, _, kh, kw = wq.data.shape
+        out_shape = (n, m,
+                     _pooled_extent(h, self.pads[0], self.pads[2], self.dilations[0], kh, self.strides[0]),
+                     _pooled_extent(w, self.pads[1], self.pads[3], self.dilations[1], kw, self.strides[1]))
+        keep = [_int_ptr(self.pads), _int_ptr(self.strides), _int_ptr(self.dilations)]
+        params = CConvParams(keep[0][1], keep[1][1], keep[2][1], 1)
+        operands = [xq, x_scale, x_zero, wq, w_scale] + ([b] if b is not None else [])
+        handles = [self._numpy_to_ctensor(t.data, t.dtype) for t in operands]
+        y = self._new_output(out_shape, self.dtype)
+        rc = self.lib.tops_qlinear_conv_forward(handles[0], handles[1], handles[2], handles[3], handles[4],
+                                                handles[5] if b is not None else None, y, ctypes.byref(params), int(self.relu))
+        out = self._finish(handles, y, out_shape, self.dtype) if not rc else None
+        if rc:
+            for hdl in handles:
+                self.lib.free_tensor(hdl)
+            self.lib.free_tensor(y)
+            capi.check(self.lib)
+        return self._publish(out)

@@ -60,6 +60,60 @@ class Graph:
             if edge not in produced:
                 raise ValueError(f"graph output {edge!r} is not produced by any node")
 
+    def fused(self) -> "Graph":
+        """A graph computing the same function with every
+
+            QuantizeLinear -> DequantizeLinear -> Conv(weights = DequantizeLinear(initializers)) [-> Relu]
+
+        chain executed by one ``QLinearConv`` node (the QuantizeLinear stays: it produces the codes).
+        A chain is taken only when nothing else reads its inner edges, the weight zero points are all
+        zero and the convolution is one the fused kernel covers (group 1; stride 1, or stride 2 with
+        dilation 1); everything else is left as it is.  Initializers are shared with this graph."""
+        from .fused_ops import QLinearConv
+        nodes = list(self.ops.values())
+        producer = {e: op for op in nodes for e in op.outputs}
+        kind = lambda op: type(op).__name__
+        dropped, replaced = set(), {}
+
+        def sole_consumer(edge):
+            return self.consumers.get(edge, 0) == 1 and edge not in self.output_name
+
+        for conv in nodes:
+            if kind(conv) != "Conv" or len(conv.inputs) < 2:
+                continue
+            dq_x, dq_w = producer.get(conv.inputs[0]), producer.get(conv.inputs[1])
+            if dq_x is None or dq_w is None or kind(dq_x) != "DequantizeLinear" or kind(dq_w) != "DequantizeLinear":
+                continue
+            q = producer.get(dq_x.inputs[0])
+            if q is None or kind(q) != "QuantizeLinear" or q.inputs[1:3] != dq_x.inputs[1:3] or q.dtype not in ("int8", "uint8"):
+                continue
+            if not all(e in self.initializers for e in dq_w.inputs) or not all(e in self.initializers for e in q.inputs[1:3]):
+                continue
+            if not (sole_consumer(dq_x.outputs[0]) and sole_consumer(dq_w.outputs[0])):
+                continue
+            w_codes, w_scale, w_zero = (self.initializers[e] for e in dq_w.inputs)
+            strides, dil = list(conv.strides), list(conv.dilations)
+            covered = conv.group == 1 and (strides == [1, 1] or (strides == [2, 2] and dil == [1, 1]))
+            if (not covered or w_codes.dtype != "int8" or w_scale.dtype != "float32" or np.any(w_zero.numpy() != 0)
+                    or w_scale.data_size != w_codes.size[0] or self.initializers[q.inputs[1]].data_size != 1):
+                continue
+            relu, out_edge = False, conv.outputs[0]
+            if sole_consumer(out_edge):
+                nxt = next((op for op in nodes if out_edge in op.inputs), None)
+                if nxt is not None and kind(nxt) == "RELU" and (nxt.dtype or "float32") == (conv.dtype or "float32"):
+                    relu, out_edge = True, nxt.outputs[0]
+                    dropped.add(nxt.name)
+            bias = conv.inputs[2] if len(conv.inputs) > 2 and conv.inputs[2] else ""
+            node = QLinearConv([q.outputs[0], q.inputs[1], q.inputs[2], dq_w.inputs[0], dq_w.inputs[1], bias], [out_edge],
+                               conv.pads, strides, dil, relu, conv.dtype or "float32")
+            node.name = conv.name + ".fused"
+            dropped.update((dq_x.name, dq_w.name))
+            replaced[conv.name] = node
+        kept = [replaced.get(op.name, op) for op in nodes if op.name not in dropped]
+        g = Graph(kept, list(self.input_name), list(self.output_name), self.model_name, self.initializers)
+        g._resident = self._resident
+        return g
+
     def make_resident(self) -> None:
         """Upload every initializer once; later calls of ``forward`` reuse the device copies."""
         if not self._resident:

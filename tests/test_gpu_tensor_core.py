@@ -253,3 +253,46 @@ def test_fused_entry_points_refuse_what_they_do_not_cover():
     x = rng.normal(0, 1, (1, 16, 8, 8)).astype(np.float32)
     with pytest.raises(capi.TensorOpsError):
         fused.conv2d_dqw(x, np.ones((16, 16, 3, 3), np.int8), np.ones(16, np.float32), x_dtype="float32")   # float32 activations
+
+
+QCONV_CASES = [  # N, C, H, W, M, k, pad, stride, x_dt, zero, relu, bias
+    (4, 64, 28, 28, 96, 3, 1, 1, "int8", 0, True, True),
+    (2, 3, 64, 64, 64, 7, 3, 2, "int8", 0, True, True),          # the stem: 7x7 stride 2 on 3 channels
+    (3, 32, 30, 30, 70, 3, 1, 2, "int8", 5, False, True),        # 3x3 stride 2, non-zero zero point
+    (2, 64, 28, 28, 128, 1, 0, 2, "int8", 0, False, False),      # the 1x1 stride-2 shortcut
+    (2, 20, 17, 19, 40, 1, 0, 1, "uint8", 128, True, True),      # channels not a multiple of 8, odd sizes
+    (2, 24, 15, 15, 48, 3, 1, 2, "uint8", 100, True, False),     # odd extent with stride 2
+    (1, 256, 14, 14, 512, 3, 1, 1, "int8", -3, False, True),
+]
+
+
+@pytest.mark.parametrize("case", QCONV_CASES, ids=lambda c: f"n{c[0]}c{c[1]}h{c[2]}m{c[4]}k{c[5]}s{c[7]}-{c[8]}z{c[9]}")
+def test_qlinear_conv_against_the_unfused_chain_in_float64(port, case):
+    """DQ(x codes) + DQ(w codes) + Conv [+ Relu] in one call against the oracle's DequantizeLinear outputs
+    convolved in float64, gated on the accumulated magnitude."""
+    from onnx_translator_b200.nn import Tensor
+    from onnx_translator_b200.nn.fused_ops import QLinearConv
+    n, c, h, wd, m, k, pad, stride, x_dt, zero, relu, with_bias = case
+    rng = np.random.default_rng(n * 1000 + c * 10 + k + stride)
+    lo, hi = (-128, 128) if x_dt == "int8" else (0, 256)
+    xq = rng.integers(lo, hi, (n, c, h, wd)).astype(np.int8 if x_dt == "int8" else np.uint8)
+    wq = rng.integers(-127, 128, (m, c, k, k)).astype(np.int8)
+    sx = np.array([0.037], np.float32)
+    zx = np.array([zero], xq.dtype)
+    ws = rng.uniform(0.005, 0.02, (m, 1, 1, 1)).astype(np.float32)
+    b = rng.normal(0, 1, m).astype(np.float32) if with_bias else None
+    x_dq = port.dequantize(xq, x_dt, sx, "float32", zx, x_dt, "float32").astype(np.float64)
+    w_dq = port.dequantize(wq, "int8", ws, "float32", np.zeros((m, 1, 1, 1), np.int8), "int8", "float32").astype(np.float64)
+    oh1, ow1 = h + 2 * pad - (k - 1), wd + 2 * pad - (k - 1)
+    full, s_full = _conv_f64(x_dq, w_dq, None if b is None else b.astype(np.float64), (pad,) * 4, (1, 1), (oh1, ow1))
+    want, s_mag = full[:, :, ::stride, ::stride], s_full[:, :, ::stride, ::stride]
+    if relu:
+        want = np.maximum(want, 0)
+    node = QLinearConv([], [], [pad] * 4, [stride, stride], [1, 1], relu, "float32")
+    T = lambda a, dt: Tensor(*a.shape, dtype=dt, data=a)
+    before = _tc_count()
+    got = node.forward(T(xq, x_dt), T(sx, "float32"), T(zx, x_dt), T(wq, "int8"), T(ws, "float32"),
+                       None if b is None else T(b, "float32"))["tensor"].numpy().astype(np.float64)
+    assert _tc_count() == before + 1
+    assert got.shape == want.shape
+    _gate(got, want, s_mag, "float32", "qlinear conv")

@@ -101,3 +101,26 @@ def test_qdq_resnet_shaped_graph_matches_the_oracle_node_for_node(port):
     assert _bits_equal(logits.numpy(), want_logits)
     assert np.allclose(prob.numpy(), want_prob, rtol=1e-6, atol=1e-45)
     assert np.allclose(prob.numpy().sum(axis=1), 1.0, atol=1e-5)
+
+
+@pytest.mark.gpu
+def test_fused_graph_replaces_every_qdq_conv_chain_and_stays_close_to_the_oracle(port):
+    """Graph.fused() turns each Q -> DQ -> Conv(DQ(w)) [-> Relu] chain into one node.  The fused
+    convolutions differ from the chain within the tensor-core tolerance, which moves a few activation
+    codes by one step in later layers; the logits stay within 1 % (relative L2) of the oracle's."""
+    import oracle_graph
+    from onnx_translator_b200 import nn
+    graph, x = nn.qdq_resnet50(batch=2, seed=0, image=64, stages=(1, 1, 1, 1), widths=(8, 16, 24, 32), classes=20)
+    graph.output_name = ["logits", "prob"]
+    fused = graph.fused()
+    kinds = [type(op).__name__ for op in fused.ops.values()]
+    convs = sum(type(op).__name__ == "Conv" for op in graph.ops.values())
+    assert kinds.count("QLinearConv") == convs and kinds.count("Conv") == 0 and kinds.count("DequantizeLinear") == 0
+    assert kinds.count("QuantizeLinear") == convs and kinds.count("RELU") == 4          # only the post-add Relus remain
+    logits, prob = fused.forward(x)
+    want_logits, want_prob = oracle_graph.run(graph, port, x)
+    got = logits.numpy().astype(np.float64)
+    err = np.linalg.norm(got - want_logits) / np.linalg.norm(want_logits)
+    assert err < 1e-2, err
+    assert np.allclose(prob.numpy().sum(axis=1), 1.0, atol=1e-5)
+    assert np.abs(prob.numpy() - want_prob).max() < 1e-2 * want_prob.max()
