@@ -323,6 +323,15 @@ def run_ours(args):
         dist.all_reduce(times, op=dist.ReduceOp.MAX)
     step_ms_max, e2e_ms_max = (float(t) for t in times.cpu())
 
+    qdq_cnn = None
+    if not args.no_extra:                       # every rank runs its own batch; the time is reduced inside
+        try:
+            qdq_cnn = qdq_cnn_throughput(lib, stream, world, local)
+        except Exception as exc:
+            if world > 1:
+                raise                            # the ranks must stay in step
+            qdq_cnn = {"error": str(exc)[:300]}
+
     if rank == 0:
         peak, peak_kind = peaks()
         binary_idx = [i for i, it in enumerate(plan) if it["kind"] == "binary"]
@@ -358,6 +367,8 @@ def run_ours(args):
             "slowest_ops_GBps": dict(worst),
         }
         line["cpu_baseline"] = cpu_baseline(budget_s=20.0) if world == 1 else None
+        if qdq_cnn is not None:
+            line["qdq_cnn"] = qdq_cnn
         if world == 1 and not args.no_extra:
             try:
                 line["other_ops"] = other_ops(lib, stream, peak)
@@ -492,6 +503,44 @@ def other_ops(lib, stream, hbm_peak):
     out["conv_256x256x56x56_k3_bf16_int8_qdq_weights"] = {"TFLOPs": round(2.0 * 256 * 56 * 56 * 256 * 2304 / 1e12 / (ms / 1e3), 1),
                                                           "ms": round(ms, 4), "tensor_core_path": lib.tops_tensor_core_launches() > before}
     return out
+
+
+def qdq_cnn_throughput(lib, stream, world, local, batch=256):
+    """Images per second of the QDQ ResNet-50-shaped graph (benchmark config 5: batch 256 per GPU, float32
+    [N,3,224,224] input, int8 QDQ around every convolution), input resident, every rank its own batch
+    (batch sharding, no collective), time = max over ranks.  The graph runs through Graph.fused(): each
+    Q -> DQ -> Conv [-> Relu] chain is one tensor-core call; the other nodes are the plain operators."""
+    import torch
+    from onnx_translator_b200 import capi, nn
+    graph, x = nn.qdq_resnet50(batch=batch, seed=0)
+    fused = graph.fused()
+    xd = x.to_device()
+    fused.forward(xd)                                   # warm-up: weights become resident, pools grow
+    fused.forward(xd)
+    lib.tops_sync()
+    iters = 3
+    ev = [torch.cuda.Event(enable_timing=True) for _ in range(iters + 1)]
+    before = lib.tops_tensor_core_launches()
+    ev[0].record(stream)
+    for i in range(iters):
+        out = fused.forward(xd)
+        ev[i + 1].record(stream)
+    lib.tops_sync()
+    torch.cuda.synchronize()
+    capi.check(lib)
+    ms = float(np.median([ev[i].elapsed_time(ev[i + 1]) for i in range(iters)]))
+    t = torch.tensor([ms], dtype=torch.float64, device=f"cuda:{local}")
+    if world > 1:
+        import torch.distributed as dist
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    ms = float(t.cpu()[0])
+    prob = out.numpy()
+    flops = 2.0 * graph.macs_per_image * batch
+    return {"images_per_s": round(world * batch / (ms / 1e3), 1), "ms_per_batch": round(ms, 3), "batch_per_gpu": batch,
+            "n_gpus": world, "TFLOPs_per_gpu": round(flops / 1e12 / (ms / 1e3), 1), "gflop_per_image": round(2.0 * graph.macs_per_image / 1e9, 2),
+            "tensor_core_launches_per_batch": int((lib.tops_tensor_core_launches() - before) // iters),
+            "nodes": len(fused.ops), "nodes_unfused": len(graph.ops),
+            "softmax_rows_sum_to_one": bool(np.allclose(prob.sum(axis=1), 1.0, atol=1e-4))}
 
 
 # DRAM read + write bytes of one ew_kernel<BinaryBody> launch, averaged over the 84 launches of one

@@ -238,6 +238,14 @@ int tops_conv2d_dqw_forward(const Tensor* X, const Tensor* Wq, const Tensor* w_s
 int tops_qlinear_conv_forward(const Tensor* Xq, const Tensor* x_scale, const Tensor* x_zero, const Tensor* Wq,
                               const Tensor* w_scale, const Tensor* B, Tensor* Y, ConvParams* params, int relu);
 
+/* The same starting one operator earlier, from float32 activations:
+     Y = [Relu]( Conv( DQ( Q(X, x_scale, x_zero), x_scale, x_zero ), DQ(Wq, w_scale, 0) ) + B )
+   replaces QuantizeLinear -> DequantizeLinear -> Conv [-> Relu] (nn/Operators.py:427-450 in addition
+   to the operators named above).  The codes are those quantize_linear_forward would store, of the
+   type of x_zero (int8 when x_zero is NULL). */
+int tops_qdq_conv_forward(const Tensor* X, const Tensor* x_scale, const Tensor* x_zero, const Tensor* Wq,
+                          const Tensor* w_scale, const Tensor* B, Tensor* Y, ConvParams* params, int relu);
+
 /* Device-side exhaustive codec self-check: encodes every float32 bit pattern with the fast
    (hardware-convert) encoder and with the bit-level restatement of the reference encoder and
    returns the number of disagreements (NaN inputs excluded), or -1 on error. */

@@ -13,6 +13,9 @@
 // (rounding each to float32) and accumulates in double: the results differ by the accumulation
 // order and by those per-element roundings, the tolerance class of the tensor-core convolution.
 //
+// tops_qdq_conv_forward starts one step earlier, from the float32 activations: the QuantizeLinear that
+// produces the codes is evaluated inside the layout pass (same codes, bit for bit).
+//
 // Layout work (one pass over the activations, one over the filters):
 //   * stride 1: codes NCHW -> levels, zero-padded channels-last [N][Hp][Wp][C8] (C8 = C rounded up to 8);
 //   * stride 2: the same with a space-to-depth step, Z[A][B][(r,s,c)] = Xpad[2A + r][2B + s][c], which
@@ -21,6 +24,7 @@
 //   * filters [M][C][KH][KW] -> tap-major [taps][M][C8'] in the same channel order.
 // Then the shifted-GEMM tensor-core kernel (conv_tc.cu, tc_kernel.cuh) runs unchanged.
 #include "conv_common.cuh"
+#include "qdq_math.cuh"
 
 namespace tops {
 
@@ -37,45 +41,65 @@ __device__ __forceinline__ uint16_t level_bits(int v) {        // small integer 
     return (uint16_t)(__float_as_uint((float)v) >> 16);
 }
 
-// One CTA: 64 channels x 64 columns of one row of the levels tensor (shared-memory transpose so that
-// reads run along W of the NCHW input and writes along the channels of the NHWC output).
-template <bool SIGNED>
-__global__ void __launch_bounds__(256) codes_to_levels(const uint8_t* __restrict__ x, uint16_t* __restrict__ z, QGeom g,
-                                                       const void* __restrict__ zero_ptr) {
-    __shared__ __align__(16) uint16_t tile[64][72];            // [column][channel]
-    const int b0 = blockIdx.y * 64, a = blockIdx.x % g.Hz, n = blockIdx.x / g.Hz, c0 = blockIdx.z * 64;
+// Activations -> levels.  One CTA: 64 channels x 64 consecutive positions of one image plane (flat
+// h * W + w, so reads are contiguous whatever the plane's width); a shared-memory transpose lets the
+// reads run along the NCHW plane and the writes along the channels of the channels-last output.
+// Each input element lands in exactly one cell: (A, B) = (h + pt, w + pl) for stride 1, and
+// (A, B, r, s) = ((h + pt) / 2, (w + pl) / 2, (h + pt) % 2, (w + pl) % 2) for stride 2.  Padding
+// cells and padding channels are not written: the caller clears the tensor first.
+// XK 0: float32 values, quantised here exactly as quantize_linear_forward does (SIGNED: int8 codes,
+// else uint8); XK 1: 8-bit codes.
+template <int XK, bool SIGNED>
+__global__ void __launch_bounds__(256) activations_to_levels(const void* __restrict__ x, uint16_t* __restrict__ z, QGeom g,
+                                                             const float* __restrict__ scale_ptr, const void* __restrict__ zero_ptr) {
+    __shared__ __align__(16) uint16_t tile[64][72];            // [position][channel]
+    const int plane = g.H * g.W;
+    const int p0 = blockIdx.x * 64, n = blockIdx.y, c0 = blockIdx.z * 64;
     int zero = 0;
     if (zero_ptr) zero = SIGNED ? (int)*(const int8_t*)zero_ptr : (int)*(const uint8_t*)zero_ptr;
     {
-        const int bb = threadIdx.x & 63, cc0 = threadIdx.x >> 6;
-        const size_t plane = (size_t)g.H * g.W;
-        #pragma unroll 4
-        for (int i = 0; i < 16; i++) {
-            const int cz = c0 + cc0 + 4 * i;
-            int v = 0;
-            if (cz < g.S * g.S * g.C) {
-                const int rs = cz / g.C, c = cz - rs * g.C;
-                const int r = rs / g.S, s = rs - r * g.S;
-                const int h = g.S * a + r - g.pt, w = g.S * (b0 + bb) + s - g.pl;
-                if (h >= 0 && h < g.H && w >= 0 && w < g.W) {
-                    const uint8_t code = x[((size_t)n * g.C + c) * plane + (size_t)h * g.W + w];
-                    v = (SIGNED ? (int)(int8_t)code : (int)code) - zero;
+        const int pp = threadIdx.x & 63, cc0 = threadIdx.x >> 6;
+        const int p = p0 + pp;
+        float scale = 1.0f, inv = 1.0f;
+        if (XK == 0) { scale = __ldg(scale_ptr); inv = __fdividef(1.0f, scale); }
+        const size_t base = ((size_t)n * g.C + c0 + cc0) * (size_t)plane + (size_t)p;
+        if (p < plane) {
+            #pragma unroll 4
+            for (int i = 0; i < 16; i++) {
+                const int c = c0 + cc0 + 4 * i;
+                int level = 0;
+                if (c < g.C) {
+                    const size_t at = base + (size_t)(4 * i) * plane;
+                    if (XK == 0) {
+                        const float v = __ldg((const float*)x + at);
+                        level = quantize_code_8bit<SIGNED ? DTYPE_INT8 : DTYPE_UINT8>(v, scale, inv, zero) - zero;
+                    } else {
+                        const uint8_t code = ((const uint8_t*)x)[at];
+                        level = (SIGNED ? (int)(int8_t)code : (int)code) - zero;
+                    }
                 }
+                tile[pp][cc0 + 4 * i] = level_bits(level);
             }
-            tile[bb][cc0 + 4 * i] = level_bits(v);
         }
     }
     __syncthreads();
     const int part = threadIdx.x & 7, pos0 = threadIdx.x >> 3;     // 8 lanes x 8 channels (16 bytes) per position
     const int c = c0 + part * 8;
-    if (c < g.Cz) {
-        #pragma unroll
-        for (int pass = 0; pass < 2; pass++) {
-            const int bb = pos0 + pass * 32, b = b0 + bb;
-            if (b < g.Wz) {
-                const uint4 val = *reinterpret_cast<const uint4*>(&tile[bb][part * 8]);
-                *reinterpret_cast<uint4*>(z + (((size_t)n * g.Hz + a) * g.Wz + b) * g.Cz + c) = val;
-            }
+    if (c >= g.C) return;
+    const bool vec = (g.C & 7) == 0;                              // every 8-channel group starts on 16 bytes
+    #pragma unroll
+    for (int pass = 0; pass < 2; pass++) {
+        const int pp = pos0 + pass * 32, p = p0 + pp;
+        if (p >= plane) continue;
+        const int h = p / g.W, w = p - h * g.W;
+        int A = h + g.pt, B = w + g.pl, slot = 0;
+        if (g.S == 2) { slot = ((A & 1) * 2 + (B & 1)) * g.C; A >>= 1; B >>= 1; }
+        uint16_t* dst = z + (((size_t)n * g.Hz + A) * g.Wz + B) * g.Cz + slot + c;
+        if (vec) {
+            *reinterpret_cast<uint4*>(dst) = *reinterpret_cast<const uint4*>(&tile[pp][part * 8]);
+        } else {
+            #pragma unroll
+            for (int e = 0; e < 8; e++) if (c + e < g.C) dst[e] = tile[pp][part * 8 + e];
         }
     }
 }
@@ -103,25 +127,26 @@ __global__ void __launch_bounds__(256) filter_codes_to_levels(const int8_t* __re
 
 using namespace tops;
 
-TOPS_API int tops_qlinear_conv_forward(const Tensor* Xq, const Tensor* x_scale, const Tensor* x_zero, const Tensor* Wq,
-                                       const Tensor* w_scale, const Tensor* B, Tensor* Y, ConvParams* params, int relu) {
-    const char* name = "tops_qlinear_conv_forward";
+// x_is_float: X holds float32 values that are quantised on the way (codes of the type of x_zero, int8 when absent)
+static int qconv_run(const char* name, const Tensor* X, bool x_is_float, const Tensor* x_scale, const Tensor* x_zero, const Tensor* Wq,
+                     const Tensor* w_scale, const Tensor* B, Tensor* Y, ConvParams* params, int relu) {
     ConvGeom c;
-    if (!conv_geometry(name, Xq, Wq, B, Y, params, &c)) return tops_last_error();
-    const bool x8 = Xq->dtype == DTYPE_INT8 || Xq->dtype == DTYPE_UINT8;
-    if (!x8 || Wq->dtype != DTYPE_INT8 || !x_scale || !x_scale->data || x_scale->dtype != DTYPE_FLOAT32 || x_scale->size != 1 ||
+    if (!conv_geometry(name, X, Wq, B, Y, params, &c)) return tops_last_error();
+    const bool zero_given = x_zero && x_zero->data;
+    const int code_dt = x_is_float ? (zero_given ? (int)x_zero->dtype : DTYPE_INT8) : (int)X->dtype;
+    const bool x_ok = (code_dt == DTYPE_INT8 || code_dt == DTYPE_UINT8) && (!x_is_float || X->dtype == DTYPE_FLOAT32);
+    if (!x_ok || Wq->dtype != DTYPE_INT8 || !x_scale || !x_scale->data || x_scale->dtype != DTYPE_FLOAT32 || x_scale->size != 1 ||
         !w_scale || !w_scale->data || w_scale->dtype != DTYPE_FLOAT32 || w_scale->size != (size_t)c.M ||
-        (x_zero && x_zero->data && (x_zero->dtype != Xq->dtype || x_zero->size != 1)) ||
-        (B && B->data && B->dtype != DTYPE_FLOAT32)) {
-        set_error(TOPS_ERR_UNSUPPORTED, "%s: wants int8 / uint8 activation codes with one float32 scale (and one zero point of the same "
-                                        "type), int8 filter codes with one float32 scale per output channel, a float32 bias", name);
+        (zero_given && ((int)x_zero->dtype != code_dt || x_zero->size != 1)) || (B && B->data && B->dtype != DTYPE_FLOAT32)) {
+        set_error(TOPS_ERR_UNSUPPORTED, "%s: wants int8 / uint8 activation codes (or float32 values) with one float32 scale and one zero point "
+                                        "of the code type, int8 filter codes with one float32 scale per output channel, a float32 bias", name);
         zero_fill(Y);
         return tops_last_error();
     }
     const int dy = (int)Y->dtype;
     const bool strided = c.sh == 2 && c.sw == 2 && c.dh == 1 && c.dw == 1;
     if (c.G != 1 || !((c.sh == 1 && c.sw == 1) || strided) || c.dh < 1 || c.dw < 1 || c.pt < 0 || c.pl < 0 ||
-        (dy != DTYPE_FLOAT32 && dy != DTYPE_BFLOAT16 && dy != DTYPE_FLOAT16)) {
+        (dy != DTYPE_FLOAT32 && dy != DTYPE_BFLOAT16 && dy != DTYPE_FLOAT16) || (size_t)c.H * c.W >= 0x7FFFFFFFull || c.N > 65535) {
         set_error(TOPS_ERR_UNSUPPORTED, "%s: covers group 1, stride 1 (any dilation) or stride 2 (dilation 1), float32 / bfloat16 / float16 output", name);
         zero_fill(Y);
         return tops_last_error();
@@ -156,12 +181,20 @@ TOPS_API int tops_qlinear_conv_forward(const Tensor* Xq, const Tensor* x_scale, 
         set_error(TOPS_ERR_OOM, "%s: scratch", name);
         return tops_last_error();
     }
-    const dim3 grid(c.N * g.Hz, (g.Wz + 63) / 64, (g.Cz + 63) / 64);
-    const void* zero_ptr = (x_zero && x_zero->data) ? x_zero->data : nullptr;
-    if (Xq->dtype == DTYPE_INT8) codes_to_levels<true><<<grid, 256, 0, s>>>((const uint8_t*)Xq->data, (uint16_t*)z, g, zero_ptr);
-    else codes_to_levels<false><<<grid, 256, 0, s>>>((const uint8_t*)Xq->data, (uint16_t*)z, g, zero_ptr);
+    bool ok = TOPS_CUDA_OK(cudaMemsetAsync(z, 0, z_bytes, s));       // padding cells and padding channels
+    const dim3 grid((c.H * c.W + 63) / 64, c.N, (c.C + 63) / 64);
+    const void* zero_ptr = zero_given ? x_zero->data : nullptr;
+    const float* scale_ptr = (const float*)x_scale->data;
+    const bool is_signed = code_dt == DTYPE_INT8;
+    if (x_is_float) {
+        if (is_signed) activations_to_levels<0, true><<<grid, 256, 0, s>>>(X->data, (uint16_t*)z, g, scale_ptr, zero_ptr);
+        else           activations_to_levels<0, false><<<grid, 256, 0, s>>>(X->data, (uint16_t*)z, g, scale_ptr, zero_ptr);
+    } else {
+        if (is_signed) activations_to_levels<1, true><<<grid, 256, 0, s>>>(X->data, (uint16_t*)z, g, scale_ptr, zero_ptr);
+        else           activations_to_levels<1, false><<<grid, 256, 0, s>>>(X->data, (uint16_t*)z, g, scale_ptr, zero_ptr);
+    }
     filter_codes_to_levels<<<grid_for(wt_bytes / 2, 256, st->sm_count, 4), 256, 0, s>>>((const int8_t*)Wq->data, (uint16_t*)wt, g);
-    bool ok = TOPS_CHECK_LAUNCH(name);
+    ok = ok && TOPS_CHECK_LAUNCH(name);
     if (ok) {
         ShiftedGemm sg;
         sg.xp = z; sg.wt = wt; sg.es = 2; sg.fp8 = false; sg.a_format = 1u; sg.b_format = 1u;
@@ -171,7 +204,7 @@ TOPS_API int tops_qlinear_conv_forward(const Tensor* Xq, const Tensor* x_scale, 
         sg.bias = (B && B->data) ? B->data : nullptr;
         sg.bias_dtype = DTYPE_FLOAT32;
         sg.status = device_status_word();
-        sg.fs.a_scale = (const float*)x_scale->data;
+        sg.fs.a_scale = scale_ptr;
         sg.fs.b_scale = (const float*)w_scale->data;
         sg.fs.b_per_column = 1;
         sg.relu = relu ? 1 : 0;
@@ -182,4 +215,14 @@ TOPS_API int tops_qlinear_conv_forward(const Tensor* Xq, const Tensor* x_scale, 
     if (!ok) return tops_last_error();
     finish_op();
     return TOPS_OK;
+}
+
+TOPS_API int tops_qlinear_conv_forward(const Tensor* Xq, const Tensor* x_scale, const Tensor* x_zero, const Tensor* Wq,
+                                       const Tensor* w_scale, const Tensor* B, Tensor* Y, ConvParams* params, int relu) {
+    return qconv_run("tops_qlinear_conv_forward", Xq, false, x_scale, x_zero, Wq, w_scale, B, Y, params, relu);
+}
+
+TOPS_API int tops_qdq_conv_forward(const Tensor* X, const Tensor* x_scale, const Tensor* x_zero, const Tensor* Wq,
+                                   const Tensor* w_scale, const Tensor* B, Tensor* Y, ConvParams* params, int relu) {
+    return qconv_run("tops_qdq_conv_forward", X, true, x_scale, x_zero, Wq, w_scale, B, Y, params, relu);
 }

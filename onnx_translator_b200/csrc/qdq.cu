@@ -4,52 +4,11 @@
 // scale and zero point at full size.  Here they are broadcast operands: a scalar, a [1,C,1,1]
 // tensor or a full-size tensor all take the same kernel, and only X and Y stream through HBM.
 #include "elementwise.cuh"
+#include "qdq_math.cuh"
 
 namespace tops {
 
-// ---- Quantize ------------------------------------------------------------------------------------------
-// Reference arithmetic: r = (s != 0) ? rint(x / s) + z : z, all in double, then the generic store
-// (integers: rint again + saturate; fp8: encode the integer-valued r).
-//
-// Fast path (x, s exact in float32; z a small integer): rint of the DOUBLE quotient equals rintf of
-// the correctly rounded FLOAT quotient unless a half-integer lies within one float ulp of it; only
-// those rare elements (and |q| >= 2^22) take the double division.
-//
-// The quotient itself is never needed, only its rounding, so the fast path does not divide at all:
-// q ~ x * (1/s) with an approximate reciprocal is within 2^-21 |q| of x / s; adding and subtracting
-// 1.5 * 2^23 rounds it to the nearest integer r (ties to even) and leaves r in the low mantissa
-// bits.  r equals rint(x / s) -- for the exact quotient and for its double rounding alike --
-// whenever q is further than 2^-19 |q| from a tie; the rest (about 1e-5 of the elements for
-// |q| ~ 50, plus s == 0, non-finite x and |q| >= 2^21) take the double division.
-// Returns rint(x / s) + z as an integer; `ok` tells whether the fast path was conclusive.
-__device__ __forceinline__ int quantize_round_fast(float x, float inv_s, int z, bool& ok) {
-    const float q = __fmul_rn(x, inv_s);
-    const float t = __fadd_rn(q, 12582912.0f);
-    const float r = __fsub_rn(t, 12582912.0f);
-    const float aq = fabsf(q);
-    ok = (aq < 2097152.0f) && (__fsub_rn(0.5f, fabsf(__fsub_rn(q, r))) > aq * 1.9073486e-6f);
-    return (__float_as_int(t) - 0x4B400000) + z;
-}
-// 8-bit outputs with an 8-bit zero point: the same rounding and the same tie margin (2^-19 |q|,
-// folded into one multiply-add).  For int8 / uint8, quotients of 4096 and more saturate whichever
-// way they round (|z| <= 255), so they stay on the fast path up to the limit of the magic-number
-// rounding; fp8 outputs take the double division from 2^21 on like every other type.
-// `z_minus_magic` = z - 0x4B400000, the same for every element of a run with one zero point.
-__device__ __forceinline__ int quantize_round_8bit(float x, float inv_s, int z_minus_magic, bool& ok) {
-    const float q = __fmul_rn(x, inv_s);
-    const float t = __fadd_rn(q, 12582912.0f);
-    const float d = __fsub_rn(q, __fsub_rn(t, 12582912.0f));
-    ok = (fmaf(fabsf(q), 1.9073486e-6f, fabsf(d)) < 0.5f) & (fabsf(q) < 2097152.0f);
-    return __float_as_int(t) + z_minus_magic;
-}
-// The reference's arithmetic, element by element.
-template <int DO>
-__device__ __forceinline__ typename Storage<DO>::type quantize_exact(double x, double s, double z) {
-    double r = z;
-    if (s != 0.0) r = __dadd_rn(rint(__ddiv_rn(x, s)), z);
-    return from_f64<DO>(r);
-}
-
+// ---- Quantize (arithmetic: qdq_math.cuh) -------------------------------------------------------------
 template <int DX, int DS, int DZ, int DO, bool ALIGNED>
 struct QuantizeBody {
     static constexpr int kV = vec_width(dtype_bytes(DX), dtype_bytes(DO), dtype_bytes(DO), 64);

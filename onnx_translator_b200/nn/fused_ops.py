@@ -14,11 +14,13 @@ from .Operators import _int_ptr, _pooled_extent
 class QLinearConv(Ops):
     """DequantizeLinear(activation codes) + DequantizeLinear(weight codes) + Conv [+ Relu] in one call
     (replaces nn/Operators.py:452-473 twice, :475-548 and :170-200).
-    inputs: [x_codes, x_scale, x_zero, w_codes, w_scale, bias or ""]."""
+    inputs: [x_codes, x_scale, x_zero, w_codes, w_scale, bias or ""].  With ``from_float`` the first input
+    is the float32 tensor and the QuantizeLinear that makes the codes (:427-450) is part of the call too."""
 
-    def __init__(self, inputs, outputs, pads, strides, dilations, relu, dtype="float32"):
+    def __init__(self, inputs, outputs, pads, strides, dilations, relu, dtype="float32", from_float=False):
         super().__init__(inputs, outputs)
         self.pads, self.strides, self.dilations, self.relu, self.dtype = list(pads), list(strides), list(dilations), bool(relu), dtype
+        self.from_float = bool(from_float)
 
     def forward(self, xq: Tensor, x_scale: Tensor, x_zero: Tensor, wq: Tensor, w_scale: Tensor, b: Tensor = None) -> dict:
         n, _, h, w = xq.data.shape
@@ -31,7 +33,8 @@ class QLinearConv(Ops):
         operands = [xq, x_scale, x_zero, wq, w_scale] + ([b] if b is not None else [])
         handles = [self._numpy_to_ctensor(t.data, t.dtype) for t in operands]
         y = self._new_output(out_shape, self.dtype)
-        rc = self.lib.tops_qlinear_conv_forward(handles[0], handles[1], handles[2], handles[3], handles[4],
+        entry = self.lib.tops_qdq_conv_forward if self.from_float else self.lib.tops_qlinear_conv_forward
+        rc = entry(handles[0], handles[1], handles[2], handles[3], handles[4],
                                                 handles[5] if b is not None else None, y, ctypes.byref(params), int(self.relu))
         out = self._finish(handles, y, out_shape, self.dtype) if not rc else None
         if rc:

@@ -65,7 +65,8 @@ class Graph:
 
             QuantizeLinear -> DequantizeLinear -> Conv(weights = DequantizeLinear(initializers)) [-> Relu]
 
-        chain executed by one ``QLinearConv`` node (the QuantizeLinear stays: it produces the codes).
+        chain executed by one ``QLinearConv`` node (the QuantizeLinear is part of it unless something else
+        reads the codes).
         A chain is taken only when nothing else reads its inner edges, the weight zero points are all
         zero and the convolution is one the fused kernel covers (group 1; stride 1, or stride 2 with
         dilation 1); everything else is left as it is.  Initializers are shared with this graph."""
@@ -104,14 +105,20 @@ class Graph:
                     relu, out_edge = True, nxt.outputs[0]
                     dropped.add(nxt.name)
             bias = conv.inputs[2] if len(conv.inputs) > 2 and conv.inputs[2] else ""
-            node = QLinearConv([q.outputs[0], q.inputs[1], q.inputs[2], dq_w.inputs[0], dq_w.inputs[1], bias], [out_edge],
-                               conv.pads, strides, dil, relu, conv.dtype or "float32")
+            # the QuantizeLinear joins the call when only this chain reads its codes
+            from_float = sole_consumer(q.outputs[0]) and q.name not in dropped
+            if from_float:
+                dropped.add(q.name)
+            node = QLinearConv([q.inputs[0] if from_float else q.outputs[0], q.inputs[1], q.inputs[2], dq_w.inputs[0], dq_w.inputs[1], bias],
+                               [out_edge], conv.pads, strides, dil, relu, conv.dtype or "float32", from_float=from_float)
             node.name = conv.name + ".fused"
             dropped.update((dq_x.name, dq_w.name))
             replaced[conv.name] = node
         kept = [replaced.get(op.name, op) for op in nodes if op.name not in dropped]
         g = Graph(kept, list(self.input_name), list(self.output_name), self.model_name, self.initializers)
         g._resident = self._resident
+        if hasattr(self, "macs_per_image"):
+            g.macs_per_image = self.macs_per_image
         return g
 
     def make_resident(self) -> None:
@@ -206,6 +213,7 @@ class _QdqBuilder:
         self.init: Dict[str, object] = {}
         self.live = {"x": calibration}          # calibration values of the float32 edges
         self.counter = 0
+        self.macs_per_image = 0                 # multiply-accumulates of the convolutions and the classifier
 
     def _name(self, stem):
         self.counter += 1
@@ -244,6 +252,8 @@ class _QdqBuilder:
                               group=1, dtype=f32))
         for edge in (q, dq, wdq):
             self.live.pop(edge, None)
+        _, _, oh, ow = self.live[y].data.shape
+        self.macs_per_image += oh * ow * c_out * c_in * k * k
         if relu:
             y = self.add(ops.RELU([y], [f"{tag}.relu"], dtype=f32))
         return y
@@ -285,4 +295,6 @@ def qdq_resnet50(batch: int = 256, seed: int = 0, image: int = 224, stages: Sequ
     b.init["fc.b"] = _tensor(np.zeros(classes, np.float32), f32)
     y = b.add(ops.Gemm([y, "fc.w", "fc.b"], ["logits"], alpha=1.0, beta=1.0, transA=0, transB=1, dtype=f32))
     b.add(ops.Softmax([y], ["prob"], axis=1, dtype=f32))
-    return Graph(b.nodes, "x", ["prob"], "qdq_resnet50", b.init), _tensor(x, f32)
+    graph = Graph(b.nodes, "x", ["prob"], "qdq_resnet50", b.init)
+    graph.macs_per_image = b.macs_per_image + classes * c_in
+    return graph, _tensor(x, f32)

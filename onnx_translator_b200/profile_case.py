@@ -142,6 +142,17 @@ def main():
         call = lambda: lib.conv2d_forward(x.handle, w.handle, None, o.handle, ctypes.byref(prm))
         nbytes = x.size * ITEM[dt] + w.size * ITEM[dt] + o.size * ITEM[out_dt]
         flops = 2.0 * n_ * hw * hw * c_ * c_ * 9
+    elif args.op == "qdq_resnet50":
+        # the QDQ ResNet-50-shaped graph through Graph.fused(); --batch images of 224 x 224
+        from . import nn
+        graph, x_host = nn.qdq_resnet50(batch=args.batch, seed=0)
+        fused = graph.fused()
+        xd = x_host.to_device()
+        keep = [graph, fused, xd]
+        call = lambda: fused.forward(xd)
+        nbytes = 0
+        flops = 2.0 * graph.macs_per_image * args.batch
+        dt = out_dt = "float32"
     else:
         raise SystemExit(f"unknown op {args.op}")
 

@@ -296,3 +296,17 @@ def test_qlinear_conv_against_the_unfused_chain_in_float64(port, case):
     assert _tc_count() == before + 1
     assert got.shape == want.shape
     _gate(got, want, s_mag, "float32", "qlinear conv")
+    # one operator earlier: float32 activations whose QuantizeLinear codes are exactly xq (values at and
+    # around the rounding ties and beyond the saturation limits included) must give the same bits
+    x = ((xq.astype(np.float64) - zero) * sx[0]).astype(np.float32)
+    x.reshape(-1)[::7] += np.float32(0.3 * sx[0])
+    x.reshape(-1)[3::11] -= np.float32(0.49 * sx[0])
+    x.reshape(-1)[5::13] = np.float32(1e6)
+    x.reshape(-1)[6::17] = np.nextafter((xq.reshape(-1)[6::17].astype(np.float64) - zero + 0.5) * sx[0], np.inf).astype(np.float32)
+    codes = port.quantize(x, "float32", sx, "float32", zx, x_dt, x_dt)
+    from_codes = node.forward(T(codes, x_dt), T(sx, "float32"), T(zx, x_dt), T(wq, "int8"), T(ws, "float32"),
+                              None if b is None else T(b, "float32"))["tensor"].numpy()
+    node_f = QLinearConv([], [], [pad] * 4, [stride, stride], [1, 1], relu, "float32", from_float=True)
+    from_float = node_f.forward(T(x, "float32"), T(sx, "float32"), T(zx, x_dt), T(wq, "int8"), T(ws, "float32"),
+                                None if b is None else T(b, "float32"))["tensor"].numpy()
+    assert np.array_equal(from_codes.view(np.uint32), from_float.view(np.uint32))
