@@ -536,7 +536,20 @@ def qdq_cnn_throughput(lib, stream, world, local, batch=256):
     ms = float(t.cpu()[0])
     prob = out.numpy()
     flops = 2.0 * graph.macs_per_image * batch
-    return {"images_per_s": round(world * batch / (ms / 1e3), 1), "ms_per_batch": round(ms, 3), "batch_per_gpu": batch,
+    cpu = None
+    if world == 1:
+        # the same graph (unfused, as the reference would run it) on the host cores, one image
+        import oracle
+        from oracle import graph as oracle_graph
+        kind = "reference" if oracle.available("ref") else "port"
+        host = oracle.HostOracle("ref" if kind == "reference" else "port")
+        cores = oracle.use_all_host_threads()
+        one = nn.Tensor(1, 3, 224, 224, dtype="float32", data=np.ascontiguousarray(x.numpy()[:1]))
+        t0 = time.perf_counter()
+        oracle_graph.run(graph, host, one)
+        dt = time.perf_counter() - t0
+        cpu = {"images_per_s": round(1.0 / dt, 3), "cores": cores, "kind": kind, "sample": f"1 image, {dt:.1f} s, C functions node by node"}
+    return {"cpu_baseline": cpu, "images_per_s": round(world * batch / (ms / 1e3), 1), "ms_per_batch": round(ms, 3), "batch_per_gpu": batch,
             "n_gpus": world, "TFLOPs_per_gpu": round(flops / 1e12 / (ms / 1e3), 1), "gflop_per_image": round(2.0 * graph.macs_per_image / 1e9, 2),
             "tensor_core_launches_per_batch": int((lib.tops_tensor_core_launches() - before) // iters),
             "nodes": len(fused.ops), "nodes_unfused": len(graph.ops),

@@ -1,5 +1,5 @@
-"""Runs a ``Graph`` of onnx_translator_b200 on the CPU oracle, node by node: the checker for whole
-graphs.  Edges are numpy arrays in storage convention; node attributes are read from the very
+"""Test infrastructure, like the rest of this package: runs a ``Graph`` of onnx_translator_b200 on the
+CPU oracle, node by node -- the checker for whole graphs and the CPU baseline of the graph benchmark.  Edges are numpy arrays in storage convention; node attributes are read from the very
 operator objects the device runner executes."""
 import numpy as np
 

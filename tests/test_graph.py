@@ -69,7 +69,7 @@ def _bits_equal(got, want):
 
 @pytest.mark.gpu
 def test_small_cnn_graph_matches_the_oracle(port):
-    import oracle_graph
+    from oracle import graph as oracle_graph
     from onnx_translator_b200 import nn
     graph, x = nn.small_cnn(seed=0)
     prob, side = graph.forward(x)
@@ -85,7 +85,7 @@ def test_qdq_resnet_shaped_graph_matches_the_oracle_node_for_node(port):
     """A small instance of the QDQ ResNet-50-shaped graph (same node pattern, one block per stage).
     With every convolution on the exact kernel the logits agree bit for bit; the softmax within 1e-6."""
     import os
-    import oracle_graph
+    from oracle import graph as oracle_graph
     from onnx_translator_b200 import nn
     os.environ["TOPS_DISABLE_TC"] = "1"
     try:
@@ -108,7 +108,7 @@ def test_fused_graph_replaces_every_qdq_conv_chain_and_stays_close_to_the_oracle
     """Graph.fused() turns each Q -> DQ -> Conv(DQ(w)) [-> Relu] chain into one node.  The fused
     convolutions differ from the chain within the tensor-core tolerance, which moves a few activation
     codes by one step in later layers; the logits stay within 1 % (relative L2) of the oracle's."""
-    import oracle_graph
+    from oracle import graph as oracle_graph
     from onnx_translator_b200 import nn
     graph, x = nn.qdq_resnet50(batch=2, seed=0, image=64, stages=(1, 1, 1, 1), widths=(8, 16, 24, 32), classes=20)
     graph.output_name = ["logits", "prob"]
