@@ -228,23 +228,24 @@ int tops_conv2d_dqw_forward(const Tensor* X, const Tensor* Wq, const Tensor* w_s
                             ConvParams* params);
 
 /* The convolution of a QDQ network in one call, starting from the activation codes:
-     Y = [Relu]( Conv( DQ(Xq, x_scale, x_zero), DQ(Wq, w_scale, 0) ) + B )
-   replaces DequantizeLinear (activations), DequantizeLinear (weights), Conv and an optional Relu
+     Y = [Relu]( Conv( DQ(Xq, x_scale, x_zero), DQ(Wq, w_scale, 0) ) + B [+ R] )
+   replaces DequantizeLinear (activations), DequantizeLinear (weights), Conv, an optional Add of a
+   residual tensor R (float32, shape of Y, NULL for none) and an optional Relu
    (nn/Operators.py:452-473, 475-548, 170-200).  Xq int8 / uint8 NCHW with one scale and one zero
    point (x_zero may be NULL for 0), Wq int8 [M, C, KH, KW] with one float32 scale per output
    channel, B float32 or NULL, Y float32 / bfloat16 / float16.  Group 1; stride 1 with any dilation,
    or stride 2 with dilation 1; any C (the library pads channels in its scratch copy).  The integer
    levels are exact on the bfloat16 tensor path; see csrc/qconv.cu for the arithmetic. */
 int tops_qlinear_conv_forward(const Tensor* Xq, const Tensor* x_scale, const Tensor* x_zero, const Tensor* Wq,
-                              const Tensor* w_scale, const Tensor* B, Tensor* Y, ConvParams* params, int relu);
+                              const Tensor* w_scale, const Tensor* B, const Tensor* R, Tensor* Y, ConvParams* params, int relu);
 
 /* The same starting one operator earlier, from float32 activations:
-     Y = [Relu]( Conv( DQ( Q(X, x_scale, x_zero), x_scale, x_zero ), DQ(Wq, w_scale, 0) ) + B )
+     Y = [Relu]( Conv( DQ( Q(X, x_scale, x_zero), x_scale, x_zero ), DQ(Wq, w_scale, 0) ) + B [+ R] )
    replaces QuantizeLinear -> DequantizeLinear -> Conv [-> Relu] (nn/Operators.py:427-450 in addition
    to the operators named above).  The codes are those quantize_linear_forward would store, of the
    type of x_zero (int8 when x_zero is NULL). */
 int tops_qdq_conv_forward(const Tensor* X, const Tensor* x_scale, const Tensor* x_zero, const Tensor* Wq,
-                          const Tensor* w_scale, const Tensor* B, Tensor* Y, ConvParams* params, int relu);
+                          const Tensor* w_scale, const Tensor* B, const Tensor* R, Tensor* Y, ConvParams* params, int relu);
 
 /* Device-side exhaustive codec self-check: encodes every float32 bit pattern with the fast
    (hardware-convert) encoder and with the bit-level restatement of the reference encoder and

@@ -120,8 +120,8 @@ SIGNATURES = {
     "tops_conv2d_noalloc_limits": (_SZ, [ctypes.POINTER(_SZ), ctypes.POINTER(_SZ)]),
     "tops_gemm_qdq_forward": (_I, [_P, _P, _P, _P, _P, _P, _P, ctypes.c_float, ctypes.c_float, _I, _I]),
     "tops_conv2d_dqw_forward": (_I, [_P, _P, _P, _P, _P, ctypes.POINTER(CConvParams)]),
-    "tops_qlinear_conv_forward": (_I, [_P, _P, _P, _P, _P, _P, _P, ctypes.POINTER(CConvParams), _I]),
-    "tops_qdq_conv_forward": (_I, [_P, _P, _P, _P, _P, _P, _P, ctypes.POINTER(CConvParams), _I]),
+    "tops_qlinear_conv_forward": (_I, [_P, _P, _P, _P, _P, _P, _P, _P, ctypes.POINTER(CConvParams), _I]),
+    "tops_qdq_conv_forward": (_I, [_P, _P, _P, _P, _P, _P, _P, _P, ctypes.POINTER(CConvParams), _I]),
     "tops_selftest_encoder": (ctypes.c_longlong, [_I]),
     "tops_tensor_core_launches": (ctypes.c_longlong, []),
     "tops_selftest_cos": (ctypes.c_longlong, []),

@@ -47,6 +47,7 @@ struct ShiftedGemm {
     int* status = nullptr;
     EpilogueScales fs;
     int relu = 0;
+    const float* residual = nullptr;          // float32, shape of Y: added to the result before the optional Relu
 };
 bool shifted_gemm_launch(const ShiftedGemm& g);
 

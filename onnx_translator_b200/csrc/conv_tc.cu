@@ -198,6 +198,7 @@ bool shifted_gemm_launch(const ShiftedGemm& g) {
     p.cv.KW = g.KW; p.cv.dil_h = g.dil_h; p.cv.dil_w = g.dil_w;
     p.fs = g.fs;
     p.relu = g.relu;
+    p.residual = g.residual;
     const uint32_t idesc = umma::instr_desc(g.a_format, g.b_format, kBM, kBN);
     const int tiles = p.tiles_m * p.tiles_n;
     const int grid = tiles < st->sm_count ? tiles : st->sm_count;

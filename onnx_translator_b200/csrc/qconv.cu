@@ -1,6 +1,6 @@
 // Convolution of a quantised graph in one call:
 //
-//     Y = [Relu]( Conv( DequantizeLinear(Xq, x_scale, x_zero), DequantizeLinear(Wq, w_scale, 0) ) + B )
+//     Y = [Relu]( Conv( DequantizeLinear(Xq, x_scale, x_zero), DequantizeLinear(Wq, w_scale, 0) ) + B [+ R] )
 //
 // i.e. the chain QuantizeLinear -> DequantizeLinear -> Conv (weights through DequantizeLinear) [-> Relu]
 // that wraps every convolution of a QDQ network (reference operators: nn/Operators.py:427-473, 475-548,
@@ -52,33 +52,37 @@ __device__ __forceinline__ uint16_t level_bits(int v) {        // small integer 
 template <int XK, bool SIGNED>
 __global__ void __launch_bounds__(256) activations_to_levels(const void* __restrict__ x, uint16_t* __restrict__ z, QGeom g,
                                                              const float* __restrict__ scale_ptr, const void* __restrict__ zero_ptr) {
-    __shared__ __align__(16) uint16_t tile[64][72];            // [position][channel]
+    // [position][channel pair], 33 words per row: conflict-free for the column-wise fill (consecutive
+    // lanes = consecutive positions) and for the row-wise drain (8 lanes x 4 words per position)
+    __shared__ uint32_t tile[64][33];
     const int plane = g.H * g.W;
     const int p0 = blockIdx.x * 64, n = blockIdx.y, c0 = blockIdx.z * 64;
     int zero = 0;
     if (zero_ptr) zero = SIGNED ? (int)*(const int8_t*)zero_ptr : (int)*(const uint8_t*)zero_ptr;
     {
-        const int pp = threadIdx.x & 63, cc0 = threadIdx.x >> 6;
+        const int pp = threadIdx.x & 63, cq = threadIdx.x >> 6;
         const int p = p0 + pp;
         float scale = 1.0f, inv = 1.0f;
         if (XK == 0) { scale = __ldg(scale_ptr); inv = __fdividef(1.0f, scale); }
-        const size_t base = ((size_t)n * g.C + c0 + cc0) * (size_t)plane + (size_t)p;
         if (p < plane) {
             #pragma unroll 4
-            for (int i = 0; i < 16; i++) {
-                const int c = c0 + cc0 + 4 * i;
-                int level = 0;
-                if (c < g.C) {
-                    const size_t at = base + (size_t)(4 * i) * plane;
-                    if (XK == 0) {
-                        const float v = __ldg((const float*)x + at);
-                        level = quantize_code_8bit<SIGNED ? DTYPE_INT8 : DTYPE_UINT8>(v, scale, inv, zero) - zero;
-                    } else {
-                        const uint8_t code = ((const uint8_t*)x)[at];
-                        level = (SIGNED ? (int)(int8_t)code : (int)code) - zero;
+            for (int i = 0; i < 8; i++) {
+                const int cp = cq + 4 * i, c = c0 + 2 * cp;             // channels c and c + 1 share a word
+                int level[2] = {0, 0};
+                #pragma unroll
+                for (int e = 0; e < 2; e++) {
+                    if (c + e < g.C) {
+                        const size_t at = ((size_t)n * g.C + c + e) * (size_t)plane + (size_t)p;
+                        if (XK == 0) {
+                            const float v = __ldg((const float*)x + at);
+                            level[e] = quantize_code_8bit<SIGNED ? DTYPE_INT8 : DTYPE_UINT8>(v, scale, inv, zero) - zero;
+                        } else {
+                            const uint8_t code = ((const uint8_t*)x)[at];
+                            level[e] = (SIGNED ? (int)(int8_t)code : (int)code) - zero;
+                        }
                     }
                 }
-                tile[pp][cc0 + 4 * i] = level_bits(level);
+                tile[pp][cp] = (uint32_t)level_bits(level[0]) | ((uint32_t)level_bits(level[1]) << 16);
             }
         }
     }
@@ -95,11 +99,13 @@ __global__ void __launch_bounds__(256) activations_to_levels(const void* __restr
         int A = h + g.pt, B = w + g.pl, slot = 0;
         if (g.S == 2) { slot = ((A & 1) * 2 + (B & 1)) * g.C; A >>= 1; B >>= 1; }
         uint16_t* dst = z + (((size_t)n * g.Hz + A) * g.Wz + B) * g.Cz + slot + c;
+        const uint4 val = make_uint4(tile[pp][part * 4], tile[pp][part * 4 + 1], tile[pp][part * 4 + 2], tile[pp][part * 4 + 3]);
         if (vec) {
-            *reinterpret_cast<uint4*>(dst) = *reinterpret_cast<const uint4*>(&tile[pp][part * 8]);
+            *reinterpret_cast<uint4*>(dst) = val;
         } else {
+            const uint32_t words[4] = {val.x, val.y, val.z, val.w};
             #pragma unroll
-            for (int e = 0; e < 8; e++) if (c + e < g.C) dst[e] = tile[pp][part * 8 + e];
+            for (int e = 0; e < 8; e++) if (c + e < g.C) dst[e] = (uint16_t)(words[e >> 1] >> ((e & 1) * 16));
         }
     }
 }
@@ -129,7 +135,7 @@ using namespace tops;
 
 // x_is_float: X holds float32 values that are quantised on the way (codes of the type of x_zero, int8 when absent)
 static int qconv_run(const char* name, const Tensor* X, bool x_is_float, const Tensor* x_scale, const Tensor* x_zero, const Tensor* Wq,
-                     const Tensor* w_scale, const Tensor* B, Tensor* Y, ConvParams* params, int relu) {
+                     const Tensor* w_scale, const Tensor* B, const Tensor* residual, Tensor* Y, ConvParams* params, int relu) {
     ConvGeom c;
     if (!conv_geometry(name, X, Wq, B, Y, params, &c)) return tops_last_error();
     const bool zero_given = x_zero && x_zero->data;
@@ -137,9 +143,10 @@ static int qconv_run(const char* name, const Tensor* X, bool x_is_float, const T
     const bool x_ok = (code_dt == DTYPE_INT8 || code_dt == DTYPE_UINT8) && (!x_is_float || X->dtype == DTYPE_FLOAT32);
     if (!x_ok || Wq->dtype != DTYPE_INT8 || !x_scale || !x_scale->data || x_scale->dtype != DTYPE_FLOAT32 || x_scale->size != 1 ||
         !w_scale || !w_scale->data || w_scale->dtype != DTYPE_FLOAT32 || w_scale->size != (size_t)c.M ||
-        (zero_given && ((int)x_zero->dtype != code_dt || x_zero->size != 1)) || (B && B->data && B->dtype != DTYPE_FLOAT32)) {
+        (zero_given && ((int)x_zero->dtype != code_dt || x_zero->size != 1)) || (B && B->data && B->dtype != DTYPE_FLOAT32) ||
+        (residual && residual->data && (residual->dtype != DTYPE_FLOAT32 || residual->size != Y->size))) {
         set_error(TOPS_ERR_UNSUPPORTED, "%s: wants int8 / uint8 activation codes (or float32 values) with one float32 scale and one zero point "
-                                        "of the code type, int8 filter codes with one float32 scale per output channel, a float32 bias", name);
+                                        "of the code type, int8 filter codes with one float32 scale per output channel, a float32 bias, a float32 residual of Y's size", name);
         zero_fill(Y);
         return tops_last_error();
     }
@@ -208,6 +215,7 @@ static int qconv_run(const char* name, const Tensor* X, bool x_is_float, const T
         sg.fs.b_scale = (const float*)w_scale->data;
         sg.fs.b_per_column = 1;
         sg.relu = relu ? 1 : 0;
+        sg.residual = (residual && residual->data) ? (const float*)residual->data : nullptr;
         ok = shifted_gemm_launch(sg);
     }
     cudaFreeAsync(z, s);
@@ -218,11 +226,13 @@ static int qconv_run(const char* name, const Tensor* X, bool x_is_float, const T
 }
 
 TOPS_API int tops_qlinear_conv_forward(const Tensor* Xq, const Tensor* x_scale, const Tensor* x_zero, const Tensor* Wq,
-                                       const Tensor* w_scale, const Tensor* B, Tensor* Y, ConvParams* params, int relu) {
-    return qconv_run("tops_qlinear_conv_forward", Xq, false, x_scale, x_zero, Wq, w_scale, B, Y, params, relu);
+                                       const Tensor* w_scale, const Tensor* B, const Tensor* residual, Tensor* Y,
+                                       ConvParams* params, int relu) {
+    return qconv_run("tops_qlinear_conv_forward", Xq, false, x_scale, x_zero, Wq, w_scale, B, residual, Y, params, relu);
 }
 
 TOPS_API int tops_qdq_conv_forward(const Tensor* X, const Tensor* x_scale, const Tensor* x_zero, const Tensor* Wq,
-                                   const Tensor* w_scale, const Tensor* B, Tensor* Y, ConvParams* params, int relu) {
-    return qconv_run("tops_qdq_conv_forward", X, true, x_scale, x_zero, Wq, w_scale, B, Y, params, relu);
+                                   const Tensor* w_scale, const Tensor* B, const Tensor* residual, Tensor* Y,
+                                   ConvParams* params, int relu) {
+    return qconv_run("tops_qdq_conv_forward", X, true, x_scale, x_zero, Wq, w_scale, B, residual, Y, params, relu);
 }

@@ -42,6 +42,7 @@ struct TcParams {
     ConvView cv;           // convolution mode only
     EpilogueScales fs;
     int relu = 0;          // clamp the result at zero before it is stored (v > 0 ? v : 0)
+    const float* residual = nullptr;   // convolution mode: float32 tensor of the output's shape added before the clamp
 };
 
 __device__ __forceinline__ void tile_coords(int tile, int tiles_m, int tiles_n, int& tm, int& tn) {
@@ -186,16 +187,43 @@ tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUt
                 }
                 __syncwarp();
             }
+            // convolution mode: where this lane's row goes in the NCHW output, and the residual values
+            // of the first column chunk, requested before the accumulator is even complete
+            bool conv_row = false;
+            size_t conv_base = 0, plane_out = 0;
+            float res_next[32];
+            const bool with_res = MODE == kModeConv && p.residual != nullptr;
+            if constexpr (MODE == kModeConv) {
+                const int img = m / p.cv.plane, rem = m - img * p.cv.plane;
+                const int oh = rem / p.cv.Wp, ow = rem - oh * p.cv.Wp;
+                conv_row = img < p.cv.images && oh < p.cv.OH && ow < p.cv.OW;
+                plane_out = (size_t)p.cv.OH * p.cv.OW;
+                conv_base = ((size_t)img * p.cv.OC + (size_t)tn * kBN) * plane_out + (size_t)oh * p.cv.OW + ow;
+            }
+            auto fetch_residual = [&](int chunk, float (&dst)[32]) {
+                const float* src = p.residual + conv_base + (size_t)(chunk * 32) * plane_out;
+                #pragma unroll
+                for (int j = 0; j < 32; j++)
+                    dst[j] = (conv_row && tn * kBN + chunk * 32 + j < p.N) ? __ldg(src + (size_t)j * plane_out) : 0.0f;
+            };
+            if (with_res) fetch_residual(0, res_next);
             if (!umma::mbar_wait(&acc_full[buf], use, abort_flag)) break;
             umma::fence_after_sync();
             const uint32_t t_row = tmem_base + ((uint32_t)(quarter * 32) << 16) + buf * kBN;
             #pragma unroll 1
             for (int c = 0; c < kBN / 32; c++) {
+                const int n0 = tn * kBN + c * 32;
+                if (n0 >= p.N) break;                              // warp-uniform: no columns left in this tile
+                float res_cur[32];
+                if (with_res) {                                    // the next chunk's values travel while this one is processed
+                    #pragma unroll
+                    for (int j = 0; j < 32; j++) res_cur[j] = res_next[j];
+                    if (n0 + 32 < p.N && c + 1 < kBN / 32) fetch_residual(c + 1, res_next);
+                }
                 uint32_t r[32];
                 umma::tmem_load_32x32(t_row + (uint32_t)(c * 32), r);
                 umma::tmem_load_wait();
-                const int n0 = tn * kBN + c * 32;
-                if (n0 < p.N) {                                    // warp-uniform
+                {
                     float v[32];
                     #pragma unroll
                     for (int j = 0; j < 32; j++) {
@@ -227,18 +255,22 @@ tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUt
                         #pragma unroll
                         for (int j = 0; j < 32; j++) v[j] = __fmaf_rn(p.beta, cv[j], v[j]);
                     }
-                    if (p.relu) {
+                    if (p.relu && (MODE != kModeConv || !p.residual)) {
                         #pragma unroll
                         for (int j = 0; j < 32; j++) v[j] = v[j] > 0.0f ? v[j] : 0.0f;
                     }
                     if constexpr (MODE == kModeConv) {
                         // NCHW output: for one output channel, consecutive lanes (consecutive padded
                         // positions) are consecutive pixels, so each store instruction is contiguous.
-                        const int img = m / p.cv.plane, rem = m - img * p.cv.plane;
-                        const int oh = rem / p.cv.Wp, ow = rem - oh * p.cv.Wp;
-                        if (img < p.cv.images && oh < p.cv.OH && ow < p.cv.OW) {
-                            const size_t plane_out = (size_t)p.cv.OH * p.cv.OW;
-                            const size_t base = ((size_t)img * p.cv.OC + n0) * plane_out + (size_t)oh * p.cv.OW + ow;
+                        if (conv_row) {
+                            const size_t base = conv_base + (size_t)(c * 32) * plane_out;
+                            if (with_res) {                            // Add(conv, residual) [-> Relu], as separate float32 operators would round
+                                #pragma unroll
+                                for (int j = 0; j < 32; j++) {
+                                    v[j] = __fadd_rn(v[j], res_cur[j]);
+                                    if (p.relu) v[j] = v[j] > 0.0f ? v[j] : 0.0f;
+                                }
+                            }
                             if (p.dy == DTYPE_FLOAT32) {
                                 float* dst = (float*)p.Y + base;
                                 #pragma unroll

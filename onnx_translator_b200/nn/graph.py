@@ -66,7 +66,8 @@ class Graph:
             QuantizeLinear -> DequantizeLinear -> Conv(weights = DequantizeLinear(initializers)) [-> Relu]
 
         chain executed by one ``QLinearConv`` node (the QuantizeLinear is part of it unless something else
-        reads the codes).
+        reads the codes); a following Add of another float32 tensor [-> Relu] -- the tail of a residual
+        block -- joins that node's epilogue.
         A chain is taken only when nothing else reads its inner edges, the weight zero points are all
         zero and the convolution is one the fused kernel covers (group 1; stride 1, or stride 2 with
         dilation 1); everything else is left as it is.  Initializers are shared with this graph."""
@@ -115,6 +116,39 @@ class Graph:
             dropped.update((dq_x.name, dq_w.name))
             replaced[conv.name] = node
         kept = [replaced.get(op.name, op) for op in nodes if op.name not in dropped]
+
+        # second pass: QLinearConv -> Add(., other float32 tensor) [-> Relu] joins the convolution's epilogue
+        order = {op.name: i for i, op in enumerate(kept)}
+        made_by = {e: op for op in kept for e in op.outputs}
+        readers: Dict[str, list] = {}
+        for op in kept:
+            for e in op.inputs:
+                if e:
+                    readers.setdefault(e, []).append(op)
+        gone = set()
+        for add in kept:
+            if kind(add) != "ADD" or add.name in gone or (add.dtype or "float32") != "float32":
+                continue
+            cands = []
+            for mine, other in ((add.inputs[0], add.inputs[1]), (add.inputs[1], add.inputs[0])):
+                conv = made_by.get(mine)
+                if (conv is not None and kind(conv) == "QLinearConv" and not conv.relu and conv.dtype == "float32" and mine != other
+                        and len(conv.inputs) == 6 and len(readers.get(mine, [])) == 1 and mine not in self.output_name
+                        and order.get(getattr(made_by.get(other), "name", None), -1) < order[conv.name]):
+                    cands.append((order[conv.name], conv, other))
+            if not cands:
+                continue
+            _, conv, other = max(cands, key=lambda t: t[0])
+            out_edge, relu = add.outputs[0], False
+            after = readers.get(out_edge, [])
+            if len(after) == 1 and kind(after[0]) == "RELU" and out_edge not in self.output_name and (after[0].dtype or "float32") == "float32":
+                relu, out_edge = True, after[0].outputs[0]
+                gone.add(after[0].name)
+            gone.add(add.name)
+            conv.inputs = list(conv.inputs) + [other]
+            conv.outputs = [out_edge]
+            conv.relu = relu
+        kept = [op for op in kept if op.name not in gone]
         g = Graph(kept, list(self.input_name), list(self.output_name), self.model_name, self.initializers)
         g._resident = self._resident
         if hasattr(self, "macs_per_image"):

@@ -310,3 +310,27 @@ def test_qlinear_conv_against_the_unfused_chain_in_float64(port, case):
     from_float = node_f.forward(T(x, "float32"), T(sx, "float32"), T(zx, x_dt), T(wq, "int8"), T(ws, "float32"),
                                 None if b is None else T(b, "float32"))["tensor"].numpy()
     assert np.array_equal(from_codes.view(np.uint32), from_float.view(np.uint32))
+
+
+def test_qlinear_conv_with_residual_equals_the_three_operators_bit_for_bit():
+    """Conv + Add(residual) + Relu in the epilogue rounds exactly like the three float32 operators in sequence."""
+    from onnx_translator_b200.nn import Tensor
+    from onnx_translator_b200.nn import Operators as ops
+    from onnx_translator_b200.nn.fused_ops import QLinearConv
+    rng = np.random.default_rng(8)
+    n, c, h, m = 3, 32, 20, 72
+    x = rng.normal(0, 1, (n, c, h, h)).astype(np.float32)
+    wq = rng.integers(-127, 128, (m, c, 3, 3)).astype(np.int8)
+    sx, zx = np.array([0.03], np.float32), np.array([2], np.int8)
+    ws = rng.uniform(0.005, 0.02, (m, 1, 1, 1)).astype(np.float32)
+    b = rng.normal(0, 1, m).astype(np.float32)
+    res = rng.normal(0, 3, (n, m, h, h)).astype(np.float32)
+    T = lambda a, dt: Tensor(*a.shape, dtype=dt, data=a)
+    args = (T(x, "float32"), T(sx, "float32"), T(zx, "int8"), T(wq, "int8"), T(ws, "float32"), T(b, "float32"))
+    plain = QLinearConv([], [], [1] * 4, [1, 1], [1, 1], False, "float32", from_float=True).forward(*args)["tensor"]
+    want = ops.RELU([], [], dtype="float32").forward(ops.ADD([], [], dtype="float32").forward(plain, T(res, "float32"))["tensor"])["tensor"].numpy()
+    got = QLinearConv([], [], [1] * 4, [1, 1], [1, 1], True, "float32", from_float=True).forward(*args, T(res, "float32"))["tensor"].numpy()
+    assert np.array_equal(got.view(np.uint32), want.view(np.uint32))
+    no_relu = QLinearConv([], [], [1] * 4, [1, 1], [1, 1], False, "float32", from_float=True).forward(*args, T(res, "float32"))["tensor"].numpy()
+    want2 = ops.ADD([], [], dtype="float32").forward(plain, T(res, "float32"))["tensor"].numpy()
+    assert np.array_equal(no_relu.view(np.uint32), want2.view(np.uint32))

@@ -116,7 +116,8 @@ def test_fused_graph_replaces_every_qdq_conv_chain_and_stays_close_to_the_oracle
     kinds = [type(op).__name__ for op in fused.ops.values()]
     convs = sum(type(op).__name__ == "Conv" for op in graph.ops.values())
     assert kinds.count("QLinearConv") == convs and kinds.count("Conv") == 0 and kinds.count("DequantizeLinear") == 0
-    assert kinds.count("QuantizeLinear") == 0 and kinds.count("RELU") == 4              # only the post-add Relus remain
+    assert kinds.count("QuantizeLinear") == 0 and kinds.count("RELU") == 0 and kinds.count("ADD") == 0
+    assert sum(len(op.inputs) == 7 for op in fused.ops.values()) == 4                   # the four residual tails
     logits, prob = fused.forward(x)
     want_logits, want_prob = oracle_graph.run(graph, port, x)
     got = logits.numpy().astype(np.float64)
