@@ -158,6 +158,7 @@ tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUt
         if (p.fs.a_scale) alpha = __fmul_rn(alpha, __ldg(p.fs.a_scale));
         if (p.fs.b_scale && !p.fs.b_per_column) alpha = __fmul_rn(alpha, __ldg(p.fs.b_scale));
         const float y_scale = p.fs.y_scale ? __ldg(p.fs.y_scale) : 0.0f;
+        const float y_inv = y_scale != 0.0f ? __frcp_rn(y_scale) : 0.0f;     // y / s as y * (1 / s): off by an ulp at most, like the accumulation itself
         for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x, local++) {
             const uint32_t buf = local & 1u, use = (local >> 1) & 1u;
             int tm, tn;
@@ -308,7 +309,7 @@ tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUt
                             #pragma unroll
                             for (int e = 0; e < 4; e++) {
                                 float q = v[j + e];
-                                if (p.fs.y_scale) q = y_scale != 0.0f ? rintf(__fdiv_rn(q, y_scale)) : 0.0f;
+                                if (p.fs.y_scale) q = rintf(__fmul_rn(q, y_inv));
                                 uint32_t code;
                                 if (p.dy == DTYPE_FLOAT8_E4M3) code = encode_e4m3(q);
                                 else if (p.dy == DTYPE_FLOAT8_E5M2) code = encode_e5m2(q);
