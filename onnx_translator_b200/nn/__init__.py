@@ -73,7 +73,12 @@ class Ops:
         self.parameters = {}
         self.name = None
         self.dtype = None
-        self.lib = self._get_lib()
+
+    @property
+    def lib(self):
+        """The operator library, opened at the first use: a node can be constructed (and a graph built and
+        inspected) on a machine without a GPU; running it there raises."""
+        return self._get_lib()
 
     # -- marshalling ---------------------------------------------------------------------------
     def _numpy_to_ctensor(self, arr, dtype: str):

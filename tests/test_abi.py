@@ -123,6 +123,7 @@ def test_no_gpu_means_errors_not_a_cpu_path(lib):
     lib.tops_clear_error()
     from onnx_translator_b200 import nn
     nn.Ops._lib = None
-    with pytest.raises(capi.TensorOpsError):
-        nn.Ops([], [])
+    node = nn.Operators.RELU([], [], dtype="float32")           # constructing a node needs no GPU ...
+    with pytest.raises(capi.TensorOpsError):                     # ... running it without one fails loudly
+        node.forward(nn.Tensor(4, dtype="float32"))
     lib.tops_clear_error()

@@ -125,3 +125,29 @@ def test_fused_graph_replaces_every_qdq_conv_chain_and_stays_close_to_the_oracle
     assert err < 1e-2, err
     assert np.allclose(prob.numpy().sum(axis=1), 1.0, atol=1e-5)
     assert np.abs(prob.numpy() - want_prob).max() < 1e-2 * want_prob.max()
+
+
+# ---- golden outputs of the small CNN (made by tests/golden/make_graph_golden.py from the compiled reference) ----
+def _small_cnn_golden():
+    import os
+    return np.load(os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden", "small_cnn.npz"))
+
+
+def test_oracle_port_reproduces_the_small_cnn_golden_outputs(port):
+    """No GPU involved: building the graph needs none, and the C restatement runs it on the host."""
+    from oracle import graph as oracle_graph
+    from onnx_translator_b200 import nn
+    graph, x = nn.small_cnn(seed=0)
+    prob, side = oracle_graph.run(graph, port, x)
+    gold = _small_cnn_golden()
+    assert _bits_equal(side, gold["side"]) and _bits_equal(prob, gold["prob"])
+
+
+@pytest.mark.gpu
+def test_small_cnn_graph_reproduces_the_golden_outputs():
+    from onnx_translator_b200 import nn
+    graph, x = nn.small_cnn(seed=0)
+    prob, side = graph.forward(x)
+    gold = _small_cnn_golden()
+    assert _bits_equal(side.numpy(), gold["side"])
+    assert np.allclose(prob.numpy(), gold["prob"], rtol=1e-6, atol=0)
