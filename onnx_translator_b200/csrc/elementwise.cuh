@@ -208,8 +208,20 @@ __device__ __forceinline__ void encode_ints(const int (&v)[V], Run<typename Stor
 
 // ---- the kernels ---------------------------------------------------------------------------------------
 // Run kernel: a thread owns one run of V consecutive outputs per step (generic bodies, V = 1).
+// Both kernels may be launched with programmatic stream serialisation: the grid is then scheduled
+// while the previous kernel of the stream drains, and waits here -- before its first access to
+// memory -- until that kernel has completed and its writes are visible.  Without the launch
+// attribute the wait returns at once.
+// Once past the wait a block lets the NEXT kernel of the stream be scheduled onto free SMs (it will
+// sit in its own wait until this grid has finished).
+__device__ __forceinline__ void wait_for_previous_kernel() {
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+}
+
 template <class Body>
 __global__ void __launch_bounds__(kEwThreads) ew_kernel(const Body body, const uint32_t n) {
+    wait_for_previous_kernel();
     constexpr uint32_t V = Body::kV;
     const uint32_t runs = (n + V - 1) / V;
     const uint32_t step = gridDim.x * blockDim.x;
@@ -226,6 +238,7 @@ __global__ void __launch_bounds__(kEwThreads) ew_kernel(const Body body, const u
 // streams' widths, and the loads of all G runs are issued before the first result is needed.
 template <class Body>
 __global__ void __launch_bounds__(kEwThreads) ew_kernel_tiled(const Body body, const uint32_t n) {
+    wait_for_previous_kernel();
     constexpr uint32_t V = Body::kV, G = Body::kGroups, TILE = 32u * V * G;
     const uint32_t lane = threadIdx.x & 31u;
     const uint32_t warp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, warps = (gridDim.x * blockDim.x) >> 5;
@@ -353,14 +366,24 @@ template <class Body>
 bool launch_body(const char* name, const Body& body, size_t n) {
     DeviceState* st = acquire_device();
     if (!st) return false;
+    // programmatic stream serialisation (see wait_for_previous_kernel); TOPS_PDL=0 switches it off
+    static const bool overlap = [] { const char* e = getenv("TOPS_PDL"); return !(e && e[0] == '0'); }();
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cudaLaunchConfig_t cfg = {};
+    cfg.blockDim = dim3(kEwThreads);
+    cfg.stream = current_stream();
+    cfg.attrs = attr;
+    cfg.numAttrs = overlap ? 1 : 0;
     if constexpr (Body::kGroups > 0) {
         const size_t tile = (size_t)32 * Body::kV * Body::kGroups;
-        const int grid = grid_for(((n + tile - 1) / tile) * 32, kEwThreads, st->sm_count, kEwCtasPerSm);
-        ew_kernel_tiled<Body><<<grid, kEwThreads, 0, current_stream()>>>(body, (uint32_t)n);
+        cfg.gridDim = dim3(grid_for(((n + tile - 1) / tile) * 32, kEwThreads, st->sm_count, kEwCtasPerSm));
+        check_cuda(cudaLaunchKernelEx(&cfg, ew_kernel_tiled<Body>, body, (uint32_t)n), name);
     } else {
         const size_t runs = (n + Body::kV - 1) / Body::kV;
-        const int grid = grid_for(runs, kEwThreads, st->sm_count, kEwCtasPerSm);
-        ew_kernel<Body><<<grid, kEwThreads, 0, current_stream()>>>(body, (uint32_t)n);
+        cfg.gridDim = dim3(grid_for(runs, kEwThreads, st->sm_count, kEwCtasPerSm));
+        check_cuda(cudaLaunchKernelEx(&cfg, ew_kernel<Body>, body, (uint32_t)n), name);
     }
     return TOPS_CHECK_LAUNCH(name);
 }
