@@ -154,6 +154,7 @@ tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUt
         float* my_bias = bias_stage + quarter * kBN;                 // this warp's private copy: no cross-warp sync
         uint32_t* my_stage = out_stage + quarter * 32 * kStageRowWords;
         float* my_scale = scale_stage + quarter * kBN;
+        int staged_tn = -1;
         float alpha = p.alpha;
         if (p.fs.a_scale) alpha = __fmul_rn(alpha, __ldg(p.fs.a_scale));
         if (p.fs.b_scale && !p.fs.b_per_column) alpha = __fmul_rn(alpha, __ldg(p.fs.b_scale));
@@ -166,7 +167,9 @@ tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUt
             const int m = tm * kBM + quarter * 32 + lane;
             // beta * C for this tile, fetched while the tensor core is still working on it
             float row_bias = 0.0f;
-            if (p.bias.mode == kBiasPerColumn) {
+            const bool restage = tn != staged_tn;                 // per-column operands of a column block are staged once
+            staged_tn = tn;
+            if (p.bias.mode == kBiasPerColumn && restage) {
                 __syncwarp();
                 #pragma unroll
                 for (int j = 0; j < kBN / 32; j++) {
@@ -179,7 +182,7 @@ tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUt
             } else if (p.bias.mode == kBiasPerRow && m < p.M) {
                 row_bias = __fmul_rn(p.beta, (float)load_f64_rt(p.bias.ptr, p.bias.dtype, (size_t)m));
             }
-            if (p.fs.b_per_column) {
+            if (p.fs.b_per_column && restage) {
                 __syncwarp();
                 #pragma unroll
                 for (int j = 0; j < kBN / 32; j++) {

@@ -61,6 +61,7 @@ def main():
     ap.add_argument("--batch", type=int, default=8)
     ap.add_argument("--channels", type=int, default=256)
     ap.add_argument("--hw", type=int, default=56)
+    ap.add_argument("--ksize", type=int, default=1)
     args = ap.parse_args()
 
     lib = capi.load()
@@ -142,6 +143,24 @@ def main():
         call = lambda: lib.conv2d_forward(x.handle, w.handle, None, o.handle, ctypes.byref(prm))
         nbytes = x.size * ITEM[dt] + w.size * ITEM[dt] + o.size * ITEM[out_dt]
         flops = 2.0 * n_ * hw * hw * c_ * c_ * 9
+    elif args.op == "qconv":
+        # one Q -> DQ -> Conv(DQ(W)) -> Relu chain in one call: float32 [batch, channels, hw, hw] -> [batch, n, hw, hw],
+        # ksize x ksize filters (stride 1, "same" padding)
+        n_, c_, hw, ks, m_ = args.batch, args.channels, args.hw, args.ksize, args.n
+        x = DeviceArray.from_numpy(rng.standard_normal((n_, c_, hw, hw)).astype(np.float32), "float32")
+        wq = DeviceArray.from_numpy(rng.integers(-127, 128, (m_, c_, ks, ks)).astype(np.int8), "int8")
+        ws = DeviceArray.from_numpy(rng.uniform(0.005, 0.02, m_).astype(np.float32), "float32")
+        sx = DeviceArray.from_numpy(np.array([0.03], np.float32), "float32")
+        zx = DeviceArray.from_numpy(np.zeros(1, np.int8), "int8")
+        o = DeviceArray.empty((n_, m_, hw, hw), "float32")
+        pad = ks // 2
+        keep = [_ints([pad] * 4), _ints([1, 1]), _ints([1, 1])]
+        prm = CConvParams(keep[0][1], keep[1][1], keep[2][1], 1)
+        call = lambda: lib.tops_qdq_conv_forward(x.handle, sx.handle, zx.handle, wq.handle, ws.handle, None, None, o.handle,
+                                                 ctypes.byref(prm), 1)
+        nbytes = x.size * 4 + o.size * 4
+        flops = 2.0 * n_ * hw * hw * m_ * c_ * ks * ks
+        dt = out_dt = "float32"
     elif args.op == "qdq_resnet50":
         # the QDQ ResNet-50-shaped graph through Graph.fused(); --batch images of 224 x 224
         from . import nn
