@@ -62,27 +62,38 @@ __global__ void __launch_bounds__(256) activations_to_levels(const void* __restr
     {
         const int pp = threadIdx.x & 63, cq = threadIdx.x >> 6;
         const int p = p0 + pp;
-        float scale = 1.0f, inv = 1.0f;
-        if (XK == 0) { scale = __ldg(scale_ptr); inv = __fdividef(1.0f, scale); }
         if (p < plane) {
-            #pragma unroll 4
+            // this thread's 16 values (8 channel pairs) first, so that all loads are in flight together
+            float v[16];
+            #pragma unroll
             for (int i = 0; i < 8; i++) {
-                const int cp = cq + 4 * i, c = c0 + 2 * cp;             // channels c and c + 1 share a word
-                int level[2] = {0, 0};
                 #pragma unroll
                 for (int e = 0; e < 2; e++) {
-                    if (c + e < g.C) {
-                        const size_t at = ((size_t)n * g.C + c + e) * (size_t)plane + (size_t)p;
-                        if (XK == 0) {
-                            const float v = __ldg((const float*)x + at);
-                            level[e] = quantize_code_8bit<SIGNED ? DTYPE_INT8 : DTYPE_UINT8>(v, scale, inv, zero) - zero;
-                        } else {
-                            const uint8_t code = ((const uint8_t*)x)[at];
-                            level[e] = (SIGNED ? (int)(int8_t)code : (int)code) - zero;
-                        }
+                    const int c = c0 + 2 * (cq + 4 * i) + e;
+                    float value = 0.0f;
+                    if (c < g.C) {
+                        const size_t at = ((size_t)n * g.C + c) * (size_t)plane + (size_t)p;
+                        if (XK == 0) value = __ldg((const float*)x + at);
+                        else { const uint8_t code = ((const uint8_t*)x)[at]; value = (float)(SIGNED ? (int)(int8_t)code : (int)code); }
                     }
+                    v[2 * i + e] = value;
                 }
-                tile[pp][cp] = (uint32_t)level_bits(level[0]) | ((uint32_t)level_bits(level[1]) << 16);
+            }
+            const float zf = (float)zero;
+            float scale = 1.0f, inv = 1.0f;
+            if (XK == 0) { scale = __ldg(scale_ptr); inv = __fdividef(1.0f, scale); }
+            #pragma unroll
+            for (int i = 0; i < 8; i++) {
+                float level[2];
+                #pragma unroll
+                for (int e = 0; e < 2; e++) {
+                    const int c = c0 + 2 * (cq + 4 * i) + e;
+                    if (c >= g.C) level[e] = 0.0f;
+                    else if (XK == 0) level[e] = quantize_level_8bit<SIGNED ? DTYPE_INT8 : DTYPE_UINT8>(v[2 * i + e], scale, inv, zf);
+                    else level[e] = __fsub_rn(v[2 * i + e], zf);
+                }
+                // bfloat16 bits of two small integers: the upper halves of their float32 patterns
+                tile[pp][cq + 4 * i] = __byte_perm(__float_as_uint(level[0]), __float_as_uint(level[1]), 0x7632);
             }
         }
     }

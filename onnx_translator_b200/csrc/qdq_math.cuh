@@ -62,4 +62,19 @@ __device__ __forceinline__ int quantize_code_8bit(float x, float s, float inv_s,
     return r < lo ? lo : (r > hi ? hi : r);
 }
 
+// The same code minus the zero point, i.e. the integer level the dequantised value is a multiple of,
+// as a float (exact: |level| <= 255), without leaving the float pipe on the fast path: the rounded
+// quotient is already a float integer, the saturation limits are float integers too.
+template <int DO>
+__device__ __forceinline__ float quantize_level_8bit(float x, float s, float inv_s, float zf) {
+    const float q = __fmul_rn(x, inv_s);
+    const float t = __fadd_rn(q, 12582912.0f);
+    const float r = __fsub_rn(t, 12582912.0f);
+    const float d = __fsub_rn(q, r);
+    const bool ok = (fmaf(fabsf(q), 1.9073486e-6f, fabsf(d)) < 0.5f) & (fabsf(q) < 2097152.0f);
+    if (!ok) return (float)((int)quantize_exact<DO>((double)x, (double)s, (double)zf)) - zf;
+    constexpr float lo = DO == DTYPE_INT8 ? -128.0f : 0.0f, hi = DO == DTYPE_INT8 ? 127.0f : 255.0f;
+    return __fsub_rn(fminf(fmaxf(__fadd_rn(r, zf), lo), hi), zf);
+}
+
 }  // namespace tops
