@@ -151,3 +151,52 @@ def test_small_cnn_graph_reproduces_the_golden_outputs():
     gold = _small_cnn_golden()
     assert _bits_equal(side.numpy(), gold["side"])
     assert np.allclose(prob.numpy(), gold["prob"], rtol=1e-6, atol=0)
+
+
+def _hand_built_qdq_block(shared_codes=False, weight_zero=0, stride=1, group=1):
+    """x -> Q -> DQ -> Conv(DQ(w)) -> Relu -> Q -> DQ -> Conv(DQ(w2)) -> Add(., x) -> Relu, built without a GPU."""
+    from onnx_translator_b200 import nn
+    from onnx_translator_b200.nn import Operators as ops
+    f32 = "float32"
+    T = lambda a, dt: nn.Tensor(*np.asarray(a).shape, dtype=dt, data=np.asarray(a))
+    init = {"s": T(np.array([0.1], np.float32), f32), "z": T(np.zeros(1, np.int8), "int8"),
+            "w1": T(np.ones((8, 8, 3, 3), np.int8), "int8"), "w1s": T(np.full((8, 1, 1, 1), 0.01, np.float32), f32),
+            "w1z": T(np.full((8, 1, 1, 1), weight_zero, np.int8), "int8"),
+            "w2": T(np.ones((8, 8, 1, 1), np.int8), "int8"), "w2s": T(np.full((8, 1, 1, 1), 0.01, np.float32), f32),
+            "w2z": T(np.zeros((8, 1, 1, 1), np.int8), "int8"), "b": T(np.zeros(8, np.float32), f32)}
+    nodes = [
+        ops.QuantizeLinear(["x", "s", "z"], ["xq"], axis=1, dtype="int8"),
+        ops.DequantizeLinear(["xq", "s", "z"], ["xdq"], dtype=f32),
+        ops.DequantizeLinear(["w1", "w1s", "w1z"], ["w1dq"], dtype=f32),
+        ops.Conv(["xdq", "w1dq", "b"], ["c1"], pads=[1, 1, 1, 1], strides=[stride, stride], dilations=[1, 1], group=group, dtype=f32),
+        ops.RELU(["c1"], ["r1"], dtype=f32),
+        ops.QuantizeLinear(["r1", "s", "z"], ["r1q"], axis=1, dtype="int8"),
+        ops.DequantizeLinear(["r1q", "s", "z"], ["r1dq"], dtype=f32),
+        ops.DequantizeLinear(["w2", "w2s", "w2z"], ["w2dq"], dtype=f32),
+        ops.Conv(["r1dq", "w2dq"], ["c2"], pads=[0, 0, 0, 0], strides=[1, 1], dilations=[1, 1], group=1, dtype=f32),
+        ops.ADD(["c2", "x"], ["sum"], dtype=f32),
+        ops.RELU(["sum"], ["y"], dtype=f32),
+    ]
+    outputs = ["y", "xq"] if shared_codes else ["y"]
+    return Graph(nodes, "x", outputs, "block", init)
+
+
+def test_fusion_pass_rewrites_chains_and_residual_tails_without_a_gpu():
+    fused = _hand_built_qdq_block().fused()
+    kinds = [type(op).__name__ for op in fused.ops.values()]
+    assert kinds == ["QLinearConv", "QLinearConv"]
+    first, second = fused.ops.values()
+    assert first.from_float and first.relu and first.inputs == ["x", "s", "z", "w1", "w1s", "b"] and first.outputs == ["r1"]
+    assert second.from_float and second.relu and second.inputs == ["r1", "s", "z", "w2", "w2s", "", "x"] and second.outputs == ["y"]
+
+
+def test_fusion_pass_leaves_what_it_must_not_touch():
+    # the codes are a graph output too: the QuantizeLinear stays and the fused node starts from the codes
+    g = _hand_built_qdq_block(shared_codes=True).fused()
+    kinds = [type(op).__name__ for op in g.ops.values()]
+    assert kinds[0] == "QuantizeLinear" and kinds[1] == "QLinearConv" and not list(g.ops.values())[1].from_float
+    # non-zero weight zero points, grouped or stride-3 convolutions are not what the fused kernel computes
+    for bad in (dict(weight_zero=3), dict(group=2), dict(stride=3)):
+        kinds = [type(op).__name__ for op in _hand_built_qdq_block(**bad).fused().ops.values()]
+        assert kinds[:5] == ["QuantizeLinear", "DequantizeLinear", "DequantizeLinear", "Conv", "RELU"], bad
+        assert kinds.count("QLinearConv") == 1                                   # the second chain is still taken
