@@ -204,12 +204,12 @@ bool shifted_gemm_launch(const ShiftedGemm& g) {
     const int grid = tiles < st->sm_count ? tiles : st->sm_count;
     if (g.fp8) {
         static bool attr = false;
-        if (!attr) { cudaFuncSetAttribute(tc_kernel<true, kModeConv>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kTcSmemBytes); attr = true; }
-        tc_kernel<true, kModeConv><<<grid, kTcThreads, kTcSmemBytes, s>>>(map_a, map_b, p, idesc);
+        if (!attr) { cudaFuncSetAttribute(tc_kernel<true, kModeConv>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)tc_smem_bytes(kModeConv)); attr = true; }
+        tc_kernel<true, kModeConv><<<grid, tc_threads(kModeConv), tc_smem_bytes(kModeConv), s>>>(map_a, map_b, p, idesc);
     } else {
         static bool attr = false;
-        if (!attr) { cudaFuncSetAttribute(tc_kernel<false, kModeConv>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kTcSmemBytes); attr = true; }
-        tc_kernel<false, kModeConv><<<grid, kTcThreads, kTcSmemBytes, s>>>(map_a, map_b, p, idesc);
+        if (!attr) { cudaFuncSetAttribute(tc_kernel<false, kModeConv>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)tc_smem_bytes(kModeConv)); attr = true; }
+        tc_kernel<false, kModeConv><<<grid, tc_threads(kModeConv), tc_smem_bytes(kModeConv), s>>>(map_a, map_b, p, idesc);
     }
     if (!TOPS_CHECK_LAUNCH("conv2d_forward (tensor cores)")) return false;
     count_tensor_core_launch();

@@ -125,8 +125,8 @@ static bool gemm_split_f32(const Tensor* A, const Tensor* B, Tensor* Y, const Ge
         const int tiles = p.tiles_m * p.tiles_n;
         const int grid = tiles < st->sm_count ? tiles : st->sm_count;
         static bool attr = false;
-        if (!attr) { cudaFuncSetAttribute(tc_kernel<false, kModeSplit>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kTcSmemBytes); attr = true; }
-        tc_kernel<false, kModeSplit><<<grid, kTcThreads, kTcSmemBytes, s>>>(map_a, map_b, p, idesc);
+        if (!attr) { cudaFuncSetAttribute(tc_kernel<false, kModeSplit>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)tc_smem_bytes(kModeSplit)); attr = true; }
+        tc_kernel<false, kModeSplit><<<grid, tc_threads(kModeSplit), tc_smem_bytes(kModeSplit), s>>>(map_a, map_b, p, idesc);
         ok = TOPS_CHECK_LAUNCH("gemm_forward (tensor cores, float32 split)");
         if (ok) count_tensor_core_launch();
     }
@@ -188,12 +188,12 @@ bool gemm_tensor_core(const Tensor* A, const Tensor* B, Tensor* Y, const GemmSha
     cudaStream_t s = current_stream();
     if (fp8) {
         static bool attr = false;
-        if (!attr) { cudaFuncSetAttribute(tc_kernel<true, kModeGemm>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kTcSmemBytes); attr = true; }
-        tc_kernel<true, kModeGemm><<<grid, kTcThreads, kTcSmemBytes, s>>>(map_a, map_b, p, idesc);
+        if (!attr) { cudaFuncSetAttribute(tc_kernel<true, kModeGemm>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)tc_smem_bytes(kModeGemm)); attr = true; }
+        tc_kernel<true, kModeGemm><<<grid, tc_threads(kModeGemm), tc_smem_bytes(kModeGemm), s>>>(map_a, map_b, p, idesc);
     } else {
         static bool attr = false;
-        if (!attr) { cudaFuncSetAttribute(tc_kernel<false, kModeGemm>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kTcSmemBytes); attr = true; }
-        tc_kernel<false, kModeGemm><<<grid, kTcThreads, kTcSmemBytes, s>>>(map_a, map_b, p, idesc);
+        if (!attr) { cudaFuncSetAttribute(tc_kernel<false, kModeGemm>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)tc_smem_bytes(kModeGemm)); attr = true; }
+        tc_kernel<false, kModeGemm><<<grid, tc_threads(kModeGemm), tc_smem_bytes(kModeGemm), s>>>(map_a, map_b, p, idesc);
     }
     TOPS_CHECK_LAUNCH("gemm_forward (tensor cores)");
     count_tensor_core_launch();

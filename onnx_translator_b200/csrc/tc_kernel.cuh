@@ -12,10 +12,22 @@ constexpr int kBM = 128, kBN = 256, kRowBytes = 128, kStages = 4;
 constexpr int kTileABytes = kBM * kRowBytes;       // 16 KB
 constexpr int kTileBBytes = kBN * kRowBytes;       // 32 KB
 constexpr int kStageBytes = kTileABytes + kTileBBytes;
-constexpr int kTcThreads = 192;
 constexpr int kStageRowWords = 36;                 // 32 words of payload + 4 of padding: conflict-free 16-byte accesses
-constexpr size_t kTcSmemBytes = (size_t)kStages * kStageBytes + 1024 /*alignment slack*/ + 128 /*barriers*/ + 4 * kBN * 4 /*bias*/ +
-                                4 * 32 * kStageRowWords * 4 /*output staging*/ + 4 * kBN * 4 /*column scales*/;
+
+// Per mode: the convolution's K loops are short and its epilogue (strided NCHW stores, optional
+// residual loads) is what bounds it, so it trades one pipeline stage for a second set of four
+// epilogue warps -- twice as many loads and stores in flight per SM.  A warp may only read the
+// quarter of tensor memory given by its index modulo 4, so warps w and w + 4 share a quarter and
+// take alternate 32-column chunks.
+constexpr int kModeGemm = 0, kModeConv = 1, kModeSplit = 2;
+__host__ __device__ constexpr int tc_stages(int mode) { return mode == kModeConv ? 3 : kStages; }
+__host__ __device__ constexpr int tc_epilogue_warps(int mode) { return mode == kModeConv ? 8 : 4; }
+__host__ __device__ constexpr int tc_threads(int mode) { return 64 + 32 * tc_epilogue_warps(mode); }
+__host__ __device__ constexpr size_t tc_smem_bytes(int mode) {
+    return (size_t)tc_stages(mode) * kStageBytes + 1024 /*alignment slack*/ + 128 /*barriers*/ +
+           (size_t)tc_epilogue_warps(mode) * kBN * 4 /*bias*/ + (size_t)tc_epilogue_warps(mode) * kBN * 4 /*column scales*/ +
+           (mode == kModeConv ? 0 : 4 * 32 * kStageRowWords * 4) /*output staging (row-major outputs only)*/;
+}
 
 // Convolution as shifted GEMMs over a zero-padded channels-last copy of the input: row q of the
 // GEMM is the padded position (n, oh, ow) = (q / plane, (q % plane) / Wp, q % Wp); filter tap
@@ -57,31 +69,31 @@ __device__ __forceinline__ void tile_coords(int tile, int tiles_m, int tiles_n, 
 
 // MODE 0: Gemm.  MODE 1: Conv2d as shifted GEMMs (ConvView).  MODE 2: Gemm on float32 operands that
 // were split into three bfloat16 planes each (see gemm_tc.cu); the K loop walks six plane pairs.
-constexpr int kModeGemm = 0, kModeConv = 1, kModeSplit = 2;
 
 template <bool FP8, int MODE>
-__global__ void __launch_bounds__(kTcThreads, 1)
+__global__ void __launch_bounds__(tc_threads(MODE), 1)
 tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, const TcParams p,
                const uint32_t idesc) {
+    constexpr int kSt = tc_stages(MODE), kEpi = tc_epilogue_warps(MODE);
     extern __shared__ uint8_t smem_raw[];
     uint8_t* tiles = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
-    uint64_t* bars = (uint64_t*)(tiles + (size_t)kStages * kStageBytes);
-    uint64_t* full = bars;                    // [kStages]  TMA -> MMA
-    uint64_t* empty = bars + kStages;         // [kStages]  MMA -> TMA
-    uint64_t* acc_full = bars + 2 * kStages;  // [2]        MMA -> epilogue
-    uint64_t* acc_empty = acc_full + 2;       // [2]        epilogue -> MMA
+    uint64_t* bars = (uint64_t*)(tiles + (size_t)kSt * kStageBytes);
+    uint64_t* full = bars;                    // [kSt]  TMA -> MMA
+    uint64_t* empty = bars + kSt;             // [kSt]  MMA -> TMA
+    uint64_t* acc_full = bars + 2 * kSt;      // [2]    MMA -> epilogue
+    uint64_t* acc_empty = acc_full + 2;       // [2]    epilogue -> MMA
     uint32_t* tmem_slot = (uint32_t*)(acc_empty + 2);
     volatile int* abort_flag = (volatile int*)(tmem_slot + 1);
-    float* bias_stage = (float*)(bars + 16);           // 4 warps x kBN floats
-    uint32_t* out_stage = (uint32_t*)(bias_stage + 4 * kBN);   // 4 warps x 32 rows x kStageRowWords
-    float* scale_stage = (float*)(out_stage + 4 * 32 * kStageRowWords);   // 4 warps x kBN floats
+    float* bias_stage = (float*)(bars + 16);                   // kEpi warps x kBN floats
+    float* scale_stage = bias_stage + kEpi * kBN;              // kEpi warps x kBN floats
+    uint32_t* out_stage = (uint32_t*)(scale_stage + kEpi * kBN);   // 4 warps x 32 rows x kStageRowWords (not in convolution mode)
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int total_tiles = p.tiles_m * p.tiles_n;
 
     if (threadIdx.x == 0) {
-        for (int s = 0; s < kStages; s++) { umma::mbar_init(&full[s], 1); umma::mbar_init(&empty[s], 1); }
-        for (int b = 0; b < 2; b++) { umma::mbar_init(&acc_full[b], 1); umma::mbar_init(&acc_empty[b], 4); }
+        for (int s = 0; s < kSt; s++) { umma::mbar_init(&full[s], 1); umma::mbar_init(&empty[s], 1); }
+        for (int b = 0; b < 2; b++) { umma::mbar_init(&acc_full[b], 1); umma::mbar_init(&acc_empty[b], kEpi); }
         *abort_flag = 0;
         umma::mbar_fence_init();
         umma::tma_prefetch_desc(&map_a);
@@ -100,7 +112,7 @@ tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUt
                 int tm, tn;
                 tile_coords(tile, p.tiles_m, p.tiles_n, tm, tn);
                 for (int kb = 0; kb < p.k_blocks; kb++, it++) {
-                    const uint32_t s = it % kStages, ph = (it / kStages) & 1u;
+                    const uint32_t s = it % kSt, ph = (it / kSt) & 1u;
                     if (!umma::mbar_wait(&empty[s], ph ^ 1u, abort_flag)) break;
                     uint8_t* a_tile = tiles + (size_t)s * kStageBytes;
                     umma::mbar_expect_tx(&full[s], kStageBytes);
@@ -133,7 +145,7 @@ tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUt
                 const uint32_t d_tmem = tmem_base + buf * kBN;
                 bool ok = true;
                 for (int kb = 0; kb < p.k_blocks; kb++, it++) {
-                    const uint32_t s = it % kStages, ph = (it / kStages) & 1u;
+                    const uint32_t s = it % kSt, ph = (it / kSt) & 1u;
                     if (!umma::mbar_wait(&full[s], ph, abort_flag)) { ok = false; break; }
                     umma::fence_after_sync();
                     const uint8_t* a_tile = tiles + (size_t)s * kStageBytes;
@@ -150,10 +162,13 @@ tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUt
         }
     } else {
         const int quarter = warp & 3;                               // TMEM lanes this warp may read
+        const int epi = warp - 2;                                   // 0 .. kEpi-1
+        constexpr int kChunkStep = kEpi / 4;                        // warps that share a quarter alternate chunks
+        const int first_chunk = epi >> 2;
         uint32_t local = 0;
-        float* my_bias = bias_stage + quarter * kBN;                 // this warp's private copy: no cross-warp sync
+        float* my_bias = bias_stage + epi * kBN;                     // this warp's private copy: no cross-warp sync
         uint32_t* my_stage = out_stage + quarter * 32 * kStageRowWords;
-        float* my_scale = scale_stage + quarter * kBN;
+        float* my_scale = scale_stage + epi * kBN;
         int staged_tn = -1;
         float alpha = p.alpha;
         if (p.fs.a_scale) alpha = __fmul_rn(alpha, __ldg(p.fs.a_scale));
@@ -210,19 +225,19 @@ tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUt
                 for (int j = 0; j < 32; j++)
                     dst[j] = (conv_row && tn * kBN + chunk * 32 + j < p.N) ? __ldg(src + (size_t)j * plane_out) : 0.0f;
             };
-            if (with_res) fetch_residual(0, res_next);
+            if (with_res) fetch_residual(first_chunk, res_next);
             if (!umma::mbar_wait(&acc_full[buf], use, abort_flag)) break;
             umma::fence_after_sync();
             const uint32_t t_row = tmem_base + ((uint32_t)(quarter * 32) << 16) + buf * kBN;
             #pragma unroll 1
-            for (int c = 0; c < kBN / 32; c++) {
+            for (int c = first_chunk; c < kBN / 32; c += kChunkStep) {
                 const int n0 = tn * kBN + c * 32;
                 if (n0 >= p.N) break;                              // warp-uniform: no columns left in this tile
                 float res_cur[32];
                 if (with_res) {                                    // the next chunk's values travel while this one is processed
                     #pragma unroll
                     for (int j = 0; j < 32; j++) res_cur[j] = res_next[j];
-                    if (n0 + 32 < p.N && c + 1 < kBN / 32) fetch_residual(c + 1, res_next);
+                    if (n0 + 32 * kChunkStep < p.N && c + kChunkStep < kBN / 32) fetch_residual(c + kChunkStep, res_next);
                 }
                 uint32_t r[32];
                 umma::tmem_load_32x32(t_row + (uint32_t)(c * 32), r);
