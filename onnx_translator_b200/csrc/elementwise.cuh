@@ -124,6 +124,20 @@ __device__ __forceinline__ void decode_floats(const Run<typename Storage<DT>::ty
             const float2 p = __half22float2(*reinterpret_cast<const __half2*>(&r.v[j]));
             f[j] = p.x; f[j + 1] = p.y;
         }
+    } else if constexpr (DT == DTYPE_FLOAT8_E4M3 && V % 2 == 0) {
+        #pragma unroll
+        for (int j = 0; j < V; j += 2) {                    // two codes per hardware convert
+            const __half2_raw h = __nv_cvt_fp8x2_to_halfraw2(*reinterpret_cast<const uint16_t*>(&r.v[j]), __NV_E4M3);
+            const float2 p = __half22float2(*reinterpret_cast<const __half2*>(&h));
+            f[j] = p.x; f[j + 1] = p.y;
+        }
+    } else if constexpr (DT == DTYPE_FLOAT8_E5M2 && V % 2 == 0) {
+        #pragma unroll
+        for (int j = 0; j < V; j += 2) {                    // an e5m2 code is the upper byte of a float16
+            const uint32_t h = __byte_perm((uint32_t)*reinterpret_cast<const uint16_t*>(&r.v[j]), 0u, 0x1404);
+            const float2 p = __half22float2(*reinterpret_cast<const __half2*>(&h));
+            f[j] = p.x; f[j + 1] = p.y;
+        }
     } else if constexpr ((DT == DTYPE_INT8 || DT == DTYPE_UINT8) && V % 4 == 0) {
         // 8-bit integers to float without the conversion unit: the byte becomes the low mantissa
         // byte of 2^23 (signed bytes are first biased by 128), then the constant is subtracted

@@ -46,12 +46,51 @@ struct QuantizeBody {
             float inv = uniform_scale ? __fdividef(1.0f, to_f32<DS>(rs.v[0])) : 0.0f;
             constexpr bool kEightBit = (DO == DTYPE_INT8 || DO == DTYPE_UINT8 || DO == DTYPE_FLOAT8_E4M3 || DO == DTYPE_FLOAT8_E5M2) &&
                                        (DZ == DTYPE_INT8 || DZ == DTYPE_UINT8);
-            if (kEightBit && uniform_scale && z.st2 == 0) {
+            constexpr bool kFp8Out = DO == DTYPE_FLOAT8_E4M3 || DO == DTYPE_FLOAT8_E5M2;
+            if constexpr (kEightBit && kFp8Out && kV % 2 == 0) {
+                // fp8 targets: the rounded quotient plus the zero point stays a float (an exact integer)
+                // and is encoded two at a time by the hardware convert, which agrees with the reference's
+                // encoder for integer values below its overflow threshold (e5m2: 61440 -> Inf) -- larger
+                // quotients take the element-wise path below.
+                float fr[kV];
+                constexpr float kLimit = DO == DTYPE_FLOAT8_E5M2 ? 57000.0f : 2097152.0f;
+                #pragma unroll
+                for (int j = 0; j < kV; j++) {
+                    if (!uniform_scale) inv = __fdividef(1.0f, to_f32<DS>(rs.v[j]));
+                    const float q = __fmul_rn(fx[j], inv);
+                    const float t = __fadd_rn(q, 12582912.0f);
+                    const float rq = __fsub_rn(t, 12582912.0f);
+                    const float d = __fsub_rn(q, rq);
+                    all_ok = all_ok & (fmaf(fabsf(q), 1.9073486e-6f, fabsf(d)) < 0.5f) & (fabsf(q) < kLimit);
+                    fr[j] = __fadd_rn(rq, (float)to_i32_narrow<DZ>(rz.v[j]));
+                }
+                if (all_ok) {
+                    #pragma unroll
+                    for (int j = 0; j < kV; j += 2) {
+                        const __nv_fp8x2_storage_t two = __nv_cvt_float2_to_fp8x2(make_float2(fr[j], fr[j + 1]), __NV_SATFINITE,
+                                                                                  DO == DTYPE_FLOAT8_E4M3 ? __NV_E4M3 : __NV_E5M2);
+                        *reinterpret_cast<uint16_t*>(&ro.v[j]) = (uint16_t)two;
+                    }
+                    put3<DO, kV, ALIGNED>(out, i0, nv, ro);
+                    return;
+                }
+                #pragma unroll
+                for (int j = 0; j < kV; j++) v[j] = 0;
+                all_ok = false;
+            } else if (kEightBit && uniform_scale && z.st2 == 0) {
                 const int zm = to_i32_narrow<DZ>(rz.v[0]) - 0x4B400000;
                 #pragma unroll
                 for (int j = 0; j < kV; j++) {
                     bool ok;
                     v[j] = quantize_round_8bit(fx[j], inv, zm, ok);
+                    all_ok = all_ok & ok;
+                }
+            } else if (kEightBit) {
+                #pragma unroll
+                for (int j = 0; j < kV; j++) {
+                    if (!uniform_scale) inv = __fdividef(1.0f, to_f32<DS>(rs.v[j]));
+                    bool ok;
+                    v[j] = quantize_round_8bit(fx[j], inv, to_i32_narrow<DZ>(rz.v[j]) - 0x4B400000, ok);
                     all_ok = all_ok & ok;
                 }
             } else {
@@ -153,6 +192,22 @@ struct DequantizeBody {
             encode_floats<DO, kV>(f, ro);
             put3<DO, kV, ALIGNED>(out, i0, nv, ro);
             return;
+        }
+        if constexpr (!kDiffExact && dtype_exact_in_f32(DX) && dtype_exact_in_f32(DS) && dtype_exact_in_f32(DZ) &&
+                      DO != DTYPE_FLOAT64 && !dtype_is_int(DO)) {
+            // e.g. e5m2 or float16 codes: with a zero point of zero the product is a single rounding too
+            bool zero_points_zero = true;
+            #pragma unroll
+            for (int j = 0; j < kV; j++) zero_points_zero = zero_points_zero && to_f32<DZ>(rz.v[j]) == 0.0f;
+            if (zero_points_zero) {
+                float fx[kV], f[kV];
+                decode_floats<DX, kV>(rx, fx);
+                #pragma unroll
+                for (int j = 0; j < kV; j++) f[j] = __fmul_rn(fx[j], to_f32<DS>(rs.v[j]));
+                encode_floats<DO, kV>(f, ro);
+                put3<DO, kV, ALIGNED>(out, i0, nv, ro);
+                return;
+            }
         }
         #pragma unroll
         for (int j = 0; j < kV; j++) {
