@@ -247,6 +247,36 @@ int tops_qlinear_conv_forward(const Tensor* Xq, const Tensor* x_scale, const Ten
 int tops_qdq_conv_forward(const Tensor* X, const Tensor* x_scale, const Tensor* x_zero, const Tensor* Wq,
                           const Tensor* w_scale, const Tensor* B, const Tensor* R, Tensor* Y, ConvParams* params, int relu);
 
+/* The general form of the two calls above, which can also keep the activations between two
+   quantised convolutions as integer levels: with y_levels the result is quantised with the NEXT
+   convolution's input scale and zero point (the arithmetic of quantize_linear_forward) and stored
+   as bfloat16 levels in the channels-last, zero-padded layout that convolution reads; passing that
+   tensor as x with x_levels set skips the float32 tensor, the QuantizeLinear and the layout pass
+   between the two.  The levels tensor has the shape tops_qconv_levels_shape reports for the
+   convolution that will READ it and belongs to the caller; its padding cells and padding channels
+   are never written, so it must be zero-filled (create_tensor) unless that shape equals [N, H, W, C].  y and y_levels may both be given. */
+typedef struct QConvCall {
+    const Tensor* x;            /* float32 NCHW values, int8 / uint8 NCHW codes, or (x_levels) bfloat16 levels */
+    int x_levels;               /* non-zero: x was written as y_levels for this very convolution */
+    int x_shape[4];             /* logical N, C, H, W of the input; read only when x_levels is set */
+    const Tensor* x_scale;      /* float32[1] */
+    const Tensor* x_zero;       /* int8 / uint8 [1] or NULL; ignored with x_levels (already subtracted) */
+    const Tensor* w_codes;      /* int8 [M, C, KH, KW], zero point 0 */
+    const Tensor* w_scale;      /* float32 [M] */
+    const Tensor* bias;         /* float32 [M] or NULL */
+    const Tensor* residual;     /* float32, the output's shape, or NULL */
+    ConvParams* params;
+    int relu;
+    Tensor* y;                  /* float32 / bfloat16 / float16 NCHW, or NULL when only y_levels is wanted */
+    Tensor* y_levels;           /* NULL, or bfloat16 levels for the next convolution */
+    const Tensor* next_scale;   /* float32[1]: QuantizeLinear scale of the next convolution's input */
+    const Tensor* next_zero;    /* its zero point (int8 / uint8 [1]) or NULL */
+    ConvParams* next_params;    /* the next convolution's attributes ... */
+    int next_kernel[2];         /* ... and filter extent KH, KW */
+} QConvCall;
+int tops_qconv_forward(const QConvCall* call);
+int tops_qconv_levels_shape(const int x_shape[4], const int kernel[2], const ConvParams* params, int levels_shape[4]);
+
 /* Device-side exhaustive codec self-check: encodes every float32 bit pattern with the fast
    (hardware-convert) encoder and with the bit-level restatement of the reference encoder and
    returns the number of disagreements (NaN inputs excluded), or -1 on error. */

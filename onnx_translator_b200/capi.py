@@ -33,6 +33,15 @@ class CConvParams(ctypes.Structure):
                 ("dilations", ctypes.POINTER(ctypes.c_int)), ("group", ctypes.c_int)]
 
 
+class CQConvCall(ctypes.Structure):
+    """QConvCall of tensor_ops_b200.h."""
+    _fields_ = [("x", ctypes.c_void_p), ("x_levels", ctypes.c_int), ("x_shape", ctypes.c_int * 4),
+                ("x_scale", ctypes.c_void_p), ("x_zero", ctypes.c_void_p), ("w_codes", ctypes.c_void_p), ("w_scale", ctypes.c_void_p),
+                ("bias", ctypes.c_void_p), ("residual", ctypes.c_void_p), ("params", ctypes.POINTER(CConvParams)), ("relu", ctypes.c_int),
+                ("y", ctypes.c_void_p), ("y_levels", ctypes.c_void_p), ("next_scale", ctypes.c_void_p), ("next_zero", ctypes.c_void_p),
+                ("next_params", ctypes.POINTER(CConvParams)), ("next_kernel", ctypes.c_int * 2)]
+
+
 class CPoolParams(ctypes.Structure):
     _fields_ = [("pads", ctypes.POINTER(ctypes.c_int)), ("strides", ctypes.POINTER(ctypes.c_int)),
                 ("dilations", ctypes.POINTER(ctypes.c_int)), ("kernel_shape", ctypes.POINTER(ctypes.c_int))]
@@ -122,6 +131,9 @@ SIGNATURES = {
     "tops_conv2d_dqw_forward": (_I, [_P, _P, _P, _P, _P, ctypes.POINTER(CConvParams)]),
     "tops_qlinear_conv_forward": (_I, [_P, _P, _P, _P, _P, _P, _P, _P, ctypes.POINTER(CConvParams), _I]),
     "tops_qdq_conv_forward": (_I, [_P, _P, _P, _P, _P, _P, _P, _P, ctypes.POINTER(CConvParams), _I]),
+    "tops_qconv_forward": (_I, [ctypes.POINTER(CQConvCall)]),
+    "tops_qconv_levels_shape": (_I, [ctypes.POINTER(ctypes.c_int), ctypes.POINTER(ctypes.c_int), ctypes.POINTER(CConvParams),
+                                     ctypes.POINTER(ctypes.c_int)]),
     "tops_selftest_encoder": (ctypes.c_longlong, [_I]),
     "tops_tensor_core_launches": (ctypes.c_longlong, []),
     "tops_selftest_cos": (ctypes.c_longlong, []),

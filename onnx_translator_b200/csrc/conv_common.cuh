@@ -48,6 +48,7 @@ struct ShiftedGemm {
     EpilogueScales fs;
     int relu = 0;
     const float* residual = nullptr;          // float32, shape of Y: added to the result before the optional Relu
+    LevelsOut lv;                             // result as levels for the next quantised convolution (Y may then be null)
 };
 bool shifted_gemm_launch(const ShiftedGemm& g);
 

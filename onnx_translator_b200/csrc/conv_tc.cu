@@ -199,18 +199,27 @@ bool shifted_gemm_launch(const ShiftedGemm& g) {
     p.fs = g.fs;
     p.relu = g.relu;
     p.residual = g.residual;
+    p.lv = g.lv;
     const uint32_t idesc = umma::instr_desc(g.a_format, g.b_format, kBM, kBN);
     const int tiles = p.tiles_m * p.tiles_n;
     const int grid = tiles < st->sm_count ? tiles : st->sm_count;
-    if (g.fp8) {
-        static bool attr = false;
-        if (!attr) { cudaFuncSetAttribute(tc_kernel<true, kModeConv>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)tc_smem_bytes(kModeConv)); attr = true; }
-        tc_kernel<true, kModeConv><<<grid, tc_threads(kModeConv), tc_smem_bytes(kModeConv), s>>>(map_a, map_b, p, idesc);
-    } else {
-        static bool attr = false;
-        if (!attr) { cudaFuncSetAttribute(tc_kernel<false, kModeConv>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)tc_smem_bytes(kModeConv)); attr = true; }
-        tc_kernel<false, kModeConv><<<grid, tc_threads(kModeConv), tc_smem_bytes(kModeConv), s>>>(map_a, map_b, p, idesc);
-    }
+    const int epi = (g.residual ? kEpiResidual : 0) | (g.lv.z ? kEpiLevels : 0);
+    if (g.fp8 && epi != kEpiPlain) return false;                     // the quantised extras exist for 16-bit operands only
+#define TOPS_CONV_LAUNCH(F8, E)                                                                                              \
+    do {                                                                                                                     \
+        static bool attr = false;                                                                                            \
+        if (!attr) {                                                                                                         \
+            cudaFuncSetAttribute(tc_kernel<F8, kModeConv, E>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)tc_smem_bytes(kModeConv)); \
+            attr = true;                                                                                                     \
+        }                                                                                                                    \
+        tc_kernel<F8, kModeConv, E><<<grid, tc_threads(kModeConv), tc_smem_bytes(kModeConv), s>>>(map_a, map_b, p, idesc);   \
+    } while (0)
+    if (g.fp8) TOPS_CONV_LAUNCH(true, kEpiPlain);
+    else if (epi == kEpiPlain) TOPS_CONV_LAUNCH(false, kEpiPlain);
+    else if (epi == kEpiResidual) TOPS_CONV_LAUNCH(false, kEpiResidual);
+    else if (epi == kEpiLevels) TOPS_CONV_LAUNCH(false, kEpiLevels);
+    else TOPS_CONV_LAUNCH(false, kEpiResidual | kEpiLevels);
+#undef TOPS_CONV_LAUNCH
     if (!TOPS_CHECK_LAUNCH("conv2d_forward (tensor cores)")) return false;
     count_tensor_core_launch();
     return true;

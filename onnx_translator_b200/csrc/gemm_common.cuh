@@ -46,6 +46,19 @@ struct EpilogueScales {
     const float* y_scale = nullptr;    // one value; only with 8-bit output types
 };
 
+// Convolution mode can hand its result to the NEXT quantised convolution directly: the value is
+// quantised with that convolution's input scale and zero point (the arithmetic of
+// quantize_linear_forward) and stored as a bfloat16 integer level in the channels-last, zero-padded
+// (stride 2: space-to-depth) layout that convolution's tensor-core pass reads -- no float32 tensor in
+// between.  `z` is cleared by the caller where the layout has padding cells.
+struct LevelsOut {
+    uint16_t* z = nullptr;             // [images][Hz][Wz][Cz]
+    const float* scale = nullptr;      // one value
+    const void* zero = nullptr;        // one int8 / uint8 value, or null for 0
+    int zero_signed = 1;
+    int S = 1, pt = 0, pl = 0, Hz = 0, Wz = 0, Cz = 0, C = 0;
+};
+
 BiasView make_bias_view(const Tensor* C, int M, int N);
 
 // Exact double-accumulating path (any dtypes).

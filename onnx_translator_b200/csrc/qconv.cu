@@ -144,109 +144,201 @@ __global__ void __launch_bounds__(256) filter_codes_to_levels(const int8_t* __re
 
 using namespace tops;
 
-// x_is_float: X holds float32 values that are quantised on the way (codes of the type of x_zero, int8 when absent)
-static int qconv_run(const char* name, const Tensor* X, bool x_is_float, const Tensor* x_scale, const Tensor* x_zero, const Tensor* Wq,
-                     const Tensor* w_scale, const Tensor* B, const Tensor* residual, Tensor* Y, ConvParams* params, int relu) {
-    ConvGeom c;
-    if (!conv_geometry(name, X, Wq, B, Y, params, &c)) return tops_last_error();
-    const bool zero_given = x_zero && x_zero->data;
-    const int code_dt = x_is_float ? (zero_given ? (int)x_zero->dtype : DTYPE_INT8) : (int)X->dtype;
-    const bool x_ok = (code_dt == DTYPE_INT8 || code_dt == DTYPE_UINT8) && (!x_is_float || X->dtype == DTYPE_FLOAT32);
-    if (!x_ok || Wq->dtype != DTYPE_INT8 || !x_scale || !x_scale->data || x_scale->dtype != DTYPE_FLOAT32 || x_scale->size != 1 ||
-        !w_scale || !w_scale->data || w_scale->dtype != DTYPE_FLOAT32 || w_scale->size != (size_t)c.M ||
-        (zero_given && ((int)x_zero->dtype != code_dt || x_zero->size != 1)) || (B && B->data && B->dtype != DTYPE_FLOAT32) ||
-        (residual && residual->data && (residual->dtype != DTYPE_FLOAT32 || residual->size != Y->size))) {
-        set_error(TOPS_ERR_UNSUPPORTED, "%s: wants int8 / uint8 activation codes (or float32 values) with one float32 scale and one zero point "
-                                        "of the code type, int8 filter codes with one float32 scale per output channel, a float32 bias, a float32 residual of Y's size", name);
-        zero_fill(Y);
-        return tops_last_error();
-    }
-    const int dy = (int)Y->dtype;
-    const bool strided = c.sh == 2 && c.sw == 2 && c.dh == 1 && c.dw == 1;
-    if (c.G != 1 || !((c.sh == 1 && c.sw == 1) || strided) || c.dh < 1 || c.dw < 1 || c.pt < 0 || c.pl < 0 ||
-        (dy != DTYPE_FLOAT32 && dy != DTYPE_BFLOAT16 && dy != DTYPE_FLOAT16) || (size_t)c.H * c.W >= 0x7FFFFFFFull || c.N > 65535) {
-        set_error(TOPS_ERR_UNSUPPORTED, "%s: covers group 1, stride 1 (any dilation) or stride 2 (dilation 1), float32 / bfloat16 / float16 output", name);
-        zero_fill(Y);
-        return tops_last_error();
-    }
-    if (Y->size == 0) return TOPS_OK;
+namespace tops {
 
+// Geometry of the levels tensor a convolution reads: rows / columns / channels and filter extents
+// after the optional space-to-depth step.  False when the fused kernel does not cover the case.
+static bool levels_geometry(int C, int H, int W, int M, int KH, int KW, const ConvParams* prm, QGeom* g, int* OH, int* OW,
+                            int* dil_h, int* dil_w) {
+    if (!prm || !prm->pads || !prm->strides || !prm->dilations || prm->group != 1) return false;
+    const int pt = prm->pads[0], pl = prm->pads[1], pb = prm->pads[2], pr = prm->pads[3];
+    const int sh = prm->strides[0], sw = prm->strides[1], dh = prm->dilations[0], dw = prm->dilations[1];
+    const bool strided = sh == 2 && sw == 2 && dh == 1 && dw == 1;
+    if (!((sh == 1 && sw == 1) || strided) || dh < 1 || dw < 1 || pt < 0 || pl < 0 || pb < 0 || pr < 0 || KH < 1 || KW < 1) return false;
+    const int eh = H + pt + pb - dh * (KH - 1) - 1, ew = W + pl + pr - dw * (KW - 1) - 1;
+    if (eh < 0 || ew < 0) return false;
+    *OH = eh / sh + 1;
+    *OW = ew / sw + 1;
+    g->C = C; g->H = H; g->W = W; g->S = sh; g->pt = pt; g->pl = pl; g->M = M; g->KH = KH; g->KW = KW;
+    g->KHz = strided ? (KH + 1) / 2 : KH;
+    g->KWz = strided ? (KW + 1) / 2 : KW;
+    *dil_h = strided ? 1 : dh;
+    *dil_w = strided ? 1 : dw;
+    const int need_h = *OH + (g->KHz - 1) * *dil_h, need_w = *OW + (g->KWz - 1) * *dil_w;     // rows / columns the taps reach
+    const int have_h = strided ? (H + pt + 1) / 2 : H + pt, have_w = strided ? (W + pl + 1) / 2 : W + pl;
+    g->Hz = need_h > have_h ? need_h : have_h;
+    g->Wz = need_w > have_w ? need_w : have_w;
+    g->Cz = (g->S * g->S * C + 7) & ~7;
+    return true;
+}
+
+static bool one_f32(const Tensor* t) { return t && t->data && t->dtype == DTYPE_FLOAT32 && t->size == 1; }
+
+static int qconv_fail(const char* name, int code, const char* what, Tensor* y) {
+    set_error(code, "%s: %s", name, what);
+    zero_fill(y);
+    return tops_last_error();
+}
+
+static int qconv_run(const char* name, const QConvCall& q) {
+    const Tensor *X = q.x, *Wq = q.w_codes, *B = q.bias, *R = q.residual;
+    Tensor* Y = q.y;
+    if (!X || !X->data || !Wq || !Wq->data || Wq->ndim != 4 || X->ndim != 4 || (!Y && !q.y_levels))
+        return qconv_fail(name, TOPS_ERR_INVALID, "null argument, or tensors that are not 4-D, or no output given", Y);
+    const int N = q.x_levels ? q.x_shape[0] : X->shape[0], C = q.x_levels ? q.x_shape[1] : X->shape[1];
+    const int H = q.x_levels ? q.x_shape[2] : X->shape[2], W = q.x_levels ? q.x_shape[3] : X->shape[3];
+    const int M = Wq->shape[0], KH = Wq->shape[2], KW = Wq->shape[3];
     QGeom g;
-    g.C = c.C; g.H = c.H; g.W = c.W; g.S = c.sh; g.pt = c.pt; g.pl = c.pl; g.M = c.M; g.KH = c.KH; g.KW = c.KW;
-    g.KHz = strided ? (c.KH + 1) / 2 : c.KH;
-    g.KWz = strided ? (c.KW + 1) / 2 : c.KW;
-    const int dil_h = strided ? 1 : c.dh, dil_w = strided ? 1 : c.dw;
-    const int need_h = c.OH + (g.KHz - 1) * dil_h, need_w = c.OW + (g.KWz - 1) * dil_w;       // rows / columns the taps reach
-    const int have_h = strided ? (c.H + c.pt + 1) / 2 : c.H + c.pt, have_w = strided ? (c.W + c.pl + 1) / 2 : c.W + c.pl;
-    g.Hz = need_h > have_h ? need_h : have_h;
-    g.Wz = need_w > have_w ? need_w : have_w;
-    g.Cz = (g.S * g.S * c.C + 7) & ~7;
-    const size_t rows = (size_t)c.N * g.Hz * g.Wz;
-    if (rows >= 0x7FFFFF00ull) {
-        set_error(TOPS_ERR_UNSUPPORTED, "%s: more than 2^31 padded positions", name);
-        zero_fill(Y);
-        return tops_last_error();
+    int OH, OW, dil_h, dil_w;
+    if (N < 1 || N > 65535 || C < 1 || Wq->shape[1] != C || (size_t)H * W >= 0x7FFFFFFFull ||
+        !levels_geometry(C, H, W, M, KH, KW, q.params, &g, &OH, &OW, &dil_h, &dil_w))
+        return qconv_fail(name, TOPS_ERR_UNSUPPORTED, "covers group 1, stride 1 (any dilation) or stride 2 (dilation 1), W of shape [M, C, KH, KW]", Y);
+
+    const bool zero_given = q.x_zero && q.x_zero->data;
+    const bool x_is_float = !q.x_levels && X->dtype == DTYPE_FLOAT32;
+    const int code_dt = q.x_levels ? DTYPE_INT8 : x_is_float ? (zero_given ? (int)q.x_zero->dtype : DTYPE_INT8) : (int)X->dtype;
+    if (q.x_levels) {
+        if (X->dtype != DTYPE_BFLOAT16 || X->shape[0] != N || X->shape[1] != g.Hz || X->shape[2] != g.Wz || X->shape[3] != g.Cz)
+            return qconv_fail(name, TOPS_ERR_INVALID, "the levels tensor does not have the shape tops_qconv_levels_shape gives for this convolution", Y);
+    } else if ((code_dt != DTYPE_INT8 && code_dt != DTYPE_UINT8) || (zero_given && ((int)q.x_zero->dtype != code_dt || q.x_zero->size != 1))) {
+        return qconv_fail(name, TOPS_ERR_UNSUPPORTED, "wants float32 values or int8 / uint8 codes, and one zero point of the code type", Y);
     }
+    if (Wq->dtype != DTYPE_INT8 || !one_f32(q.x_scale) || !q.w_scale || !q.w_scale->data || q.w_scale->dtype != DTYPE_FLOAT32 ||
+        q.w_scale->size != (size_t)M || (B && B->data && (B->dtype != DTYPE_FLOAT32 || B->size < (size_t)M)))
+        return qconv_fail(name, TOPS_ERR_UNSUPPORTED, "wants int8 filter codes, one float32 activation scale, one float32 scale per output channel, a float32 bias", Y);
+    const size_t out_elems = (size_t)N * M * OH * OW;
+    int dy = DTYPE_FLOAT32;
+    if (Y) {
+        dy = (int)Y->dtype;
+        if (!Y->data || Y->ndim != 4 || Y->shape[0] != N || Y->shape[1] != M || Y->shape[2] != OH || Y->shape[3] != OW ||
+            (dy != DTYPE_FLOAT32 && dy != DTYPE_BFLOAT16 && dy != DTYPE_FLOAT16))
+            return qconv_fail(name, TOPS_ERR_INVALID, "Y must be [N, M, OH, OW] in float32 / bfloat16 / float16", Y);
+    }
+    if (R && R->data && (R->dtype != DTYPE_FLOAT32 || R->size != out_elems))
+        return qconv_fail(name, TOPS_ERR_INVALID, "the residual must be float32 with the output's element count", Y);
+
+    LevelsOut lv;
+    if (q.y_levels) {
+        QGeom ng;
+        int noh, now, ndh, ndw;
+        const bool nz = q.next_zero && q.next_zero->data;
+        if (!q.y_levels->data || q.y_levels->dtype != DTYPE_BFLOAT16 || q.y_levels->ndim != 4 || !one_f32(q.next_scale) || (M & 7) ||
+            (nz && ((q.next_zero->dtype != DTYPE_INT8 && q.next_zero->dtype != DTYPE_UINT8) || q.next_zero->size != 1)) ||
+            !levels_geometry(M, OH, OW, 1, q.next_kernel[0], q.next_kernel[1], q.next_params, &ng, &noh, &now, &ndh, &ndw) ||
+            q.y_levels->shape[0] != N || q.y_levels->shape[1] != ng.Hz || q.y_levels->shape[2] != ng.Wz || q.y_levels->shape[3] != ng.Cz)
+            return qconv_fail(name, TOPS_ERR_INVALID, "levels output: needs a bfloat16 tensor of the shape tops_qconv_levels_shape gives for the next "
+                                                     "convolution, its float32 scale (and 8-bit zero point), and an output channel count that is a multiple of 8", Y);
+        lv.z = (uint16_t*)q.y_levels->data;
+        lv.scale = (const float*)q.next_scale->data;
+        lv.zero = nz ? q.next_zero->data : nullptr;
+        lv.zero_signed = !nz || q.next_zero->dtype == DTYPE_INT8;
+        lv.S = ng.S; lv.pt = ng.pt; lv.pl = ng.pl; lv.Hz = ng.Hz; lv.Wz = ng.Wz; lv.Cz = ng.Cz; lv.C = M;
+    }
+    if (out_elems == 0) return TOPS_OK;
+    const size_t rows = (size_t)N * g.Hz * g.Wz;
+    if (rows >= 0x7FFFFF00ull) return qconv_fail(name, TOPS_ERR_UNSUPPORTED, "more than 2^31 padded positions", Y);
+
     DeviceState* st = acquire_device();
     if (!st) return tops_last_error();
     cudaStream_t s = current_stream();
-    const size_t z_bytes = rows * g.Cz * 2, wt_bytes = (size_t)g.KHz * g.KWz * c.M * g.Cz * 2;
+    const size_t z_bytes = rows * g.Cz * 2, wt_bytes = (size_t)g.KHz * g.KWz * M * g.Cz * 2;
     void *z = nullptr, *wt = nullptr;
-    if (cudaMallocAsync(&z, z_bytes, s) != cudaSuccess) { cudaGetLastError(); set_error(TOPS_ERR_OOM, "%s: scratch", name); return tops_last_error(); }
+    bool ok = true;
+    if (q.x_levels) {
+        z = X->data;
+    } else {
+        if (cudaMallocAsync(&z, z_bytes, s) != cudaSuccess) { cudaGetLastError(); return qconv_fail(name, TOPS_ERR_OOM, "scratch", nullptr); }
+        // padding cells and padding channels are zero; a 1x1 convolution without padding over a channel
+        // count that is a multiple of 8 has neither
+        const bool every_cell_written = g.S == 1 && g.Hz == H && g.Wz == W && g.Cz == C;
+        ok = every_cell_written || TOPS_CUDA_OK(cudaMemsetAsync(z, 0, z_bytes, s));
+        const dim3 grid((H * W + 63) / 64, N, (C + 63) / 64);
+        const void* zero_ptr = zero_given ? q.x_zero->data : nullptr;
+        const float* scale_ptr = (const float*)q.x_scale->data;
+        const bool is_signed = code_dt == DTYPE_INT8;
+        if (x_is_float) {
+            if (is_signed) activations_to_levels<0, true><<<grid, 256, 0, s>>>(X->data, (uint16_t*)z, g, scale_ptr, zero_ptr);
+            else           activations_to_levels<0, false><<<grid, 256, 0, s>>>(X->data, (uint16_t*)z, g, scale_ptr, zero_ptr);
+        } else {
+            if (is_signed) activations_to_levels<1, true><<<grid, 256, 0, s>>>(X->data, (uint16_t*)z, g, scale_ptr, zero_ptr);
+            else           activations_to_levels<1, false><<<grid, 256, 0, s>>>(X->data, (uint16_t*)z, g, scale_ptr, zero_ptr);
+        }
+    }
     if (cudaMallocAsync(&wt, wt_bytes, s) != cudaSuccess) {
         cudaGetLastError();
-        cudaFreeAsync(z, s);
-        set_error(TOPS_ERR_OOM, "%s: scratch", name);
-        return tops_last_error();
-    }
-    // padding cells and padding channels are zero; a 1x1 convolution without padding over a channel
-    // count that is a multiple of 8 has neither
-    const bool every_cell_written = g.S == 1 && g.Hz == c.H && g.Wz == c.W && g.Cz == c.C;
-    bool ok = every_cell_written || TOPS_CUDA_OK(cudaMemsetAsync(z, 0, z_bytes, s));
-    const dim3 grid((c.H * c.W + 63) / 64, c.N, (c.C + 63) / 64);
-    const void* zero_ptr = zero_given ? x_zero->data : nullptr;
-    const float* scale_ptr = (const float*)x_scale->data;
-    const bool is_signed = code_dt == DTYPE_INT8;
-    if (x_is_float) {
-        if (is_signed) activations_to_levels<0, true><<<grid, 256, 0, s>>>(X->data, (uint16_t*)z, g, scale_ptr, zero_ptr);
-        else           activations_to_levels<0, false><<<grid, 256, 0, s>>>(X->data, (uint16_t*)z, g, scale_ptr, zero_ptr);
-    } else {
-        if (is_signed) activations_to_levels<1, true><<<grid, 256, 0, s>>>(X->data, (uint16_t*)z, g, scale_ptr, zero_ptr);
-        else           activations_to_levels<1, false><<<grid, 256, 0, s>>>(X->data, (uint16_t*)z, g, scale_ptr, zero_ptr);
+        if (!q.x_levels) cudaFreeAsync(z, s);
+        return qconv_fail(name, TOPS_ERR_OOM, "scratch", nullptr);
     }
     filter_codes_to_levels<<<grid_for(wt_bytes / 2, 256, st->sm_count, 4), 256, 0, s>>>((const int8_t*)Wq->data, (uint16_t*)wt, g);
     ok = ok && TOPS_CHECK_LAUNCH(name);
     if (ok) {
         ShiftedGemm sg;
         sg.xp = z; sg.wt = wt; sg.es = 2; sg.fp8 = false; sg.a_format = 1u; sg.b_format = 1u;
-        sg.images = c.N; sg.Hp = g.Hz; sg.Wp = g.Wz; sg.C = g.Cz; sg.M = c.M;
-        sg.KH = g.KHz; sg.KW = g.KWz; sg.dil_h = dil_h; sg.dil_w = dil_w; sg.OH = c.OH; sg.OW = c.OW;
-        sg.Y = Y->data; sg.dy = dy;
+        sg.images = N; sg.Hp = g.Hz; sg.Wp = g.Wz; sg.C = g.Cz; sg.M = M;
+        sg.KH = g.KHz; sg.KW = g.KWz; sg.dil_h = dil_h; sg.dil_w = dil_w; sg.OH = OH; sg.OW = OW;
+        sg.Y = Y ? Y->data : nullptr; sg.dy = dy;
         sg.bias = (B && B->data) ? B->data : nullptr;
         sg.bias_dtype = DTYPE_FLOAT32;
         sg.status = device_status_word();
-        sg.fs.a_scale = scale_ptr;
-        sg.fs.b_scale = (const float*)w_scale->data;
+        sg.fs.a_scale = (const float*)q.x_scale->data;
+        sg.fs.b_scale = (const float*)q.w_scale->data;
         sg.fs.b_per_column = 1;
-        sg.relu = relu ? 1 : 0;
-        sg.residual = (residual && residual->data) ? (const float*)residual->data : nullptr;
+        sg.relu = q.relu ? 1 : 0;
+        sg.residual = (R && R->data) ? (const float*)R->data : nullptr;
+        sg.lv = lv;
         ok = shifted_gemm_launch(sg);
     }
-    cudaFreeAsync(z, s);
+    if (!q.x_levels) cudaFreeAsync(z, s);
     cudaFreeAsync(wt, s);
     if (!ok) return tops_last_error();
     finish_op();
     return TOPS_OK;
 }
 
+}  // namespace tops
+
+TOPS_API int tops_qconv_forward(const QConvCall* call) {
+    if (!call) { set_error(TOPS_ERR_INVALID, "tops_qconv_forward: null call"); return tops_last_error(); }
+    return qconv_run("tops_qconv_forward", *call);
+}
+
+TOPS_API int tops_qconv_levels_shape(const int x_shape[4], const int kernel[2], const ConvParams* params, int levels_shape[4]) {
+    QGeom g;
+    int oh, ow, dh, dw;
+    if (!x_shape || !kernel || !levels_shape || !levels_geometry(x_shape[1], x_shape[2], x_shape[3], 1, kernel[0], kernel[1], params, &g, &oh, &ow, &dh, &dw)) {
+        set_error(TOPS_ERR_UNSUPPORTED, "tops_qconv_levels_shape: null argument or a convolution the quantised kernel does not cover");
+        return tops_last_error();
+    }
+    levels_shape[0] = x_shape[0]; levels_shape[1] = g.Hz; levels_shape[2] = g.Wz; levels_shape[3] = g.Cz;
+    return TOPS_OK;
+}
+
+static QConvCall plain_call(const Tensor* X, const Tensor* x_scale, const Tensor* x_zero, const Tensor* Wq, const Tensor* w_scale,
+                            const Tensor* B, const Tensor* R, Tensor* Y, ConvParams* params, int relu) {
+    QConvCall q = {};
+    q.x = X; q.x_scale = x_scale; q.x_zero = x_zero; q.w_codes = Wq; q.w_scale = w_scale; q.bias = B; q.residual = R;
+    q.params = params; q.relu = relu; q.y = Y;
+    return q;
+}
+
 TOPS_API int tops_qlinear_conv_forward(const Tensor* Xq, const Tensor* x_scale, const Tensor* x_zero, const Tensor* Wq,
                                        const Tensor* w_scale, const Tensor* B, const Tensor* residual, Tensor* Y,
                                        ConvParams* params, int relu) {
-    return qconv_run("tops_qlinear_conv_forward", Xq, false, x_scale, x_zero, Wq, w_scale, B, residual, Y, params, relu);
+    if (Xq && Xq->dtype == DTYPE_FLOAT32) {
+        set_error(TOPS_ERR_UNSUPPORTED, "tops_qlinear_conv_forward: wants int8 / uint8 codes (tops_qdq_conv_forward takes float32 values)");
+        zero_fill(Y);
+        return tops_last_error();
+    }
+    return qconv_run("tops_qlinear_conv_forward", plain_call(Xq, x_scale, x_zero, Wq, w_scale, B, residual, Y, params, relu));
 }
 
 TOPS_API int tops_qdq_conv_forward(const Tensor* X, const Tensor* x_scale, const Tensor* x_zero, const Tensor* Wq,
                                    const Tensor* w_scale, const Tensor* B, const Tensor* residual, Tensor* Y,
                                    ConvParams* params, int relu) {
-    return qconv_run("tops_qdq_conv_forward", X, true, x_scale, x_zero, Wq, w_scale, B, residual, Y, params, relu);
+    if (X && X->dtype != DTYPE_FLOAT32) {
+        set_error(TOPS_ERR_UNSUPPORTED, "tops_qdq_conv_forward: wants float32 values (tops_qlinear_conv_forward takes the codes)");
+        zero_fill(Y);
+        return tops_last_error();
+    }
+    return qconv_run("tops_qdq_conv_forward", plain_call(X, x_scale, x_zero, Wq, w_scale, B, residual, Y, params, relu));
 }

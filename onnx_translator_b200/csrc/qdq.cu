@@ -54,6 +54,8 @@ struct QuantizeBody {
                 // quotients take the element-wise path below.
                 float fr[kV];
                 constexpr float kLimit = DO == DTYPE_FLOAT8_E5M2 ? 57000.0f : 2097152.0f;
+                const bool uniform_zero = ALIGNED && !g.simple && z.st2 == 0;     // one int -> float conversion per run then
+                const float zf0 = (float)to_i32_narrow<DZ>(rz.v[0]);
                 #pragma unroll
                 for (int j = 0; j < kV; j++) {
                     if (!uniform_scale) inv = __fdividef(1.0f, to_f32<DS>(rs.v[j]));
@@ -62,7 +64,7 @@ struct QuantizeBody {
                     const float rq = __fsub_rn(t, 12582912.0f);
                     const float d = __fsub_rn(q, rq);
                     all_ok = all_ok & (fmaf(fabsf(q), 1.9073486e-6f, fabsf(d)) < 0.5f) & (fabsf(q) < kLimit);
-                    fr[j] = __fadd_rn(rq, (float)to_i32_narrow<DZ>(rz.v[j]));
+                    fr[j] = __fadd_rn(rq, uniform_zero ? zf0 : (float)to_i32_narrow<DZ>(rz.v[j]));
                 }
                 if (all_ok) {
                     #pragma unroll

@@ -4,6 +4,7 @@
 #include "gemm_common.cuh"
 #include "umma.cuh"
 #include "elementwise.cuh"
+#include "qdq_math.cuh"
 
 namespace tops {
 
@@ -55,6 +56,7 @@ struct TcParams {
     EpilogueScales fs;
     int relu = 0;          // clamp the result at zero before it is stored (v > 0 ? v : 0)
     const float* residual = nullptr;   // convolution mode: float32 tensor of the output's shape added before the clamp
+    LevelsOut lv;                      // convolution mode: also / instead write the result as levels for the next convolution
 };
 
 __device__ __forceinline__ void tile_coords(int tile, int tiles_m, int tiles_n, int& tm, int& tn) {
@@ -70,7 +72,11 @@ __device__ __forceinline__ void tile_coords(int tile, int tiles_m, int tiles_n, 
 // MODE 0: Gemm.  MODE 1: Conv2d as shifted GEMMs (ConvView).  MODE 2: Gemm on float32 operands that
 // were split into three bfloat16 planes each (see gemm_tc.cu); the K loop walks six plane pairs.
 
-template <bool FP8, int MODE>
+// EPI (convolution mode only) selects the epilogue extras that are compiled in, so that a kernel
+// carries registers only for what it uses: bit 0 = residual operand, bit 1 = levels output.
+constexpr int kEpiPlain = 0, kEpiResidual = 1, kEpiLevels = 2;
+
+template <bool FP8, int MODE, int EPI = kEpiPlain>
 __global__ void __launch_bounds__(tc_threads(MODE), 1)
 tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, const TcParams p,
                const uint32_t idesc) {
@@ -211,7 +217,7 @@ tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUt
             bool conv_row = false;
             size_t conv_base = 0, plane_out = 0;
             float res_next[32];
-            const bool with_res = MODE == kModeConv && p.residual != nullptr;
+            constexpr bool with_res = MODE == kModeConv && (EPI & kEpiResidual) != 0;
             if constexpr (MODE == kModeConv) {
                 const int img = m / p.cv.plane, rem = m - img * p.cv.plane;
                 const int oh = rem / p.cv.Wp, ow = rem - oh * p.cv.Wp;
@@ -225,7 +231,7 @@ tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUt
                 for (int j = 0; j < 32; j++)
                     dst[j] = (conv_row && tn * kBN + chunk * 32 + j < p.N) ? __ldg(src + (size_t)j * plane_out) : 0.0f;
             };
-            if (with_res) fetch_residual(first_chunk, res_next);
+            if constexpr (with_res) fetch_residual(first_chunk, res_next);
             if (!umma::mbar_wait(&acc_full[buf], use, abort_flag)) break;
             umma::fence_after_sync();
             const uint32_t t_row = tmem_base + ((uint32_t)(quarter * 32) << 16) + buf * kBN;
@@ -234,7 +240,7 @@ tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUt
                 const int n0 = tn * kBN + c * 32;
                 if (n0 >= p.N) break;                              // warp-uniform: no columns left in this tile
                 float res_cur[32];
-                if (with_res) {                                    // the next chunk's values travel while this one is processed
+                if constexpr (with_res) {                          // the next chunk's values travel while this one is processed
                     #pragma unroll
                     for (int j = 0; j < 32; j++) res_cur[j] = res_next[j];
                     if (n0 + 32 * kChunkStep < p.N && c + kChunkStep < kBN / 32) fetch_residual(c + kChunkStep, res_next);
@@ -274,7 +280,7 @@ tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUt
                         #pragma unroll
                         for (int j = 0; j < 32; j++) v[j] = __fmaf_rn(p.beta, cv[j], v[j]);
                     }
-                    if (p.relu && (MODE != kModeConv || !p.residual)) {
+                    if (p.relu && !with_res) {
                         #pragma unroll
                         for (int j = 0; j < 32; j++) v[j] = v[j] > 0.0f ? v[j] : 0.0f;
                     }
@@ -283,14 +289,62 @@ tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUt
                         // positions) are consecutive pixels, so each store instruction is contiguous.
                         if (conv_row) {
                             const size_t base = conv_base + (size_t)(c * 32) * plane_out;
-                            if (with_res) {                            // Add(conv, residual) [-> Relu], as separate float32 operators would round
+                            if constexpr (with_res) {                  // Add(conv, residual) [-> Relu], as separate float32 operators would round
                                 #pragma unroll
                                 for (int j = 0; j < 32; j++) {
                                     v[j] = __fadd_rn(v[j], res_cur[j]);
                                     if (p.relu) v[j] = v[j] > 0.0f ? v[j] : 0.0f;
                                 }
                             }
-                            if (p.dy == DTYPE_FLOAT32) {
+                            if constexpr ((EPI & kEpiLevels) != 0) {
+                                // levels for the next convolution: this row is input pixel (oh, ow) of that convolution
+                                const int rem2 = m - (m / p.cv.plane) * p.cv.plane;
+                                const int oh2 = rem2 / p.cv.Wp, ow2 = rem2 - oh2 * p.cv.Wp;
+                                int A = oh2 + p.lv.pt, B = ow2 + p.lv.pl, slot = 0;
+                                if (p.lv.S == 2) { slot = ((A & 1) * 2 + (B & 1)) * p.lv.C; A >>= 1; B >>= 1; }
+                                uint16_t* zdst = p.lv.z + (((size_t)(m / p.cv.plane) * p.lv.Hz + A) * p.lv.Wz + B) * p.lv.Cz + slot + n0;
+                                const float ls = __ldg(p.lv.scale), linv = __fdividef(1.0f, ls);
+                                float zf = 0.0f;
+                                if (p.lv.zero) zf = p.lv.zero_signed ? (float)*(const int8_t*)p.lv.zero : (float)*(const uint8_t*)p.lv.zero;
+                                // eight values at a time on the fast path without branches (their dependency chains
+                                // interleave); a group in which the fast rounding could not decide some value -- a tie
+                                // closer than 2^-19 |q|, which also catches |q| >= 2^18 and NaN -- is redone with the
+                                // reference's double division
+                                const float lo = p.lv.zero_signed ? -128.0f : 0.0f, hi = p.lv.zero_signed ? 127.0f : 255.0f;
+                                uint32_t packed[16];
+                                #pragma unroll
+                                for (int j0 = 0; j0 < 32; j0 += 8) {
+                                    float level[8];
+                                    bool decided = true;
+                                    #pragma unroll
+                                    for (int e = 0; e < 8; e++) {
+                                        const float q = __fmul_rn(v[j0 + e], linv);
+                                        const float rq = __fsub_rn(__fadd_rn(q, 12582912.0f), 12582912.0f);
+                                        decided = decided & (fmaf(fabsf(q), 1.9073486e-6f, fabsf(__fsub_rn(q, rq))) < 0.5f);
+                                        level[e] = __fsub_rn(fminf(fmaxf(__fadd_rn(rq, zf), lo), hi), zf);
+                                    }
+                                    if (!decided) {
+                                        #pragma unroll
+                                        for (int e = 0; e < 8; e++)
+                                            level[e] = p.lv.zero_signed ? quantize_level_8bit<DTYPE_INT8>(v[j0 + e], ls, linv, zf)
+                                                                        : quantize_level_8bit<DTYPE_UINT8>(v[j0 + e], ls, linv, zf);
+                                    }
+                                    #pragma unroll
+                                    for (int e = 0; e < 8; e += 2)
+                                        packed[(j0 + e) >> 1] = __byte_perm(__float_as_uint(level[e]), __float_as_uint(level[e + 1]), 0x7632);
+                                }
+                                if (n0 + 32 <= p.N) {                  // 64 contiguous bytes of this pixel's channels
+                                    #pragma unroll
+                                    for (int q4 = 0; q4 < 4; q4++)
+                                        *reinterpret_cast<uint4*>(zdst + 8 * q4) = make_uint4(packed[4 * q4], packed[4 * q4 + 1], packed[4 * q4 + 2], packed[4 * q4 + 3]);
+                                } else {
+                                    #pragma unroll
+                                    for (int j = 0; j < 32; j++) if (n0 + j < p.N) zdst[j] = (uint16_t)(packed[j >> 1] >> ((j & 1) * 16));
+                                }
+                            }
+                            if (p.Y == nullptr) {
+                                // levels only
+                            } else if (p.dy == DTYPE_FLOAT32) {
                                 float* dst = (float*)p.Y + base;
                                 #pragma unroll
                                 for (int j = 0; j < 32; j++) if (n0 + j < p.N) dst[(size_t)j * plane_out] = v[j];

@@ -7,26 +7,51 @@ import ctypes
 
 from . import Ops, Tensor
 from .. import capi
-from ..capi import CConvParams
+from ..capi import CConvParams, CQConvCall
+from ..device import DeviceArray
 from .Operators import _int_ptr, _pooled_extent
 
 
+def _conv_params(pads, strides, dilations):
+    keep = [_int_ptr(pads), _int_ptr(strides), _int_ptr(dilations)]
+    return CConvParams(keep[0][1], keep[1][1], keep[2][1], 1), keep
+
+
 class QLinearConv(Ops):
-    """DequantizeLinear(activation codes) + DequantizeLinear(weight codes) + Conv [+ Relu] in one call
-    (replaces nn/Operators.py:452-473 twice, :475-548 and :170-200).
-    inputs: [x_codes, x_scale, x_zero, w_codes, w_scale, bias or "", residual or ""]; a residual is a float32
-    tensor of the output's shape that is added before the optional Relu (the Add node :170-200 of a
-    residual block).  With ``from_float`` the first input
-    is the float32 tensor and the QuantizeLinear that makes the codes (:427-450) is part of the call too."""
+    """DequantizeLinear(activation codes) + DequantizeLinear(weight codes) + Conv [+ Add(residual)] [+ Relu]
+    in one call (replaces nn/Operators.py:452-473 twice, :475-548 and :170-200).
+
+    inputs: [x, x_scale, x_zero, w_codes, w_scale, bias or "", residual or "", next_scale or "", next_zero or ""]
+
+    * ``from_float``: x is the float32 tensor and the QuantizeLinear that makes the codes (:427-450) is part of
+      the call; otherwise x holds the int8 / uint8 codes.
+    * ``levels_in``: x is the levels tensor the producing QLinearConv wrote for this convolution.
+    * ``next_conv`` (dict with pads, strides, dilations, kernel): the result is handed to the next quantised
+      convolution as integer levels (quantised with next_scale / next_zero) instead of as float32."""
 
     def __init__(self, inputs, outputs, pads, strides, dilations, relu, dtype="float32", from_float=False):
         super().__init__(inputs, outputs)
         self.pads, self.strides, self.dilations, self.relu, self.dtype = list(pads), list(strides), list(dilations), bool(relu), dtype
         self.from_float = bool(from_float)
+        self.levels_in = False
+        self.next_conv = None
 
-    def forward(self, xq: Tensor, x_scale: Tensor, x_zero: Tensor, wq: Tensor, w_scale: Tensor, b: Tensor = None,
-                residual: Tensor = None) -> dict:
-        n, _, h, w = xq.data.shape
+    def _levels_tensor(self, logical_shape, conv):
+        """bfloat16 levels tensor for the convolution described by ``conv`` reading ``logical_shape``."""
+        params, keep = _conv_params(conv["pads"], conv["strides"], conv["dilations"])
+        shape = (ctypes.c_int * 4)()
+        rc = self.lib.tops_qconv_levels_shape((ctypes.c_int * 4)(*logical_shape), (ctypes.c_int * 2)(*conv["kernel"]),
+                                              ctypes.byref(params), shape)
+        if rc:
+            capi.check(self.lib)
+        # padding cells and padding channels are never written by the producer: they must read as zero
+        n, c, h, w = logical_shape
+        padded = tuple(shape) != (n, h, w, c)
+        return DeviceArray.empty(tuple(shape), "bfloat16", zero=padded, lib=self.lib)
+
+    def forward(self, x: Tensor, x_scale: Tensor, x_zero: Tensor, wq: Tensor, w_scale: Tensor, b: Tensor = None,
+                residual: Tensor = None, next_scale: Tensor = None, next_zero: Tensor = None) -> dict:
+        n, _, h, w = x.logical_shape if self.levels_in else x.data.shape
         m, _, kh, kw = wq.data.shape
         out_shape = (n, m,
                      _pooled_extent(h, self.pads[0], self.pads[2], self.dilations[0], kh, self.strides[0]),
@@ -35,22 +60,41 @@ class QLinearConv(Ops):
             # a broadcasting Add is not what the fused epilogue does: run the three operators
             from .Operators import ADD, RELU
             plain = QLinearConv([], [], self.pads, self.strides, self.dilations, False, self.dtype, self.from_float)
-            y = ADD([], [], dtype=self.dtype).forward(plain.forward(xq, x_scale, x_zero, wq, w_scale, b)["tensor"], residual)["tensor"]
+            plain.levels_in = self.levels_in
+            y = ADD([], [], dtype=self.dtype).forward(plain.forward(x, x_scale, x_zero, wq, w_scale, b)["tensor"], residual)["tensor"]
             return self._publish(RELU([], [], dtype=self.dtype).forward(y)["tensor"] if self.relu else y)
-        keep = [_int_ptr(self.pads), _int_ptr(self.strides), _int_ptr(self.dilations)]
-        params = CConvParams(keep[0][1], keep[1][1], keep[2][1], 1)
-        operands = [xq, x_scale, x_zero, wq, w_scale] + [t for t in (b, residual) if t is not None]
-        handles = [self._numpy_to_ctensor(t.data, t.dtype) for t in operands]
-        b_handle = handles[5] if b is not None else None
-        r_handle = handles[-1] if residual is not None else None
-        y = self._new_output(out_shape, self.dtype)
-        entry = self.lib.tops_qdq_conv_forward if self.from_float else self.lib.tops_qlinear_conv_forward
-        rc = entry(handles[0], handles[1], handles[2], handles[3], handles[4], b_handle, r_handle, y,
-                   ctypes.byref(params), int(self.relu))
-        out = self._finish(handles, y, out_shape, self.dtype) if not rc else None
+
+        params, keep = _conv_params(self.pads, self.strides, self.dilations)
+        operands = [t for t in (x, x_scale, x_zero, wq, w_scale, b, residual, next_scale, next_zero) if t is not None]
+        handles = {id(t): self._numpy_to_ctensor(t.data, t.dtype) for t in operands}
+        ptr = lambda t: None if t is None else ctypes.cast(handles[id(t)], ctypes.c_void_p)
+        call = CQConvCall()
+        call.x, call.x_levels = ptr(x), int(self.levels_in)
+        if self.levels_in:
+            call.x_shape = (ctypes.c_int * 4)(*x.logical_shape)
+        call.x_scale, call.x_zero, call.w_codes, call.w_scale = ptr(x_scale), ptr(x_zero), ptr(wq), ptr(w_scale)
+        call.bias, call.residual = ptr(b), ptr(residual)
+        call.params, call.relu = ctypes.pointer(params), int(self.relu)
+        y_handle = levels = None
+        if self.next_conv is not None:
+            levels = self._levels_tensor(out_shape, self.next_conv)
+            next_params, keep_next = _conv_params(self.next_conv["pads"], self.next_conv["strides"], self.next_conv["dilations"])
+            call.y_levels = ctypes.cast(levels.handle, ctypes.c_void_p)
+            call.next_scale, call.next_zero = ptr(next_scale), ptr(next_zero)
+            call.next_params = ctypes.pointer(next_params)
+            call.next_kernel = (ctypes.c_int * 2)(*self.next_conv["kernel"])
+        else:
+            y_handle = self._new_output(out_shape, self.dtype)
+            call.y = ctypes.cast(y_handle, ctypes.c_void_p)
+        rc = self.lib.tops_qconv_forward(ctypes.byref(call))
+        for hdl in handles.values():
+            self.lib.free_tensor(hdl)
         if rc:
-            for hdl in handles:
-                self.lib.free_tensor(hdl)
-            self.lib.free_tensor(y)
+            if y_handle is not None:
+                self.lib.free_tensor(y_handle)
             capi.check(self.lib)
-        return self._publish(out)
+        if levels is not None:
+            out = Tensor(*levels.shape, dtype="bfloat16", data=levels)
+            out.logical_shape = out_shape
+            return self._publish(out)
+        return self._publish(self._finish([], y_handle, out_shape, self.dtype))

@@ -67,7 +67,8 @@ class Graph:
 
         chain executed by one ``QLinearConv`` node (the QuantizeLinear is part of it unless something else
         reads the codes); a following Add of another float32 tensor [-> Relu] -- the tail of a residual
-        block -- joins that node's epilogue.
+        block -- joins that node's epilogue; and where one such node feeds exactly one other, the edge
+        between them carries integer levels in the consumer's layout instead of a float32 tensor.
         A chain is taken only when nothing else reads its inner edges, the weight zero points are all
         zero and the convolution is one the fused kernel covers (group 1; stride 1, or stride 2 with
         dilation 1); everything else is left as it is.  Initializers are shared with this graph."""
@@ -149,6 +150,30 @@ class Graph:
             conv.outputs = [out_edge]
             conv.relu = relu
         kept = [op for op in kept if op.name not in gone]
+
+        # third pass: a float32 edge between two fused convolutions that nobody else reads never needs to exist:
+        # the producer quantises with the consumer's scale and writes the integer levels in the consumer's layout
+        made_by = {e: op for op in kept for e in op.outputs}
+        readers = {}
+        for op in kept:
+            for e in op.inputs:
+                if e:
+                    readers.setdefault(e, []).append(op)
+        for consumer in kept:
+            if kind(consumer) != "QLinearConv" or not consumer.from_float:
+                continue
+            edge = consumer.inputs[0]
+            producer_node = made_by.get(edge)
+            if (producer_node is None or kind(producer_node) != "QLinearConv" or producer_node.next_conv is not None
+                    or producer_node.dtype != "float32" or len(readers.get(edge, [])) != 1 or edge in self.output_name):
+                continue
+            w_codes = self.initializers[consumer.inputs[3]]
+            if self.initializers[producer_node.inputs[3]].size[0] % 8:
+                continue                                    # the levels layout wants channel groups of eight
+            producer_node.next_conv = dict(pads=list(consumer.pads), strides=list(consumer.strides), dilations=list(consumer.dilations),
+                                           kernel=[int(w_codes.size[2]), int(w_codes.size[3])])
+            producer_node.inputs = (list(producer_node.inputs) + ["", ""])[:7] + [consumer.inputs[1], consumer.inputs[2]]
+            consumer.levels_in = True
         g = Graph(kept, list(self.input_name), list(self.output_name), self.model_name, self.initializers)
         g._resident = self._resident
         if hasattr(self, "macs_per_image"):

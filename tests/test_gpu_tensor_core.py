@@ -334,3 +334,42 @@ def test_qlinear_conv_with_residual_equals_the_three_operators_bit_for_bit():
     no_relu = QLinearConv([], [], [1] * 4, [1, 1], [1, 1], False, "float32", from_float=True).forward(*args, T(res, "float32"))["tensor"].numpy()
     want2 = ops.ADD([], [], dtype="float32").forward(plain, T(res, "float32"))["tensor"].numpy()
     assert np.array_equal(no_relu.view(np.uint32), want2.view(np.uint32))
+
+
+@pytest.mark.parametrize("nxt", [(3, 1, 1, "int8", 0), (3, 2, 1, "int8", 4), (1, 1, 0, "uint8", 128), (1, 2, 0, "int8", -2), (5, 1, 2, "uint8", 17)],
+                         ids=lambda c: f"next-k{c[0]}s{c[1]}p{c[2]}-{c[3]}z{c[4]}")
+def test_levels_edge_between_two_quantised_convolutions_is_bit_identical(nxt):
+    """conv A -> (integer levels in B's layout) -> conv B must equal conv A -> float32 -> Q -> conv B bit for bit:
+    the epilogue of A quantises with the arithmetic of QuantizeLinear and writes B's padded / space-to-depth layout."""
+    from onnx_translator_b200.nn import Tensor
+    from onnx_translator_b200.nn.fused_ops import QLinearConv
+    k2, s2, p2, code_dt, zero2 = nxt
+    rng = np.random.default_rng(k2 * 10 + s2)
+    n, c, h, m1, m2 = 3, 16, 22, 40, 24
+    T = lambda a, dt: Tensor(*a.shape, dtype=dt, data=a)
+    x = T(rng.normal(0, 1, (n, c, h, h)).astype(np.float32), "float32")
+    sx, zx = T(np.array([0.03], np.float32), "float32"), T(np.zeros(1, np.int8), "int8")
+    w1 = T(rng.integers(-127, 128, (m1, c, 3, 3)).astype(np.int8), "int8")
+    w1s = T(rng.uniform(0.002, 0.01, (m1, 1, 1, 1)).astype(np.float32), "float32")
+    b1 = T(rng.normal(0, 0.5, m1).astype(np.float32), "float32")
+    res = T(rng.normal(0, 1, (n, m1, h, h)).astype(np.float32), "float32")
+    s2t = T(np.array([0.05], np.float32), "float32")
+    z2t = T(np.array([zero2], np.int8 if code_dt == "int8" else np.uint8), code_dt)
+    w2 = T(rng.integers(-127, 128, (m2, m1, k2, k2)).astype(np.int8), "int8")
+    w2s = T(rng.uniform(0.002, 0.01, (m2, 1, 1, 1)).astype(np.float32), "float32")
+
+    def conv_a(next_conv):
+        node = QLinearConv([], [], [1] * 4, [1, 1], [1, 1], True, "float32", from_float=True)
+        node.next_conv = next_conv
+        return node.forward(x, sx, zx, w1, w1s, b1, res, *((s2t, z2t) if next_conv else ()))["tensor"]
+
+    def conv_b(inp, levels_in):
+        node = QLinearConv([], [], [p2] * 4, [s2, s2], [1, 1], False, "float32", from_float=True)
+        node.levels_in = levels_in
+        return node.forward(inp, s2t, z2t, w2, w2s)["tensor"].numpy()
+
+    want = conv_b(conv_a(None), False)
+    levels = conv_a(dict(pads=[p2] * 4, strides=[s2, s2], dilations=[1, 1], kernel=[k2, k2]))
+    assert levels.dtype == "bfloat16" and levels.logical_shape == (n, m1, h, h)
+    got = conv_b(levels, True)
+    assert got.shape == want.shape and np.array_equal(got.view(np.uint32), want.view(np.uint32))

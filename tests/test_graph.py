@@ -186,7 +186,9 @@ def test_fusion_pass_rewrites_chains_and_residual_tails_without_a_gpu():
     kinds = [type(op).__name__ for op in fused.ops.values()]
     assert kinds == ["QLinearConv", "QLinearConv"]
     first, second = fused.ops.values()
-    assert first.from_float and first.relu and first.inputs == ["x", "s", "z", "w1", "w1s", "b"] and first.outputs == ["r1"]
+    assert first.from_float and first.relu and first.inputs == ["x", "s", "z", "w1", "w1s", "b", "", "s", "z"] and first.outputs == ["r1"]
+    assert first.next_conv == dict(pads=[0, 0, 0, 0], strides=[1, 1], dilations=[1, 1], kernel=[1, 1]) and not first.levels_in
+    assert second.levels_in and second.next_conv is None                       # the edge r1 carries integer levels
     assert second.from_float and second.relu and second.inputs == ["r1", "s", "z", "w2", "w2s", "", "x"] and second.outputs == ["y"]
 
 
@@ -200,3 +202,23 @@ def test_fusion_pass_leaves_what_it_must_not_touch():
         kinds = [type(op).__name__ for op in _hand_built_qdq_block(**bad).fused().ops.values()]
         assert kinds[:5] == ["QuantizeLinear", "DequantizeLinear", "DequantizeLinear", "Conv", "RELU"], bad
         assert kinds.count("QLinearConv") == 1                                   # the second chain is still taken
+
+
+@pytest.mark.gpu
+def test_levels_edges_do_not_change_the_fused_graph_result():
+    """The third fusion pass (integer levels between consecutive fused convolutions) is exact: same logits, bit for
+    bit, as the fused graph whose edges are float32 tensors."""
+    from onnx_translator_b200 import nn
+    graph, x = nn.qdq_resnet50(batch=2, seed=0, image=64, stages=(1, 2, 1, 1), widths=(8, 16, 24, 32), classes=20)
+    graph.output_name = ["logits"]
+    with_levels = graph.fused()
+    assert sum(getattr(op, "levels_in", False) for op in with_levels.ops.values()) == 2 * 5     # conv2 and conv3 of each block
+    plain = graph.fused()
+    for op in plain.ops.values():
+        if type(op).__name__ == "QLinearConv":
+            if op.next_conv is not None:
+                op.next_conv, op.inputs = None, op.inputs[:7]
+            op.levels_in = False
+    a = with_levels.forward(x).numpy()
+    b = plain.forward(x).numpy()
+    assert np.array_equal(a.view(np.uint32), b.view(np.uint32))
