@@ -27,7 +27,8 @@ class QLinearConv(Ops):
       the call; otherwise x holds the int8 / uint8 codes.
     * ``levels_in``: x is the levels tensor the producing QLinearConv wrote for this convolution.
     * ``next_conv`` (dict with pads, strides, dilations, kernel): the result is handed to the next quantised
-      convolution as integer levels (quantised with next_scale / next_zero) instead of as float32."""
+      convolution as integer levels (quantised with next_scale / next_zero) instead of as float32 -- or, with
+      ``also_float``, besides the float32 tensor (two outputs), when other nodes read the float32 values too."""
 
     def __init__(self, inputs, outputs, pads, strides, dilations, relu, dtype="float32", from_float=False):
         super().__init__(inputs, outputs)
@@ -35,6 +36,7 @@ class QLinearConv(Ops):
         self.from_float = bool(from_float)
         self.levels_in = False
         self.next_conv = None
+        self.also_float = False       # with next_conv: outputs are (float32 tensor, levels tensor) instead of the levels alone
 
     def _levels_tensor(self, logical_shape, conv):
         """bfloat16 levels tensor for the convolution described by ``conv`` reading ``logical_shape``."""
@@ -83,7 +85,7 @@ class QLinearConv(Ops):
             call.next_scale, call.next_zero = ptr(next_scale), ptr(next_zero)
             call.next_params = ctypes.pointer(next_params)
             call.next_kernel = (ctypes.c_int * 2)(*self.next_conv["kernel"])
-        else:
+        if self.next_conv is None or self.also_float:
             y_handle = self._new_output(out_shape, self.dtype)
             call.y = ctypes.cast(y_handle, ctypes.c_void_p)
         rc = self.lib.tops_qconv_forward(ctypes.byref(call))
@@ -93,8 +95,9 @@ class QLinearConv(Ops):
             if y_handle is not None:
                 self.lib.free_tensor(y_handle)
             capi.check(self.lib)
+        result = None if y_handle is None else self._finish([], y_handle, out_shape, self.dtype)
         if levels is not None:
             out = Tensor(*levels.shape, dtype="bfloat16", data=levels)
             out.logical_shape = out_shape
-            return self._publish(out)
-        return self._publish(self._finish([], y_handle, out_shape, self.dtype))
+            result = out if result is None else (result, out)
+        return self._publish(result)

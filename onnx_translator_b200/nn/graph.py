@@ -67,8 +67,9 @@ class Graph:
 
         chain executed by one ``QLinearConv`` node (the QuantizeLinear is part of it unless something else
         reads the codes); a following Add of another float32 tensor [-> Relu] -- the tail of a residual
-        block -- joins that node's epilogue; and where one such node feeds exactly one other, the edge
-        between them carries integer levels in the consumer's layout instead of a float32 tensor.
+        block -- joins that node's epilogue; and where one such node feeds another, the edge between them
+        carries integer levels in the consumer's layout instead of (or, when the float32 values have
+        other readers, besides) a float32 tensor.
         A chain is taken only when nothing else reads its inner edges, the weight zero points are all
         zero and the convolution is one the fused kernel covers (group 1; stride 1, or stride 2 with
         dilation 1); everything else is left as it is.  Initializers are shared with this graph."""
@@ -165,8 +166,9 @@ class Graph:
             edge = consumer.inputs[0]
             producer_node = made_by.get(edge)
             if (producer_node is None or kind(producer_node) != "QLinearConv" or producer_node.next_conv is not None
-                    or producer_node.dtype != "float32" or len(readers.get(edge, [])) != 1 or edge in self.output_name):
+                    or producer_node.dtype != "float32" or len(producer_node.outputs) != 1):
                 continue
+            shared = len(readers.get(edge, [])) != 1 or edge in self.output_name    # the float32 values are needed elsewhere too
             w_codes = self.initializers[consumer.inputs[3]]
             if self.initializers[producer_node.inputs[3]].size[0] % 8:
                 continue                                    # the levels layout wants channel groups of eight
@@ -174,6 +176,10 @@ class Graph:
                                            kernel=[int(w_codes.size[2]), int(w_codes.size[3])])
             producer_node.inputs = (list(producer_node.inputs) + ["", ""])[:7] + [consumer.inputs[1], consumer.inputs[2]]
             consumer.levels_in = True
+            if shared:                                      # second output: the levels; the float32 edge stays for the others
+                producer_node.also_float = True
+                producer_node.outputs = [edge, edge + ".levels"]
+                consumer.inputs = [edge + ".levels"] + list(consumer.inputs[1:])
         g = Graph(kept, list(self.input_name), list(self.output_name), self.model_name, self.initializers)
         g._resident = self._resident
         if hasattr(self, "macs_per_image"):

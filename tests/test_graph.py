@@ -117,7 +117,7 @@ def test_fused_graph_replaces_every_qdq_conv_chain_and_stays_close_to_the_oracle
     convs = sum(type(op).__name__ == "Conv" for op in graph.ops.values())
     assert kinds.count("QLinearConv") == convs and kinds.count("Conv") == 0 and kinds.count("DequantizeLinear") == 0
     assert kinds.count("QuantizeLinear") == 0 and kinds.count("RELU") == 0 and kinds.count("ADD") == 0
-    assert sum(len(op.inputs) == 7 for op in fused.ops.values()) == 4                   # the four residual tails
+    assert sum(len(op.inputs) >= 7 and bool(op.inputs[6]) for op in fused.ops.values()) == 4     # the four residual tails
     logits, prob = fused.forward(x)
     want_logits, want_prob = oracle_graph.run(graph, port, x)
     got = logits.numpy().astype(np.float64)
@@ -212,13 +212,16 @@ def test_levels_edges_do_not_change_the_fused_graph_result():
     graph, x = nn.qdq_resnet50(batch=2, seed=0, image=64, stages=(1, 2, 1, 1), widths=(8, 16, 24, 32), classes=20)
     graph.output_name = ["logits"]
     with_levels = graph.fused()
-    assert sum(getattr(op, "levels_in", False) for op in with_levels.ops.values()) == 2 * 5     # conv2 and conv3 of each block
+    # conv2 and conv3 of each of the five blocks, plus the first convolution reading each later block's input
+    assert sum(getattr(op, "levels_in", False) for op in with_levels.ops.values()) == 2 * 5 + 4
+    assert sum(getattr(op, "also_float", False) for op in with_levels.ops.values()) == 4
     plain = graph.fused()
     for op in plain.ops.values():
         if type(op).__name__ == "QLinearConv":
             if op.next_conv is not None:
-                op.next_conv, op.inputs = None, op.inputs[:7]
-            op.levels_in = False
+                op.next_conv, op.inputs, op.also_float, op.outputs = None, op.inputs[:7], False, op.outputs[:1]
+            if op.levels_in:
+                op.levels_in, op.inputs = False, [op.inputs[0].replace(".levels", "")] + list(op.inputs[1:])
     a = with_levels.forward(x).numpy()
     b = plain.forward(x).numpy()
     assert np.array_equal(a.view(np.uint32), b.view(np.uint32))
