@@ -222,6 +222,7 @@ def test_levels_edges_do_not_change_the_fused_graph_result():
                 op.next_conv, op.inputs, op.also_float, op.outputs = None, op.inputs[:7], False, op.outputs[:1]
             if op.levels_in:
                 op.levels_in, op.inputs = False, [op.inputs[0].replace(".levels", "")] + list(op.inputs[1:])
+    plain = Graph(list(plain.ops.values()), "x", ["logits"], "plain", plain.initializers)     # recount the edge readers
     a = with_levels.forward(x).numpy()
     b = plain.forward(x).numpy()
     assert np.array_equal(a.view(np.uint32), b.view(np.uint32))
