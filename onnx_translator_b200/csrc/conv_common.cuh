@@ -40,6 +40,7 @@ bool conv_tc_run(const Tensor* X, const Tensor* W, const Tensor* B, Tensor* Y, c
 struct ShiftedGemm {
     const void* xp = nullptr; const void* wt = nullptr;
     int es = 2; bool fp8 = false;
+    int a_row_stride_bytes = 0;               // 0: C * es.  Smaller than that: row q also covers the cells after it (merged taps)
     unsigned a_format = 1, b_format = 1;      // tcgen05 operand formats (16-bit: 0 = float16, 1 = bfloat16; fp8: 0 = e4m3, 1 = e5m2)
     int images = 0, Hp = 0, Wp = 0, C = 0, M = 0, KH = 1, KW = 1, dil_h = 1, dil_w = 1, OH = 0, OW = 0;
     void* Y = nullptr; int dy = DTYPE_FLOAT32;
@@ -51,6 +52,8 @@ struct ShiftedGemm {
     LevelsOut lv;                             // result as levels for the next quantised convolution (Y may then be null)
 };
 bool shifted_gemm_launch(const ShiftedGemm& g);
+// Whether the driver accepts the activation map of `g` (no launch): used to choose a layout before the filters are laid out.
+bool shifted_gemm_map_ok(const ShiftedGemm& g);
 
 // Fills a ConvGeom from the ABI arguments; false (with the error recorded) when they are inconsistent.
 bool conv_geometry(const char* name, const Tensor* X, const Tensor* W, const Tensor* B, Tensor* Y, const ConvParams* params, ConvGeom* c);

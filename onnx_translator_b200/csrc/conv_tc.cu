@@ -155,6 +155,14 @@ bool conv_tc_run(const Tensor* X, const Tensor* W, const Tensor* B, Tensor* Y, c
     return shifted_gemm_launch(sg);
 }
 
+bool shifted_gemm_map_ok(const ShiftedGemm& g) {
+    CUtensorMap map_a;
+    const uint64_t dims_a[2] = {(uint64_t)g.C, (uint64_t)g.images * g.Hp * g.Wp};
+    const uint64_t strides_a[1] = {g.a_row_stride_bytes ? (uint64_t)g.a_row_stride_bytes : (uint64_t)g.C * g.es};
+    const uint32_t box_a[2] = {(uint32_t)(kRowBytes / g.es), (uint32_t)kBM};
+    return make_tensor_map(&map_a, g.xp, g.es, g.fp8, !g.fp8 && g.a_format == 0u, 2, dims_a, strides_a, box_a, nullptr);
+}
+
 // The tensor-core part shared by every convolution path: KH * KW shifted GEMMs over a padded
 // channels-last activation tensor and tap-major filters that are already in place.
 bool shifted_gemm_launch(const ShiftedGemm& g) {
@@ -166,7 +174,7 @@ bool shifted_gemm_launch(const ShiftedGemm& g) {
     const int k_step = kRowBytes / es;
     CUtensorMap map_a, map_b;
     const uint64_t dims_a[2] = {(uint64_t)g.C, (uint64_t)rows};
-    const uint64_t strides_a[1] = {(uint64_t)g.C * es};
+    const uint64_t strides_a[1] = {g.a_row_stride_bytes ? (uint64_t)g.a_row_stride_bytes : (uint64_t)g.C * es};
     const uint32_t box_a[2] = {(uint32_t)k_step, (uint32_t)kBM};
     const uint64_t dims_b[3] = {(uint64_t)g.C, (uint64_t)g.M, (uint64_t)taps};
     const uint64_t strides_b[2] = {(uint64_t)g.C * es, (uint64_t)g.M * g.C * es};

@@ -121,14 +121,43 @@ __global__ void __launch_bounds__(256) activations_to_levels(const void* __restr
     }
 }
 
-// int8 filter codes [M][C][KH][KW] -> bfloat16 levels [KHz*KWz][M][Cz] in the channel order of the activations
-__global__ void __launch_bounds__(256) filter_codes_to_levels(const int8_t* __restrict__ w, uint16_t* __restrict__ wt, QGeom g) {
+// The same for few input channels (C <= 8, e.g. the RGB stem): the 64-channel tiles above would be almost
+// empty, so here a thread owns one plane position and all of its channels.
+template <int XK, bool SIGNED>
+__global__ void __launch_bounds__(256) activations_to_levels_few_channels(const void* __restrict__ x, uint16_t* __restrict__ z, QGeom g,
+                                                                          const float* __restrict__ scale_ptr, const void* __restrict__ zero_ptr) {
+    const int plane = g.H * g.W, n = blockIdx.y;
+    const int p = blockIdx.x * blockDim.x + threadIdx.x;
+    if (p >= plane) return;
+    int zero = 0;
+    if (zero_ptr) zero = SIGNED ? (int)*(const int8_t*)zero_ptr : (int)*(const uint8_t*)zero_ptr;
+    const float zf = (float)zero;
+    float scale = 1.0f, inv = 1.0f;
+    if (XK == 0) { scale = __ldg(scale_ptr); inv = __fdividef(1.0f, scale); }
+    const int h = p / g.W, w = p - h * g.W;
+    int A = h + g.pt, B = w + g.pl, slot = 0;
+    if (g.S == 2) { slot = ((A & 1) * 2 + (B & 1)) * g.C; A >>= 1; B >>= 1; }
+    uint16_t* dst = z + (((size_t)n * g.Hz + A) * g.Wz + B) * g.Cz + slot;
+    for (int c = 0; c < g.C; c++) {
+        const size_t at = ((size_t)n * g.C + c) * (size_t)plane + (size_t)p;
+        float level;
+        if (XK == 0) level = quantize_level_8bit<SIGNED ? DTYPE_INT8 : DTYPE_UINT8>(__ldg((const float*)x + at), scale, inv, zf);
+        else { const uint8_t code = ((const uint8_t*)x)[at]; level = __fsub_rn((float)(SIGNED ? (int)(int8_t)code : (int)code), zf); }
+        dst[c] = (uint16_t)(__float_as_uint(level) >> 16);
+    }
+}
+
+// int8 filter codes [M][C][KH][KW] -> bfloat16 levels in the channel order of the activations:
+// [KHz*KWz][M][Cz], or with `merged` [KHz][M][KWz*Cz] (the taps of one filter row side by side, for
+// the layout in which one activation row covers KWz neighbouring cells)
+__global__ void __launch_bounds__(256) filter_codes_to_levels(const int8_t* __restrict__ w, uint16_t* __restrict__ wt, QGeom g, int merged) {
     const size_t total = (size_t)g.KHz * g.KWz * g.M * g.Cz;
     for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
         const int cz = (int)(i % g.Cz);
         const size_t t1 = i / g.Cz;
-        const int m = (int)(t1 % g.M), tap = (int)(t1 / g.M);
-        const int ta = tap / g.KWz, tb = tap - ta * g.KWz;
+        int m, ta, tb;
+        if (merged) { tb = (int)(t1 % g.KWz); const size_t t2 = t1 / g.KWz; m = (int)(t2 % g.M); ta = (int)(t2 / g.M); }
+        else { m = (int)(t1 % g.M); const int tap = (int)(t1 / g.M); ta = tap / g.KWz; tb = tap - ta * g.KWz; }
         int v = 0;
         if (cz < g.S * g.S * g.C) {
             const int rs = cz / g.C, c = cz - rs * g.C;
@@ -247,16 +276,23 @@ static int qconv_run(const char* name, const QConvCall& q) {
     if (q.x_levels) {
         z = X->data;
     } else {
-        if (cudaMallocAsync(&z, z_bytes, s) != cudaSuccess) { cudaGetLastError(); return qconv_fail(name, TOPS_ERR_OOM, "scratch", nullptr); }
+        // 128 bytes of slack: with merged taps the last rows of the activation matrix reach past the last cell
+        if (cudaMallocAsync(&z, z_bytes + 128, s) != cudaSuccess) { cudaGetLastError(); return qconv_fail(name, TOPS_ERR_OOM, "scratch", nullptr); }
         // padding cells and padding channels are zero; a 1x1 convolution without padding over a channel
         // count that is a multiple of 8 has neither
         const bool every_cell_written = g.S == 1 && g.Hz == H && g.Wz == W && g.Cz == C;
-        ok = every_cell_written || TOPS_CUDA_OK(cudaMemsetAsync(z, 0, z_bytes, s));
+        ok = every_cell_written || TOPS_CUDA_OK(cudaMemsetAsync(z, 0, z_bytes + 128, s));
         const dim3 grid((H * W + 63) / 64, N, (C + 63) / 64);
+        const dim3 grid_few((H * W + 255) / 256, N);
         const void* zero_ptr = zero_given ? q.x_zero->data : nullptr;
         const float* scale_ptr = (const float*)q.x_scale->data;
         const bool is_signed = code_dt == DTYPE_INT8;
-        if (x_is_float) {
+        if (C <= 8) {
+            if (x_is_float && is_signed)       activations_to_levels_few_channels<0, true><<<grid_few, 256, 0, s>>>(X->data, (uint16_t*)z, g, scale_ptr, zero_ptr);
+            else if (x_is_float)               activations_to_levels_few_channels<0, false><<<grid_few, 256, 0, s>>>(X->data, (uint16_t*)z, g, scale_ptr, zero_ptr);
+            else if (is_signed)                activations_to_levels_few_channels<1, true><<<grid_few, 256, 0, s>>>(X->data, (uint16_t*)z, g, scale_ptr, zero_ptr);
+            else                               activations_to_levels_few_channels<1, false><<<grid_few, 256, 0, s>>>(X->data, (uint16_t*)z, g, scale_ptr, zero_ptr);
+        } else if (x_is_float) {
             if (is_signed) activations_to_levels<0, true><<<grid, 256, 0, s>>>(X->data, (uint16_t*)z, g, scale_ptr, zero_ptr);
             else           activations_to_levels<0, false><<<grid, 256, 0, s>>>(X->data, (uint16_t*)z, g, scale_ptr, zero_ptr);
         } else {
@@ -269,13 +305,23 @@ static int qconv_run(const char* name, const QConvCall& q) {
         if (!q.x_levels) cudaFreeAsync(z, s);
         return qconv_fail(name, TOPS_ERR_OOM, "scratch", nullptr);
     }
-    filter_codes_to_levels<<<grid_for(wt_bytes / 2, 256, st->sm_count, 4), 256, 0, s>>>((const int8_t*)Wq->data, (uint16_t*)wt, g);
+    // Few channels: the KWz taps of a filter row are KWz neighbouring cells, i.e. contiguous memory, so one
+    // activation "row" of KWz * Cz channels (rows overlapping, one cell apart) feeds a whole filter row per K
+    // block instead of a mostly empty K block per tap.  Only for scratch built here (it has the slack the last
+    // rows need) and only if the driver accepts the overlapping map.
+    ShiftedGemm sg;
+    sg.xp = z; sg.wt = wt; sg.es = 2; sg.fp8 = false; sg.a_format = 1u; sg.b_format = 1u;
+    sg.images = N; sg.Hp = g.Hz; sg.Wp = g.Wz; sg.C = g.Cz; sg.M = M;
+    sg.KH = g.KHz; sg.KW = g.KWz; sg.dil_h = dil_h; sg.dil_w = dil_w; sg.OH = OH; sg.OW = OW;
+    bool merged = false;
+    if (!q.x_levels && dil_w == 1 && g.KWz > 1 && g.Cz * g.KWz <= 64) {
+        ShiftedGemm trial = sg;
+        trial.C = g.Cz * g.KWz; trial.KW = 1; trial.a_row_stride_bytes = g.Cz * 2;
+        if (shifted_gemm_map_ok(trial)) { sg = trial; merged = true; }
+    }
+    filter_codes_to_levels<<<grid_for(wt_bytes / 2, 256, st->sm_count, 4), 256, 0, s>>>((const int8_t*)Wq->data, (uint16_t*)wt, g, merged ? 1 : 0);
     ok = ok && TOPS_CHECK_LAUNCH(name);
     if (ok) {
-        ShiftedGemm sg;
-        sg.xp = z; sg.wt = wt; sg.es = 2; sg.fp8 = false; sg.a_format = 1u; sg.b_format = 1u;
-        sg.images = N; sg.Hp = g.Hz; sg.Wp = g.Wz; sg.C = g.Cz; sg.M = M;
-        sg.KH = g.KHz; sg.KW = g.KWz; sg.dil_h = dil_h; sg.dil_w = dil_w; sg.OH = OH; sg.OW = OW;
         sg.Y = Y ? Y->data : nullptr; sg.dy = dy;
         sg.bias = (B && B->data) ? B->data : nullptr;
         sg.bias_dtype = DTYPE_FLOAT32;

@@ -263,6 +263,10 @@ QCONV_CASES = [  # N, C, H, W, M, k, pad, stride, x_dt, zero, relu, bias
     (2, 20, 17, 19, 40, 1, 0, 1, "uint8", 128, True, True),      # channels not a multiple of 8, odd sizes
     (2, 24, 15, 15, 48, 3, 1, 2, "uint8", 100, True, False),     # odd extent with stride 2
     (1, 256, 14, 14, 512, 3, 1, 1, "int8", -3, False, True),
+    (2, 3, 20, 22, 32, 3, 1, 1, "int8", 0, True, True),            # few channels: the taps of a filter row share a K block
+    (2, 16, 20, 20, 40, 3, 1, 1, "uint8", 7, False, True),
+    (3, 8, 18, 18, 24, 5, 2, 1, "int8", 1, True, False),
+    (2, 5, 33, 31, 16, 7, 3, 2, "int8", -4, True, True),
 ]
 
 
