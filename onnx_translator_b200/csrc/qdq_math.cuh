@@ -30,15 +30,14 @@ __device__ __forceinline__ int quantize_round_fast(float x, float inv_s, int z, 
     return (__float_as_int(t) - 0x4B400000) + z;
 }
 // 8-bit outputs with an 8-bit zero point: the same rounding and the same tie margin (2^-19 |q|,
-// folded into one multiply-add).  For int8 / uint8, quotients of 4096 and more saturate whichever
-// way they round (|z| <= 255), so they stay on the fast path up to the limit of the magic-number
-// rounding; fp8 outputs take the double division from 2^21 on like every other type.
+// folded into one multiply-add, which also sends |q| >= 2^18 to the double division: the margin
+// alone reaches 0.5 there).
 // `z_minus_magic` = z - 0x4B400000, the same for every element of a run with one zero point.
 __device__ __forceinline__ int quantize_round_8bit(float x, float inv_s, int z_minus_magic, bool& ok) {
     const float q = __fmul_rn(x, inv_s);
     const float t = __fadd_rn(q, 12582912.0f);
     const float d = __fsub_rn(q, __fsub_rn(t, 12582912.0f));
-    ok = (fmaf(fabsf(q), 1.9073486e-6f, fabsf(d)) < 0.5f) & (fabsf(q) < 2097152.0f);
+    ok = fmaf(fabsf(q), 1.9073486e-6f, fabsf(d)) < 0.5f;      // false too for |q| >= 2^18 (the margin alone is 0.5 there), Inf, NaN
     return __float_as_int(t) + z_minus_magic;
 }
 // The reference's arithmetic, element by element.
@@ -50,19 +49,7 @@ __device__ __forceinline__ typename Storage<DO>::type quantize_exact(double x, d
 }
 
 
-// One float32 value to its 8-bit code (DO = DTYPE_INT8 or DTYPE_UINT8), bit for bit what
-// quantize_linear_forward stores: the fast rounding where it is conclusive, the reference's double
-// division otherwise.  `inv_s` = approximate 1 / s, `z` the zero point.
-template <int DO>
-__device__ __forceinline__ int quantize_code_8bit(float x, float s, float inv_s, int z) {
-    bool ok;
-    int r = quantize_round_8bit(x, inv_s, z - 0x4B400000, ok);
-    if (!ok) return (int)quantize_exact<DO>((double)x, (double)s, (double)z);
-    constexpr int lo = DO == DTYPE_INT8 ? -128 : 0, hi = DO == DTYPE_INT8 ? 127 : 255;
-    return r < lo ? lo : (r > hi ? hi : r);
-}
-
-// The same code minus the zero point, i.e. the integer level the dequantised value is a multiple of,
+// The 8-bit code of one float32 value minus the zero point, i.e. the integer level the dequantised value is a multiple of,
 // as a float (exact: |level| <= 255), without leaving the float pipe on the fast path: the rounded
 // quotient is already a float integer, the saturation limits are float integers too.
 template <int DO>
@@ -71,7 +58,7 @@ __device__ __forceinline__ float quantize_level_8bit(float x, float s, float inv
     const float t = __fadd_rn(q, 12582912.0f);
     const float r = __fsub_rn(t, 12582912.0f);
     const float d = __fsub_rn(q, r);
-    const bool ok = (fmaf(fabsf(q), 1.9073486e-6f, fabsf(d)) < 0.5f) & (fabsf(q) < 2097152.0f);
+    const bool ok = fmaf(fabsf(q), 1.9073486e-6f, fabsf(d)) < 0.5f;     // false too for |q| >= 2^18, Inf, NaN
     if (!ok) return (float)((int)quantize_exact<DO>((double)x, (double)s, (double)zf)) - zf;
     constexpr float lo = DO == DTYPE_INT8 ? -128.0f : 0.0f, hi = DO == DTYPE_INT8 ? 127.0f : 255.0f;
     return __fsub_rn(fminf(fmaxf(__fadd_rn(r, zf), lo), hi), zf);
