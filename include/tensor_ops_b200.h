@@ -131,6 +131,34 @@ void softmax_forward(const Tensor* input, Tensor* output, int axis);
 void flatten_forward(const Tensor* input, Tensor* output);
 void reshape_forward(const Tensor* input, Tensor* output);
 
+/* ---- operators around the hot path in exported CNNs (same signatures as the reference) -------- */
+
+/* tensor_ops/tensor_ops.h:282 (tensor_ops.c:1497-1519).  Element-wise conversion.  float32 /
+   float64 / float16 / bfloat16 sources going to an integer type are truncated toward zero, then
+   saturated; every other pair is read as a double and stored like any operator result (so an fp8
+   source going to an integer rounds to nearest-even). */
+void cast_forward(const Tensor* input, Tensor* output);
+
+/* tensor_ops/tensor_ops.h:276 (tensor_ops.c:1523-1543).  output = min(max(input, min), max) compared
+   in double, lower bound first; either bound may be NULL; a NaN value or bound changes nothing.
+   Superset: the bounds broadcast against the input (the reference wants them at full size). */
+void clip_forward(const Tensor* input, Tensor* output, const Tensor* min, const Tensor* max);
+
+/* tensor_ops/tensor_ops.h:464 (tensor_ops.c:2735-2789).  NCHW average pooling: double sum of the taps
+   inside the plane in kh -> kw order divided by their number, or by the number of all taps when
+   count_include_pad is set; a window without taps gives 0. */
+void average_pool_forward(const Tensor* X, Tensor* Y, PoolParams* params, int count_include_pad);
+
+/* tensor_ops/tensor_ops.h:466 (tensor_ops.c:2844-2868).  Mean of every H x W plane of a 4-D tensor
+   (sequential double sum); output has one element per plane. */
+void global_average_pool_forward(const Tensor* input, Tensor* output);
+
+/* tensor_ops/tensor_ops.h:476 (tensor_ops.c:3041-3083).  Inference batch normalisation over dimension
+   1: y = x * a + k with a = scale / sqrt(var + epsilon), k = B - mean * a, all in double, the product
+   and the sum rounded separately. */
+void batch_norm_forward(const Tensor* input, const Tensor* scale, const Tensor* B, const Tensor* mean,
+                        const Tensor* var, Tensor* output, float epsilon);
+
 /* ---- additive interface (no counterpart in the reference) -------------------------------------- */
 
 /* Error codes kept by the library (sticky until cleared; the first error wins). */

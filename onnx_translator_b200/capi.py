@@ -123,6 +123,11 @@ SIGNATURES = {
     "tops_host_alloc": (_V, [_SZ]),
     "tops_host_free": (None, [_V]),
     "tops_dtype_size": (_SZ, [_I]),
+    "cast_forward": (None, [_P, _P]),
+    "clip_forward": (None, [_P, _P, _P, _P]),
+    "average_pool_forward": (None, [_P, _P, ctypes.POINTER(CPoolParams), _I]),
+    "global_average_pool_forward": (None, [_P, _P]),
+    "batch_norm_forward": (None, [_P, _P, _P, _P, _P, _P, ctypes.c_float]),
     "tops_quantize_linear_axis_forward": (None, [_P, _P, _P, _P, _I]),
     "tops_dequantize_linear_axis_forward": (None, [_P, _P, _P, _P, _I]),
     "tops_conv2d_forward_noalloc": (None, [_P, _P, _P, _P, ctypes.POINTER(CConvParams)]),

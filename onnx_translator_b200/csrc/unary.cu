@@ -1,9 +1,15 @@
-// Relu, Abs and Cos (tensor_ops.c:708-757, 815-854).
+// Relu, Abs and Cos (tensor_ops.c:708-757, 815-854); Cast (tensor_ops.c:1497-1519).
 #include "elementwise.cuh"
 
 namespace tops {
 
-enum UnaryOp { kRelu = 0, kAbs = 1, kCos = 2 };
+enum UnaryOp { kRelu = 0, kAbs = 1, kCos = 2, kCast = 3 };
+
+// Cast truncates toward zero only for float32 / float64 / float16 / bfloat16 sources going to an integer type;
+// every other pair is a double followed by the generic store (fp8 -> integer rounds to nearest-even).
+__host__ __device__ constexpr bool cast_truncates(int dx, int dout) {
+    return (dx == DTYPE_FLOAT32 || dx == DTYPE_FLOAT64 || dx == DTYPE_FLOAT16 || dx == DTYPE_BFLOAT16) && dtype_is_int(dout);
+}
 
 bool cos_fast(const Tensor* x, Tensor* y, const double* lut);     // cos_fast.cu
 
@@ -30,6 +36,9 @@ template <int DX, int DO, int OP>
 __device__ __forceinline__ typename Storage<DO>::type unary_elem(typename Storage<DX>::type s, const double* lut) {
     if constexpr (OP == kCos) {
         return from_f64<DO>(cos_by_table(to_f64<DX>(s), lut));
+    } else if constexpr (OP == kCast) {
+        if constexpr (cast_truncates(DX, DO)) return from_i64<DO>(x86_f64_to_i64(to_f64<DX>(s)));
+        else return from_f64<DO>(to_f64<DX>(s));
     } else if constexpr (dtype_is_int(DX)) {                   // branch on the INPUT dtype
         if constexpr (dtype_is_narrow_int(DX) && DO != DTYPE_INT64) {
             const int v = to_i32_narrow<DX>(s);
@@ -76,12 +85,12 @@ struct UnaryBody {
         Run<typename Storage<DO>::type, kV> res;
         constexpr bool float_lane = OP != kCos && dtype_exact_in_f32(DX) && !dtype_is_int(DX) &&
                                     !dtype_is_int(DO) && DO != DTYPE_FLOAT64;
-        constexpr bool int_lane = OP != kCos && dtype_is_narrow_int(DX) && dtype_is_narrow_int(DO);
+        constexpr bool int_lane = OP != kCos && OP != kCast && dtype_is_narrow_int(DX) && dtype_is_narrow_int(DO);
         if constexpr (float_lane) {
             float f[kV];
             decode_floats<DX, kV>(in, f);
             #pragma unroll
-            for (int j = 0; j < kV; j++) f[j] = (OP == kRelu) ? (f[j] > 0 ? f[j] : 0.0f) : fabsf(f[j]);
+            for (int j = 0; j < kV; j++) f[j] = (OP == kCast) ? f[j] : (OP == kRelu) ? (f[j] > 0 ? f[j] : 0.0f) : fabsf(f[j]);
             encode_floats<DO, kV>(f, res);
         } else if constexpr (int_lane) {
             int v[kV];
@@ -108,6 +117,10 @@ struct UnaryGenericBody {
     __device__ __forceinline__ void operator()(uint32_t i, uint32_t) const {
         if constexpr (OP == kCos) {
             store_f64_rt(out, dout, i, cos_by_table(load_f64_rt(x, dx, i), lut));
+        } else if constexpr (OP == kCast) {
+            const double v = load_f64_rt(x, dx, i);
+            if (cast_truncates(dx, dout)) store_i64_rt(out, dout, i, x86_f64_to_i64(v));
+            else store_f64_rt(out, dout, i, v);
         } else if (dtype_is_int(dx)) {
             const long long v = load_i64_rt(x, dx, i);
             long long r;
@@ -171,15 +184,22 @@ static void unary_forward(const char* name, const Tensor* x, Tensor* y) {
     const int dx = (int)x->dtype, dout = (int)y->dtype;
     bool done = false, ok = true;
 #define TOPS_SAME(DT) if (!done && dx == DT && dout == DT) { ok = run_typed<DT, DT, OP>(name, x, y, lut); done = true; }
+#define TOPS_PAIR(DA, DB) if (!done && dx == DA && dout == DB) { ok = run_typed<DA, DB, OP>(name, x, y, lut); done = true; }
     if (OP == kCos) {
         if (cos_fast(x, y, lut)) done = true;          // float32 / float16 / bfloat16, same dtype out
         TOPS_SAME(DTYPE_FLOAT64)
+    } else if (OP == kCast) {                          // the conversions exported networks contain; the rest is generic
+        TOPS_PAIR(DTYPE_FLOAT32, DTYPE_FLOAT16) TOPS_PAIR(DTYPE_FLOAT16, DTYPE_FLOAT32) TOPS_PAIR(DTYPE_FLOAT32, DTYPE_BFLOAT16)
+        TOPS_PAIR(DTYPE_BFLOAT16, DTYPE_FLOAT32) TOPS_PAIR(DTYPE_FLOAT32, DTYPE_INT32) TOPS_PAIR(DTYPE_INT32, DTYPE_FLOAT32)
+        TOPS_PAIR(DTYPE_FLOAT32, DTYPE_INT8) TOPS_PAIR(DTYPE_INT8, DTYPE_FLOAT32) TOPS_PAIR(DTYPE_UINT8, DTYPE_FLOAT32)
+        TOPS_PAIR(DTYPE_FLOAT32, DTYPE_FLOAT32) TOPS_PAIR(DTYPE_INT64, DTYPE_FLOAT32) TOPS_PAIR(DTYPE_FLOAT32, DTYPE_INT64)
     } else {
         TOPS_SAME(DTYPE_FLOAT8_E4M3) TOPS_SAME(DTYPE_FLOAT8_E5M2) TOPS_SAME(DTYPE_FLOAT16) TOPS_SAME(DTYPE_BFLOAT16)
         TOPS_SAME(DTYPE_FLOAT32) TOPS_SAME(DTYPE_FLOAT64) TOPS_SAME(DTYPE_INT4) TOPS_SAME(DTYPE_INT8)
         TOPS_SAME(DTYPE_UINT8) TOPS_SAME(DTYPE_INT16) TOPS_SAME(DTYPE_INT32) TOPS_SAME(DTYPE_INT64)
     }
 #undef TOPS_SAME
+#undef TOPS_PAIR
     if (!done) ok = run_generic<OP>(name, x, y, lut);
     (void)ok;
     finish_op();
@@ -192,3 +212,4 @@ using namespace tops;
 TOPS_API void relu_forward(const Tensor* input, Tensor* output) { unary_forward<kRelu>("relu_forward", input, output); }
 TOPS_API void abs_forward(const Tensor* input, Tensor* output)  { unary_forward<kAbs>("abs_forward", input, output); }
 TOPS_API void cos_forward(const Tensor* input, Tensor* output)  { unary_forward<kCos>("cos_forward", input, output); }
+TOPS_API void cast_forward(const Tensor* input, Tensor* output) { unary_forward<kCast>("cast_forward", input, output); }

@@ -314,3 +314,90 @@ class Reshape(Flatten):
             known = int(np.prod([s for s in shape if s != -1], dtype=np.int64))
             shape[shape.index(-1)] = total // known if known else 0
         return tuple(int(s) for s in shape)
+
+
+# ---- operators around the hot path in exported CNNs ------------------------------------------------------------
+class Cast(_Unary):
+    """Element-wise conversion to ``dtype`` (nn/Operators.py:1270-1280)."""
+    _c_name = "cast_forward"
+
+
+class Clip(Ops):
+    """min(max(x, min), max) with optional bounds that broadcast against x (nn/Operators.py:1282-1340)."""
+
+    def __init__(self, inputs, outputs, dtype, version="17"):
+        super().__init__(inputs, outputs)
+        self.dtype = dtype
+        self.version = version
+
+    def forward(self, input: Tensor, min_val: Tensor = None, max_val: Tensor = None) -> dict:
+        shapes = [self._shape_of(t) for t in (input, min_val, max_val) if t is not None]
+        out_shape = np.broadcast_shapes(*shapes)
+        out_dtype = self.dtype if self.dtype else input.dtype
+        operands = [t for t in (input, min_val, max_val) if t is not None]
+        handles = {id(t): self._numpy_to_ctensor(t.data, t.dtype) for t in operands}
+        y = self._new_output(out_shape, out_dtype)
+        self.lib.clip_forward(handles[id(input)], y, handles[id(min_val)] if min_val is not None else None,
+                              handles[id(max_val)] if max_val is not None else None)
+        return self._publish(self._finish(list(handles.values()), y, out_shape, out_dtype))
+
+    def forward_(self, input: Tensor_, min_val: Tensor_ = None, max_val: Tensor_ = None) -> dict:
+        return self._publish(Tensor_(*input.size, dtype=self.dtype))
+
+
+class AveragePool(MaxPool):
+    """Average pooling over NCHW (nn/Operators.py:2895-2960)."""
+
+    def __init__(self, inputs, outputs, kernel_shape, pads, strides, dtype, dilations=[1, 1], count_include_pad=0, version="17"):
+        super().__init__(inputs, outputs, kernel_shape, pads, strides, dtype, dilations, version)
+        self.count_include_pad = count_include_pad
+
+    def forward(self, x: Tensor) -> dict:
+        n, c, h, w = x.data.shape
+        out_shape = (n, c,
+                     _pooled_extent(h, self.pads[0], self.pads[2], self.dilations[0], self.kernel_shape[0], self.strides[0]),
+                     _pooled_extent(w, self.pads[1], self.pads[3], self.dilations[1], self.kernel_shape[1], self.strides[1]))
+        keep = [_int_ptr(self.pads), _int_ptr(self.strides), _int_ptr(self.dilations), _int_ptr(self.kernel_shape)]
+        params = CPoolParams(keep[0][1], keep[1][1], keep[2][1], keep[3][1])
+        xh = self._numpy_to_ctensor(x.data, x.dtype)
+        y = self._new_output(out_shape, self.dtype)
+        self.lib.average_pool_forward(xh, y, ctypes.byref(params), int(self.count_include_pad))
+        return self._publish(self._finish([xh], y, out_shape, self.dtype))
+
+
+class GlobalAveragePool(Ops):
+    """Mean over H x W of a 4-D tensor, output [N, C, 1, 1] (nn/Operators.py:2998-3025)."""
+
+    def __init__(self, inputs, outputs, dtype="float32", version="17"):
+        super().__init__(inputs, outputs)
+        self.dtype = dtype
+        self.version = version
+
+    def forward(self, x: Tensor) -> dict:
+        n, c = x.data.shape[:2]
+        out_shape = (n, c, 1, 1)
+        xh = self._numpy_to_ctensor(x.data, x.dtype)
+        y = self._new_output(out_shape, self.dtype)
+        self.lib.global_average_pool_forward(xh, y)
+        return self._publish(self._finish([xh], y, out_shape, self.dtype))
+
+    def forward_(self, x: Tensor_) -> dict:
+        return self._publish(Tensor_(x.size[0], x.size[1], 1, 1, dtype=self.dtype))
+
+
+class BatchNormalization(Ops):
+    """Inference batch normalisation over dimension 1 (nn/Operators.py:3281-3320)."""
+
+    def __init__(self, inputs, outputs, epsilon=1e-5, momentum=0.9, dtype="float32", version="17"):
+        super().__init__(inputs, outputs)
+        self.epsilon, self.momentum, self.dtype, self.version = epsilon, momentum, dtype, version
+
+    def forward(self, x: Tensor, scale: Tensor, B: Tensor, mean: Tensor, var: Tensor) -> dict:
+        shape = self._shape_of(x)
+        handles = [self._numpy_to_ctensor(t.data, t.dtype) for t in (x, scale, B, mean, var)]
+        y = self._new_output(shape, self.dtype)
+        self.lib.batch_norm_forward(handles[0], handles[1], handles[2], handles[3], handles[4], y, ctypes.c_float(self.epsilon))
+        return self._publish(self._finish(handles, y, shape, self.dtype))
+
+    def forward_(self, x: Tensor_, *_) -> dict:
+        return self._publish(Tensor_(*x.size, dtype=self.dtype))

@@ -104,12 +104,16 @@ class HostOracle:
                      mul="orc_mul", div="orc_div", quantize="orc_quantize_linear",
                      dequantize="orc_dequantize_linear", conv="orc_conv2d", pool="orc_max_pool",
                      gemm="orc_gemm", softmax="orc_softmax", flatten="orc_flatten",
+                     cast="orc_cast", clip="orc_clip", average_pool="orc_average_pool",
+                     global_average_pool="orc_global_average_pool", batch_norm="orc_batch_norm",
                      init="orc_init_cos_lut"),
         "ref": dict(relu="relu_forward", abs="abs_forward", cos="cos_forward", add="add_forward",
                     sub="sub_forward", mul="mul_forward", div="div_forward",
                     quantize="quantize_linear_forward", dequantize="dequantize_linear_forward",
                     conv="conv2d_forward", pool="max_pool_forward", gemm="gemm_forward",
-                    softmax="softmax_forward", flatten="flatten_forward", init="init_cos_lut"),
+                    softmax="softmax_forward", flatten="flatten_forward", cast="cast_forward", clip="clip_forward",
+                    average_pool="average_pool_forward", global_average_pool="global_average_pool_forward",
+                    batch_norm="batch_norm_forward", init="init_cos_lut"),
     }
 
     def __init__(self, kind: str = "port"):
@@ -128,6 +132,8 @@ class HostOracle:
         self._fn["gemm"].argtypes = [ctypes.c_void_p] * 4 + [ctypes.c_float, ctypes.c_float,
                                                              ctypes.c_int, ctypes.c_int]
         self._fn["softmax"].argtypes = [ctypes.c_void_p, ctypes.c_void_p, ctypes.c_int]
+        self._fn["average_pool"].argtypes = [ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_int]
+        self._fn["batch_norm"].argtypes = [ctypes.c_void_p] * 6 + [ctypes.c_float]
         self._fn["init"]()
         if kind == "port":
             self.lib.orc_encode.restype = ctypes.c_uint32
@@ -201,6 +207,44 @@ class HostOracle:
         keep = (_ints(pads), _ints(strides), _ints(dilations), _ints(kernel))
         prm = _CPoolParams(*[ctypes.cast(k, ctypes.POINTER(ctypes.c_int)) for k in keep])
         self._fn["pool"](xi.ref, yo.ref, ctypes.byref(prm))
+        return yo.arr
+
+    # -- operators around the hot path ----------------------------------------------------------
+    def cast(self, x, x_dt: str, out_dt: str) -> np.ndarray:
+        return self.unary("cast", x, x_dt, out_dt)
+
+    def clip(self, x, x_dt, lo, lo_dt, hi, hi_dt, out_dt) -> np.ndarray:
+        """Bounds (either may be None) are broadcast to the input's shape first, as nn/Operators.py does."""
+        xi = _Wrapped(x, x_dt)
+        bounds = []
+        for b, dt in ((lo, lo_dt), (hi, hi_dt)):
+            bounds.append(None if b is None else _Wrapped(np.broadcast_to(np.asarray(b, dtype=DTYPE_STORAGE[dt]), xi.arr.shape), dt))
+        yo = _out(xi.arr.shape, out_dt)
+        self._fn["clip"](xi.ref, yo.ref, bounds[0].ref if bounds[0] else None, bounds[1].ref if bounds[1] else None)
+        return yo.arr
+
+    def average_pool(self, x, x_dt, out_dt, kernel, pads, strides, dilations=(1, 1), count_include_pad=0):
+        xi = _Wrapped(x, x_dt)
+        n, c, h, wd = xi.arr.shape
+        oh = (h + pads[0] + pads[2] - dilations[0] * (kernel[0] - 1) - 1) // strides[0] + 1
+        ow = (wd + pads[1] + pads[3] - dilations[1] * (kernel[1] - 1) - 1) // strides[1] + 1
+        yo = _out((n, c, oh, ow), out_dt)
+        keep = (_ints(pads), _ints(strides), _ints(dilations), _ints(kernel))
+        prm = _CPoolParams(*[ctypes.cast(k, ctypes.POINTER(ctypes.c_int)) for k in keep])
+        self._fn["average_pool"](xi.ref, yo.ref, ctypes.byref(prm), int(count_include_pad))
+        return yo.arr
+
+    def global_average_pool(self, x, x_dt, out_dt):
+        xi = _Wrapped(x, x_dt)
+        yo = _out(xi.arr.shape[:2] + (1, 1), out_dt)
+        self._fn["global_average_pool"](xi.ref, yo.ref)
+        return yo.arr
+
+    def batch_norm(self, x, x_dt, scale, bias, mean, var, p_dt, out_dt, epsilon=1e-5):
+        xi = _Wrapped(x, x_dt)
+        ps = [_Wrapped(t, p_dt) for t in (scale, bias, mean, var)]
+        yo = _out(xi.arr.shape, out_dt)
+        self._fn["batch_norm"](xi.ref, ps[0].ref, ps[1].ref, ps[2].ref, ps[3].ref, yo.ref, ctypes.c_float(epsilon))
         return yo.arr
 
     def gemm(self, a, a_dt, b, b_dt, c, c_dt, out_dt, alpha=1.0, beta=1.0, transA=0, transB=0):

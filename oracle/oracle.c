@@ -560,6 +560,108 @@ ORC_API void orc_softmax(const OrcTensor* x, OrcTensor* y, int axis) {
     }
 }
 
+/* ------------------------------------------------------------------------------------------
+ * Operators that surround the hot path in exported CNNs.
+ * ---------------------------------------------------------------------------------------- */
+
+/* Cast.  tensor_ops.c:1497-1519: float32 / float64 / float16 / bfloat16 sources going to an integer
+   type are TRUNCATED toward zero (C cast to int64, then the saturating integer store); every other
+   pair goes through a double and the generic store (so fp8 -> int rounds to nearest-even, and
+   int64 -> int64 passes through a double). */
+ORC_API void orc_cast(const OrcTensor* x, OrcTensor* y) {
+    if (!unary_args_ok(x, y)) return;
+    const int truncating = (x->dtype == DT_F32 || x->dtype == DT_F64 || x->dtype == DT_F16 || x->dtype == DT_BF16) &&
+                           is_integer_dtype(y->dtype);
+    #pragma omp parallel for
+    for (size_t i = 0; i < x->size; i++) {
+        const double v = load_f64(x, i);
+        if (truncating) store_i64(y, i, trunc_to_i64_x86(v));
+        else store_f64(y, i, v);
+    }
+}
+
+/* Clip.  tensor_ops.c:1523-1543: compare in double, lower bound first; a NaN value or a NaN bound
+   leaves the value as it is.  Bounds are optional and indexed like the input. */
+ORC_API void orc_clip(const OrcTensor* x, OrcTensor* y, const OrcTensor* lo, const OrcTensor* hi) {
+    if (!x || !y) return;
+    const int has_lo = lo && lo->data, has_hi = hi && hi->data;
+    #pragma omp parallel for
+    for (size_t i = 0; i < y->size; i++) {
+        double v = load_f64(x, i);
+        if (has_lo) { const double b = load_f64(lo, i); if (v < b) v = b; }
+        if (has_hi) { const double b = load_f64(hi, i); if (v > b) v = b; }
+        store_f64(y, i, v);
+    }
+}
+
+/* AveragePool.  tensor_ops.c:2735-2789: double sum over the taps inside the plane in kh -> kw
+   order, divided by their number (or by the number of all taps with count_include_pad); a window
+   without taps gives 0. */
+ORC_API void orc_average_pool(const OrcTensor* x, OrcTensor* y, const OrcPoolParams* p, int count_include_pad) {
+    if (!x || !y || !p) return;
+    const int N = x->shape[0], C = x->shape[1], H = x->shape[2], W = x->shape[3];
+    const int OH = y->shape[2], OW = y->shape[3];
+    const int KH = p->kernel_shape[0], KW = p->kernel_shape[1];
+    const int pt = p->pads[0], pl = p->pads[1];
+    const int sh = p->strides[0], sw = p->strides[1];
+    const int dh = p->dilations[0], dw = p->dilations[1];
+    #pragma omp parallel for collapse(2)
+    for (int n = 0; n < N; n++)
+    for (int c = 0; c < C; c++) {
+        const size_t in_plane = ((size_t)n * C + (size_t)c) * H * W;
+        const size_t out_plane = ((size_t)n * C + (size_t)c) * OH * OW;
+        for (int oh = 0; oh < OH; oh++)
+        for (int ow = 0; ow < OW; ow++) {
+            double sum = 0.0;
+            int count = 0;
+            for (int kh = 0; kh < KH; kh++)
+            for (int kw = 0; kw < KW; kw++) {
+                const int ih = oh * sh + kh * dh - pt;
+                const int iw = ow * sw + kw * dw - pl;
+                if (ih < 0 || ih >= H || iw < 0 || iw >= W) { if (count_include_pad) count++; continue; }
+                sum += load_f64(x, in_plane + (size_t)ih * W + (size_t)iw);
+                count++;
+            }
+            store_f64(y, out_plane + (size_t)oh * OW + (size_t)ow, count > 0 ? sum / count : 0.0);
+        }
+    }
+}
+
+/* GlobalAveragePool.  tensor_ops.c:2844-2868: 4-D inputs only; sequential double sum of each
+   H x W plane divided by H * W. */
+ORC_API void orc_global_average_pool(const OrcTensor* x, OrcTensor* y) {
+    if (!x || !y || x->ndim != 4) return;
+    const int planes = x->shape[0] * x->shape[1], spatial = x->shape[2] * x->shape[3];
+    #pragma omp parallel for
+    for (int n = 0; n < planes; n++) {
+        double sum = 0.0;
+        for (int i = 0; i < spatial; i++) sum += load_f64(x, (size_t)n * spatial + i);
+        store_f64(y, (size_t)n, sum / spatial);
+    }
+}
+
+/* BatchNormalization (inference).  tensor_ops.c:3041-3083: per channel a = scale / sqrt(var + eps)
+   (eps arrives as a float and is widened), k = bias - mean * a; then y = x * a + k with separate
+   roundings of the product and the sum (no fused multiply-add in the reference's build). */
+ORC_API void orc_batch_norm(const OrcTensor* x, const OrcTensor* scale, const OrcTensor* bias, const OrcTensor* mean,
+                            const OrcTensor* var, OrcTensor* y, float epsilon) {
+    if (!x || !scale || !bias || !mean || !var || !y) return;
+    const int N = x->shape[0], C = x->shape[1];
+    size_t spatial = 1;
+    for (int d = 2; d < x->ndim; d++) spatial *= (size_t)x->shape[d];
+    #pragma omp parallel for collapse(2)
+    for (int n = 0; n < N; n++)
+    for (int c = 0; c < C; c++) {
+        const double inv_std = 1.0 / sqrt(load_f64(var, c) + (double)epsilon);
+        const double a = load_f64(scale, c) * inv_std;
+        const double k = load_f64(bias, c) - load_f64(mean, c) * a;
+        const size_t base = ((size_t)n * C + (size_t)c) * spatial;
+        for (size_t i = 0; i < spatial; i++) {
+            store_f64(y, base + i, load_f64(x, base + i) * a + k);       /* two roundings: this file is built with -ffp-contract=off */
+        }
+    }
+}
+
 /* Flatten / Reshape: a byte copy.  tensor_ops.c:1289-1299 */
 ORC_API void orc_flatten(const OrcTensor* x, OrcTensor* y) {
     if (!x || !y || x->size != y->size) return;

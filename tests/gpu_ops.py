@@ -60,3 +60,29 @@ def flatten(x, x_dt, out_shape, copy=True):
     node = ops.Flatten([], [], axis=1, dtype=x_dt, copy=copy)
     out = node.forward(_t(x, x_dt))["tensor"].numpy()
     return out.reshape(out_shape)
+
+
+# ---- operators around the hot path -------------------------------------------------------------------------------
+def cast(x, x_dt, out_dt):
+    return ops.Cast([], [], dtype=out_dt).forward(_t(x, x_dt))["tensor"].numpy()
+
+
+def clip(x, x_dt, lo, lo_dt, hi, hi_dt, out_dt):
+    lo_t = None if lo is None else _t(lo, lo_dt)
+    hi_t = None if hi is None else _t(hi, hi_dt)
+    return ops.Clip([], [], dtype=out_dt).forward(_t(x, x_dt), lo_t, hi_t)["tensor"].numpy()
+
+
+def average_pool(x, x_dt, out_dt, kernel, pads, strides, dilations=(1, 1), count_include_pad=0):
+    node = ops.AveragePool([], [], kernel_shape=list(kernel), pads=list(pads), strides=list(strides), dtype=out_dt,
+                           dilations=list(dilations), count_include_pad=count_include_pad)
+    return node.forward(_t(x, x_dt))["tensor"].numpy()
+
+
+def global_average_pool(x, x_dt, out_dt):
+    return ops.GlobalAveragePool([], [], dtype=out_dt).forward(_t(x, x_dt))["tensor"].numpy()
+
+
+def batch_norm(x, x_dt, scale, bias, mean, var, p_dt, out_dt, epsilon=1e-5):
+    node = ops.BatchNormalization([], [], epsilon=epsilon, dtype=out_dt)
+    return node.forward(_t(x, x_dt), _t(scale, p_dt), _t(bias, p_dt), _t(mean, p_dt), _t(var, p_dt))["tensor"].numpy()

@@ -122,8 +122,9 @@ def test_no_gpu_means_errors_not_a_cpu_path(lib):
     assert lib.tops_last_error() != 0
     lib.tops_clear_error()
     from onnx_translator_b200 import nn
+    from onnx_translator_b200.nn import Operators
     nn.Ops._lib = None
-    node = nn.Operators.RELU([], [], dtype="float32")           # constructing a node needs no GPU ...
+    node = Operators.RELU([], [], dtype="float32")              # constructing a node needs no GPU ...
     with pytest.raises(capi.TensorOpsError):                     # ... running it without one fails loudly
         node.forward(nn.Tensor(4, dtype="float32"))
     lib.tops_clear_error()

@@ -67,3 +67,38 @@ def test_cuda_library_reproduces_golden_vectors(case):
         assert np.all(np.abs(g - w) <= (1e-6 + ulp) * np.abs(w) + step + 1e-45)
     else:
         assert_same_codes(got, want, out_dt, _ids(case))
+
+
+# ---- Cast, Clip, AveragePool, GlobalAveragePool, BatchNormalization (tests/golden/make_adjacent_golden.py) --------------
+with open(os.path.join(HERE, "golden", "adjacent_ops.json")) as _f:
+    ADJ_CASES = json.load(_f)
+ADJ_ARRAYS = np.load(os.path.join(HERE, "golden", "adjacent_ops.npz"))
+
+
+def _run_adjacent(backend, case):
+    ins = [None if k is None else ADJ_ARRAYS[k] for k in case["inputs"]]
+    p, op = case["params"], case["op"]
+    if op == "cast":
+        return backend.cast(ins[0], p["x_dt"], p["out_dt"])
+    if op == "clip":
+        return backend.clip(ins[0], p["x_dt"], ins[1], p["b_dt"], ins[2], p["b_dt"], p["out_dt"])
+    if op == "average_pool":
+        return backend.average_pool(ins[0], p["x_dt"], p["out_dt"], tuple(p["kernel"]), tuple(p["pads"]), tuple(p["strides"]),
+                                    tuple(p["dilations"]), p["count_include_pad"])
+    if op == "global_average_pool":
+        return backend.global_average_pool(ins[0], p["x_dt"], p["out_dt"])
+    if op == "batch_norm":
+        return backend.batch_norm(ins[0], p["x_dt"], ins[1], ins[2], ins[3], ins[4], p["p_dt"], p["out_dt"], p["epsilon"])
+    raise AssertionError(op)
+
+
+@pytest.mark.parametrize("case", ADJ_CASES, ids=_ids)
+def test_oracle_reproduces_adjacent_golden_vectors(port, case):
+    assert_same_codes(_run_adjacent(port, case), ADJ_ARRAYS[f"c{case['id']}_out"], case["params"]["out_dt"], _ids(case))
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("case", ADJ_CASES, ids=_ids)
+def test_cuda_library_reproduces_adjacent_golden_vectors(case):
+    import gpu_ops
+    assert_same_codes(_run_adjacent(gpu_ops, case), ADJ_ARRAYS[f"c{case['id']}_out"], case["params"]["out_dt"], _ids(case))

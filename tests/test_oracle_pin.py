@@ -265,3 +265,75 @@ def test_codec_exhaustive_against_reference(port, ref, dt):
     for low in (0x000, 0x001, 0x7FF, 0x800, 0x801, 0xFFF):
         x = (hi | np.uint32(low)).view(np.float32)
         assert_same_codes(port.unary("abs", x, "float32", dt), ref.unary("abs", x, "float32", dt), dt, f"encode low={low:#x}")
+
+
+# ---- operators around the hot path: Cast, Clip, AveragePool, GlobalAveragePool, BatchNormalization --------------------
+@pytest.mark.parametrize("x_dt", ALL_DTYPES)
+def test_cast_all_dtype_pairs(port, ref, x_dt):
+    """float32 / float64 / float16 / bfloat16 -> integer truncates; everything else takes the generic store."""
+    rng = np.random.default_rng(zlib.crc32(f"cast{x_dt}".encode()))
+    x = make(rng, (33, 21), x_dt)
+    if x_dt in FLOAT_DTYPES and x_dt not in ("float8_e4m3", "float8_e5m2"):
+        with np.errstate(over="ignore", invalid="ignore"):
+            x.reshape(-1)[:51] = from_f64(_special_values(x_dt), x_dt)
+    for out_dt in OUT_SAMPLE:
+        assert_same_codes(port.cast(x, x_dt, out_dt), ref.cast(x, x_dt, out_dt), out_dt, f"cast {x_dt}->{out_dt}")
+
+
+@pytest.mark.parametrize("plan", [("float32", "float32", "float32"), ("float16", "float32", "float16"), ("int8", "int8", "int8"),
+                                  ("int32", "float32", "int32"), ("bfloat16", "bfloat16", "float32"), ("float64", "float64", "float64"),
+                                  ("float8_e4m3", "float32", "float8_e4m3"), ("uint8", "uint8", "int16")], ids="-".join)
+def test_clip(port, ref, plan):
+    x_dt, b_dt, out_dt = plan
+    rng = np.random.default_rng(zlib.crc32("clip".encode() + "-".join(plan).encode()))
+    x = make(rng, (6, 5, 7), x_dt)
+    if x_dt in ("float32", "float64"):
+        x.reshape(-1)[:4] = [np.nan, np.inf, -np.inf, -0.0]
+    lo = from_f64(np.array([-3.0]), b_dt) if b_dt not in ("uint8",) else np.array([2], np.uint8)
+    hi = from_f64(np.array([5.0]), b_dt) if b_dt not in ("uint8",) else np.array([9], np.uint8)
+    for lo_, hi_ in ((lo, hi), (lo, None), (None, hi), (None, None)):
+        assert_same_codes(port.clip(x, x_dt, lo_, b_dt, hi_, b_dt, out_dt), ref.clip(x, x_dt, lo_, b_dt, hi_, b_dt, out_dt), out_dt)
+    if b_dt == "float32":                                    # a NaN bound leaves the values alone
+        nan = np.array([np.nan], np.float32)
+        assert_same_codes(port.clip(x, x_dt, nan, b_dt, hi, b_dt, out_dt), ref.clip(x, x_dt, nan, b_dt, hi, b_dt, out_dt), out_dt)
+
+
+@pytest.mark.parametrize("plan", [
+    ("float32", "float32", (2, 3, 9, 8), (3, 3), (1, 1, 1, 1), (2, 2), (1, 1)),
+    ("float16", "float16", (1, 4, 12, 12), (2, 2), (0, 0, 0, 0), (2, 2), (1, 1)),
+    ("int8", "int8", (2, 2, 7, 7), (3, 2), (1, 0, 1, 1), (1, 2), (1, 1)),
+    ("bfloat16", "float32", (1, 2, 10, 11), (3, 3), (2, 2, 2, 2), (1, 1), (2, 2)),
+    ("float32", "float32", (1, 1, 3, 3), (2, 2), (2, 2, 2, 2), (3, 3), (1, 1)),          # windows made of padding only
+    ("float64", "float64", (3, 5, 7, 7), (7, 7), (0, 0, 0, 0), (1, 1), (1, 1)),
+], ids=lambda p: f"{p[0]}-{p[2]}-k{p[3]}")
+@pytest.mark.parametrize("include_pad", [0, 1])
+def test_average_pool(port, ref, plan, include_pad):
+    x_dt, out_dt, xs, kernel, pads, strides, dil = plan
+    rng = np.random.default_rng(23)
+    x = make(rng, xs, x_dt)
+    args = (x, x_dt, out_dt, kernel, pads, strides, dil, include_pad)
+    assert_same_codes(port.average_pool(*args), ref.average_pool(*args), out_dt)
+
+
+@pytest.mark.parametrize("plan", [("float32", "float32", (4, 6, 7, 7)), ("float16", "float16", (2, 3, 5, 9)), ("int8", "float32", (1, 8, 4, 4)),
+                                  ("bfloat16", "bfloat16", (3, 2, 1, 1)), ("float32", "int32", (2, 2, 3, 3))], ids=lambda p: f"{p[0]}-{p[1]}")
+def test_global_average_pool(port, ref, plan):
+    x_dt, out_dt, xs = plan
+    x = make(np.random.default_rng(31), xs, x_dt)
+    assert_same_codes(port.global_average_pool(x, x_dt, out_dt), ref.global_average_pool(x, x_dt, out_dt), out_dt)
+
+
+@pytest.mark.parametrize("plan", [("float32", "float32", "float32", (3, 5, 6, 7)), ("float16", "float32", "float16", (2, 4, 5, 5)),
+                                  ("bfloat16", "bfloat16", "float32", (1, 3, 8, 2)), ("float64", "float64", "float64", (2, 2, 3, 3)),
+                                  ("float32", "float32", "float32", (4, 6)), ("int8", "float32", "float32", (2, 3, 4, 4))],
+                         ids=lambda p: f"{p[0]}-{p[1]}-{p[2]}-{len(p[3])}d")
+def test_batch_norm(port, ref, plan):
+    x_dt, p_dt, out_dt, xs = plan
+    rng = np.random.default_rng(37)
+    x = make(rng, xs, x_dt)
+    c = xs[1]
+    scale, bias, mean = (from_f64(rng.normal(0, 1, c), p_dt) for _ in range(3))
+    var = from_f64(rng.uniform(0.1, 2.0, c), p_dt)
+    for eps in (1e-5, 1e-3):
+        args = (x, x_dt, scale, bias, mean, var, p_dt, out_dt, eps)
+        assert_same_codes(port.batch_norm(*args), ref.batch_norm(*args), out_dt)
