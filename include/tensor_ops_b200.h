@@ -159,6 +159,45 @@ void global_average_pool_forward(const Tensor* input, Tensor* output);
 void batch_norm_forward(const Tensor* input, const Tensor* scale, const Tensor* B, const Tensor* mean,
                         const Tensor* var, Tensor* output, float epsilon);
 
+/* tensor_ops/tensor_ops.h:230-240 (tensor_ops.c:1351-1403).  Element-wise maximum, minimum and power
+   with the dtype dispatch and broadcasting of add_forward; pow_forward has no integer branch (pow() in
+   double, then the store of the output type).  A NaN on either side of max / min yields B's element. */
+void max_forward(const Tensor* A, const Tensor* B, Tensor* O);
+void min_forward(const Tensor* A, const Tensor* B, Tensor* O);
+void pow_forward(const Tensor* A, const Tensor* B, Tensor* O);
+
+/* tensor_ops/tensor_ops.h:184-204, 265-298, 345-349, 441-452, 488-489, 507 (tensor_ops.c:595-604 and the
+   one-line definitions at :1273-1286, :1484-1493, :1758-1760, :2622-2665, :3032-3035, :3340).  Element-wise
+   functions: the element is read as a double, the expression is evaluated in double, the result is stored
+   like any operator result.  neg, reciprocal, ceil, floor, sqrt, round, softsign and hard_swish are
+   bit-identical to the reference; the transcendental ones agree to within one unit in the last place of a
+   double before that store. */
+void exp_forward(const Tensor* input, Tensor* output);
+void log_forward(const Tensor* input, Tensor* output);
+void sqrt_forward(const Tensor* input, Tensor* output);
+void sigmoid_forward(const Tensor* input, Tensor* output);
+void tanh_forward(const Tensor* input, Tensor* output);
+void neg_forward(const Tensor* input, Tensor* output);
+void reciprocal_forward(const Tensor* input, Tensor* output);
+void ceil_forward(const Tensor* input, Tensor* output);
+void floor_forward(const Tensor* input, Tensor* output);
+void sin_forward(const Tensor* input, Tensor* output);
+void tan_forward(const Tensor* input, Tensor* output);
+void atan_forward(const Tensor* input, Tensor* output);
+void softplus_forward(const Tensor* input, Tensor* output);
+void softsign_forward(const Tensor* input, Tensor* output);
+void hard_swish_forward(const Tensor* input, Tensor* output);
+void acos_forward(const Tensor* input, Tensor* output);
+void asin_forward(const Tensor* input, Tensor* output);
+void cosh_forward(const Tensor* input, Tensor* output);
+void sinh_forward(const Tensor* input, Tensor* output);
+void asinh_forward(const Tensor* input, Tensor* output);
+void acosh_forward(const Tensor* input, Tensor* output);
+void atanh_forward(const Tensor* input, Tensor* output);
+void round_forward(const Tensor* input, Tensor* output);
+void erf_forward(const Tensor* input, Tensor* output);
+void gelu_forward(const Tensor* input, Tensor* output);
+
 /* ---- additive interface (no counterpart in the reference) -------------------------------------- */
 
 /* Error codes kept by the library (sticky until cleared; the first error wins). */

@@ -124,6 +124,12 @@ SIGNATURES = {
     "tops_host_free": (None, [_V]),
     "tops_dtype_size": (_SZ, [_I]),
     "cast_forward": (None, [_P, _P]),
+    "max_forward": (None, [_P, _P, _P]),
+    "min_forward": (None, [_P, _P, _P]),
+    "pow_forward": (None, [_P, _P, _P]),
+    **{name + "_forward": (None, [_P, _P]) for name in (
+        "exp", "log", "sqrt", "sigmoid", "tanh", "neg", "reciprocal", "ceil", "floor", "sin", "tan", "atan", "softplus", "softsign",
+        "hard_swish", "acos", "asin", "cosh", "sinh", "asinh", "acosh", "atanh", "round", "erf", "gelu")},
     "clip_forward": (None, [_P, _P, _P, _P]),
     "average_pool_forward": (None, [_P, _P, ctypes.POINTER(CPoolParams), _I]),
     "global_average_pool_forward": (None, [_P, _P]),

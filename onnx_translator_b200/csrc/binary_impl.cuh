@@ -15,12 +15,14 @@
 
 namespace tops {
 
-enum BinaryOp { kAdd = 0, kSub = 1, kMul = 2, kDiv = 3 };
+enum BinaryOp { kAdd = 0, kSub = 1, kMul = 2, kDiv = 3, kMax = 4, kMin = 5, kPow = 6 };   // Max / Min / Pow: tensor_ops.c:1351-1403
 
 template <int OP> __device__ __forceinline__ long long int_op64(long long a, long long b) {
     if constexpr (OP == kAdd) return (long long)((unsigned long long)a + (unsigned long long)b);
     else if constexpr (OP == kSub) return (long long)((unsigned long long)a - (unsigned long long)b);
     else if constexpr (OP == kMul) return (long long)((unsigned long long)a * (unsigned long long)b);
+    else if constexpr (OP == kMax) return a > b ? a : b;
+    else if constexpr (OP == kMin) return a < b ? a : b;
     else {
         if (b == 0) return a >= 0 ? 0x7FFFFFFFFFFFFFFFll : (long long)0x8000000000000000ull;
         if (b == -1) return (long long)(0ull - (unsigned long long)a);          // avoids INT64_MIN / -1
@@ -44,25 +46,34 @@ template <int OP> __device__ __forceinline__ int int_op32(int a, int b) {      /
     if constexpr (OP == kAdd) return a + b;
     else if constexpr (OP == kSub) return a - b;
     else if constexpr (OP == kMul) return a * b;
+    else if constexpr (OP == kMax) return a > b ? a : b;
+    else if constexpr (OP == kMin) return a < b ? a : b;
     else return narrow_int_quotient((float)a, (float)b);
 }
 template <int OP> __device__ __forceinline__ float float_op32(float a, float b) {
     if constexpr (OP == kAdd) return __fadd_rn(a, b);
     else if constexpr (OP == kSub) return __fsub_rn(a, b);
     else if constexpr (OP == kMul) return __fmul_rn(a, b);
+    else if constexpr (OP == kMax) return a > b ? a : b;       // a NaN on either side yields b, as the reference's ternary
+    else if constexpr (OP == kMin) return a < b ? a : b;
     else return __fdiv_rn(a, b);
 }
 template <int OP> __device__ __forceinline__ double float_op64(double a, double b) {
     if constexpr (OP == kAdd) return __dadd_rn(a, b);
     else if constexpr (OP == kSub) return __dsub_rn(a, b);
     else if constexpr (OP == kMul) return __dmul_rn(a, b);
+    else if constexpr (OP == kMax) return a > b ? a : b;
+    else if constexpr (OP == kMin) return a < b ? a : b;
+    else if constexpr (OP == kPow) return pow(a, b);
     else return __ddiv_rn(a, b);
 }
 
 template <int DA, int DB, int DO, int OP>
 __device__ __forceinline__ typename Storage<DO>::type
 binary_elem(typename Storage<DA>::type sa, typename Storage<DB>::type sb) {
-    if constexpr (dtype_is_int(DO)) {
+    if constexpr (OP == kPow) {                                  // always double, then the generic store
+        return from_f64<DO>(pow(to_f64<DA>(sa), to_f64<DB>(sb)));
+    } else if constexpr (dtype_is_int(DO)) {
         if constexpr (dtype_is_narrow_int(DA) && dtype_is_narrow_int(DB) && DO != DTYPE_INT64) {
             return from_i32<DO>(int_op32<OP>(to_i32_narrow<DA>(sa), to_i32_narrow<DB>(sb)));
         } else {
@@ -102,9 +113,9 @@ struct BinaryBody {
         const Run<typename Storage<DA>::type, kV>& ra = r.ra;
         const Run<typename Storage<DB>::type, kV>& rb = r.rb;
         Run<typename Storage<DO>::type, kV> ro;
-        constexpr bool int_lane = dtype_is_int(DO) && DO != DTYPE_INT64 && dtype_is_narrow_int(DA) && dtype_is_narrow_int(DB) &&
+        constexpr bool int_lane = OP != kPow && dtype_is_int(DO) && DO != DTYPE_INT64 && dtype_is_narrow_int(DA) && dtype_is_narrow_int(DB) &&
                                   dtype_is_narrow_int(DO);
-        constexpr bool float_lane = !dtype_is_int(DO) && DO != DTYPE_FLOAT64 && dtype_exact_in_f32(DA) && dtype_exact_in_f32(DB);
+        constexpr bool float_lane = OP != kPow && !dtype_is_int(DO) && DO != DTYPE_FLOAT64 && dtype_exact_in_f32(DA) && dtype_exact_in_f32(DB);
         if constexpr (int_lane) {
             int v[kV];
             if constexpr (OP == kDiv && kV % 4 == 0 && (DA == DTYPE_INT8 || DA == DTYPE_UINT8) && (DB == DTYPE_INT8 || DB == DTYPE_UINT8)) {
@@ -146,7 +157,7 @@ struct BinaryGenericBody {
         uint32_t p;
         const uint32_t ia = a.flat ? i : operand_offset(g, a, i, p);
         const uint32_t ib = b.flat ? i : operand_offset(g, b, i, p);
-        if (dtype_is_int(dout)) {
+        if (OP != kPow && dtype_is_int(dout)) {
             store_i64_rt(out, dout, i, int_op64<OP>(load_i64_rt(a.ptr, da, ia), load_i64_rt(b.ptr, db, ib)));
         } else {
             store_f64_rt(out, dout, i, float_op64<OP>(load_f64_rt(a.ptr, da, ia), load_f64_rt(b.ptr, db, ib)));

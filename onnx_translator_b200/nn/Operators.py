@@ -401,3 +401,50 @@ class BatchNormalization(Ops):
 
     def forward_(self, x: Tensor_, *_) -> dict:
         return self._publish(Tensor_(*x.size, dtype=self.dtype))
+
+
+# ---- element-wise families beyond the hot path (same templates, more expressions) -------------------------------------
+class Max(_Binary):
+    """Element-wise maximum with broadcasting (nn/Operators.py:933-949)."""
+    _c_name = "max_forward"
+
+
+class Min(_Binary):
+    """Element-wise minimum with broadcasting (nn/Operators.py:951-967)."""
+    _c_name = "min_forward"
+
+
+class Pow(_Binary):
+    """a ** b in double with broadcasting (nn/Operators.py:914-931)."""
+    _c_name = "pow_forward"
+
+
+def _unary_class(name, c_name, where):
+    return type(name, (_Unary,), {"_c_name": c_name, "__doc__": f"Element-wise {c_name[:-8]} ({where})."})
+
+
+EXP = _unary_class("EXP", "exp_forward", "nn/Operators.py:706-718")
+LOG = _unary_class("LOG", "log_forward", "nn/Operators.py:720-732")
+SQRT = _unary_class("SQRT", "sqrt_forward", "nn/Operators.py:734-746")
+SIGMOID = _unary_class("SIGMOID", "sigmoid_forward", "nn/Operators.py:748-760")
+TANH = _unary_class("TANH", "tanh_forward", "nn/Operators.py:762-774")
+Neg = _unary_class("Neg", "neg_forward", "nn/Operators.py:1222-1232")
+Reciprocal = _unary_class("Reciprocal", "reciprocal_forward", "nn/Operators.py:1234-1244")
+Ceil = _unary_class("Ceil", "ceil_forward", "nn/Operators.py:1246-1256")
+Floor = _unary_class("Floor", "floor_forward", "nn/Operators.py:1258-1268")
+Sin = _unary_class("Sin", "sin_forward", "nn/Operators.py:1733-1741")
+Tan = _unary_class("Tan", "tan_forward", "nn/Operators.py:1743-1751")
+Atan = _unary_class("Atan", "atan_forward", "nn/Operators.py:1753-1761")
+Softplus = _unary_class("Softplus", "softplus_forward", "nn/Operators.py:2709-2715")
+Softsign = _unary_class("Softsign", "softsign_forward", "nn/Operators.py:2717-2723")
+HardSwish = _unary_class("HardSwish", "hard_swish_forward", "nn/Operators.py:2725-2731")
+Acos = _unary_class("Acos", "acos_forward", "nn/Operators.py:2733-2739")
+Asin = _unary_class("Asin", "asin_forward", "nn/Operators.py:2741-2747")
+Cosh = _unary_class("Cosh", "cosh_forward", "nn/Operators.py:2749-2755")
+Sinh = _unary_class("Sinh", "sinh_forward", "nn/Operators.py:2757-2763")
+Asinh = _unary_class("Asinh", "asinh_forward", "nn/Operators.py:2765-2771")
+Acosh = _unary_class("Acosh", "acosh_forward", "nn/Operators.py:2773-2779")
+Atanh = _unary_class("Atanh", "atanh_forward", "nn/Operators.py:2781-2787")
+Round = _unary_class("Round", "round_forward", "nn/Operators.py:3265-3271")
+Erf = _unary_class("Erf", "erf_forward", "nn/Operators.py:3273-3279")
+Gelu = _unary_class("Gelu", "gelu_forward", "nn/Operators.py:3582-3596")

@@ -106,14 +106,15 @@ class HostOracle:
                      gemm="orc_gemm", softmax="orc_softmax", flatten="orc_flatten",
                      cast="orc_cast", clip="orc_clip", average_pool="orc_average_pool",
                      global_average_pool="orc_global_average_pool", batch_norm="orc_batch_norm",
-                     init="orc_init_cos_lut"),
+                     max="orc_max", min="orc_min", pow="orc_pow", init="orc_init_cos_lut"),
         "ref": dict(relu="relu_forward", abs="abs_forward", cos="cos_forward", add="add_forward",
                     sub="sub_forward", mul="mul_forward", div="div_forward",
                     quantize="quantize_linear_forward", dequantize="dequantize_linear_forward",
                     conv="conv2d_forward", pool="max_pool_forward", gemm="gemm_forward",
                     softmax="softmax_forward", flatten="flatten_forward", cast="cast_forward", clip="clip_forward",
                     average_pool="average_pool_forward", global_average_pool="global_average_pool_forward",
-                    batch_norm="batch_norm_forward", init="init_cos_lut"),
+                    batch_norm="batch_norm_forward", max="max_forward", min="min_forward", pow="pow_forward",
+                    init="init_cos_lut"),
     }
 
     def __init__(self, kind: str = "port"):
@@ -207,6 +208,25 @@ class HostOracle:
         keep = (_ints(pads), _ints(strides), _ints(dilations), _ints(kernel))
         prm = _CPoolParams(*[ctypes.cast(k, ctypes.POINTER(ctypes.c_int)) for k in keep])
         self._fn["pool"](xi.ref, yo.ref, ctypes.byref(prm))
+        return yo.arr
+
+    # The one-line unary operators: the port has one entry point with a selector, the reference one
+    # function per operator.
+    UNARY_MATH = ("exp", "log", "sqrt", "sigmoid", "tanh", "neg", "reciprocal", "ceil", "floor", "sin", "tan", "atan",
+                  "softplus", "softsign", "hard_swish", "acos", "asin", "cosh", "sinh", "asinh", "acosh", "atanh", "round",
+                  "erf", "gelu")
+
+    def unary_math(self, op: str, x, x_dt: str, out_dt: str) -> np.ndarray:
+        xi = _Wrapped(x, x_dt)
+        yo = _out(xi.arr.shape, out_dt)
+        if self.kind == "port":
+            fn = self.lib.orc_unary_math
+            fn.restype = None
+            fn(ctypes.c_int(self.UNARY_MATH.index(op)), xi.ref, yo.ref)
+        else:
+            fn = getattr(self.lib, op + "_forward")
+            fn.restype = None
+            fn(xi.ref, yo.ref)
         return yo.arr
 
     # -- operators around the hot path ----------------------------------------------------------

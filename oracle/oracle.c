@@ -351,7 +351,7 @@ ORC_API void orc_cos(const OrcTensor* x, OrcTensor* y) {
  * Operands must already have the output's size; broadcasting is the caller's job
  * (nn/__init__.py:210-248).
  * ---------------------------------------------------------------------------------------- */
-enum { OP_ADD = 0, OP_SUB = 1, OP_MUL = 2, OP_DIV = 3 };
+enum { OP_ADD = 0, OP_SUB = 1, OP_MUL = 2, OP_DIV = 3, OP_MAX = 4, OP_MIN = 5 };
 
 /* int64 arithmetic wraps (the reference relies on two's-complement behaviour at -O3). */
 static int64_t int_binary(int op, int64_t a, int64_t b) {
@@ -359,6 +359,8 @@ static int64_t int_binary(int op, int64_t a, int64_t b) {
         case OP_ADD: return (int64_t)((uint64_t)a + (uint64_t)b);
         case OP_SUB: return (int64_t)((uint64_t)a - (uint64_t)b);
         case OP_MUL: return (int64_t)((uint64_t)a * (uint64_t)b);
+        case OP_MAX: return a > b ? a : b;                      /* tensor_ops.c:1351-1352 */
+        case OP_MIN: return a < b ? a : b;
         default:
             if (b == 0) return a >= 0 ? INT64_MAX : INT64_MIN;   /* tensor_ops.c:684 */
             if (a == INT64_MIN && b == -1) return INT64_MIN;     /* idiv would trap; keep wrap */
@@ -371,6 +373,8 @@ static double float_binary(int op, double a, double b) {
         case OP_ADD: return a + b;
         case OP_SUB: return a - b;
         case OP_MUL: return a * b;
+        case OP_MAX: return a > b ? a : b;                      /* a NaN on either side yields b */
+        case OP_MIN: return a < b ? a : b;
         default:     return a / b;
     }
 }
@@ -394,6 +398,61 @@ ORC_API void orc_add(const OrcTensor* a, const OrcTensor* b, OrcTensor* o) { bin
 ORC_API void orc_sub(const OrcTensor* a, const OrcTensor* b, OrcTensor* o) { binary_forward(OP_SUB, a, b, o); }
 ORC_API void orc_mul(const OrcTensor* a, const OrcTensor* b, OrcTensor* o) { binary_forward(OP_MUL, a, b, o); }
 ORC_API void orc_div(const OrcTensor* a, const OrcTensor* b, OrcTensor* o) { binary_forward(OP_DIV, a, b, o); }
+/* Max / Min follow the same output-dtype dispatch (tensor_ops.c:1367-1403). */
+ORC_API void orc_max(const OrcTensor* a, const OrcTensor* b, OrcTensor* o) { binary_forward(OP_MAX, a, b, o); }
+ORC_API void orc_min(const OrcTensor* a, const OrcTensor* b, OrcTensor* o) { binary_forward(OP_MIN, a, b, o); }
+/* Pow has no integer branch: always pow() in double and the generic store (tensor_ops.c:1355-1364). */
+ORC_API void orc_pow(const OrcTensor* a, const OrcTensor* b, OrcTensor* o) {
+    if (!a || !b || !o) return;
+    #pragma omp parallel for
+    for (size_t i = 0; i < o->size; i++) store_f64(o, i, pow(load_f64(a, i), load_f64(b, i)));
+}
+
+/* ------------------------------------------------------------------------------------------
+ * The one-line unary operators (tensor_ops.c:595-604 is the shared shape: read as double, one
+ * libm expression, generic store).  `which` selects the expression; the comments give the lines
+ * of the reference's definitions.
+ * ---------------------------------------------------------------------------------------- */
+enum { UM_EXP, UM_LOG, UM_SQRT, UM_SIGMOID, UM_TANH, UM_NEG, UM_RECIPROCAL, UM_CEIL, UM_FLOOR, UM_SIN, UM_TAN, UM_ATAN,
+       UM_SOFTPLUS, UM_SOFTSIGN, UM_HARD_SWISH, UM_ACOS, UM_ASIN, UM_COSH, UM_SINH, UM_ASINH, UM_ACOSH, UM_ATANH, UM_ROUND,
+       UM_ERF, UM_GELU, UM_COUNT };
+
+static double unary_math_value(int which, double v) {
+    switch (which) {
+        case UM_EXP:        return exp(v);                                   /* :1273 */
+        case UM_LOG:        return log(v);                                   /* :1277 */
+        case UM_SQRT:       return sqrt(v);                                  /* :1280 */
+        case UM_SIGMOID:    return 1.0 / (1.0 + exp(-v));                    /* :1283 */
+        case UM_TANH:       return tanh(v);                                  /* :1286 */
+        case UM_NEG:        return -v;                                       /* :1484 */
+        case UM_RECIPROCAL: return 1.0 / v;                                  /* :1487 */
+        case UM_CEIL:       return ceil(v);                                  /* :1490 */
+        case UM_FLOOR:      return floor(v);                                 /* :1493 */
+        case UM_SIN:        return sin(v);                                   /* :1758 */
+        case UM_TAN:        return tan(v);                                   /* :1759 */
+        case UM_ATAN:       return atan(v);                                  /* :1760 */
+        case UM_SOFTPLUS:   return log(1.0 + exp(v));                        /* :2622 */
+        case UM_SOFTSIGN:   return v / (1.0 + fabs(v));                      /* :2625 */
+        case UM_HARD_SWISH: return v * fmax(0.0, fmin(1.0, v / 6.0 + 0.5));  /* :2629 */
+        case UM_ACOS:       return acos(v);                                  /* :2647 */
+        case UM_ASIN:       return asin(v);                                  /* :2650 */
+        case UM_COSH:       return cosh(v);                                  /* :2653 */
+        case UM_SINH:       return sinh(v);                                  /* :2656 */
+        case UM_ASINH:      return asinh(v);                                 /* :2659 */
+        case UM_ACOSH:      return acosh(v);                                 /* :2662 */
+        case UM_ATANH:      return atanh(v);                                 /* :2665 */
+        case UM_ROUND:      return rint(v);                                  /* :3032 */
+        case UM_ERF:        return erf(v);                                   /* :3035 */
+        case UM_GELU:       return 0.5 * v * (1.0 + erf(v * 0.70710678118654752440));   /* :3340 */
+        default:            return v;
+    }
+}
+
+ORC_API void orc_unary_math(int which, const OrcTensor* x, OrcTensor* y) {
+    if (!unary_args_ok(x, y) || which < 0 || which >= UM_COUNT) return;
+    #pragma omp parallel for
+    for (size_t i = 0; i < x->size; i++) store_f64(y, i, unary_math_value(which, load_f64(x, i)));
+}
 
 /* ------------------------------------------------------------------------------------------
  * QuantizeLinear / DequantizeLinear.  tensor_ops.c:999-1034.  X, scale and zero point are all

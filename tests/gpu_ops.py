@@ -86,3 +86,15 @@ def global_average_pool(x, x_dt, out_dt):
 def batch_norm(x, x_dt, scale, bias, mean, var, p_dt, out_dt, epsilon=1e-5):
     node = ops.BatchNormalization([], [], epsilon=epsilon, dtype=out_dt)
     return node.forward(_t(x, x_dt), _t(scale, p_dt), _t(bias, p_dt), _t(mean, p_dt), _t(var, p_dt))["tensor"].numpy()
+
+
+_BINARY.update({"max": ops.Max, "min": ops.Min, "pow": ops.Pow})
+_MATH = {"exp": ops.EXP, "log": ops.LOG, "sqrt": ops.SQRT, "sigmoid": ops.SIGMOID, "tanh": ops.TANH, "neg": ops.Neg,
+         "reciprocal": ops.Reciprocal, "ceil": ops.Ceil, "floor": ops.Floor, "sin": ops.Sin, "tan": ops.Tan, "atan": ops.Atan,
+         "softplus": ops.Softplus, "softsign": ops.Softsign, "hard_swish": ops.HardSwish, "acos": ops.Acos, "asin": ops.Asin,
+         "cosh": ops.Cosh, "sinh": ops.Sinh, "asinh": ops.Asinh, "acosh": ops.Acosh, "atanh": ops.Atanh, "round": ops.Round,
+         "erf": ops.Erf, "gelu": ops.Gelu}
+
+
+def unary_math(op, x, x_dt, out_dt):
+    return _MATH[op]([], [], dtype=out_dt).forward(_t(x, x_dt))["tensor"].numpy()

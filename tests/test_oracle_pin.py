@@ -337,3 +337,33 @@ def test_batch_norm(port, ref, plan):
     for eps in (1e-5, 1e-3):
         args = (x, x_dt, scale, bias, mean, var, p_dt, out_dt, eps)
         assert_same_codes(port.batch_norm(*args), ref.batch_norm(*args), out_dt)
+
+
+# ---- Max / Min / Pow and the one-line unary operators ----------------------------------------------------------------
+@pytest.mark.parametrize("plan", [("float32", "float32", "float32"), ("float16", "float16", "float16"), ("bfloat16", "float32", "float32"),
+                                  ("int8", "int8", "int8"), ("int32", "int32", "int32"), ("int32", "float16", "float64"), ("uint8", "int8", "int16"),
+                                  ("int64", "int64", "int64"), ("float32", "float32", "int8"), ("float8_e4m3", "float8_e4m3", "float8_e4m3")], ids="-".join)
+@pytest.mark.parametrize("op", ["max", "min", "pow"])
+def test_max_min_pow(port, ref, op, plan):
+    a_dt, b_dt, out_dt = plan
+    rng = np.random.default_rng(zlib.crc32((op + "-".join(plan)).encode()))
+    a, b = make(rng, (9, 31), a_dt), make(rng, (9, 31), b_dt)
+    if a_dt == "float32":
+        a.reshape(-1)[:6] = [np.nan, 1.0, np.inf, -np.inf, 0.0, -0.0]
+        b.reshape(-1)[:6] = [1.0, np.nan, 1.0, 2.0, -0.0, 0.0]
+    if op == "pow" and b_dt in ("float32", "float16", "bfloat16"):
+        b = from_f64(np.clip(np.asarray(rng.normal(0, 1.5, b.shape)), -4, 4), b_dt)
+    assert_same_codes(port.binary(op, a, a_dt, b, b_dt, out_dt), ref.binary(op, a, a_dt, b, b_dt, out_dt), out_dt, f"{op} {plan}")
+
+
+@pytest.mark.parametrize("op", ["exp", "log", "sqrt", "sigmoid", "tanh", "neg", "reciprocal", "ceil", "floor", "sin", "tan", "atan", "softplus",
+                                "softsign", "hard_swish", "acos", "asin", "cosh", "sinh", "asinh", "acosh", "atanh", "round", "erf", "gelu"])
+def test_unary_math_family(port, ref, op):
+    """Same libm on both sides: the restatement and the reference agree bit for bit."""
+    rng = np.random.default_rng(zlib.crc32(op.encode()))
+    for x_dt, out_dt in (("float32", "float32"), ("float16", "float16"), ("bfloat16", "float32"), ("float64", "float64"), ("int8", "float32"),
+                         ("float32", "int32"), ("float8_e4m3", "float16")):
+        x = make(rng, (7, 53), x_dt, -3, 3) if x_dt in FLOAT_DTYPES else make(rng, (7, 53), x_dt)
+        if x_dt == "float32":
+            x.reshape(-1)[:8] = [0.0, -0.0, 1.0, -1.0, 0.5, np.inf, -np.inf, np.nan]
+        assert_same_codes(port.unary_math(op, x, x_dt, out_dt), ref.unary_math(op, x, x_dt, out_dt), out_dt, f"{op} {x_dt}->{out_dt}")
