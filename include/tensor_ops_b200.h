@@ -198,6 +198,18 @@ void round_forward(const Tensor* input, Tensor* output);
 void erf_forward(const Tensor* input, Tensor* output);
 void gelu_forward(const Tensor* input, Tensor* output);
 
+/* tensor_ops/tensor_ops.h:298 (tensor_ops.c:1546-1606).  Y[..., m, n] = sum over k of A[..., m, k] * B[..., k, n];
+   A, B and Y have rank >= 2 (the caller promotes 1-D operands), the leading dimensions broadcast numpy-style
+   with operands of lower rank aligned to the right.  The sum runs in double in increasing k; 16-bit and 8-bit
+   float operand pairs (and large float32 problems) use the tensor cores exactly as in gemm_forward. */
+void matmul_forward(const Tensor* A, const Tensor* B, Tensor* Y);
+
+/* tensor_ops/tensor_ops.h:547 (tensor_ops.c:3760-3809).  scale = (max(x, 0) - min(x, 0)) / 255 (1 if 0),
+   zero point = round(-min / scale) clamped to 0..255, y = clamp(rint(x / scale) + zero point, 0, 255).
+   y is uint8 in the reference's caller; any dtype is stored through the ordinary conversion.  y_scale and y_zp
+   hold one element each. */
+void dynamic_quantize_linear_forward(const Tensor* x, Tensor* y, Tensor* y_scale, Tensor* y_zp);
+
 /* ---- additive interface (no counterpart in the reference) -------------------------------------- */
 
 /* Error codes kept by the library (sticky until cleared; the first error wins). */

@@ -134,6 +134,8 @@ SIGNATURES = {
     "average_pool_forward": (None, [_P, _P, ctypes.POINTER(CPoolParams), _I]),
     "global_average_pool_forward": (None, [_P, _P]),
     "batch_norm_forward": (None, [_P, _P, _P, _P, _P, _P, ctypes.c_float]),
+    "matmul_forward": (None, [_P, _P, _P]),
+    "dynamic_quantize_linear_forward": (None, [_P, _P, _P, _P]),
     "tops_quantize_linear_axis_forward": (None, [_P, _P, _P, _P, _I]),
     "tops_dequantize_linear_axis_forward": (None, [_P, _P, _P, _P, _I]),
     "tops_conv2d_forward_noalloc": (None, [_P, _P, _P, _P, ctypes.POINTER(CConvParams)]),

@@ -16,7 +16,9 @@ constexpr int kPerThread = 4;  // 16 x 16 threads, 4 x 4 outputs each
 template <bool EXACT_PRODUCTS>
 __global__ void __launch_bounds__(256) gemm_exact_kernel(const void* __restrict__ A, const void* __restrict__ B,
                                                           void* __restrict__ Y, int da, int db, int dy,
-                                                          GemmShape g, BiasView bias, double alpha, double beta) {
+                                                          GemmShape g, BiasView bias, double alpha, double beta, BatchStrides batch) {
+    // blockIdx.z walks equally spaced problems (MatMul batches); a stride of 0 re-reads a broadcast operand
+    const size_t a_base = (size_t)blockIdx.z * batch.a, b_base = (size_t)blockIdx.z * batch.b, y_base = (size_t)blockIdx.z * batch.y;
     __shared__ double sa[kTileK][kTile + 1];
     __shared__ double sb[kTileK][kTile + 1];
     const int tx = threadIdx.x & 15, ty = threadIdx.x >> 4;
@@ -30,7 +32,7 @@ __global__ void __launch_bounds__(256) gemm_exact_kernel(const void* __restrict_
             if (g.transA) { mm = e % kTile; kk = e / kTile; } else { kk = e % kTileK; mm = e / kTileK; }
             const int m = m0 + mm, k = k0 + kk;
             double v = 0.0;
-            if (m < g.M && k < g.K) v = load_f64_rt(A, da, g.transA ? (size_t)k * g.lda + m : (size_t)m * g.lda + k);
+            if (m < g.M && k < g.K) v = load_f64_rt(A, da, a_base + (g.transA ? (size_t)k * g.lda + m : (size_t)m * g.lda + k));
             sa[kk][mm] = v;
         }
         for (int e = threadIdx.x; e < kTileK * kTile; e += 256) {
@@ -38,7 +40,7 @@ __global__ void __launch_bounds__(256) gemm_exact_kernel(const void* __restrict_
             if (g.transB) { kk = e % kTileK; nn = e / kTileK; } else { nn = e % kTile; kk = e / kTile; }
             const int n = n0 + nn, k = k0 + kk;
             double v = 0.0;
-            if (n < g.N && k < g.K) v = load_f64_rt(B, db, g.transB ? (size_t)n * g.ldb + k : (size_t)k * g.ldb + n);
+            if (n < g.N && k < g.K) v = load_f64_rt(B, db, b_base + (g.transB ? (size_t)n * g.ldb + k : (size_t)k * g.ldb + n));
             sb[kk][nn] = v;
         }
         __syncthreads();
@@ -71,7 +73,7 @@ __global__ void __launch_bounds__(256) gemm_exact_kernel(const void* __restrict_
                 const double cv = ci >= 0 ? load_f64_rt(bias.ptr, bias.dtype, (size_t)ci) : 0.0;
                 r = __dadd_rn(r, __dmul_rn(beta, cv));
             }
-            store_f64_rt(Y, dy, (size_t)m * g.N + n, r);
+            store_f64_rt(Y, dy, y_base + (size_t)m * g.N + n, r);
         }
 }
 
@@ -101,15 +103,22 @@ BiasView make_bias_view(const Tensor* C, int M, int N) {
 }
 
 bool gemm_exact(const Tensor* A, const Tensor* B, Tensor* Y, const GemmShape& g, const BiasView& bias,
-                float alpha, float beta) {
+                float alpha, float beta, int batches, BatchStrides batch) {
     DeviceState* st = acquire_device();
     if (!st) return false;
-    dim3 grid((g.N + kTile - 1) / kTile, (g.M + kTile - 1) / kTile);
     const bool exact = dtype_exact_in_f32((int)A->dtype) && dtype_exact_in_f32((int)B->dtype);
-    if (exact) gemm_exact_kernel<true><<<grid, 256, 0, current_stream()>>>(A->data, B->data, Y->data, (int)A->dtype, (int)B->dtype,
-                                                                           (int)Y->dtype, g, bias, (double)alpha, (double)beta);
-    else gemm_exact_kernel<false><<<grid, 256, 0, current_stream()>>>(A->data, B->data, Y->data, (int)A->dtype, (int)B->dtype,
-                                                                      (int)Y->dtype, g, bias, (double)alpha, (double)beta);
+    const size_t ea = (size_t)dtype_bytes((int)A->dtype), eb = (size_t)dtype_bytes((int)B->dtype), ey = (size_t)dtype_bytes((int)Y->dtype);
+    for (int first = 0; first < batches; first += 65535) {         // grid.z limit
+        const int nb = batches - first < 65535 ? batches - first : 65535;
+        dim3 grid((g.N + kTile - 1) / kTile, (g.M + kTile - 1) / kTile, nb);
+        const void* a = (const char*)A->data + (size_t)first * batch.a * ea;
+        const void* b = (const char*)B->data + (size_t)first * batch.b * eb;
+        void* y = (char*)Y->data + (size_t)first * batch.y * ey;
+        if (exact) gemm_exact_kernel<true><<<grid, 256, 0, current_stream()>>>(a, b, y, (int)A->dtype, (int)B->dtype, (int)Y->dtype, g, bias,
+                                                                               (double)alpha, (double)beta, batch);
+        else gemm_exact_kernel<false><<<grid, 256, 0, current_stream()>>>(a, b, y, (int)A->dtype, (int)B->dtype, (int)Y->dtype, g, bias,
+                                                                          (double)alpha, (double)beta, batch);
+    }
     return TOPS_CHECK_LAUNCH("gemm_forward");
 }
 

@@ -61,9 +61,12 @@ struct LevelsOut {
 
 BiasView make_bias_view(const Tensor* C, int M, int N);
 
-// Exact double-accumulating path (any dtypes).
+// Element distances between consecutive problems of a batched launch (0: the operand is shared).
+struct BatchStrides { size_t a = 0, b = 0, y = 0; };
+
+// Exact double-accumulating path (any dtypes); `batches` equally spaced problems of one shape.
 bool gemm_exact(const Tensor* A, const Tensor* B, Tensor* Y, const GemmShape& g, const BiasView& bias,
-                float alpha, float beta);
+                float alpha, float beta, int batches = 1, BatchStrides batch = BatchStrides());
 
 // Tensor-core path.  Returns false when the case is outside what it covers (caller falls back
 // to the exact kernel, which is still a GPU kernel of this library).

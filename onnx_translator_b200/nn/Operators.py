@@ -448,3 +448,70 @@ Atanh = _unary_class("Atanh", "atanh_forward", "nn/Operators.py:2781-2787")
 Round = _unary_class("Round", "round_forward", "nn/Operators.py:3265-3271")
 Erf = _unary_class("Erf", "erf_forward", "nn/Operators.py:3273-3279")
 Gelu = _unary_class("Gelu", "gelu_forward", "nn/Operators.py:3582-3596")
+
+
+# ---- MatMul and DynamicQuantizeLinear ----------------------------------------------------------------------------------
+def _matmul_shapes(shape_a, shape_b):
+    """(library shapes of A and B, library output shape, final shape) with numpy's rules for 1-D operands
+    (nn/Operators.py:1367-1425)."""
+    a_1d, b_1d = len(shape_a) == 1, len(shape_b) == 1
+    sa = [1] + list(shape_a) if a_1d else list(shape_a)
+    sb = list(shape_b) + [1] if b_1d else list(shape_b)
+    if sa[-1] != sb[-2]:
+        raise ValueError(f"MatMul shape mismatch: {sa[-1]} != {sb[-2]} (Original shapes: A={tuple(shape_a)}, B={tuple(shape_b)})")
+    try:
+        batch = np.broadcast_shapes(tuple(sa[:-2]), tuple(sb[:-2]))
+    except ValueError:
+        raise ValueError(f"MatMul batch broadcast failed: {sa[:-2]} vs {sb[:-2]}")
+    out = list(batch) + [sa[-2], sb[-1]]
+    final = list(out)
+    if b_1d:
+        final.pop(-1)
+    if a_1d:
+        final.pop(-1 if b_1d else -2)
+    return tuple(sa), tuple(sb), tuple(out), tuple(final)
+
+
+class MatMul(Ops):
+    """numpy-style matrix product: 1-D operands are promoted, leading dimensions broadcast (nn/Operators.py:1361-1432)."""
+
+    def __init__(self, inputs, outputs, dtype, version="17"):
+        super().__init__(inputs, outputs)
+        self.dtype, self.version = dtype, version
+
+    def forward(self, input_a: Tensor, input_b: Tensor) -> dict:
+        sa, sb, out_shape, final = _matmul_shapes(self._shape_of(input_a), self._shape_of(input_b))
+        data_a = input_a.data if tuple(input_a.data.shape) == sa else input_a.data.reshape(*sa)
+        data_b = input_b.data if tuple(input_b.data.shape) == sb else input_b.data.reshape(*sb)
+        handles = [self._numpy_to_ctensor(data_a, input_a.dtype), self._numpy_to_ctensor(data_b, input_b.dtype)]
+        y = self._new_output(out_shape, self.dtype)
+        self.lib.matmul_forward(handles[0], handles[1], y)
+        result = self._finish(handles, y, out_shape, self.dtype)
+        if final != out_shape:
+            result = Tensor(*final, dtype=self.dtype, data=result.data.reshape(*final))
+        return self._publish(result)
+
+    def forward_(self, input_a: Tensor_, input_b: Tensor_) -> dict:
+        return self._publish(Tensor_(*_matmul_shapes(tuple(input_a.size), tuple(input_b.size))[3], dtype=self.dtype))
+
+
+class DynamicQuantizeLinear(Ops):
+    """uint8 codes with the scale and zero point taken from the tensor's own range (nn/Operators.py:3892-3925).
+    Returns [y, y_scale, y_zero_point]."""
+
+    def __init__(self, inputs, outputs, dtype="uint8", version="17"):
+        super().__init__(inputs, outputs)
+        self.dtype, self.version = "uint8", version
+
+    def forward(self, x: Tensor) -> dict:
+        shape = self._shape_of(x)
+        xh = self._numpy_to_ctensor(x.data, x.dtype)
+        outs = [self._new_output(shape, "uint8"), self._new_output((1,), "float32"), self._new_output((1,), "uint8")]
+        self.lib.dynamic_quantize_linear_forward(xh, outs[0], outs[1], outs[2])
+        y = self._finish([xh], outs[0], shape, "uint8")
+        scale = self._finish([], outs[1], (1,), "float32")
+        zero = self._finish([], outs[2], (1,), "uint8")
+        return self._publish([y, scale, zero])
+
+    def forward_(self, x: Tensor_) -> dict:
+        return self._publish([Tensor_(*x.size, dtype="uint8"), Tensor_(1, dtype="float32"), Tensor_(1, dtype="uint8")])

@@ -106,7 +106,8 @@ class HostOracle:
                      gemm="orc_gemm", softmax="orc_softmax", flatten="orc_flatten",
                      cast="orc_cast", clip="orc_clip", average_pool="orc_average_pool",
                      global_average_pool="orc_global_average_pool", batch_norm="orc_batch_norm",
-                     max="orc_max", min="orc_min", pow="orc_pow", init="orc_init_cos_lut"),
+                     max="orc_max", min="orc_min", pow="orc_pow", matmul="orc_matmul",
+                     dynamic_quantize="orc_dynamic_quantize_linear", init="orc_init_cos_lut"),
         "ref": dict(relu="relu_forward", abs="abs_forward", cos="cos_forward", add="add_forward",
                     sub="sub_forward", mul="mul_forward", div="div_forward",
                     quantize="quantize_linear_forward", dequantize="dequantize_linear_forward",
@@ -114,6 +115,7 @@ class HostOracle:
                     softmax="softmax_forward", flatten="flatten_forward", cast="cast_forward", clip="clip_forward",
                     average_pool="average_pool_forward", global_average_pool="global_average_pool_forward",
                     batch_norm="batch_norm_forward", max="max_forward", min="min_forward", pow="pow_forward",
+                    matmul="matmul_forward", dynamic_quantize="dynamic_quantize_linear_forward",
                     init="init_cos_lut"),
     }
 
@@ -285,6 +287,21 @@ class HostOracle:
                          ctypes.addressof(ci.c) if ci is not None else None,
                          ctypes.addressof(yo.c), float(alpha), float(beta), int(transA), int(transB))
         return yo.arr
+
+    def matmul(self, a, a_dt, b, b_dt, out_dt):
+        """Operands of rank >= 2 (the caller promotes 1-D operands, nn/Operators.py:1367-1377)."""
+        ai, bi = _Wrapped(a, a_dt), _Wrapped(b, b_dt)
+        batch = np.broadcast_shapes(ai.arr.shape[:-2], bi.arr.shape[:-2])
+        yo = _out(tuple(batch) + (ai.arr.shape[-2], bi.arr.shape[-1]), out_dt)
+        self._fn["matmul"](ai.ref, bi.ref, yo.ref)
+        return yo.arr
+
+    def dynamic_quantize_linear(self, x, x_dt, y_dt="uint8", scale_dt="float32", zp_dt="uint8"):
+        """Returns (codes, scale[1], zero point[1])."""
+        xi = _Wrapped(x, x_dt)
+        yo, so, zo = _out(xi.arr.shape, y_dt), _out((1,), scale_dt), _out((1,), zp_dt)
+        self._fn["dynamic_quantize"](xi.ref, yo.ref, so.ref, zo.ref)
+        return yo.arr, so.arr, zo.arr
 
     def softmax(self, x, x_dt, out_dt, axis=-1):
         xi = _Wrapped(x, x_dt)

@@ -721,6 +721,71 @@ ORC_API void orc_batch_norm(const OrcTensor* x, const OrcTensor* scale, const Or
     }
 }
 
+/* MatMul with numpy-style broadcasting of the leading (batch) dimensions.  tensor_ops.c:1546-1606: every output
+   element Y[..., m, n] is the double sum over k, in increasing k, of A[..., m, k] * B[..., k, n]; a batch
+   dimension of extent 1 in an operand is read at index 0, and an operand of lower rank is aligned to the right. */
+static size_t matmul_batch_offset(const OrcTensor* t, const int* y_coords, int y_ndim) {
+    const int lead = t->ndim - 2, shift = y_ndim - t->ndim;
+    size_t offset = 0;
+    for (int d = 0; d < lead; d++) {
+        const int c = t->shape[d] == 1 ? 0 : y_coords[d + shift];
+        offset = offset * (size_t)t->shape[d] + (size_t)c;
+    }
+    return offset * (size_t)t->shape[t->ndim - 2] * (size_t)t->shape[t->ndim - 1];
+}
+
+ORC_API void orc_matmul(const OrcTensor* a, const OrcTensor* b, OrcTensor* y) {
+    if (!a || !b || !y || y->ndim < 2 || y->ndim > 16 || a->ndim < 2 || b->ndim < 2) return;
+    const int M = a->shape[a->ndim - 2], K = a->shape[a->ndim - 1], N = b->shape[b->ndim - 1];
+    const size_t per_batch = (size_t)M * (size_t)N;
+    const size_t batches = per_batch ? y->size / per_batch : 0;
+    #pragma omp parallel for
+    for (size_t bi = 0; bi < batches; bi++) {
+        int coords[16];
+        size_t rest = bi;
+        for (int d = y->ndim - 3; d >= 0; d--) { coords[d] = (int)(rest % (size_t)y->shape[d]); rest /= (size_t)y->shape[d]; }
+        const size_t a0 = matmul_batch_offset(a, coords, y->ndim), b0 = matmul_batch_offset(b, coords, y->ndim);
+        for (int m = 0; m < M; m++)
+        for (int n = 0; n < N; n++) {
+            double sum = 0.0;
+            for (int k = 0; k < K; k++) sum += load_f64(a, a0 + (size_t)m * K + k) * load_f64(b, b0 + (size_t)k * N + n);
+            store_f64(y, bi * per_batch + (size_t)m * N + n, sum);
+        }
+    }
+}
+
+/* DynamicQuantizeLinear.  tensor_ops.c:3760-3809: the range [min(x, 0), max(x, 0)] (NaNs never win a comparison) is
+   mapped onto 0..255: scale = (max - min) / 255 as a double (1 if that is 0), zero point = round-half-away(-min / scale)
+   clamped to 0..255 and narrowed like a C cast, y = clamp(rint(x / scale) + zp, 0, 255) through the ordinary store.
+   The division uses the DOUBLE scale; y_scale receives it rounded to its own type. */
+ORC_API void orc_dynamic_quantize_linear(const OrcTensor* x, OrcTensor* y, OrcTensor* y_scale, OrcTensor* y_zp) {
+    if (!x || !y || !y_scale || !y_zp) return;
+    double lo = DBL_MAX, hi = -DBL_MAX;
+    for (size_t i = 0; i < x->size; i++) {
+        const double v = load_f64(x, i);
+        if (v < lo) lo = v;
+        if (v > hi) hi = v;
+    }
+    lo = fmin(lo, 0.0);
+    hi = fmax(hi, 0.0);
+    double scale = (hi - lo) / 255.0;
+    if (scale == 0.0) scale = 1.0;
+    double zd = round(0.0 - lo / scale);
+    if (zd < 0.0) zd = 0.0;
+    if (zd > 255.0) zd = 255.0;
+    const uint8_t zp = (uint8_t)trunc_to_i64_x86(zd);          /* a NaN (infinite range) narrows to 0 */
+    store_f64(y_scale, 0, scale);
+    if (y_zp->dtype == DT_U8) ((uint8_t*)y_zp->data)[0] = zp;
+    else store_f64(y_zp, 0, (double)zp);
+    #pragma omp parallel for
+    for (size_t i = 0; i < x->size; i++) {
+        double q = rint(load_f64(x, i) / scale) + (double)zp;
+        if (q < 0.0) q = 0.0;
+        if (q > 255.0) q = 255.0;
+        store_f64(y, i, q);
+    }
+}
+
 /* Flatten / Reshape: a byte copy.  tensor_ops.c:1289-1299 */
 ORC_API void orc_flatten(const OrcTensor* x, OrcTensor* y) {
     if (!x || !y || x->size != y->size) return;

@@ -98,3 +98,12 @@ _MATH = {"exp": ops.EXP, "log": ops.LOG, "sqrt": ops.SQRT, "sigmoid": ops.SIGMOI
 
 def unary_math(op, x, x_dt, out_dt):
     return _MATH[op]([], [], dtype=out_dt).forward(_t(x, x_dt))["tensor"].numpy()
+
+
+def matmul(a, a_dt, b, b_dt, out_dt):
+    return ops.MatMul([], [], dtype=out_dt).forward(_t(a, a_dt), _t(b, b_dt))["tensor"].numpy()
+
+
+def dynamic_quantize_linear(x, x_dt):
+    y, scale, zero = ops.DynamicQuantizeLinear([], []).forward(_t(x, x_dt))["tensor"]
+    return y.numpy(), scale.numpy(), zero.numpy()

@@ -11,7 +11,7 @@ import zlib
 import numpy as np
 import pytest
 
-from datagen import ALL_DTYPES, FLOAT_DTYPES, INT_DTYPES, assert_same_codes, from_f64, make
+from datagen import ALL_DTYPES, FLOAT_DTYPES, INT_DTYPES, assert_same_codes, from_f64, make, to_f64
 
 OUT_SAMPLE = ("float8_e4m3", "float8_e5m2", "float16", "bfloat16", "float32", "float64",
               "int4", "int8", "uint8", "int16", "int32", "int64")
@@ -367,3 +367,51 @@ def test_unary_math_family(port, ref, op):
         if x_dt == "float32":
             x.reshape(-1)[:8] = [0.0, -0.0, 1.0, -1.0, 0.5, np.inf, -np.inf, np.nan]
         assert_same_codes(port.unary_math(op, x, x_dt, out_dt), ref.unary_math(op, x, x_dt, out_dt), out_dt, f"{op} {x_dt}->{out_dt}")
+
+
+# ---- MatMul and DynamicQuantizeLinear --------------------------------------------------------------------------------
+MATMUL_PLANS = [  # a_dt, b_dt, out_dt, a shape, b shape
+    ("float32", "float32", "float32", (7, 13), (13, 5)),
+    ("float32", "float32", "float32", (3, 2, 7, 13), (13, 5)),
+    ("float16", "float16", "float16", (4, 6, 9), (4, 9, 11)),
+    ("bfloat16", "float32", "float32", (2, 1, 6, 8), (1, 3, 8, 4)),
+    ("float64", "float64", "float64", (5, 17), (2, 17, 3)),
+    ("int8", "int8", "int32", (3, 5, 12), (12, 7)),
+    ("int32", "float32", "float64", (1, 4, 6), (5, 6, 2)),
+    ("float8_e4m3", "float8_e4m3", "float16", (2, 8, 16), (2, 16, 8)),
+    ("float32", "float32", "int8", (1, 9), (9, 1)),
+]
+
+
+@pytest.mark.parametrize("plan", MATMUL_PLANS, ids=lambda p: f"{p[0]}-{p[1]}-{p[2]}-{len(p[3])}x{len(p[4])}")
+def test_matmul(port, ref, plan):
+    a_dt, b_dt, out_dt, a_shape, b_shape = plan
+    rng = np.random.default_rng(zlib.crc32(repr(plan).encode()))
+    a, b = make(rng, a_shape, a_dt), make(rng, b_shape, b_dt)
+    assert_same_codes(port.matmul(a, a_dt, b, b_dt, out_dt), ref.matmul(a, a_dt, b, b_dt, out_dt), out_dt)
+
+
+@pytest.mark.parametrize("x_dt", ["float32", "float16", "bfloat16", "float64", "int8", "float8_e5m2"])
+def test_dynamic_quantize_linear(port, ref, x_dt):
+    rng = np.random.default_rng(zlib.crc32(x_dt.encode()))
+    cases = [make(rng, (5, 77), x_dt), np.abs(to_f64(make(rng, (300,), x_dt), x_dt)), -np.abs(to_f64(make(rng, (300,), x_dt), x_dt)),
+             np.zeros((4, 4)), np.full((3,), 2.5), np.zeros((0,))]
+    cases = [cases[0]] + [from_f64(c, x_dt) for c in cases[1:]]
+    if x_dt == "float32":
+        odd = make(rng, (64,), x_dt)
+        odd[:3] = [np.nan, 1e30, -3.0]
+        cases.append(odd)
+        inf = make(rng, (16,), x_dt)
+        inf[2], inf[5] = -np.inf, np.inf
+        cases.append(inf)
+        halves = (np.arange(-40, 41) * 0.5 * (10.0 / 255.0)).astype(np.float32)        # quotients at and near .5 ties
+        cases.append(np.concatenate([halves, np.float32([-5.0, 5.0])]))
+    for x in cases:
+        got, want = port.dynamic_quantize_linear(x, x_dt), ref.dynamic_quantize_linear(x, x_dt)
+        for g, w, dt in zip(got, want, ("uint8", "float32", "uint8")):
+            assert_same_codes(g, w, dt)
+    # other output types go through the ordinary store
+    x = make(rng, (33,), x_dt)
+    got, want = port.dynamic_quantize_linear(x, x_dt, "int16", "float64", "int32"), ref.dynamic_quantize_linear(x, x_dt, "int16", "float64", "int32")
+    for g, w, dt in zip(got, want, ("int16", "float64", "int32")):
+        assert_same_codes(g, w, dt)
