@@ -455,7 +455,30 @@ def other_ops(lib, stream, hbm_peak):
         mem(f"quantize_f32_to_{label}", n * 5, lambda: lib.quantize_linear_forward(x.handle, sc.handle, zp.handle, q.handle))
         mem(f"dequantize_{label}_to_f32", n * 5, lambda: lib.dequantize_linear_forward(q.handle, sc.handle, zp.handle, back.handle))
         del q
+    # the range-driven quantiser: x is read twice (range, then codes), the codes written once
+    dq = DeviceArray.empty((8192, 8192), "uint8")
+    dsc, dzp = DeviceArray.empty((1,), "float32"), DeviceArray.empty((1,), "uint8")
+    mem("dynamic_quantize_f32_to_uint8", n * 9, lambda: lib.dynamic_quantize_linear_forward(x.handle, dq.handle, dsc.handle, dzp.handle))
+    del dq
+    # operators next to the hot path, same elementwise engine (float32 8192 x 8192)
+    half = DeviceArray.empty((8192, 8192), "float16")
+    mem("cast_f32_to_f16", n * 6, lambda: lib.cast_forward(x.handle, half.handle))
+    del half
+    lo_t, hi_t = DeviceArray.from_numpy(np.array([-1.0], np.float32), "float32"), DeviceArray.from_numpy(np.array([1.0], np.float32), "float32")
+    mem("clip_f32", n * 8, lambda: lib.clip_forward(x.handle, back.handle, lo_t.handle, hi_t.handle))
+    mem("max_f32_f32", n * 12, lambda: lib.max_forward(x.handle, back.handle, back.handle))
+    for fn in ("exp", "sigmoid", "gelu", "sqrt"):
+        mem(f"{fn}_f32", n * 8, lambda: getattr(lib, fn + "_forward")(x.handle, back.handle))
     del x, back
+    bx = DeviceArray.from_numpy(rng.standard_normal((64, 256, 56, 56)).astype(np.float32), "float32")
+    by = DeviceArray.empty((64, 256, 56, 56), "float32")
+    bp = [DeviceArray.from_numpy(v.astype(np.float32), "float32") for v in (rng.normal(1, 0.1, 256), rng.normal(0, 0.1, 256),
+                                                                              rng.normal(0, 0.1, 256), rng.uniform(0.5, 2, 256))]
+    mem("batch_norm_f32_64x256x56x56", bx.size * 8, lambda: lib.batch_norm_forward(bx.handle, bp[0].handle, bp[1].handle, bp[2].handle, bp[3].handle,
+                                                                                    by.handle, ctypes.c_float(1e-5)))
+    gy = DeviceArray.empty((64, 256, 1, 1), "float32")
+    mem("global_average_pool_f32_64x256x56x56", bx.size * 4, lambda: lib.global_average_pool_forward(bx.handle, gy.handle))
+    del bx, by, gy
 
     sx = DeviceArray.from_numpy(rng.uniform(-10, 10, (65536, 1000)).astype(np.float32), "float32")
     sy = DeviceArray.empty((65536, 1000), "float32")
@@ -502,6 +525,17 @@ def other_ops(lib, stream, hbm_peak):
             del yq
         del a, b, y
     del a32, b32
+    # MatMul: [8, 2048, 4096] x [4096, 4096] (one B: a single tall problem) and 64 heads of [1024, 128] x [128, 1024]
+    for label, a_shape, b_shape in (("8x2048x4096_by_4096x4096", (8, 2048, 4096), (4096, 4096)), ("64x1024x128_by_64x128x1024", (64, 1024, 128), (64, 128, 1024))):
+        a = DeviceArray.from_numpy(bf16(rng.normal(0, 0.02, a_shape).astype(np.float32)), "bfloat16")
+        b = DeviceArray.from_numpy(bf16(rng.normal(0, 0.02, b_shape).astype(np.float32)), "bfloat16")
+        y = DeviceArray.empty(a_shape[:-1] + (b_shape[-1],), "bfloat16")
+        before = lib.tops_tensor_core_launches()
+        ms = timed(lambda: lib.matmul_forward(a.handle, b.handle, y.handle))
+        mm_flops = 2.0 * np.prod(a_shape) * b_shape[-1]
+        out[f"matmul_bf16_{label}"] = {"TFLOPs": round(mm_flops / 1e12 / (ms / 1e3), 1), "ms": round(ms, 4),
+                                       "tensor_core_path": lib.tops_tensor_core_launches() > before, "includes": "transposition of B"}
+        del a, b, y
 
     cx = DeviceArray.from_numpy(bf16(rng.standard_normal((256, 256, 56, 56)).astype(np.float32)), "bfloat16")
     cw = DeviceArray.from_numpy(bf16(rng.normal(0, 0.02, (256, 256, 3, 3)).astype(np.float32)), "bfloat16")

@@ -114,7 +114,7 @@ __global__ void __launch_bounds__(kDqThreads) dynamic_quantize_kernel(const void
                                                                       void* y_scale, int ds, void* y_zero, int dz) {
     using S = typename Storage<DX>::type;
     const DynamicScale q = fold_range(partials, n_partials, y_scale, ds, y_zero, dz);
-    const float inv = __fdividef(1.0f, (float)q.scale);
+    const float inv = quantize_reciprocal((float)q.scale);
     const int z = (int)q.zero;
     const int z_minus_magic = z - 0x4B400000;
     const size_t runs = n / V;

@@ -81,7 +81,7 @@ __global__ void __launch_bounds__(256) activations_to_levels(const void* __restr
             }
             const float zf = (float)zero;
             float scale = 1.0f, inv = 1.0f;
-            if (XK == 0) { scale = __ldg(scale_ptr); inv = __fdividef(1.0f, scale); }
+            if (XK == 0) { scale = __ldg(scale_ptr); inv = quantize_reciprocal(scale); }
             #pragma unroll
             for (int i = 0; i < 8; i++) {
                 float level[2];
@@ -133,7 +133,7 @@ __global__ void __launch_bounds__(256) activations_to_levels_few_channels(const 
     if (zero_ptr) zero = SIGNED ? (int)*(const int8_t*)zero_ptr : (int)*(const uint8_t*)zero_ptr;
     const float zf = (float)zero;
     float scale = 1.0f, inv = 1.0f;
-    if (XK == 0) { scale = __ldg(scale_ptr); inv = __fdividef(1.0f, scale); }
+    if (XK == 0) { scale = __ldg(scale_ptr); inv = quantize_reciprocal(scale); }
     const int h = p / g.W, w = p - h * g.W;
     int A = h + g.pt, B = w + g.pl, slot = 0;
     if (g.S == 2) { slot = ((A & 1) * 2 + (B & 1)) * g.C; A >>= 1; B >>= 1; }

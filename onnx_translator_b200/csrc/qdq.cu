@@ -43,7 +43,7 @@ struct QuantizeBody {
             int v[kV];
             bool all_ok = true;
             const bool uniform_scale = ALIGNED && !g.simple && s.st2 == 0;    // one scale for the whole run
-            float inv = uniform_scale ? __fdividef(1.0f, to_f32<DS>(rs.v[0])) : 0.0f;
+            float inv = uniform_scale ? quantize_reciprocal(to_f32<DS>(rs.v[0])) : 0.0f;
             constexpr bool kEightBit = (DO == DTYPE_INT8 || DO == DTYPE_UINT8 || DO == DTYPE_FLOAT8_E4M3 || DO == DTYPE_FLOAT8_E5M2) &&
                                        (DZ == DTYPE_INT8 || DZ == DTYPE_UINT8);
             constexpr bool kFp8Out = DO == DTYPE_FLOAT8_E4M3 || DO == DTYPE_FLOAT8_E5M2;
@@ -58,7 +58,7 @@ struct QuantizeBody {
                 const float zf0 = (float)to_i32_narrow<DZ>(rz.v[0]);
                 #pragma unroll
                 for (int j = 0; j < kV; j++) {
-                    if (!uniform_scale) inv = __fdividef(1.0f, to_f32<DS>(rs.v[j]));
+                    if (!uniform_scale) inv = quantize_reciprocal(to_f32<DS>(rs.v[j]));
                     const float q = __fmul_rn(fx[j], inv);
                     const float t = __fadd_rn(q, 12582912.0f);
                     const float rq = __fsub_rn(t, 12582912.0f);
@@ -91,7 +91,7 @@ struct QuantizeBody {
             } else if (kEightBit) {
                 #pragma unroll
                 for (int j = 0; j < kV; j++) {
-                    if (!uniform_scale) inv = __fdividef(1.0f, to_f32<DS>(rs.v[j]));
+                    if (!uniform_scale) inv = quantize_reciprocal(to_f32<DS>(rs.v[j]));
                     bool ok;
                     v[j] = quantize_round_8bit(fx[j], inv, to_i32_narrow<DZ>(rz.v[j]) - 0x4B400000, ok);
                     all_ok = all_ok & ok;
@@ -99,7 +99,7 @@ struct QuantizeBody {
             } else {
                 #pragma unroll
                 for (int j = 0; j < kV; j++) {
-                    if (!uniform_scale) inv = __fdividef(1.0f, to_f32<DS>(rs.v[j]));
+                    if (!uniform_scale) inv = quantize_reciprocal(to_f32<DS>(rs.v[j]));
                     bool ok;
                     v[j] = quantize_round_fast(fx[j], inv, to_i32_narrow<DZ>(rz.v[j]), ok);
                     all_ok = all_ok && ok;

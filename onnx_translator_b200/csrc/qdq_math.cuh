@@ -20,6 +20,12 @@ namespace tops {
 // bits.  r equals rint(x / s) -- for the exact quotient and for its double rounding alike --
 // whenever q is further than 2^-19 |q| from a tie; the rest (about 1e-5 of the elements for
 // |q| ~ 50, plus s == 0, non-finite x and |q| >= 2^21) take the double division.
+// The approximate reciprocal the fast paths multiply by.  The hardware divide returns 0 for |s| above 2^126
+// (a subnormal reciprocal), which would pass the tie test with a quotient of 0: a NaN sends those
+// elements to the exact division instead.
+__device__ __forceinline__ float quantize_reciprocal(float s) {
+    return fabsf(s) < 8.5e37f ? __fdividef(1.0f, s) : __int_as_float(0x7FC00000);
+}
 // Returns rint(x / s) + z as an integer; `ok` tells whether the fast path was conclusive.
 __device__ __forceinline__ int quantize_round_fast(float x, float inv_s, int z, bool& ok) {
     const float q = __fmul_rn(x, inv_s);

@@ -303,7 +303,7 @@ tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUt
                                 int A = oh2 + p.lv.pt, B = ow2 + p.lv.pl, slot = 0;
                                 if (p.lv.S == 2) { slot = ((A & 1) * 2 + (B & 1)) * p.lv.C; A >>= 1; B >>= 1; }
                                 uint16_t* zdst = p.lv.z + (((size_t)(m / p.cv.plane) * p.lv.Hz + A) * p.lv.Wz + B) * p.lv.Cz + slot + n0;
-                                const float ls = __ldg(p.lv.scale), linv = __fdividef(1.0f, ls);
+                                const float ls = __ldg(p.lv.scale), linv = quantize_reciprocal(ls);
                                 float zf = 0.0f;
                                 if (p.lv.zero) zf = p.lv.zero_signed ? (float)*(const int8_t*)p.lv.zero : (float)*(const uint8_t*)p.lv.zero;
                                 // eight values at a time on the fast path without branches (their dependency chains

@@ -102,3 +102,54 @@ def test_oracle_reproduces_adjacent_golden_vectors(port, case):
 def test_cuda_library_reproduces_adjacent_golden_vectors(case):
     import gpu_ops
     assert_same_codes(_run_adjacent(gpu_ops, case), ADJ_ARRAYS[f"c{case['id']}_out"], case["params"]["out_dt"], _ids(case))
+
+
+# ---- Max / Min / Pow, one-line unary operators, MatMul, DynamicQuantizeLinear (tests/golden/make_family_golden.py) ------
+with open(os.path.join(HERE, "golden", "family_ops.json")) as _f:
+    FAM_CASES = json.load(_f)
+FAM_ARRAYS = np.load(os.path.join(HERE, "golden", "family_ops.npz"))
+# operators whose expression consists of exactly rounded steps: identical codes on every implementation
+FAM_EXACT = {"max", "min", "matmul", "dynamic_quantize"} | {"unary:" + n for n in ("neg", "reciprocal", "ceil", "floor", "sqrt", "round", "softsign", "hard_swish")}
+
+
+def _run_family(backend, case):
+    ins = [FAM_ARRAYS[k] for k in case["inputs"]]
+    p, op = case["params"], case["op"]
+    if op in ("max", "min", "pow"):
+        return (backend.binary(op, ins[0], p["a_dt"], ins[1], p["b_dt"], p["out_dt"]),)
+    if op.startswith("unary:"):
+        return (backend.unary_math(op[6:], ins[0], p["x_dt"], p["out_dt"]),)
+    if op == "matmul":
+        return (backend.matmul(ins[0], p["a_dt"], ins[1], p["b_dt"], p["out_dt"]),)
+    if op == "dynamic_quantize":
+        return tuple(backend.dynamic_quantize_linear(ins[0], p["x_dt"]))
+    raise AssertionError(op)
+
+
+def _family_out_dtypes(case):
+    return ("uint8", "float32", "uint8") if case["op"] == "dynamic_quantize" else (case["params"]["out_dt"],)
+
+
+@pytest.mark.parametrize("case", FAM_CASES, ids=_ids)
+def test_oracle_reproduces_family_golden_vectors(port, case):
+    """The oracle calls the same glibc functions as the reference: identical codes for every operator."""
+    for k, (got, dt) in enumerate(zip(_run_family(port, case), _family_out_dtypes(case))):
+        assert_same_codes(got, FAM_ARRAYS[f"c{case['id']}_out{k}"], dt, _ids(case))
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("case", FAM_CASES, ids=_ids)
+def test_cuda_library_reproduces_family_golden_vectors(case):
+    import gpu_ops
+    for k, (got, dt) in enumerate(zip(_run_family(gpu_ops, case), _family_out_dtypes(case))):
+        want = FAM_ARRAYS[f"c{case['id']}_out{k}"]
+        if case["op"] in FAM_EXACT:
+            assert_same_codes(got, want, dt, _ids(case))
+        elif dt.startswith("int") or dt.startswith("uint"):      # a value at a .5 tie may round either way
+            assert np.abs(got.astype(np.int64) - want.astype(np.int64)).max() <= 1
+        else:                                                   # CUDA libm against glibc: 2 ulp of the output type
+            g, w = to_f64(got, dt), to_f64(want, dt)
+            ulp = {"float32": 2.0 ** -23, "float64": 2.0 ** -52, "float16": 2.0 ** -10, "bfloat16": 2.0 ** -7}[dt]
+            with np.errstate(invalid="ignore"):
+                ok = (np.isnan(g) & np.isnan(w)) | (g == w) | (np.abs(g - w) <= 2 * ulp * np.abs(w) + 2.0 ** -50)
+            assert ok.all(), _ids(case)

@@ -201,6 +201,23 @@ def test_quantize_edge_values(port):
                               port.quantize(x, "float32", sv, "float32", zv, zp_dt, out_dt), out_dt, f"{out_dt} s={s}")
 
 
+def test_quantize_with_scales_at_the_ends_of_the_float_range(port):
+    """Scales whose reciprocal is subnormal or infinite in float32: the approximate reciprocal is useless
+    there and every element has to reach the exact division."""
+    x = np.tile(np.array([3e38, -3e38, 1.2e38, 0.0, 1e-40, -2e-45, 1.0, 2.9e-39, np.inf], dtype=np.float32), 40)
+    for out_dt, zp_dt, zp in (("int8", "int8", 1), ("uint8", "uint8", 128), ("float8_e4m3", "int8", 0), ("int32", "int32", 5)):
+        for s in (1e38, 1.7e38, 8.6e37, 8.4e37, 1e-39, 1.4e-45, 2e-38):
+            sv = np.array([s], dtype=np.float32)
+            zv = np.array([zp]).astype(np.uint8 if zp_dt == "uint8" else np.int32)
+            assert_same_codes(gpu.quantize(x, "float32", sv, "float32", zv, zp_dt, out_dt),
+                              port.quantize(x, "float32", sv, "float32", zv, zp_dt, out_dt), out_dt, f"{out_dt} s={s}")
+        per_axis = np.array([1e38, 1e-39, 0.5, 1.7e38, 0.0, 8.6e37, 3.0, 1e-3], dtype=np.float32)
+        xa = np.tile(x[:9], (8, 5)).astype(np.float32)
+        za = np.full(8, zp).astype(np.uint8 if zp_dt == "uint8" else np.int32)
+        assert_same_codes(gpu.quantize(xa, "float32", per_axis, "float32", za, zp_dt, out_dt, axis=0),
+                          port.quantize(xa, "float32", per_axis, "float32", za, zp_dt, out_dt, axis=0), out_dt, f"{out_dt} per axis")
+
+
 @pytest.mark.parametrize("cfg", [("int8", 0.02, 0), ("uint8", 0.02, 128), ("float8_e4m3", 1 / 16, 0), ("float8_e5m2", 1 / 16, 0)],
                          ids=lambda c: c[0])
 def test_quantize_near_ties_against_double_division(port, cfg):
