@@ -1,8 +1,9 @@
 // Operators that surround the hot path in exported convolutional networks: Clip, AveragePool,
 // GlobalAveragePool and BatchNormalization (tensor_ops.c:1523-1543, 2735-2789, 2844-2868, 3041-3083).
 // All arithmetic is the reference's, in double and in its order, so the outputs are bit-identical:
-// these kernels are one thread per output (or per plane) with coalesced accesses, not tuned further.
-#include "common.cuh"
+// the generic kernels are one thread per output (or per plane) with the dtypes switched at run time; float32 /
+// float16 / bfloat16 tensors take typed variants with vector accesses.
+#include "elementwise.cuh"
 
 namespace tops {
 
@@ -23,6 +24,38 @@ __global__ void __launch_bounds__(256) clip_kernel(ClipArgs a, void* __restrict_
         if (a.has_hi) { const double b = load_f64_rt(a.hi.ptr, a.dhi, a.hi.flat ? i : operand_offset(a.g, a.hi, i, p)); if (v > b) v = b; }
         store_f64_rt(y, a.dout, first + i, v);
     }
+}
+
+// Same float type in and out, scalar bounds whose values are exact in float32: the comparisons give the same
+// answers in float32 as in double, and the stored value is the input or a bound either way.
+template <int DT>
+__global__ void __launch_bounds__(256) clip_typed_kernel(const void* __restrict__ x, void* __restrict__ y, size_t n, const void* lo, int dlo,
+                                                         const void* hi, int dhi) {
+    using S = typename Storage<DT>::type;
+    constexpr int V = 16 / (int)sizeof(S);
+    const bool has_lo = lo != nullptr, has_hi = hi != nullptr;
+    const float lof = has_lo ? (float)load_f64_rt(lo, dlo, 0) : 0.0f, hif = has_hi ? (float)load_f64_rt(hi, dhi, 0) : 0.0f;
+    const size_t runs = n / V;
+    for (size_t r = (size_t)blockIdx.x * blockDim.x + threadIdx.x; r < runs; r += (size_t)gridDim.x * blockDim.x) {
+        Run<S, V> in, out;
+        load_bytes_stream<16>((const S*)x + r * V, &in);
+        float f[V];
+        decode_floats<DT, V>(in, f);
+        #pragma unroll
+        for (int j = 0; j < V; j++) {
+            if (has_lo && f[j] < lof) f[j] = lof;
+            if (has_hi && f[j] > hif) f[j] = hif;
+        }
+        encode_floats<DT, V>(f, out);
+        store_bytes_stream<16>((S*)y + r * V, &out);
+    }
+    if (blockIdx.x == 0)
+        for (size_t i = runs * V + threadIdx.x; i < n; i += blockDim.x) {
+            float v = to_f32<DT>(((const S*)x)[i]);
+            if (has_lo && v < lof) v = lof;
+            if (has_hi && v > hif) v = hif;
+            ((S*)y)[i] = from_f32<DT>(v);
+        }
 }
 
 // ---- AveragePool --------------------------------------------------------------------------------------------
@@ -66,6 +99,49 @@ __global__ void __launch_bounds__(128) global_average_pool_kernel(const void* __
     }
 }
 
+// float32 / float16 / bfloat16 planes: a warp takes 8 planes at a time.  All 32 lanes fetch 128 consecutive
+// elements of each plane with coalesced loads into shared memory, then lanes 0..7 each add their own plane's
+// 128 values in order -- the chain of dependent additions is the reference's, the memory accesses are not.
+constexpr int kGapPlanes = 8, kGapChunk = 128, kGapWarps = 4;
+
+template <int DT>
+__global__ void __launch_bounds__(kGapWarps * 32) global_average_pool_typed(const void* __restrict__ x, void* __restrict__ y, int dout,
+                                                                             size_t planes, int spatial) {
+    using S = typename Storage<DT>::type;
+    __shared__ double tile[kGapWarps][kGapPlanes][kGapChunk + 1];     // widened by all 32 lanes, so the adding lanes only load and add
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const size_t groups = (planes + kGapPlanes - 1) / kGapPlanes;
+    for (size_t grp = (size_t)blockIdx.x * kGapWarps + warp; grp < groups; grp += (size_t)gridDim.x * kGapWarps) {
+        const size_t p0 = grp * kGapPlanes;
+        double sum = 0.0;
+        float v[kGapPlanes][kGapChunk / 32];
+        auto fetch = [&](int c0) {
+            #pragma unroll
+            for (int r = 0; r < kGapPlanes; r++)
+                #pragma unroll
+                for (int q = 0; q < kGapChunk / 32; q++) {
+                    const int c = c0 + q * 32 + lane;
+                    v[r][q] = (p0 + r < planes && c < spatial) ? to_f32<DT>(((const S*)x)[(p0 + r) * (size_t)spatial + c]) : 0.0f;
+                }
+        };
+        fetch(0);
+        for (int c0 = 0; c0 < spatial; c0 += kGapChunk) {
+            #pragma unroll
+            for (int r = 0; r < kGapPlanes; r++)
+                #pragma unroll
+                for (int q = 0; q < kGapChunk / 32; q++) tile[warp][r][q * 32 + lane] = (double)v[r][q];
+            __syncwarp();
+            if (c0 + kGapChunk < spatial) fetch(c0 + kGapChunk);          // in flight while this chunk is added up
+            if (lane < kGapPlanes) {
+                const int m = spatial - c0 < kGapChunk ? spatial - c0 : kGapChunk;
+                for (int j = 0; j < m; j++) sum = __dadd_rn(sum, tile[warp][lane][j]);
+            }
+            __syncwarp();
+        }
+        if (lane < kGapPlanes && p0 + lane < planes) store_f64_rt(y, dout, p0 + lane, __ddiv_rn(sum, (double)spatial));
+    }
+}
+
 // ---- BatchNormalization (inference) ------------------------------------------------------------------------------
 // Per channel a = scale / sqrt(var + eps), k = bias - mean * a (a small kernel fills the two tables), then
 // y = x * a + k with the product and the sum rounded separately.
@@ -87,6 +163,28 @@ __global__ void __launch_bounds__(256) batch_norm_kernel(const void* __restrict_
     const size_t base = plane * (size_t)spatial;
     for (uint32_t i = blockIdx.x * blockDim.x + threadIdx.x; i < spatial; i += gridDim.x * blockDim.x)
         store_f64_rt(y, dout, base + i, __dadd_rn(__dmul_rn(load_f64_rt(x, dx, base + i), av), kv));
+}
+
+// Same float type in and out, plane size a multiple of the vector width: vector accesses, the arithmetic unchanged.
+template <int DT>
+__global__ void __launch_bounds__(256) batch_norm_typed_kernel(const void* __restrict__ x, void* __restrict__ y, int C, uint32_t spatial,
+                                                               const double* __restrict__ a, const double* __restrict__ k, size_t first_plane) {
+    using S = typename Storage<DT>::type;
+    constexpr int V = 16 / (int)sizeof(S);
+    const size_t plane = first_plane + blockIdx.y;
+    const double av = a[plane % (size_t)C], kv = k[plane % (size_t)C];
+    const S* xp = (const S*)x + plane * (size_t)spatial;
+    S* yp = (S*)y + plane * (size_t)spatial;
+    for (uint32_t r = blockIdx.x * blockDim.x + threadIdx.x; r < spatial / V; r += gridDim.x * blockDim.x) {
+        Run<S, V> in, out;
+        load_bytes_stream<16>(xp + (size_t)r * V, &in);
+        float f[V];
+        decode_floats<DT, V>(in, f);
+        #pragma unroll
+        for (int j = 0; j < V; j++) f[j] = __double2float_rn(__dadd_rn(__dmul_rn((double)f[j], av), kv));
+        encode_floats<DT, V>(f, out);
+        store_bytes_stream<16>(yp + (size_t)r * V, &out);
+    }
 }
 
 static bool pool_args(const char* name, const Tensor* X, Tensor* Y, const PoolParams* p) {
@@ -138,7 +236,21 @@ TOPS_API void clip_forward(const Tensor* input, Tensor* output, const Tensor* mi
     if (has_lo) { a.lo = ops[where[0]]; a.lo.ptr = min_t->data; }
     if (has_hi) { a.hi = ops[where[1]]; a.hi.ptr = max_t->data; }
     a.dout = (int)output->dtype;
-    clip_kernel<<<grid_for(output->size, 256, st->sm_count, 8), 256, 0, current_stream()>>>(a, output->data, 0, (uint32_t)output->size);
+    const int dt = (int)input->dtype;
+    const bool scalar_bounds = (!has_lo || (min_t->size == 1 && dtype_exact_in_f32((int)min_t->dtype))) &&
+                               (!has_hi || (max_t->size == 1 && dtype_exact_in_f32((int)max_t->dtype)));
+    if (scalar_bounds && dt == (int)output->dtype && input->size == output->size && a.x.flat &&
+        (((uintptr_t)input->data | (uintptr_t)output->data) & 15) == 0 &&
+        (dt == DTYPE_FLOAT32 || dt == DTYPE_FLOAT16 || dt == DTYPE_BFLOAT16)) {
+        const void* lo = has_lo ? min_t->data : nullptr;
+        const void* hi = has_hi ? max_t->data : nullptr;
+        const int grid = grid_for(output->size / 4 + 1, 256, st->sm_count, 8);
+        if (dt == DTYPE_FLOAT32) clip_typed_kernel<DTYPE_FLOAT32><<<grid, 256, 0, current_stream()>>>(input->data, output->data, output->size, lo, a.dlo, hi, a.dhi);
+        else if (dt == DTYPE_FLOAT16) clip_typed_kernel<DTYPE_FLOAT16><<<grid, 256, 0, current_stream()>>>(input->data, output->data, output->size, lo, a.dlo, hi, a.dhi);
+        else clip_typed_kernel<DTYPE_BFLOAT16><<<grid, 256, 0, current_stream()>>>(input->data, output->data, output->size, lo, a.dlo, hi, a.dhi);
+    } else {
+        clip_kernel<<<grid_for(output->size, 256, st->sm_count, 8), 256, 0, current_stream()>>>(a, output->data, 0, (uint32_t)output->size);
+    }
     TOPS_CHECK_LAUNCH(name);
     finish_op();
 }
@@ -172,8 +284,18 @@ TOPS_API void global_average_pool_forward(const Tensor* input, Tensor* output) {
     if (!st || output->size == 0) return;
     const size_t planes = output->size;
     const int spatial = input->shape[2] * input->shape[3];
-    global_average_pool_kernel<<<grid_for(planes, 128, st->sm_count, 16), 128, 0, current_stream()>>>(input->data, output->data, (int)input->dtype,
-                                                                                                 (int)output->dtype, planes, spatial);
+    const int dx = (int)input->dtype;
+    if (dx == DTYPE_FLOAT32 || dx == DTYPE_FLOAT16 || dx == DTYPE_BFLOAT16) {
+        const size_t groups = (planes + kGapPlanes - 1) / kGapPlanes;
+        const int grid = grid_for(groups * 32, kGapWarps * 32, st->sm_count, 4);
+        cudaStream_t s = current_stream();
+        if (dx == DTYPE_FLOAT32) global_average_pool_typed<DTYPE_FLOAT32><<<grid, kGapWarps * 32, 0, s>>>(input->data, output->data, (int)output->dtype, planes, spatial);
+        else if (dx == DTYPE_FLOAT16) global_average_pool_typed<DTYPE_FLOAT16><<<grid, kGapWarps * 32, 0, s>>>(input->data, output->data, (int)output->dtype, planes, spatial);
+        else global_average_pool_typed<DTYPE_BFLOAT16><<<grid, kGapWarps * 32, 0, s>>>(input->data, output->data, (int)output->dtype, planes, spatial);
+    } else {
+        global_average_pool_kernel<<<grid_for(planes, 128, st->sm_count, 16), 128, 0, current_stream()>>>(input->data, output->data, dx,
+                                                                                                     (int)output->dtype, planes, spatial);
+    }
     TOPS_CHECK_LAUNCH(name);
     finish_op();
 }
@@ -202,11 +324,19 @@ TOPS_API void batch_norm_forward(const Tensor* input, const Tensor* scale, const
     batch_norm_tables<<<(C + 127) / 128, 128, 0, s>>>(scale->data, B->data, mean->data, var->data, (int)scale->dtype, (int)B->dtype, (int)mean->dtype,
                                                       (int)var->dtype, (double)epsilon, C, ak, ak + C);
     // planes on grid.y (at most 65535 per launch), the plane's elements on grid.x
-    const unsigned gx = (unsigned)((spatial + 255) / 256 < 64 ? (spatial + 255) / 256 : 64);
+    const int dt = (int)input->dtype;
+    const int vec = 16 / dtype_bytes(dt);
+    const bool typed = dt == (int)output->dtype && (dt == DTYPE_FLOAT32 || dt == DTYPE_FLOAT16 || dt == DTYPE_BFLOAT16) && spatial % vec == 0 &&
+                       (((uintptr_t)input->data | (uintptr_t)output->data) & 15) == 0;
+    const size_t per_plane = typed ? spatial / vec : spatial;
+    const unsigned gx = (unsigned)((per_plane + 255) / 256 < 64 ? (per_plane + 255) / 256 : 64);
     for (size_t first = 0; first < planes; first += 65535) {
         const unsigned gy = (unsigned)(planes - first < 65535 ? planes - first : 65535);
-        batch_norm_kernel<<<dim3(gx ? gx : 1, gy), 256, 0, s>>>(input->data, output->data, (int)input->dtype, (int)output->dtype, C,
-                                                                (uint32_t)spatial, ak, ak + C, first);
+        const dim3 grid(gx ? gx : 1, gy);
+        if (!typed) batch_norm_kernel<<<grid, 256, 0, s>>>(input->data, output->data, dt, (int)output->dtype, C, (uint32_t)spatial, ak, ak + C, first);
+        else if (dt == DTYPE_FLOAT32) batch_norm_typed_kernel<DTYPE_FLOAT32><<<grid, 256, 0, s>>>(input->data, output->data, C, (uint32_t)spatial, ak, ak + C, first);
+        else if (dt == DTYPE_FLOAT16) batch_norm_typed_kernel<DTYPE_FLOAT16><<<grid, 256, 0, s>>>(input->data, output->data, C, (uint32_t)spatial, ak, ak + C, first);
+        else batch_norm_typed_kernel<DTYPE_BFLOAT16><<<grid, 256, 0, s>>>(input->data, output->data, C, (uint32_t)spatial, ak, ak + C, first);
     }
     TOPS_CHECK_LAUNCH(name);
     cudaFreeAsync(ak, s);

@@ -71,7 +71,9 @@ bool gemm_exact(const Tensor* A, const Tensor* B, Tensor* Y, const GemmShape& g,
 // Tensor-core path.  Returns false when the case is outside what it covers (caller falls back
 // to the exact kernel, which is still a GPU kernel of this library).
 // With `fused` (operand / result scales of a DQ -> Gemm -> Q sequence) 8-bit output types are accepted too.
+// `batches` > 1: that many dense problems of shape g stored back to back in A, B and Y (no bias, no fusion,
+// 16-bit or 8-bit float operands), one launch.
 bool gemm_tensor_core(const Tensor* A, const Tensor* B, Tensor* Y, const GemmShape& g, const BiasView& bias,
-                      float alpha, float beta, const EpilogueScales* fused = nullptr);
+                      float alpha, float beta, const EpilogueScales* fused = nullptr, int batches = 1);
 
 }  // namespace tops

@@ -136,11 +136,12 @@ static bool gemm_split_f32(const Tensor* A, const Tensor* B, Tensor* Y, const Ge
 }
 
 bool gemm_tensor_core(const Tensor* A, const Tensor* B, Tensor* Y, const GemmShape& g, const BiasView& bias,
-                      float alpha, float beta, const EpilogueScales* fused) {
+                      float alpha, float beta, const EpilogueScales* fused, int batches) {
     const int da = (int)A->dtype, db = (int)B->dtype, dy = (int)Y->dtype;
     const bool fp8 = is_fp8(da) && is_fp8(db);
     const bool half16 = (da == db) && (da == DTYPE_FLOAT16 || da == DTYPE_BFLOAT16);
     // large float32 problems: three-way bfloat16 split (small ones keep the exact, bit-identical kernel)
+    if (batches > 1 && (fused || bias.mode != kBiasNone || (da == DTYPE_FLOAT32 && db == DTYPE_FLOAT32))) return false;
     if (!fused && da == DTYPE_FLOAT32 && db == DTYPE_FLOAT32 && (dy == DTYPE_FLOAT32 || dy == DTYPE_BFLOAT16 || dy == DTYPE_FLOAT16) &&
         g.transA == 0 && g.transB == 1 && g.K % 8 == 0 && g.lda == g.K && g.ldb == g.K && !getenv("TOPS_DISABLE_TC") &&
         (((uintptr_t)A->data | (uintptr_t)B->data) & 15) == 0 && (double)g.M * g.N * g.K >= 134217728.0)
@@ -159,12 +160,15 @@ bool gemm_tensor_core(const Tensor* A, const Tensor* B, Tensor* Y, const GemmSha
 
     const int k_step = kRowBytes / eb;
     CUtensorMap map_a, map_b;
-    const uint64_t dims_a[2] = {(uint64_t)g.K, (uint64_t)g.M}, dims_b[2] = {(uint64_t)g.K, (uint64_t)g.N};
-    const uint64_t strides_a[1] = {(uint64_t)g.lda * eb}, strides_b[1] = {(uint64_t)g.ldb * eb};
-    const uint32_t box_a[2] = {(uint32_t)k_step, (uint32_t)kBM}, box_b[2] = {(uint32_t)k_step, (uint32_t)kBN};
+    // batches > 1: dense problems back to back, the batch index is the third map coordinate
+    const uint64_t dims_a[3] = {(uint64_t)g.K, (uint64_t)g.M, (uint64_t)batches}, dims_b[3] = {(uint64_t)g.K, (uint64_t)g.N, (uint64_t)batches};
+    const uint64_t strides_a[2] = {(uint64_t)g.lda * eb, (uint64_t)g.lda * eb * g.M}, strides_b[2] = {(uint64_t)g.ldb * eb, (uint64_t)g.ldb * eb * g.N};
+    const uint32_t box_a[3] = {(uint32_t)k_step, (uint32_t)kBM, 1u}, box_b[3] = {(uint32_t)k_step, (uint32_t)kBN, 1u};
     const bool f16 = da == DTYPE_FLOAT16;
-    if (!make_tensor_map(&map_a, A->data, eb, fp8, f16, 2, dims_a, strides_a, box_a, nullptr) ||
-        !make_tensor_map(&map_b, B->data, eb, fp8, f16, 2, dims_b, strides_b, box_b, nullptr))
+    const int rank = batches > 1 ? 3 : 2;
+    if ((long long)((g.M + kBM - 1) / kBM) * ((g.N + kBN - 1) / kBN) * batches > 0x7FFFFFFFll) return false;
+    if (!make_tensor_map(&map_a, A->data, eb, fp8, f16, rank, dims_a, strides_a, box_a, nullptr) ||
+        !make_tensor_map(&map_b, B->data, eb, fp8, f16, rank, dims_b, strides_b, box_b, nullptr))
         return false;                                                 // let the exact kernel take it
 
     TcParams p;
@@ -178,12 +182,13 @@ bool gemm_tensor_core(const Tensor* A, const Tensor* B, Tensor* Y, const GemmSha
     p.bias = bias;
     p.status = device_status_word();
     p.vec_store = (((uintptr_t)Y->data & 15) == 0) && (((size_t)g.N * dtype_bytes(dy)) % 16 == 0);
+    p.batches = batches;
     if (fused) p.fs = *fused;
 
     const uint32_t fa = fp8 ? (da == DTYPE_FLOAT8_E5M2 ? 1u : 0u) : (da == DTYPE_BFLOAT16 ? 1u : 0u);
     const uint32_t fb = fp8 ? (db == DTYPE_FLOAT8_E5M2 ? 1u : 0u) : (db == DTYPE_BFLOAT16 ? 1u : 0u);
     const uint32_t idesc = umma::instr_desc(fa, fb, kBM, kBN);
-    const int tiles = p.tiles_m * p.tiles_n;
+    const int tiles = p.tiles_m * p.tiles_n * batches;
     const int grid = tiles < st->sm_count ? tiles : st->sm_count;
     cudaStream_t s = current_stream();
     if (fp8) {

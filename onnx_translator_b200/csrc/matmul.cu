@@ -7,7 +7,8 @@
 //     operand;
 //   * the tensor-core kernel wants both operands K-major, so B ([K, N] per batch) is transposed into
 //     scratch first -- 2 * K * N elements of traffic against M * N * K multiply-adds -- and is used for the
-//     same input types and sizes as in gemm_forward.
+//     same input types and sizes as in gemm_forward; equal batches of 16-bit / 8-bit operands are one launch
+//     (the batch is the third coordinate of the tensor maps), other batch patterns one launch per batch.
 // A batched A against a single B is one Gemm with batches * M rows.
 #include "common.cuh"
 #include "gemm_common.cuh"
@@ -136,7 +137,13 @@ TOPS_API void matmul_forward(const Tensor* A, const Tensor* B, Tensor* Y) {
             gt.ldb = K; gt.transB = 1;
             done = good;
             int coords[16];
-            for (size_t i = 0; good && i < problems; i++) {
+            size_t first = 0;
+            if (good && problems > 1 && pa == 1 && pb == 1) {        // equal batches: one launch walks them all
+                Tensor btv = *B;
+                btv.data = bt;
+                if (gemm_tensor_core(A, &btv, Y, gt, none, 1.0f, 0.0f, nullptr, (int)problems)) first = problems;
+            }
+            for (size_t i = first; good && i < problems; i++) {
                 size_t rest = i;
                 for (int d = Y->ndim - 3; d >= 0; d--) { coords[d] = (int)(rest % (size_t)Y->shape[d]); rest /= (size_t)Y->shape[d]; }
                 const size_t a_off = problems == 1 ? 0 : batch_offset(A, coords, Y->ndim);

@@ -52,6 +52,8 @@ struct TcParams {
     BiasView bias;
     int* status;           // device-visible word, set non-zero when a wait gave up
     int vec_store;         // Y base and row pitch are 16-byte aligned
+    int batches = 1;       // Gemm mode: independent problems of one shape; the tensor maps are then 3-D
+                           // (K, rows, batch) and Y holds the results back to back
     ConvView cv;           // convolution mode only
     EpilogueScales fs;
     int relu = 0;          // clamp the result at zero before it is stored (v > 0 ? v : 0)
@@ -95,7 +97,8 @@ tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUt
     uint32_t* out_stage = (uint32_t*)(scale_stage + kEpi * kBN);   // 4 warps x 32 rows x kStageRowWords (not in convolution mode)
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int total_tiles = p.tiles_m * p.tiles_n;
+    const int tiles_per_batch = p.tiles_m * p.tiles_n;
+    const int total_tiles = MODE == kModeGemm ? tiles_per_batch * p.batches : tiles_per_batch;
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < kSt; s++) { umma::mbar_init(&full[s], 1); umma::mbar_init(&empty[s], 1); }
@@ -116,7 +119,8 @@ tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUt
             uint32_t it = 0;
             for (int tile = blockIdx.x; tile < total_tiles && !*abort_flag; tile += gridDim.x) {
                 int tm, tn;
-                tile_coords(tile, p.tiles_m, p.tiles_n, tm, tn);
+                const int bt = MODE == kModeGemm ? tile / tiles_per_batch : 0;
+                tile_coords(tile - bt * tiles_per_batch, p.tiles_m, p.tiles_n, tm, tn);
                 for (int kb = 0; kb < p.k_blocks; kb++, it++) {
                     const uint32_t s = it % kSt, ph = (it / kSt) & 1u;
                     if (!umma::mbar_wait(&empty[s], ph ^ 1u, abort_flag)) break;
@@ -134,6 +138,9 @@ tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUt
                         const int shift = kh * p.cv.dil_h * p.cv.Wp + kw * p.cv.dil_w;
                         umma::tma_load_2d(a_tile, &map_a, &full[s], cb * p.k_step, tm * kBM + shift);
                         umma::tma_load_3d(a_tile + kTileABytes, &map_b, &full[s], cb * p.k_step, tn * kBN, tap);
+                    } else if (p.batches > 1) {
+                        umma::tma_load_3d(a_tile, &map_a, &full[s], kb * p.k_step, tm * kBM, bt);
+                        umma::tma_load_3d(a_tile + kTileABytes, &map_b, &full[s], kb * p.k_step, tn * kBN, bt);
                     } else {
                         umma::tma_load_2d(a_tile, &map_a, &full[s], kb * p.k_step, tm * kBM);
                         umma::tma_load_2d(a_tile + kTileABytes, &map_b, &full[s], kb * p.k_step, tn * kBN);
@@ -184,7 +191,8 @@ tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUt
         for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x, local++) {
             const uint32_t buf = local & 1u, use = (local >> 1) & 1u;
             int tm, tn;
-            tile_coords(tile, p.tiles_m, p.tiles_n, tm, tn);
+            const int bt = MODE == kModeGemm ? tile / tiles_per_batch : 0;
+            tile_coords(tile - bt * tiles_per_batch, p.tiles_m, p.tiles_n, tm, tn);
             const int m = tm * kBM + quarter * 32 + lane;
             // beta * C for this tile, fetched while the tensor core is still working on it
             float row_bias = 0.0f;
@@ -410,7 +418,7 @@ tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUt
                         const int mr = tm * kBM + quarter * 32 + row;
                         if (mr >= p.M || n >= p.N) continue;
                         const uint4 val = *(const uint4*)(my_stage + row * kStageRowWords + piece * 4);
-                        char* dst = (char*)p.Y + ((size_t)mr * p.N + n) * esize;
+                        char* dst = (char*)p.Y + (((size_t)bt * p.M + mr) * p.N + n) * esize;
                         if (p.vec_store && n + elems_per_piece <= p.N) {
                             __stcs((uint4*)dst, val);
                         } else {

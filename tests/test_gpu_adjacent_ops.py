@@ -57,6 +57,16 @@ def test_clip(port, plan):
         assert_same_codes(gpu.clip(x, x_dt, nan, b_dt, hi, b_dt, out_dt), port.clip(x, x_dt, nan, b_dt, hi, b_dt, out_dt), out_dt)
 
 
+@pytest.mark.parametrize("x_dt", ["float32", "float16", "bfloat16"])
+def test_clip_same_type_with_scalar_bounds_of_any_type(port, x_dt):
+    rng = np.random.default_rng(zlib.crc32(x_dt.encode()))
+    for n in (1001, 4096, 7):
+        x = make(rng, (n,), x_dt)
+        for b_dt, lo, hi in (("float32", -0.75, 1.25), ("float16", -0.5, 0.5), ("int8", -1, 2), ("float64", -0.1, 0.3), ("float32", 0.0, -0.0)):
+            lo_, hi_ = from_f64(np.array([lo]), b_dt), from_f64(np.array([hi]), b_dt)
+            assert_same_codes(gpu.clip(x, x_dt, lo_, b_dt, hi_, b_dt, x_dt), port.clip(x, x_dt, lo_, b_dt, hi_, b_dt, x_dt), x_dt, f"{n} {b_dt}")
+
+
 @pytest.mark.parametrize("plan", [
     ("float32", "float32", (2, 3, 9, 8), (3, 3), (1, 1, 1, 1), (2, 2), (1, 1)),
     ("float16", "float16", (1, 4, 12, 12), (2, 2), (0, 0, 0, 0), (2, 2), (1, 1)),
@@ -76,7 +86,8 @@ def test_average_pool(port, plan, include_pad):
 
 @pytest.mark.parametrize("plan", [("float32", "float32", (4, 6, 7, 7)), ("float16", "float16", (2, 3, 5, 9)), ("int8", "float32", (1, 8, 4, 4)),
                                   ("bfloat16", "bfloat16", (3, 2, 1, 1)), ("float32", "int32", (2, 2, 3, 3)), ("float32", "float32", (16, 2048, 7, 7)),
-                                  ("float32", "float32", (2, 3, 112, 112))], ids=lambda p: f"{p[0]}-{p[1]}-{p[2]}")
+                                  ("float32", "float32", (2, 3, 112, 112)), ("float16", "float16", (2, 3, 20, 13)), ("bfloat16", "float32", (5, 7, 16, 8)),
+                                  ("float32", "float16", (1, 1, 129, 1))], ids=lambda p: f"{p[0]}-{p[1]}-{p[2]}")
 def test_global_average_pool(port, plan):
     x_dt, out_dt, xs = plan
     x = make(np.random.default_rng(31), xs, x_dt)
@@ -86,7 +97,9 @@ def test_global_average_pool(port, plan):
 @pytest.mark.parametrize("plan", [("float32", "float32", "float32", (3, 5, 6, 7)), ("float16", "float32", "float16", (2, 4, 5, 5)),
                                   ("bfloat16", "bfloat16", "float32", (1, 3, 8, 2)), ("float64", "float64", "float64", (2, 2, 3, 3)),
                                   ("float32", "float32", "float32", (4, 6)), ("int8", "float32", "float32", (2, 3, 4, 4)),
-                                  ("float32", "float32", "float32", (8, 64, 56, 56))], ids=lambda p: f"{p[0]}-{p[1]}-{p[2]}-{p[3]}")
+                                  ("float32", "float32", "float32", (8, 64, 56, 56)), ("float16", "float32", "float16", (2, 4, 8, 8)),
+                                  ("bfloat16", "bfloat16", "bfloat16", (2, 3, 4, 16)), ("float32", "float64", "float32", (1, 2, 4))],
+                         ids=lambda p: f"{p[0]}-{p[1]}-{p[2]}-{p[3]}")
 def test_batch_norm(port, plan):
     x_dt, p_dt, out_dt, xs = plan
     rng = np.random.default_rng(37)

@@ -68,7 +68,9 @@ def test_matmul_promotes_one_dimensional_operands(port):
 TC_PLANS = [  # a_dt, out_dt, a shape, b shape, tensor-core launches expected
     ("bfloat16", "float32", (256, 512), (512, 384), 1),
     ("float16", "float16", (4, 8, 128, 64), (64, 256), 1),                      # collapsed to 4096 rows
-    ("bfloat16", "bfloat16", (6, 130, 72), (6, 72, 200), 6),                     # one launch per batch, ragged tiles
+    ("bfloat16", "bfloat16", (6, 130, 72), (6, 72, 200), 1),                     # equal batches: one launch, ragged tiles
+    ("float16", "float32", (2, 5, 300, 64), (2, 5, 64, 136), 1),
+    ("float8_e5m2", "float16", (3, 64, 128), (3, 128, 96), 1),
     ("float8_e4m3", "float32", (2, 3, 64, 128), (1, 3, 128, 96), 6),
     ("bfloat16", "float32", (2, 1, 64, 64), (1, 3, 64, 128), 6),                 # mixed broadcasting
     ("float32", "float32", (2, 512, 1024), (2, 1024, 768), 2),                   # float32: three-way bfloat16 split
