@@ -356,6 +356,14 @@ typedef struct QConvCall {
 int tops_qconv_forward(const QConvCall* call);
 int tops_qconv_levels_shape(const int x_shape[4], const int kernel[2], const ConvParams* params, int levels_shape[4]);
 
+/* The two halves of dynamic_quantize_linear_forward (tensor_ops.c:3760-3809), for a tensor whose rows are
+   spread over several GPUs: each rank reduces its rows to range[0] = min, range[1] = max (float64[2] in
+   device memory; NaNs never win, an empty tensor leaves +Inf / -Inf), the ranks combine their ranges
+   (all-reduce with MIN / MAX), and each rank quantises its rows with the common range.  With one rank,
+   range followed by apply equals dynamic_quantize_linear_forward bit for bit.  Return the error code. */
+int tops_dynamic_quantize_range(const Tensor* x, Tensor* range);
+int tops_dynamic_quantize_apply(const Tensor* x, const Tensor* range, Tensor* y, Tensor* y_scale, Tensor* y_zp);
+
 /* Device-side exhaustive codec self-check: encodes every float32 bit pattern with the fast
    (hardware-convert) encoder and with the bit-level restatement of the reference encoder and
    returns the number of disagreements (NaN inputs excluded), or -1 on error. */

@@ -136,6 +136,8 @@ SIGNATURES = {
     "batch_norm_forward": (None, [_P, _P, _P, _P, _P, _P, ctypes.c_float]),
     "matmul_forward": (None, [_P, _P, _P]),
     "dynamic_quantize_linear_forward": (None, [_P, _P, _P, _P]),
+    "tops_dynamic_quantize_range": (ctypes.c_int, [_P, _P]),
+    "tops_dynamic_quantize_apply": (ctypes.c_int, [_P, _P, _P, _P, _P]),
     "tops_quantize_linear_axis_forward": (None, [_P, _P, _P, _P, _I]),
     "tops_dequantize_linear_axis_forward": (None, [_P, _P, _P, _P, _I]),
     "tops_conv2d_forward_noalloc": (None, [_P, _P, _P, _P, ctypes.POINTER(CConvParams)]),

@@ -162,12 +162,59 @@ __global__ void __launch_bounds__(kDqThreads) dynamic_quantize_generic(const voi
     }
 }
 
-template <int DX>
-static void dynamic_quantize_typed(const Tensor* x, Tensor* y, Tensor* y_scale, Tensor* y_zp, double* partials, int ctas, cudaStream_t s) {
-    constexpr int V = 16;                 // 16 codes = one 16-byte store; 64 (float32) or 32 bytes of x per thread and step
-    range_partials_kernel<DX, V><<<ctas, kDqThreads, 0, s>>>(x->data, x->size, partials);
-    dynamic_quantize_kernel<DX, V><<<ctas, kDqThreads, 0, s>>>(x->data, (uint8_t*)y->data, x->size, partials, ctas, y_scale->data, (int)y_scale->dtype,
-                                                               y_zp->data, (int)y_zp->dtype);
+// Folds the per-CTA pairs into range[0] = min, range[1] = max (no clamping to 0 yet: ranges of several
+// shards are combined first).
+__global__ void __launch_bounds__(kDqThreads) fold_partials_kernel(const double* __restrict__ partials, int n_partials, double* __restrict__ range) {
+    double lo = INFINITY, hi = -INFINITY;
+    for (int i = threadIdx.x; i < n_partials; i += kDqThreads) { lo = fmin(lo, partials[2 * i]); hi = fmax(hi, partials[2 * i + 1]); }
+    #pragma unroll
+    for (int o = 16; o; o >>= 1) { lo = fmin(lo, __shfl_xor_sync(0xFFFFFFFFu, lo, o)); hi = fmax(hi, __shfl_xor_sync(0xFFFFFFFFu, hi, o)); }
+    __shared__ double s_lo[kDqThreads / 32], s_hi[kDqThreads / 32];
+    if ((threadIdx.x & 31) == 0) { s_lo[threadIdx.x >> 5] = lo; s_hi[threadIdx.x >> 5] = hi; }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        for (int w = 1; w < kDqThreads / 32; w++) { lo = fmin(lo, s_lo[w]); hi = fmax(hi, s_hi[w]); }
+        range[0] = lo;
+        range[1] = hi;
+    }
+}
+
+static int dq_ctas(size_t n) {
+    const size_t per_cta = (size_t)kDqThreads * 16;
+    const size_t want = (n + per_cta - 1) / per_cta;
+    return (int)(want < 1 ? 1 : (want > (size_t)kDqMaxCtas ? (size_t)kDqMaxCtas : want));
+}
+
+static void launch_range(const Tensor* x, double* partials, int ctas, cudaStream_t s) {
+    const int dx = (int)x->dtype;
+    const bool aligned = ((uintptr_t)x->data & 15) == 0;
+    if (aligned && dx == DTYPE_FLOAT32) range_partials_kernel<DTYPE_FLOAT32, 16><<<ctas, kDqThreads, 0, s>>>(x->data, x->size, partials);
+    else if (aligned && dx == DTYPE_FLOAT16) range_partials_kernel<DTYPE_FLOAT16, 16><<<ctas, kDqThreads, 0, s>>>(x->data, x->size, partials);
+    else if (aligned && dx == DTYPE_BFLOAT16) range_partials_kernel<DTYPE_BFLOAT16, 16><<<ctas, kDqThreads, 0, s>>>(x->data, x->size, partials);
+    else range_partials_generic<<<ctas, kDqThreads, 0, s>>>(x->data, dx, x->size, partials);
+}
+
+static void launch_quantise(const Tensor* x, Tensor* y, Tensor* y_scale, Tensor* y_zp, const double* partials, int n_partials, int ctas, cudaStream_t s) {
+    const int dx = (int)x->dtype, dy = (int)y->dtype, ds = (int)y_scale->dtype, dz = (int)y_zp->dtype;
+    const bool fast = dy == DTYPE_UINT8 && (((uintptr_t)x->data | (uintptr_t)y->data) & 15) == 0;
+    if (fast && dx == DTYPE_FLOAT32) dynamic_quantize_kernel<DTYPE_FLOAT32, 16><<<ctas, kDqThreads, 0, s>>>(x->data, (uint8_t*)y->data, x->size, partials, n_partials, y_scale->data, ds, y_zp->data, dz);
+    else if (fast && dx == DTYPE_FLOAT16) dynamic_quantize_kernel<DTYPE_FLOAT16, 16><<<ctas, kDqThreads, 0, s>>>(x->data, (uint8_t*)y->data, x->size, partials, n_partials, y_scale->data, ds, y_zp->data, dz);
+    else if (fast && dx == DTYPE_BFLOAT16) dynamic_quantize_kernel<DTYPE_BFLOAT16, 16><<<ctas, kDqThreads, 0, s>>>(x->data, (uint8_t*)y->data, x->size, partials, n_partials, y_scale->data, ds, y_zp->data, dz);
+    else dynamic_quantize_generic<<<ctas, kDqThreads, 0, s>>>(x->data, dx, y->data, dy, x->size, partials, n_partials, y_scale->data, ds, y_zp->data, dz);
+}
+
+static bool dq_outputs_ok(const char* name, const Tensor* x, Tensor* y, Tensor* y_scale, Tensor* y_zp) {
+    if (!x || !y || !y_scale || !y_zp || !y_scale->data || !y_zp->data || (x->size && (!x->data || !y->data)) || x->size != y->size ||
+        y_scale->size < 1 || y_zp->size < 1) {
+        set_error(TOPS_ERR_INVALID, "%s: null tensor, size mismatch or empty scale / zero point", name);
+        zero_fill(y);
+        return false;
+    }
+    if (!dtype_valid((int)x->dtype) || !dtype_valid((int)y->dtype) || !dtype_valid((int)y_scale->dtype) || !dtype_valid((int)y_zp->dtype)) {
+        set_error(TOPS_ERR_INVALID, "%s: bad dtype", name);
+        return false;
+    }
+    return true;
 }
 
 }  // namespace tops
@@ -176,31 +223,52 @@ using namespace tops;
 
 TOPS_API void dynamic_quantize_linear_forward(const Tensor* x, Tensor* y, Tensor* y_scale, Tensor* y_zp) {
     const char* name = "dynamic_quantize_linear_forward";
-    if (!x || !y || !y_scale || !y_zp || !y_scale->data || !y_zp->data || (x->size && (!x->data || !y->data)) || x->size != y->size ||
-        y_scale->size < 1 || y_zp->size < 1) {
-        set_error(TOPS_ERR_INVALID, "%s: null tensor, size mismatch or empty scale / zero point", name);
-        zero_fill(y);
-        return;
-    }
-    const int dx = (int)x->dtype, dy = (int)y->dtype, ds = (int)y_scale->dtype, dz = (int)y_zp->dtype;
-    if (!dtype_valid(dx) || !dtype_valid(dy) || !dtype_valid(ds) || !dtype_valid(dz)) { set_error(TOPS_ERR_INVALID, "%s: bad dtype", name); return; }
+    if (!dq_outputs_ok(name, x, y, y_scale, y_zp)) return;
     DeviceState* st = acquire_device();
     if (!st) return;
     cudaStream_t s = current_stream();
-    const size_t per_cta = (size_t)kDqThreads * 16;
-    size_t want = (x->size + per_cta - 1) / per_cta;
-    const int ctas = (int)(want < 1 ? 1 : (want > (size_t)kDqMaxCtas ? (size_t)kDqMaxCtas : want));
+    const int ctas = dq_ctas(x->size);
     double* partials = nullptr;
     if (cudaMallocAsync((void**)&partials, sizeof(double) * 2 * (size_t)ctas, s) != cudaSuccess) { cudaGetLastError(); set_error(TOPS_ERR_OOM, "%s: scratch", name); return; }
-    const bool aligned = (((uintptr_t)x->data | (uintptr_t)y->data) & 15) == 0;
-    if (dy == DTYPE_UINT8 && aligned && dx == DTYPE_FLOAT32) dynamic_quantize_typed<DTYPE_FLOAT32>(x, y, y_scale, y_zp, partials, ctas, s);
-    else if (dy == DTYPE_UINT8 && aligned && dx == DTYPE_FLOAT16) dynamic_quantize_typed<DTYPE_FLOAT16>(x, y, y_scale, y_zp, partials, ctas, s);
-    else if (dy == DTYPE_UINT8 && aligned && dx == DTYPE_BFLOAT16) dynamic_quantize_typed<DTYPE_BFLOAT16>(x, y, y_scale, y_zp, partials, ctas, s);
-    else {
-        range_partials_generic<<<ctas, kDqThreads, 0, s>>>(x->data, dx, x->size, partials);
-        dynamic_quantize_generic<<<ctas, kDqThreads, 0, s>>>(x->data, dx, y->data, dy, x->size, partials, ctas, y_scale->data, ds, y_zp->data, dz);
-    }
+    launch_range(x, partials, ctas, s);
+    launch_quantise(x, y, y_scale, y_zp, partials, ctas, ctas, s);
     TOPS_CHECK_LAUNCH(name);
     cudaFreeAsync(partials, s);
     finish_op();
+}
+
+TOPS_API int tops_dynamic_quantize_range(const Tensor* x, Tensor* range) {
+    const char* name = "tops_dynamic_quantize_range";
+    if (!x || !range || !range->data || range->size < 2 || (int)range->dtype != DTYPE_FLOAT64 || (x->size && !x->data) || !dtype_valid((int)x->dtype)) {
+        set_error(TOPS_ERR_INVALID, "%s: wants a tensor and a float64 range of two elements", name);
+        return tops_last_error();
+    }
+    DeviceState* st = acquire_device();
+    if (!st) return tops_last_error();
+    cudaStream_t s = current_stream();
+    const int ctas = dq_ctas(x->size);
+    double* partials = nullptr;
+    if (cudaMallocAsync((void**)&partials, sizeof(double) * 2 * (size_t)ctas, s) != cudaSuccess) { cudaGetLastError(); set_error(TOPS_ERR_OOM, "%s: scratch", name); return tops_last_error(); }
+    launch_range(x, partials, ctas, s);
+    fold_partials_kernel<<<1, kDqThreads, 0, s>>>(partials, ctas, (double*)range->data);
+    TOPS_CHECK_LAUNCH(name);
+    cudaFreeAsync(partials, s);
+    finish_op();
+    return tops_last_error();
+}
+
+TOPS_API int tops_dynamic_quantize_apply(const Tensor* x, const Tensor* range, Tensor* y, Tensor* y_scale, Tensor* y_zp) {
+    const char* name = "tops_dynamic_quantize_apply";
+    if (!range || !range->data || range->size < 2 || (int)range->dtype != DTYPE_FLOAT64) {
+        set_error(TOPS_ERR_INVALID, "%s: wants a float64 range of two elements", name);
+        zero_fill(y);
+        return tops_last_error();
+    }
+    if (!dq_outputs_ok(name, x, y, y_scale, y_zp)) return tops_last_error();
+    DeviceState* st = acquire_device();
+    if (!st) return tops_last_error();
+    launch_quantise(x, y, y_scale, y_zp, (const double*)range->data, 1, dq_ctas(x->size), current_stream());
+    TOPS_CHECK_LAUNCH(name);
+    finish_op();
+    return tops_last_error();
 }

@@ -97,6 +97,54 @@ def gather_columns(local, total_cols: int, group=None):
     return full.numpy() if as_numpy else full
 
 
+def combine_ranges(value_range, group=None):
+    """DynamicQuantizeLinear over row blocks: every rank holds [min, max] of its own rows (a float64 torch
+    tensor on any device, or a numpy array); afterwards every rank holds the range of the whole tensor.
+    One all-reduce of two numbers -- the only exchange the operator needs, since scale and zero point follow
+    from the range and the codes from them (tensor_ops.c:3760-3809)."""
+    import torch
+    dist = _dist()
+    if not (dist.is_available() and dist.is_initialized()) or dist.get_world_size(group) == 1:
+        return value_range
+    as_numpy = isinstance(value_range, np.ndarray)
+    t = torch.from_numpy(np.ascontiguousarray(value_range, dtype=np.float64)) if as_numpy else value_range
+    both = torch.stack([-t[0], t[1]])                 # min(a, b) = -max(-a, -b): one MAX reduction serves both ends
+    dist.all_reduce(both, op=dist.ReduceOp.MAX, group=group)
+    if as_numpy:
+        return np.array([-float(both[0]), float(both[1])], dtype=np.float64)
+    t[0], t[1] = -both[0], both[1]
+    return t
+
+
+def dynamic_quantize_rows(x_rows, x_dtype: str, lib, group=None):
+    """DynamicQuantizeLinear of a tensor whose row blocks live on different GPUs.  ``x_rows`` is this rank's
+    block (a DeviceArray); returns (codes of the block, scale, zero point) as DeviceArrays -- scale and zero
+    point are identical on every rank.  The range buffer is a torch tensor so that the process group's backend
+    (NCCL) can reduce it in place; the library sees it through tops_wrap."""
+    import ctypes
+    import torch
+    from . import capi
+    from .device import DeviceArray
+    device = torch.device("cuda", torch.cuda.current_device())
+    value_range = torch.empty(2, dtype=torch.float64, device=device)
+    shape = (ctypes.c_int * 1)(2)
+    handle = lib.tops_wrap(ctypes.c_void_p(value_range.data_ptr()), shape, 1, capi.DTYPE_MAP["float64"])
+    try:
+        if lib.tops_dynamic_quantize_range(x_rows.handle, handle):
+            capi.check(lib)
+        lib.tops_sync()                               # the library's stream is not torch's
+        combine_ranges(value_range, group=group)
+        torch.cuda.synchronize(device)
+        y = DeviceArray.empty(x_rows.shape, "uint8", lib=lib)
+        scale, zero = DeviceArray.empty((1,), "float32", lib=lib), DeviceArray.empty((1,), "uint8", lib=lib)
+        if lib.tops_dynamic_quantize_apply(x_rows.handle, handle, y.handle, scale.handle, zero.handle):
+            capi.check(lib)
+        lib.tops_sync()
+    finally:
+        lib.free_tensor(handle)
+    return y, scale, zero
+
+
 def init_from_env(backend: Optional[str] = None):
     """Create the default process group from torchrun's environment (no-op for a single process).
     Returns (rank, world, local_rank)."""

@@ -303,6 +303,24 @@ class HostOracle:
         self._fn["dynamic_quantize"](xi.ref, yo.ref, so.ref, zo.ref)
         return yo.arr, so.arr, zo.arr
 
+    def dynamic_quantize_range(self, x, x_dt) -> np.ndarray:
+        """[min, max] of the elements as float64 (the restatement only: the reference has no such entry point)."""
+        xi = _Wrapped(x, x_dt)
+        out = np.zeros(2, np.float64)
+        fn = self.lib.orc_dynamic_quantize_range
+        fn.restype, fn.argtypes = None, [ctypes.c_void_p, ctypes.c_void_p]
+        fn(xi.ref, out.ctypes.data)
+        return out
+
+    def dynamic_quantize_apply(self, x, x_dt, value_range, y_dt="uint8", scale_dt="float32", zp_dt="uint8"):
+        xi = _Wrapped(x, x_dt)
+        rng = np.ascontiguousarray(value_range, dtype=np.float64)
+        yo, so, zo = _out(xi.arr.shape, y_dt), _out((1,), scale_dt), _out((1,), zp_dt)
+        fn = self.lib.orc_dynamic_quantize_apply
+        fn.restype, fn.argtypes = None, [ctypes.c_void_p] * 5
+        fn(xi.ref, rng.ctypes.data, yo.ref, so.ref, zo.ref)
+        return yo.arr, so.arr, zo.arr
+
     def softmax(self, x, x_dt, out_dt, axis=-1):
         xi = _Wrapped(x, x_dt)
         yo = _out(xi.arr.shape, out_dt)

@@ -758,16 +758,23 @@ ORC_API void orc_matmul(const OrcTensor* a, const OrcTensor* b, OrcTensor* y) {
    mapped onto 0..255: scale = (max - min) / 255 as a double (1 if that is 0), zero point = round-half-away(-min / scale)
    clamped to 0..255 and narrowed like a C cast, y = clamp(rint(x / scale) + zp, 0, 255) through the ordinary store.
    The division uses the DOUBLE scale; y_scale receives it rounded to its own type. */
-ORC_API void orc_dynamic_quantize_linear(const OrcTensor* x, OrcTensor* y, OrcTensor* y_scale, OrcTensor* y_zp) {
-    if (!x || !y || !y_scale || !y_zp) return;
+/* The range pass alone: range[0] = min, range[1] = max over the elements, started at +-DBL_MAX like the reference
+   (so an empty or all-NaN tensor leaves them there).  Ranges of row blocks combine with min / max. */
+ORC_API void orc_dynamic_quantize_range(const OrcTensor* x, double* range) {
     double lo = DBL_MAX, hi = -DBL_MAX;
-    for (size_t i = 0; i < x->size; i++) {
+    for (size_t i = 0; x && i < x->size; i++) {
         const double v = load_f64(x, i);
         if (v < lo) lo = v;
         if (v > hi) hi = v;
     }
-    lo = fmin(lo, 0.0);
-    hi = fmax(hi, 0.0);
+    range[0] = lo;
+    range[1] = hi;
+}
+
+/* Everything after the range pass. */
+ORC_API void orc_dynamic_quantize_apply(const OrcTensor* x, const double* range, OrcTensor* y, OrcTensor* y_scale, OrcTensor* y_zp) {
+    if (!x || !y || !y_scale || !y_zp) return;
+    const double lo = fmin(range[0], 0.0), hi = fmax(range[1], 0.0);
     double scale = (hi - lo) / 255.0;
     if (scale == 0.0) scale = 1.0;
     double zd = round(0.0 - lo / scale);
@@ -784,6 +791,13 @@ ORC_API void orc_dynamic_quantize_linear(const OrcTensor* x, OrcTensor* y, OrcTe
         if (q > 255.0) q = 255.0;
         store_f64(y, i, q);
     }
+}
+
+ORC_API void orc_dynamic_quantize_linear(const OrcTensor* x, OrcTensor* y, OrcTensor* y_scale, OrcTensor* y_zp) {
+    if (!x || !y || !y_scale || !y_zp) return;
+    double range[2];
+    orc_dynamic_quantize_range(x, range);
+    orc_dynamic_quantize_apply(x, range, y, y_scale, y_zp);
 }
 
 /* Flatten / Reshape: a byte copy.  tensor_ops.c:1289-1299 */

@@ -126,3 +126,37 @@ def test_dynamic_quantize_linear_large_tensor_properties():
     assert y[3, 17] == zero[0] and y.min() == 0 and y.max() == 255
     back = (y.astype(np.float64) - float(zero[0])) * ((hi - lo) / 255.0)
     assert np.abs(back - x).max() <= 0.5 * (hi - lo) / 255.0 * (1 + 1e-6) + abs(lo / ((hi - lo) / 255.0) + float(zero[0])) * (hi - lo) / 255.0
+
+
+@pytest.mark.parametrize("x_dt", ["float32", "float16", "int32"])
+def test_dynamic_quantize_range_and_apply_equal_the_single_call(port, x_dt):
+    """The split entry points used when the rows of a tensor live on several GPUs: on one GPU, two row blocks
+    with their ranges combined on the host must give the codes, scale and zero point of the single call."""
+    import ctypes
+    from onnx_translator_b200 import capi
+    from onnx_translator_b200.device import DeviceArray
+    lib = capi.load()
+    rng = np.random.default_rng(zlib.crc32(x_dt.encode()) + 1)
+    x = make(rng, (37, 1000), x_dt)
+    if x_dt == "float32":
+        x[3, 5], x[30, 7] = np.nan, np.nan
+    want = port.dynamic_quantize_linear(x, x_dt)
+    blocks = [DeviceArray.from_numpy(np.ascontiguousarray(b), x_dt) for b in (x[:20], x[20:])]
+    ranges = [DeviceArray.empty((2,), "float64") for _ in blocks]
+    for b, r in zip(blocks, ranges):
+        assert lib.tops_dynamic_quantize_range(b.handle, r.handle) == 0
+    host = [r.numpy() for r in ranges]
+    for h, b in zip(host, (x[:20], x[20:])):
+        assert np.array_equal(h, port.dynamic_quantize_range(b, x_dt))
+    common = DeviceArray.from_numpy(np.array([min(host[0][0], host[1][0]), max(host[0][1], host[1][1])]), "float64")
+    codes = []
+    for b in blocks:
+        y, s, z = DeviceArray.empty(b.shape, "uint8"), DeviceArray.empty((1,), "float32"), DeviceArray.empty((1,), "uint8")
+        assert lib.tops_dynamic_quantize_apply(b.handle, common.handle, y.handle, s.handle, z.handle) == 0
+        codes.append(y.numpy())
+        assert_same_codes(s.numpy(), want[1], "float32")
+        assert_same_codes(z.numpy(), want[2], "uint8")
+    assert_same_codes(np.concatenate(codes), want[0], "uint8")
+    bad = DeviceArray.empty((2,), "float32")
+    assert lib.tops_dynamic_quantize_range(blocks[0].handle, bad.handle) != 0
+    lib.tops_clear_error()

@@ -415,3 +415,21 @@ def test_dynamic_quantize_linear(port, ref, x_dt):
     got, want = port.dynamic_quantize_linear(x, x_dt, "int16", "float64", "int32"), ref.dynamic_quantize_linear(x, x_dt, "int16", "float64", "int32")
     for g, w, dt in zip(got, want, ("int16", "float64", "int32")):
         assert_same_codes(g, w, dt)
+
+
+def test_dynamic_quantize_halves_equal_the_whole(port, ref):
+    """Range + apply (the split used when the rows live on several GPUs) reproduce the reference's single call."""
+    rng = np.random.default_rng(77)
+    for x_dt in ("float32", "float16", "int8"):
+        x = make(rng, (13, 21), x_dt)
+        want = ref.dynamic_quantize_linear(x, x_dt)
+        got = port.dynamic_quantize_apply(x, x_dt, port.dynamic_quantize_range(x, x_dt))
+        for g, w, dt in zip(got, want, ("uint8", "float32", "uint8")):
+            assert_same_codes(g, w, dt)
+        # two row blocks, ranges combined
+        r0, r1 = port.dynamic_quantize_range(x[:6], x_dt), port.dynamic_quantize_range(x[6:], x_dt)
+        both = np.array([min(r0[0], r1[0]), max(r0[1], r1[1])])
+        y0, y1 = port.dynamic_quantize_apply(x[:6], x_dt, both), port.dynamic_quantize_apply(x[6:], x_dt, both)
+        assert_same_codes(np.concatenate([y0[0], y1[0]]), want[0], "uint8")
+        assert_same_codes(y0[1], want[1], "float32")
+        assert_same_codes(y1[2], want[2], "uint8")

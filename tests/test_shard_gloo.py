@@ -54,7 +54,19 @@ def _worker(rank, world, port, ret):
         bb, cb, (n0, n1) = shard.gemm_shard(gb, gc, world, rank)
         mineg = port_lib.gemm(ga, "float32", bb, "float32", cb, "float32", "float32", 1.0, 1.0, 0, 1)
         ok_gemm = mineg.shape == (6, n1 - n0) and np.array_equal(shard.gather_columns(mineg, 9), fullg)
-        ret[rank] = (ok_add, ok_q, ok_bf16, ok_conv, ok_gemm)
+        # DynamicQuantizeLinear: the one operator with an exchange -- ranges of the row blocks are combined
+        # (all-reduce of two numbers), then every rank quantises its block with the common range
+        dx = rng.normal(0.2, 1.5, (11, 40)).astype(np.float32)
+        dx[2, 7], dx[9, 1] = 9.5, -7.25                       # the extremes sit in different blocks
+        dx[0, 3], dx[8, 3] = np.nan, np.nan                   # NaNs never enter the range
+        full_y, full_s, full_z = port_lib.dynamic_quantize_linear(dx, "float32")
+        block = shard.split_rows(dx, world, rank)
+        local = port_lib.dynamic_quantize_range(block, "float32")
+        common = shard.combine_ranges(local.copy())
+        my_y, my_s, my_z = port_lib.dynamic_quantize_apply(block, "float32", common)
+        ok_dq = (np.array_equal(shard.gather_rows(my_y, 11), full_y) and my_s.tobytes() == full_s.tobytes() and
+                 np.array_equal(my_z, full_z) and not np.array_equal(local, common))
+        ret[rank] = (ok_add, ok_q, ok_bf16, ok_conv, ok_gemm, ok_dq)
     finally:
         dist.destroy_process_group()
 
@@ -71,7 +83,7 @@ def test_two_ranks_reproduce_the_single_process_result():
     for p in procs:
         p.join(timeout=180)
         assert p.exitcode == 0
-    assert dict(ret) == {0: (True,) * 5, 1: (True,) * 5}
+    assert dict(ret) == {0: (True,) * 6, 1: (True,) * 6}
 
 
 def test_row_range_covers_everything_once():
