@@ -90,6 +90,40 @@ def main():
         fn = getattr(lib, args.op + "_forward")
         call = lambda: fn(a.handle, o.handle)
         nbytes = a.size * (ITEM[dt] + ITEM[out_dt])
+    elif args.op in ("exp", "log", "sqrt", "sigmoid", "tanh", "neg", "reciprocal", "ceil", "floor", "sin", "tan", "atan", "softplus", "softsign",
+                     "hard_swish", "acos", "asin", "cosh", "sinh", "asinh", "acosh", "atanh", "round", "erf", "gelu", "cast"):
+        shape = (args.rows, 512, 1024)
+        a = DeviceArray.from_numpy(_rand(rng, shape, dt, -3, 3), dt)
+        o = DeviceArray.empty(shape, out_dt)
+        fn = getattr(lib, args.op + "_forward")
+        call = lambda: fn(a.handle, o.handle)
+        nbytes = a.size * (ITEM[dt] + ITEM[out_dt])
+    elif args.op == "dynamic_quantize":
+        # range pass + quantise pass over float32 [rows, 8192]: x read twice, uint8 codes written once
+        shape = (args.rows, 8192)
+        x = DeviceArray.from_numpy(rng.standard_normal(shape).astype(np.float32), "float32")
+        o = DeviceArray.empty(shape, "uint8")
+        sc, zp = DeviceArray.empty((1,), "float32"), DeviceArray.empty((1,), "uint8")
+        call = lambda: lib.dynamic_quantize_linear_forward(x.handle, o.handle, sc.handle, zp.handle)
+        nbytes = x.size * 9
+        dt, out_dt = "float32", "uint8"
+    elif args.op == "batch_norm":
+        shape = (args.batch, args.channels, args.hw, args.hw)
+        x = DeviceArray.from_numpy(rng.standard_normal(shape).astype(np.float32), "float32")
+        o = DeviceArray.empty(shape, "float32")
+        ps = [DeviceArray.from_numpy(v.astype(np.float32), "float32") for v in (rng.normal(1, 0.1, args.channels), rng.normal(0, 0.1, args.channels),
+                                                                                rng.normal(0, 0.1, args.channels), rng.uniform(0.5, 2, args.channels))]
+        keep = ps
+        call = lambda: lib.batch_norm_forward(x.handle, ps[0].handle, ps[1].handle, ps[2].handle, ps[3].handle, o.handle, ctypes.c_float(1e-5))
+        nbytes = x.size * 8
+        dt = out_dt = "float32"
+    elif args.op == "global_average_pool":
+        shape = (args.batch, args.channels, args.hw, args.hw)
+        x = DeviceArray.from_numpy(rng.standard_normal(shape).astype(np.float32), "float32")
+        o = DeviceArray.empty(shape[:2] + (1, 1), "float32")
+        call = lambda: lib.global_average_pool_forward(x.handle, o.handle)
+        nbytes = x.size * 4
+        dt = out_dt = "float32"
     elif args.op in ("quantize", "dequantize"):
         shape = (args.rows, 8192)
         if args.op == "quantize":
