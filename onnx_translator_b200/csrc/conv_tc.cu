@@ -217,10 +217,10 @@ bool shifted_gemm_launch(const ShiftedGemm& g) {
     do {                                                                                                                     \
         static bool attr = false;                                                                                            \
         if (!attr) {                                                                                                         \
-            cudaFuncSetAttribute(tc_kernel<F8, kModeConv, E>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)tc_smem_bytes(kModeConv)); \
+            cudaFuncSetAttribute(tc_kernel<F8, kModeConv, E>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)tc_smem_bytes(kModeConv, E)); \
             attr = true;                                                                                                     \
         }                                                                                                                    \
-        tc_kernel<F8, kModeConv, E><<<grid, tc_threads(kModeConv), tc_smem_bytes(kModeConv), s>>>(map_a, map_b, p, idesc);   \
+        tc_kernel<F8, kModeConv, E><<<grid, tc_threads(kModeConv, E), tc_smem_bytes(kModeConv, E), s>>>(map_a, map_b, p, idesc);   \
     } while (0)
     if (g.fp8) TOPS_CONV_LAUNCH(true, kEpiPlain);
     else if (epi == kEpiPlain) TOPS_CONV_LAUNCH(false, kEpiPlain);

@@ -15,18 +15,21 @@ constexpr int kTileBBytes = kBN * kRowBytes;       // 32 KB
 constexpr int kStageBytes = kTileABytes + kTileBBytes;
 constexpr int kStageRowWords = 36;                 // 32 words of payload + 4 of padding: conflict-free 16-byte accesses
 
-// Per mode: the convolution's K loops are short and its epilogue (strided NCHW stores, optional
-// residual loads) is what bounds it, so it trades one pipeline stage for a second set of four
-// epilogue warps -- twice as many loads and stores in flight per SM.  A warp may only read the
-// quarter of tensor memory given by its index modulo 4, so warps w and w + 4 share a quarter and
-// take alternate 32-column chunks.
+// Per mode: the convolution's K loops are short and its epilogue is what bounds it, so it trades one pipeline
+// stage for more epilogue warps -- more loads and stores in flight per SM.  A warp may only read the quarter of
+// tensor memory given by its index modulo 4, so the warps that share a quarter take alternate column chunks.
 constexpr int kModeGemm = 0, kModeConv = 1, kModeSplit = 2;
 __host__ __device__ constexpr int tc_stages(int mode) { return mode == kModeConv ? 3 : kStages; }
-__host__ __device__ constexpr int tc_epilogue_warps(int mode) { return mode == kModeConv ? 8 : 4; }
-__host__ __device__ constexpr int tc_threads(int mode) { return 64 + 32 * tc_epilogue_warps(mode); }
-__host__ __device__ constexpr size_t tc_smem_bytes(int mode) {
+// Epilogue warps: 4 for the Gemm modes.  Convolution mode is bound by its epilogue (short K loops, strided NCHW
+// stores, residual loads, quantisation to levels), so it handles 16 accumulator columns at a time -- half the
+// registers per thread -- and runs 16 epilogue warps, or 12 where the residual is compiled in (its prefetch
+// registers do not fit the 96-register budget of 18 warps without spilling; measured slower).
+__host__ __device__ constexpr int tc_epilogue_warps(int mode, int epi = 0) { return mode != kModeConv ? 4 : ((epi & 1) ? 12 : 16); }
+__host__ __device__ constexpr int tc_chunk_columns(int mode) { return mode == kModeConv ? 16 : 32; }
+__host__ __device__ constexpr int tc_threads(int mode, int epi = 0) { return 64 + 32 * tc_epilogue_warps(mode, epi); }
+__host__ __device__ constexpr size_t tc_smem_bytes(int mode, int epi = 0) {
     return (size_t)tc_stages(mode) * kStageBytes + 1024 /*alignment slack*/ + 128 /*barriers*/ +
-           (size_t)tc_epilogue_warps(mode) * kBN * 4 /*bias*/ + (size_t)tc_epilogue_warps(mode) * kBN * 4 /*column scales*/ +
+           (size_t)tc_epilogue_warps(mode, epi) * kBN * 4 /*bias*/ + (size_t)tc_epilogue_warps(mode, epi) * kBN * 4 /*column scales*/ +
            (mode == kModeConv ? 0 : 4 * 32 * kStageRowWords * 4) /*output staging (row-major outputs only)*/;
 }
 
@@ -79,10 +82,10 @@ __device__ __forceinline__ void tile_coords(int tile, int tiles_m, int tiles_n, 
 constexpr int kEpiPlain = 0, kEpiResidual = 1, kEpiLevels = 2;
 
 template <bool FP8, int MODE, int EPI = kEpiPlain>
-__global__ void __launch_bounds__(tc_threads(MODE), 1)
+__global__ void __launch_bounds__(tc_threads(MODE, EPI), 1)
 tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, const TcParams p,
                const uint32_t idesc) {
-    constexpr int kSt = tc_stages(MODE), kEpi = tc_epilogue_warps(MODE);
+    constexpr int kSt = tc_stages(MODE), kEpi = tc_epilogue_warps(MODE, EPI);
     extern __shared__ uint8_t smem_raw[];
     uint8_t* tiles = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
     uint64_t* bars = (uint64_t*)(tiles + (size_t)kSt * kStageBytes);
@@ -177,6 +180,7 @@ tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUt
         const int quarter = warp & 3;                               // TMEM lanes this warp may read
         const int epi = warp - 2;                                   // 0 .. kEpi-1
         constexpr int kChunkStep = kEpi / 4;                        // warps that share a quarter alternate chunks
+        constexpr int kW = tc_chunk_columns(MODE);                  // accumulator columns a warp handles at a time
         const int first_chunk = epi >> 2;
         uint32_t local = 0;
         float* my_bias = bias_stage + epi * kBN;                     // this warp's private copy: no cross-warp sync
@@ -224,7 +228,7 @@ tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUt
             // of the first column chunk, requested before the accumulator is even complete
             bool conv_row = false;
             size_t conv_base = 0, plane_out = 0;
-            float res_next[32];
+            float res_next[kW];
             constexpr bool with_res = MODE == kModeConv && (EPI & kEpiResidual) != 0;
             if constexpr (MODE == kModeConv) {
                 const int img = m / p.cv.plane, rem = m - img * p.cv.plane;
@@ -233,73 +237,73 @@ tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUt
                 plane_out = (size_t)p.cv.OH * p.cv.OW;
                 conv_base = ((size_t)img * p.cv.OC + (size_t)tn * kBN) * plane_out + (size_t)oh * p.cv.OW + ow;
             }
-            auto fetch_residual = [&](int chunk, float (&dst)[32]) {
-                const float* src = p.residual + conv_base + (size_t)(chunk * 32) * plane_out;
+            auto fetch_residual = [&](int chunk, float (&dst)[kW]) {
+                const float* src = p.residual + conv_base + (size_t)(chunk * kW) * plane_out;
                 #pragma unroll
-                for (int j = 0; j < 32; j++)
-                    dst[j] = (conv_row && tn * kBN + chunk * 32 + j < p.N) ? __ldg(src + (size_t)j * plane_out) : 0.0f;
+                for (int j = 0; j < kW; j++)
+                    dst[j] = (conv_row && tn * kBN + chunk * kW + j < p.N) ? __ldg(src + (size_t)j * plane_out) : 0.0f;
             };
             if constexpr (with_res) fetch_residual(first_chunk, res_next);
             if (!umma::mbar_wait(&acc_full[buf], use, abort_flag)) break;
             umma::fence_after_sync();
             const uint32_t t_row = tmem_base + ((uint32_t)(quarter * 32) << 16) + buf * kBN;
             #pragma unroll 1
-            for (int c = first_chunk; c < kBN / 32; c += kChunkStep) {
-                const int n0 = tn * kBN + c * 32;
+            for (int c = first_chunk; c < kBN / kW; c += kChunkStep) {
+                const int n0 = tn * kBN + c * kW;
                 if (n0 >= p.N) break;                              // warp-uniform: no columns left in this tile
-                float res_cur[32];
+                float res_cur[kW];
                 if constexpr (with_res) {                          // the next chunk's values travel while this one is processed
                     #pragma unroll
-                    for (int j = 0; j < 32; j++) res_cur[j] = res_next[j];
-                    if (n0 + 32 * kChunkStep < p.N && c + kChunkStep < kBN / 32) fetch_residual(c + kChunkStep, res_next);
+                    for (int j = 0; j < kW; j++) res_cur[j] = res_next[j];
+                    if (n0 + kW * kChunkStep < p.N && c + kChunkStep < kBN / kW) fetch_residual(c + kChunkStep, res_next);
                 }
-                uint32_t r[32];
-                umma::tmem_load_32x32(t_row + (uint32_t)(c * 32), r);
+                uint32_t r[kW];
+                umma::tmem_load_chunk<kW>(t_row + (uint32_t)(c * kW), r);
                 umma::tmem_load_wait();
                 {
-                    float v[32];
+                    float v[kW];
                     #pragma unroll
-                    for (int j = 0; j < 32; j++) {
-                        const float scale = p.fs.b_per_column ? my_scale[c * 32 + j] : alpha;
+                    for (int j = 0; j < kW; j++) {
+                        const float scale = p.fs.b_per_column ? my_scale[c * kW + j] : alpha;
                         v[j] = __fadd_rn(__fmul_rn(scale, __uint_as_float(r[j])), row_bias);
                     }
                     if (p.bias.mode == kBiasPerColumn) {
                         #pragma unroll
-                        for (int j = 0; j < 32; j += 4) {
-                            const float4 b4 = *(const float4*)(my_bias + c * 32 + j);
+                        for (int j = 0; j < kW; j += 4) {
+                            const float4 b4 = *(const float4*)(my_bias + c * kW + j);
                             v[j] = __fadd_rn(v[j], b4.x); v[j + 1] = __fadd_rn(v[j + 1], b4.y);
                             v[j + 2] = __fadd_rn(v[j + 2], b4.z); v[j + 3] = __fadd_rn(v[j + 3], b4.w);
                         }
                     } else if (p.bias.mode == kBiasMatrix && m < p.M) {
-                        float cv[32];
+                        float cv[kW];
                         if (p.bias.dtype == DTYPE_FLOAT32) {            // independent loads, issued back to back
                             #pragma unroll
-                            for (int j = 0; j < 32; j++) {
+                            for (int j = 0; j < kW; j++) {
                                 const long long ci = (n0 + j < p.N) ? bias_index(p.bias, m, n0 + j) : -1;
                                 cv[j] = ci >= 0 ? __ldg((const float*)p.bias.ptr + ci) : 0.0f;
                             }
                         } else {
                             #pragma unroll
-                            for (int j = 0; j < 32; j++) {
+                            for (int j = 0; j < kW; j++) {
                                 const long long ci = (n0 + j < p.N) ? bias_index(p.bias, m, n0 + j) : -1;
                                 cv[j] = ci >= 0 ? (float)load_f64_rt(p.bias.ptr, p.bias.dtype, (size_t)ci) : 0.0f;
                             }
                         }
                         #pragma unroll
-                        for (int j = 0; j < 32; j++) v[j] = __fmaf_rn(p.beta, cv[j], v[j]);
+                        for (int j = 0; j < kW; j++) v[j] = __fmaf_rn(p.beta, cv[j], v[j]);
                     }
                     if (p.relu && !with_res) {
                         #pragma unroll
-                        for (int j = 0; j < 32; j++) v[j] = v[j] > 0.0f ? v[j] : 0.0f;
+                        for (int j = 0; j < kW; j++) v[j] = v[j] > 0.0f ? v[j] : 0.0f;
                     }
                     if constexpr (MODE == kModeConv) {
                         // NCHW output: for one output channel, consecutive lanes (consecutive padded
                         // positions) are consecutive pixels, so each store instruction is contiguous.
                         if (conv_row) {
-                            const size_t base = conv_base + (size_t)(c * 32) * plane_out;
+                            const size_t base = conv_base + (size_t)(c * kW) * plane_out;
                             if constexpr (with_res) {                  // Add(conv, residual) [-> Relu], as separate float32 operators would round
                                 #pragma unroll
-                                for (int j = 0; j < 32; j++) {
+                                for (int j = 0; j < kW; j++) {
                                     v[j] = __fadd_rn(v[j], res_cur[j]);
                                     if (p.relu) v[j] = v[j] > 0.0f ? v[j] : 0.0f;
                                 }
@@ -319,9 +323,9 @@ tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUt
                                 // closer than 2^-19 |q|, which also catches |q| >= 2^18 and NaN -- is redone with the
                                 // reference's double division
                                 const float lo = p.lv.zero_signed ? -128.0f : 0.0f, hi = p.lv.zero_signed ? 127.0f : 255.0f;
-                                uint32_t packed[16];
+                                uint32_t packed[kW / 2];
                                 #pragma unroll
-                                for (int j0 = 0; j0 < 32; j0 += 8) {
+                                for (int j0 = 0; j0 < kW; j0 += 8) {
                                     float level[8];
                                     bool decided = true;
                                     #pragma unroll
@@ -341,13 +345,13 @@ tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUt
                                     for (int e = 0; e < 8; e += 2)
                                         packed[(j0 + e) >> 1] = __byte_perm(__float_as_uint(level[e]), __float_as_uint(level[e + 1]), 0x7632);
                                 }
-                                if (n0 + 32 <= p.N) {                  // 64 contiguous bytes of this pixel's channels
+                                if (n0 + kW <= p.N) {                  // kW contiguous channels of this pixel
                                     #pragma unroll
-                                    for (int q4 = 0; q4 < 4; q4++)
+                                    for (int q4 = 0; q4 < kW / 8; q4++)
                                         *reinterpret_cast<uint4*>(zdst + 8 * q4) = make_uint4(packed[4 * q4], packed[4 * q4 + 1], packed[4 * q4 + 2], packed[4 * q4 + 3]);
                                 } else {
                                     #pragma unroll
-                                    for (int j = 0; j < 32; j++) if (n0 + j < p.N) zdst[j] = (uint16_t)(packed[j >> 1] >> ((j & 1) * 16));
+                                    for (int j = 0; j < kW; j++) if (n0 + j < p.N) zdst[j] = (uint16_t)(packed[j >> 1] >> ((j & 1) * 16));
                                 }
                             }
                             if (p.Y == nullptr) {
@@ -355,19 +359,19 @@ tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUt
                             } else if (p.dy == DTYPE_FLOAT32) {
                                 float* dst = (float*)p.Y + base;
                                 #pragma unroll
-                                for (int j = 0; j < 32; j++) if (n0 + j < p.N) dst[(size_t)j * plane_out] = v[j];
+                                for (int j = 0; j < kW; j++) if (n0 + j < p.N) dst[(size_t)j * plane_out] = v[j];
                             } else if (p.dy == DTYPE_BFLOAT16) {
                                 uint16_t* dst = (uint16_t*)p.Y + base;
                                 #pragma unroll
-                                for (int j = 0; j < 32; j++) if (n0 + j < p.N) dst[(size_t)j * plane_out] = encode_bf16(v[j]);
+                                for (int j = 0; j < kW; j++) if (n0 + j < p.N) dst[(size_t)j * plane_out] = encode_bf16(v[j]);
                             } else {
                                 uint16_t* dst = (uint16_t*)p.Y + base;
                                 #pragma unroll
-                                for (int j = 0; j < 32; j++) if (n0 + j < p.N) dst[(size_t)j * plane_out] = encode_f16(v[j]);
+                                for (int j = 0; j < kW; j++) if (n0 + j < p.N) dst[(size_t)j * plane_out] = encode_f16(v[j]);
                             }
                         }
-                        continue;
                     }
+                    if constexpr (MODE != kModeConv) {
                     // Stage this warp's 32 x 32 chunk (already in output format) in shared memory,
                     // then write it out with every store instruction covering whole 128-byte lines.
                     uint32_t* my_rows = my_stage + lane * kStageRowWords;
@@ -431,6 +435,7 @@ tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUt
                         }
                     }
                     __syncwarp();
+                    }
                 }
             }
             umma::fence_before_sync();
