@@ -178,7 +178,10 @@ bool shifted_gemm_launch(const ShiftedGemm& g) {
     const uint32_t box_a[2] = {(uint32_t)k_step, (uint32_t)kBM};
     const uint64_t dims_b[3] = {(uint64_t)g.C, (uint64_t)g.M, (uint64_t)taps};
     const uint64_t strides_b[2] = {(uint64_t)g.C * es, (uint64_t)g.M * g.C * es};
-    const uint32_t box_b[3] = {(uint32_t)k_step, (uint32_t)kBN, 1u};
+    // With at most one column block of filters the box (and the instruction, below) covers only the rows that
+    // exist, rounded up to 16: rows beyond them would be zero-filled by the copy engine at the cost of real rows.
+    const int n_cols = g.M <= kBN ? ((g.M + 15) / 16) * 16 : kBN;
+    const uint32_t box_b[3] = {(uint32_t)k_step, (uint32_t)n_cols, 1u};
     const bool f16 = !g.fp8 && g.a_format == 0u;
     if (!make_tensor_map(&map_a, g.xp, es, g.fp8, f16, 2, dims_a, strides_a, box_a, nullptr) ||
         !make_tensor_map(&map_b, g.wt, es, g.fp8, f16, 3, dims_b, strides_b, box_b, nullptr))
@@ -208,7 +211,8 @@ bool shifted_gemm_launch(const ShiftedGemm& g) {
     p.relu = g.relu;
     p.residual = g.residual;
     p.lv = g.lv;
-    const uint32_t idesc = umma::instr_desc(g.a_format, g.b_format, kBM, kBN);
+    p.stage_tx = (uint32_t)(kTileABytes + n_cols * kRowBytes);
+    const uint32_t idesc = umma::instr_desc(g.a_format, g.b_format, kBM, (uint32_t)n_cols);
     const int tiles = p.tiles_m * p.tiles_n;
     const int grid = tiles < st->sm_count ? tiles : st->sm_count;
     const int epi = (g.residual ? kEpiResidual : 0) | (g.lv.z ? kEpiLevels : 0);

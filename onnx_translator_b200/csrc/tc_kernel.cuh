@@ -55,6 +55,7 @@ struct TcParams {
     BiasView bias;
     int* status;           // device-visible word, set non-zero when a wait gave up
     int vec_store;         // Y base and row pitch are 16-byte aligned
+    uint32_t stage_tx = kStageBytes;   // bytes the two copies of a pipeline stage deliver (less when the B box is narrower than kBN)
     int batches = 1;       // Gemm mode: independent problems of one shape; the tensor maps are then 3-D
                            // (K, rows, batch) and Y holds the results back to back
     ConvView cv;           // convolution mode only
@@ -86,6 +87,10 @@ __global__ void __launch_bounds__(tc_threads(MODE, EPI), 1)
 tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, const TcParams p,
                const uint32_t idesc) {
     constexpr int kSt = tc_stages(MODE), kEpi = tc_epilogue_warps(MODE, EPI);
+    // Sixteen epilogue warps work as two groups of eight, one per accumulator buffer: consecutive tiles of the CTA
+    // are finished by different groups, so the latency chain of one tile's epilogue (accumulator ready -> tensor
+    // memory load -> arithmetic -> stores) overlaps the next tile's instead of following it.
+    constexpr int kEpiGroups = kEpi >= 16 ? 2 : 1, kEpiG = kEpi / kEpiGroups;
     extern __shared__ uint8_t smem_raw[];
     uint8_t* tiles = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
     uint64_t* bars = (uint64_t*)(tiles + (size_t)kSt * kStageBytes);
@@ -105,7 +110,7 @@ tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUt
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < kSt; s++) { umma::mbar_init(&full[s], 1); umma::mbar_init(&empty[s], 1); }
-        for (int b = 0; b < 2; b++) { umma::mbar_init(&acc_full[b], 1); umma::mbar_init(&acc_empty[b], kEpi); }
+        for (int b = 0; b < 2; b++) { umma::mbar_init(&acc_full[b], 1); umma::mbar_init(&acc_empty[b], kEpiG); }
         *abort_flag = 0;
         umma::mbar_fence_init();
         umma::tma_prefetch_desc(&map_a);
@@ -128,7 +133,7 @@ tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUt
                     const uint32_t s = it % kSt, ph = (it / kSt) & 1u;
                     if (!umma::mbar_wait(&empty[s], ph ^ 1u, abort_flag)) break;
                     uint8_t* a_tile = tiles + (size_t)s * kStageBytes;
-                    umma::mbar_expect_tx(&full[s], kStageBytes);
+                    umma::mbar_expect_tx(&full[s], p.stage_tx);
                     if constexpr (MODE == kModeSplit) {
                         // smallest products first: (a3 b1) (a2 b2) (a1 b3) (a2 b1) (a1 b2) (a1 b1)
                         const int seg = kb / p.cv.c_blocks, cb = kb - seg * p.cv.c_blocks;
@@ -179,9 +184,10 @@ tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUt
     } else {
         const int quarter = warp & 3;                               // TMEM lanes this warp may read
         const int epi = warp - 2;                                   // 0 .. kEpi-1
-        constexpr int kChunkStep = kEpi / 4;                        // warps that share a quarter alternate chunks
+        const int group = epi / kEpiG, eg = epi - group * kEpiG;     // group: which accumulator buffer's tiles this warp finishes
+        constexpr int kChunkStep = kEpiG / 4;                       // warps of a group that share a quarter alternate chunks
         constexpr int kW = tc_chunk_columns(MODE);                  // accumulator columns a warp handles at a time
-        const int first_chunk = epi >> 2;
+        const int first_chunk = eg >> 2;
         uint32_t local = 0;
         float* my_bias = bias_stage + epi * kBN;                     // this warp's private copy: no cross-warp sync
         uint32_t* my_stage = out_stage + quarter * 32 * kStageRowWords;
@@ -192,8 +198,17 @@ tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUt
         if (p.fs.b_scale && !p.fs.b_per_column) alpha = __fmul_rn(alpha, __ldg(p.fs.b_scale));
         const float y_scale = p.fs.y_scale ? __ldg(p.fs.y_scale) : 0.0f;
         const float y_inv = y_scale != 0.0f ? __frcp_rn(y_scale) : 0.0f;     // y / s as y * (1 / s): off by an ulp at most, like the accumulation itself
+        // scale and zero point of the levels output: fetched once, not once per column chunk (each fetch is a
+        // dependent global load in front of the chunk's arithmetic)
+        float lv_scale = 0.0f, lv_inv = 0.0f, lv_zero = 0.0f;
+        if constexpr (MODE == kModeConv && (EPI & kEpiLevels) != 0) {
+            lv_scale = __ldg(p.lv.scale);
+            lv_inv = quantize_reciprocal(lv_scale);
+            if (p.lv.zero) lv_zero = p.lv.zero_signed ? (float)*(const int8_t*)p.lv.zero : (float)*(const uint8_t*)p.lv.zero;
+        }
         for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x, local++) {
             const uint32_t buf = local & 1u, use = (local >> 1) & 1u;
+            if (kEpiGroups == 2 && (int)buf != group) continue;      // the other group's tile
             int tm, tn;
             const int bt = MODE == kModeGemm ? tile / tiles_per_batch : 0;
             tile_coords(tile - bt * tiles_per_batch, p.tiles_m, p.tiles_n, tm, tn);
@@ -315,9 +330,7 @@ tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUt
                                 int A = oh2 + p.lv.pt, B = ow2 + p.lv.pl, slot = 0;
                                 if (p.lv.S == 2) { slot = ((A & 1) * 2 + (B & 1)) * p.lv.C; A >>= 1; B >>= 1; }
                                 uint16_t* zdst = p.lv.z + (((size_t)(m / p.cv.plane) * p.lv.Hz + A) * p.lv.Wz + B) * p.lv.Cz + slot + n0;
-                                const float ls = __ldg(p.lv.scale), linv = quantize_reciprocal(ls);
-                                float zf = 0.0f;
-                                if (p.lv.zero) zf = p.lv.zero_signed ? (float)*(const int8_t*)p.lv.zero : (float)*(const uint8_t*)p.lv.zero;
+                                const float ls = lv_scale, linv = lv_inv, zf = lv_zero;
                                 // eight values at a time on the fast path without branches (their dependency chains
                                 // interleave); a group in which the fast rounding could not decide some value -- a tie
                                 // closer than 2^-19 |q|, which also catches |q| >= 2^18 and NaN -- is redone with the
