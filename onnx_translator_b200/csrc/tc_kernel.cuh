@@ -277,10 +277,20 @@ tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUt
                 umma::tmem_load_wait();
                 {
                     float v[kW];
-                    #pragma unroll
-                    for (int j = 0; j < kW; j++) {
-                        const float scale = p.fs.b_per_column ? my_scale[c * kW + j] : alpha;
-                        v[j] = __fadd_rn(__fmul_rn(scale, __uint_as_float(r[j])), row_bias);
+                    if constexpr (MODE == kModeConv) {                 // no per-row term here; column scales read four at a time
+                        #pragma unroll
+                        for (int j = 0; j < kW; j += 4) {
+                            float4 s4 = make_float4(alpha, alpha, alpha, alpha);
+                            if (p.fs.b_per_column) s4 = *(const float4*)(my_scale + c * kW + j);
+                            v[j] = __fmul_rn(s4.x, __uint_as_float(r[j]));         v[j + 1] = __fmul_rn(s4.y, __uint_as_float(r[j + 1]));
+                            v[j + 2] = __fmul_rn(s4.z, __uint_as_float(r[j + 2])); v[j + 3] = __fmul_rn(s4.w, __uint_as_float(r[j + 3]));
+                        }
+                    } else {
+                        #pragma unroll
+                        for (int j = 0; j < kW; j++) {
+                            const float scale = p.fs.b_per_column ? my_scale[c * kW + j] : alpha;
+                            v[j] = __fadd_rn(__fmul_rn(scale, __uint_as_float(r[j])), row_bias);
+                        }
                     }
                     if (p.bias.mode == kBiasPerColumn) {
                         #pragma unroll
@@ -309,7 +319,7 @@ tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUt
                     }
                     if (p.relu && !with_res) {
                         #pragma unroll
-                        for (int j = 0; j < kW; j++) v[j] = v[j] > 0.0f ? v[j] : 0.0f;
+                        for (int j = 0; j < kW; j++) v[j] = fmaxf(v[j], 0.0f);      // same results as v > 0 ? v : 0, NaN and -0 included
                     }
                     if constexpr (MODE == kModeConv) {
                         // NCHW output: for one output channel, consecutive lanes (consecutive padded
@@ -320,7 +330,7 @@ tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUt
                                 #pragma unroll
                                 for (int j = 0; j < kW; j++) {
                                     v[j] = __fadd_rn(v[j], res_cur[j]);
-                                    if (p.relu) v[j] = v[j] > 0.0f ? v[j] : 0.0f;
+                                    if (p.relu) v[j] = fmaxf(v[j], 0.0f);
                                 }
                             }
                             if constexpr ((EPI & kEpiLevels) != 0) {
@@ -336,6 +346,7 @@ tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUt
                                 // closer than 2^-19 |q|, which also catches |q| >= 2^18 and NaN -- is redone with the
                                 // reference's double division
                                 const float lo = p.lv.zero_signed ? -128.0f : 0.0f, hi = p.lv.zero_signed ? 127.0f : 255.0f;
+                                const float lo_z = __fsub_rn(lo, zf), hi_z = __fsub_rn(hi, zf);
                                 uint32_t packed[kW / 2];
                                 #pragma unroll
                                 for (int j0 = 0; j0 < kW; j0 += 8) {
@@ -346,7 +357,7 @@ tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUt
                                         const float q = __fmul_rn(v[j0 + e], linv);
                                         const float rq = __fsub_rn(__fadd_rn(q, 12582912.0f), 12582912.0f);
                                         decided = decided & (fmaf(fabsf(q), 1.9073486e-6f, fabsf(__fsub_rn(q, rq))) < 0.5f);
-                                        level[e] = __fsub_rn(fminf(fmaxf(__fadd_rn(rq, zf), lo), hi), zf);
+                                        level[e] = fminf(fmaxf(rq, lo_z), hi_z);              // clamp(rq + z, lo, hi) - z, all small integers
                                     }
                                     if (!decided) {
                                         #pragma unroll
