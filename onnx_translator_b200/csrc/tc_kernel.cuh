@@ -243,6 +243,7 @@ tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUt
             // of the first column chunk, requested before the accumulator is even complete
             bool conv_row = false;
             size_t conv_base = 0, plane_out = 0;
+            uint16_t* levels_row = nullptr;
             float res_next[kW];
             constexpr bool with_res = MODE == kModeConv && (EPI & kEpiResidual) != 0;
             if constexpr (MODE == kModeConv) {
@@ -251,6 +252,13 @@ tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUt
                 conv_row = img < p.cv.images && oh < p.cv.OH && ow < p.cv.OW;
                 plane_out = (size_t)p.cv.OH * p.cv.OW;
                 conv_base = ((size_t)img * p.cv.OC + (size_t)tn * kBN) * plane_out + (size_t)oh * p.cv.OW + ow;
+                if constexpr ((EPI & kEpiLevels) != 0) {
+                    // where this row's levels go: it is input pixel (oh, ow) of the next convolution -- worked out
+                    // once per tile, not once per column chunk (two integer divisions per lane)
+                    int A = oh + p.lv.pt, B = ow + p.lv.pl, slot = 0;
+                    if (p.lv.S == 2) { slot = ((A & 1) * 2 + (B & 1)) * p.lv.C; A >>= 1; B >>= 1; }
+                    levels_row = p.lv.z + (((size_t)img * p.lv.Hz + A) * p.lv.Wz + B) * p.lv.Cz + slot + tn * kBN;
+                }
             }
             auto fetch_residual = [&](int chunk, float (&dst)[kW]) {
                 const float* src = p.residual + conv_base + (size_t)(chunk * kW) * plane_out;
@@ -334,12 +342,7 @@ tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUt
                                 }
                             }
                             if constexpr ((EPI & kEpiLevels) != 0) {
-                                // levels for the next convolution: this row is input pixel (oh, ow) of that convolution
-                                const int rem2 = m - (m / p.cv.plane) * p.cv.plane;
-                                const int oh2 = rem2 / p.cv.Wp, ow2 = rem2 - oh2 * p.cv.Wp;
-                                int A = oh2 + p.lv.pt, B = ow2 + p.lv.pl, slot = 0;
-                                if (p.lv.S == 2) { slot = ((A & 1) * 2 + (B & 1)) * p.lv.C; A >>= 1; B >>= 1; }
-                                uint16_t* zdst = p.lv.z + (((size_t)(m / p.cv.plane) * p.lv.Hz + A) * p.lv.Wz + B) * p.lv.Cz + slot + n0;
+                                uint16_t* zdst = levels_row + c * kW;          // levels for the next convolution
                                 const float ls = lv_scale, linv = lv_inv, zf = lv_zero;
                                 // eight values at a time on the fast path without branches (their dependency chains
                                 // interleave); a group in which the fast rounding could not decide some value -- a tie
