@@ -352,6 +352,10 @@ typedef struct QConvCall {
     const Tensor* next_zero;    /* its zero point (int8 / uint8 [1]) or NULL */
     ConvParams* next_params;    /* the next convolution's attributes ... */
     int next_kernel[2];         /* ... and filter extent KH, KW */
+    Tensor** filter_cache;      /* NULL, or where the filters in the layout the tensor cores read are kept between calls:
+                                   *filter_cache == NULL on the first call (the library creates and fills a tensor and
+                                   stores it there), non-NULL afterwards (used as it is: same w_codes contents, same
+                                   attributes, same kind of x).  The caller releases it with free_tensor. */
 } QConvCall;
 int tops_qconv_forward(const QConvCall* call);
 int tops_qconv_levels_shape(const int x_shape[4], const int kernel[2], const ConvParams* params, int levels_shape[4]);

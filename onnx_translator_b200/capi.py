@@ -39,7 +39,8 @@ class CQConvCall(ctypes.Structure):
                 ("x_scale", ctypes.c_void_p), ("x_zero", ctypes.c_void_p), ("w_codes", ctypes.c_void_p), ("w_scale", ctypes.c_void_p),
                 ("bias", ctypes.c_void_p), ("residual", ctypes.c_void_p), ("params", ctypes.POINTER(CConvParams)), ("relu", ctypes.c_int),
                 ("y", ctypes.c_void_p), ("y_levels", ctypes.c_void_p), ("next_scale", ctypes.c_void_p), ("next_zero", ctypes.c_void_p),
-                ("next_params", ctypes.POINTER(CConvParams)), ("next_kernel", ctypes.c_int * 2)]
+                ("next_params", ctypes.POINTER(CConvParams)), ("next_kernel", ctypes.c_int * 2),
+                ("filter_cache", ctypes.POINTER(ctypes.c_void_p))]
 
 
 class CPoolParams(ctypes.Structure):

@@ -300,10 +300,23 @@ static int qconv_run(const char* name, const QConvCall& q) {
             else           activations_to_levels<1, false><<<grid, 256, 0, s>>>(X->data, (uint16_t*)z, g, scale_ptr, zero_ptr);
         }
     }
-    if (cudaMallocAsync(&wt, wt_bytes, s) != cudaSuccess) {
-        cudaGetLastError();
-        if (!q.x_levels) cudaFreeAsync(z, s);
-        return qconv_fail(name, TOPS_ERR_OOM, "scratch", nullptr);
+    // The filters in tensor-core layout: scratch of this call, or a tensor kept by the caller between calls
+    // (shape [1 + merged][elements], so that a cache made for the other layout is recognised).
+    const bool cached = q.filter_cache && *q.filter_cache;
+    Tensor* keep = nullptr;
+    if (cached) {
+        keep = *q.filter_cache;
+        if (!keep->data || keep->dtype != DTYPE_BFLOAT16 || keep->ndim != 2 || (size_t)keep->shape[1] != wt_bytes / 2) {
+            if (!q.x_levels) cudaFreeAsync(z, s);
+            return qconv_fail(name, TOPS_ERR_INVALID, "the filter cache was made for another convolution", Y);
+        }
+        wt = keep->data;
+    } else if (!q.filter_cache) {
+        if (cudaMallocAsync(&wt, wt_bytes, s) != cudaSuccess) {
+            cudaGetLastError();
+            if (!q.x_levels) cudaFreeAsync(z, s);
+            return qconv_fail(name, TOPS_ERR_OOM, "scratch", nullptr);
+        }
     }
     // Few channels: the KWz taps of a filter row are KWz neighbouring cells, i.e. contiguous memory, so one
     // activation "row" of KWz * Cz channels (rows overlapping, one cell apart) feeds a whole filter row per K
@@ -319,7 +332,22 @@ static int qconv_run(const char* name, const QConvCall& q) {
         trial.C = g.Cz * g.KWz; trial.KW = 1; trial.a_row_stride_bytes = g.Cz * 2;
         if (shifted_gemm_map_ok(trial)) { sg = trial; merged = true; }
     }
-    filter_codes_to_levels<<<grid_for(wt_bytes / 2, 256, st->sm_count, 4), 256, 0, s>>>((const int8_t*)Wq->data, (uint16_t*)wt, g, merged ? 1 : 0);
+    if (q.filter_cache && !cached) {
+        const int shape[2] = {merged ? 2 : 1, (int)(wt_bytes / 2)};
+        keep = wt_bytes / 2 <= 0x3FFFFFFFull ? tops_create_uninit(shape, 2, DTYPE_BFLOAT16) : nullptr;
+        if (!keep) {
+            if (!q.x_levels) cudaFreeAsync(z, s);
+            return qconv_fail(name, TOPS_ERR_OOM, "filter cache", nullptr);
+        }
+        *q.filter_cache = keep;
+        wt = keep->data;
+        sg.wt = wt;
+    }
+    if (cached && (keep->shape[0] == 2) != merged) {
+        if (!q.x_levels) cudaFreeAsync(z, s);
+        return qconv_fail(name, TOPS_ERR_INVALID, "the filter cache was made for the other filter layout", Y);
+    }
+    if (!cached) filter_codes_to_levels<<<grid_for(wt_bytes / 2, 256, st->sm_count, 4), 256, 0, s>>>((const int8_t*)Wq->data, (uint16_t*)wt, g, merged ? 1 : 0);
     ok = ok && TOPS_CHECK_LAUNCH(name);
     if (ok) {
         sg.Y = Y ? Y->data : nullptr; sg.dy = dy;
@@ -335,7 +363,7 @@ static int qconv_run(const char* name, const QConvCall& q) {
         ok = shifted_gemm_launch(sg);
     }
     if (!q.x_levels) cudaFreeAsync(z, s);
-    cudaFreeAsync(wt, s);
+    if (!q.filter_cache) cudaFreeAsync(wt, s);
     if (!ok) return tops_last_error();
     finish_op();
     return TOPS_OK;

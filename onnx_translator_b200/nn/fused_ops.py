@@ -37,6 +37,23 @@ class QLinearConv(Ops):
         self.levels_in = False
         self.next_conv = None
         self.also_float = False       # with next_conv: outputs are (float32 tensor, levels tensor) instead of the levels alone
+        # The filters in the layout the tensor cores read, made by the library on the first call and reused while
+        # the node keeps seeing the same weight array (replace the array, or call drop_filter_cache(), after
+        # changing weights in place).
+        self._filter_cache = ctypes.c_void_p()
+        self._filter_cache_key = None
+
+    def drop_filter_cache(self):
+        if self._filter_cache:
+            self.lib.free_tensor(ctypes.cast(self._filter_cache, capi.TensorP))
+        self._filter_cache = ctypes.c_void_p()
+        self._filter_cache_key = None
+
+    def __del__(self):
+        try:
+            self.drop_filter_cache()
+        except Exception:
+            pass
 
     def _levels_tensor(self, logical_shape, conv):
         """bfloat16 levels tensor for the convolution described by ``conv`` reading ``logical_shape``."""
@@ -77,6 +94,11 @@ class QLinearConv(Ops):
         call.x_scale, call.x_zero, call.w_codes, call.w_scale = ptr(x_scale), ptr(x_zero), ptr(wq), ptr(w_scale)
         call.bias, call.residual = ptr(b), ptr(residual)
         call.params, call.relu = ctypes.pointer(params), int(self.relu)
+        key = (id(wq.data), tuple(wq.data.shape), bool(self.levels_in), tuple(self.pads), tuple(self.strides), tuple(self.dilations))
+        if key != self._filter_cache_key:
+            self.drop_filter_cache()
+            self._filter_cache_key = key
+        call.filter_cache = ctypes.pointer(self._filter_cache)
         y_handle = levels = None
         if self.next_conv is not None:
             levels = self._levels_tensor(out_shape, self.next_conv)

@@ -377,3 +377,26 @@ def test_levels_edge_between_two_quantised_convolutions_is_bit_identical(nxt):
     assert levels.dtype == "bfloat16" and levels.logical_shape == (n, m1, h, h)
     got = conv_b(levels, True)
     assert got.shape == want.shape and np.array_equal(got.view(np.uint32), want.view(np.uint32))
+
+
+def test_filter_cache_is_reused_and_follows_the_weight_array():
+    """The node keeps the filters in tensor-core layout between calls: a second call gives identical bytes, and a
+    different weight array (not the stale cache) decides the result of the third."""
+    from onnx_translator_b200.nn import Tensor
+    from onnx_translator_b200.nn.fused_ops import QLinearConv
+    rng = np.random.default_rng(321)
+    T = lambda a, dt: Tensor(*a.shape, dtype=dt, data=a)
+    x = T(rng.normal(0, 1, (2, 32, 14, 14)).astype(np.float32), "float32")
+    sx, zx = T(np.array([0.04], np.float32), "float32"), T(np.zeros(1, np.int8), "int8")
+    w1 = T(rng.integers(-127, 128, (48, 32, 3, 3)).astype(np.int8), "int8")
+    w2 = T(rng.integers(-127, 128, (48, 32, 3, 3)).astype(np.int8), "int8")
+    ws = T(rng.uniform(0.002, 0.01, (48, 1, 1, 1)).astype(np.float32), "float32")
+    node = QLinearConv([], [], [1] * 4, [1, 1], [1, 1], True, "float32", from_float=True)
+    fresh = lambda w: QLinearConv([], [], [1] * 4, [1, 1], [1, 1], True, "float32", from_float=True).forward(x, sx, zx, w, ws)["tensor"].numpy()
+    first = node.forward(x, sx, zx, w1, ws)["tensor"].numpy()
+    assert node._filter_cache.value
+    kept = node._filter_cache.value
+    second = node.forward(x, sx, zx, w1, ws)["tensor"].numpy()
+    assert node._filter_cache.value == kept and np.array_equal(first, second) and np.array_equal(first, fresh(w1))
+    third = node.forward(x, sx, zx, w2, ws)["tensor"].numpy()
+    assert np.array_equal(third, fresh(w2)) and not np.array_equal(third, first)
