@@ -21,6 +21,8 @@
 //   * stride 2: the same with a space-to-depth step, Z[A][B][(r,s,c)] = Xpad[2A + r][2B + s][c], which
 //     turns the stride-2 KH x KW convolution into a stride-1 ceil(KH/2) x ceil(KW/2) convolution over
 //     4C channels (filter taps that fall outside the original window are zero);
+//   * stride 2 with a 1 x 1 filter and no padding only ever reads every second pixel: the layout pass keeps just
+//     those (a stride-1 1 x 1 convolution over the subsampled image, C channels instead of 4C);
 //   * filters [M][C][KH][KW] -> tap-major [taps][M][C8'] in the same channel order.
 // Then the shifted-GEMM tensor-core kernel (conv_tc.cu, tc_kernel.cuh) runs unchanged.
 #include "conv_common.cuh"
@@ -35,6 +37,7 @@ struct QGeom {
     int Hz, Wz, Cz;        // levels tensor: rows, columns, channels (S*S*C rounded up to 8)
     int KH, KW, KHz, KWz;  // original and space-to-depth filter extents
     int M;
+    int sub, srcW, src_plane;   // sub = 1: the layout pass reads every second row and column of a srcW-wide source plane
 };
 
 __device__ __forceinline__ uint16_t level_bits(int v) {        // small integer -> bfloat16 bits (exact for |v| <= 256)
@@ -63,6 +66,8 @@ __global__ void __launch_bounds__(256) activations_to_levels(const void* __restr
         const int pp = threadIdx.x & 63, cq = threadIdx.x >> 6;
         const int p = p0 + pp;
         if (p < plane) {
+            size_t src_p = (size_t)p;
+            if (g.sub) { const int hs = p / g.W; src_p = (size_t)(2 * hs) * g.srcW + 2 * (p - hs * g.W); }
             // this thread's 16 values (8 channel pairs) first, so that all loads are in flight together
             float v[16];
             #pragma unroll
@@ -72,7 +77,7 @@ __global__ void __launch_bounds__(256) activations_to_levels(const void* __restr
                     const int c = c0 + 2 * (cq + 4 * i) + e;
                     float value = 0.0f;
                     if (c < g.C) {
-                        const size_t at = ((size_t)n * g.C + c) * (size_t)plane + (size_t)p;
+                        const size_t at = ((size_t)n * g.C + c) * (size_t)g.src_plane + src_p;
                         if (XK == 0) value = __ldg((const float*)x + at);
                         else { const uint8_t code = ((const uint8_t*)x)[at]; value = (float)(SIGNED ? (int)(int8_t)code : (int)code); }
                     }
@@ -198,6 +203,7 @@ static bool levels_geometry(int C, int H, int W, int M, int KH, int KW, const Co
     g->Hz = need_h > have_h ? need_h : have_h;
     g->Wz = need_w > have_w ? need_w : have_w;
     g->Cz = (g->S * g->S * C + 7) & ~7;
+    g->sub = 0; g->srcW = W; g->src_plane = H * W;
     return true;
 }
 
@@ -223,6 +229,11 @@ static int qconv_run(const char* name, const QConvCall& q) {
         !levels_geometry(C, H, W, M, KH, KW, q.params, &g, &OH, &OW, &dil_h, &dil_w))
         return qconv_fail(name, TOPS_ERR_UNSUPPORTED, "covers group 1, stride 1 (any dilation) or stride 2 (dilation 1), W of shape [M, C, KH, KW]", Y);
 
+    if (!q.x_levels && g.S == 2 && KH == 1 && KW == 1 && C > 8 && !q.params->pads[0] && !q.params->pads[1] && !q.params->pads[2] && !q.params->pads[3]) {
+        // every second pixel is all this convolution reads: lay out just those, then it is a stride-1 1 x 1 convolution
+        g.H = OH; g.W = OW; g.S = 1; g.pt = g.pl = 0; g.Hz = OH; g.Wz = OW; g.Cz = (C + 7) & ~7;
+        g.sub = 1; g.srcW = W; g.src_plane = H * W;
+    }
     const bool zero_given = q.x_zero && q.x_zero->data;
     const bool x_is_float = !q.x_levels && X->dtype == DTYPE_FLOAT32;
     const int code_dt = q.x_levels ? DTYPE_INT8 : x_is_float ? (zero_given ? (int)q.x_zero->dtype : DTYPE_INT8) : (int)X->dtype;

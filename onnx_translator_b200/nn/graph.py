@@ -160,7 +160,10 @@ class Graph:
             for e in op.inputs:
                 if e:
                     readers.setdefault(e, []).append(op)
-        for consumer in kept:
+        # a producer serves one reader: stride-1 readers first (they read every pixel; a 1 x 1 stride-2 reader's own
+        # layout pass only touches a quarter of them)
+        by_preference = sorted(kept, key=lambda op: 0 if list(getattr(op, "strides", [1, 1])) == [1, 1] else 1)
+        for consumer in by_preference:
             if kind(consumer) != "QLinearConv" or not consumer.from_float:
                 continue
             edge = consumer.inputs[0]
