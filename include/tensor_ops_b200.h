@@ -241,6 +241,19 @@ int   tops_sync(void);
    memmove()s into Tensor.data and reads results back through the pointer keeps working. */
 int tops_set_memory_mode(int managed);
 
+/* A fixed sequence of operator calls as one CUDA graph (no counterpart in the reference, whose interpreter
+   nn/__init__.py:408-456 walks the node list on every run).  Between tops_capture_begin and tops_capture_end the
+   operator calls made on this thread's device are recorded instead of executed: kernels, memsets and the
+   operators' own stream-ordered scratch.  Inside that window create no tensors, free none and transfer nothing:
+   only operator calls on tensors that exist already and stay alive as long as the graph is used (same pointers
+   on every launch).  tops_capture_launch enqueues the whole sequence on the current stream with one driver call.
+   Not available in managed-memory mode.  tops_capture_end returns NULL (error recorded) when the sequence cannot
+   be captured; the stream is usable again afterwards. */
+int   tops_capture_begin(void);
+void* tops_capture_end(void);
+int   tops_capture_launch(void* captured);
+void  tops_capture_free(void* captured);
+
 /* Like create_tensor without the zero fill (operators overwrite the whole output). */
 Tensor* tops_create_uninit(const int* shape, int ndim, DataType dtype);
 /* Describe device memory owned by someone else (e.g. a framework tensor); never freed here. */
@@ -273,7 +286,7 @@ void tops_dequantize_linear_axis_forward(const Tensor* X, const Tensor* Scale, c
    tensors from the CUDA memory pool on each call; a process that has given the whole device to its
    own allocator, runs under a fixed memory budget, or is in a phase where an allocation may block or
    fail cannot accept that.  This variant computes the same result with scratch in a fixed 36 MiB
-   array inside the library image (reserved on every GPU that loads the library, until exit).
+   array inside the library image (held by every GPU on which the library's device code is loaded, until exit).
    Limits: the padded channels-last copy of X (N*Hp*Wp*C elements) must fit 32 MiB and the filter copy
    (KH*KW*M*C elements) 4 MiB; only what the tensor-core path covers is accepted (group 1, stride 1,
    fp16 / bf16 / fp8 inputs of one kind, fp32 / bf16 / fp16 output, C a multiple of 16 bytes).
@@ -281,8 +294,13 @@ void tops_dequantize_linear_axis_forward(const Tensor* X, const Tensor* Scale, c
    The first call on a device resolves the array's device address (and creates the library stream
    if nothing ran there yet): make it before any stream capture.  All calls share the array, which
    keeps the previous call's contents (each call overwrites all it reads); calls that overlap on the
-   GPU race, so keep them ordered on one stream.  tops_conv2d_noalloc_limits reports the limits. */
+   GPU race, so keep them ordered on one stream.  tops_conv2d_noalloc_limits reports the limits.
+   tops_conv2d_noalloc_prepare does the per-device set-up (stream, array address) ahead of time, outside
+   the allocation-free phase, and creates the pinned host word through which an expired device-side wait
+   is reported; without it (and without any earlier tensor-core operator call) such a time-out ends the
+   kernel but is not reported.  Returns the error code. */
 void   tops_conv2d_forward_noalloc(const Tensor* X, const Tensor* W, const Tensor* B, Tensor* Y, ConvParams* params);
+int    tops_conv2d_noalloc_prepare(void);
 size_t tops_conv2d_noalloc_limits(size_t* input_bytes, size_t* filter_bytes);
 
 /* Fused forms of the operator sequences of quantised graphs (no single counterpart in the
@@ -356,6 +374,12 @@ typedef struct QConvCall {
                                    *filter_cache == NULL on the first call (the library creates and fills a tensor and
                                    stores it there), non-NULL afterwards (used as it is: same w_codes contents, same
                                    attributes, same kind of x).  The caller releases it with free_tensor. */
+    /* Channels-last float32 edges.  The ABI's tensors are NCHW; a graph runner that owns the edge between two of
+       these calls may keep it as [N, H, W, C] instead -- the order the tensor cores produce and consume -- and say
+       so here.  Each flag describes one tensor of THIS call; the tensor's header carries the channels-last shape. */
+    int x_channels_last;        /* x (float32 values or 8-bit codes, not levels) is [N, H, W, C] */
+    int y_channels_last;        /* y is float32 [N, OH, OW, M] */
+    int residual_channels_last; /* residual is float32 [N, OH, OW, M] */
 } QConvCall;
 int tops_qconv_forward(const QConvCall* call);
 int tops_qconv_levels_shape(const int x_shape[4], const int kernel[2], const ConvParams* params, int levels_shape[4]);

@@ -40,7 +40,8 @@ class CQConvCall(ctypes.Structure):
                 ("bias", ctypes.c_void_p), ("residual", ctypes.c_void_p), ("params", ctypes.POINTER(CConvParams)), ("relu", ctypes.c_int),
                 ("y", ctypes.c_void_p), ("y_levels", ctypes.c_void_p), ("next_scale", ctypes.c_void_p), ("next_zero", ctypes.c_void_p),
                 ("next_params", ctypes.POINTER(CConvParams)), ("next_kernel", ctypes.c_int * 2),
-                ("filter_cache", ctypes.POINTER(ctypes.c_void_p))]
+                ("filter_cache", ctypes.POINTER(ctypes.c_void_p)),
+                ("x_channels_last", ctypes.c_int), ("y_channels_last", ctypes.c_int), ("residual_channels_last", ctypes.c_int)]
 
 
 class CPoolParams(ctypes.Structure):
@@ -113,6 +114,10 @@ SIGNATURES = {
     "tops_set_stream": (_I, [_V]),
     "tops_sync": (_I, []),
     "tops_set_memory_mode": (_I, [_I]),
+    "tops_capture_begin": (_I, []),
+    "tops_capture_end": (_V, []),
+    "tops_capture_launch": (_I, [_V]),
+    "tops_capture_free": (None, [_V]),
     "tops_create_uninit": (_P, [_IP, _I, _I]),
     "tops_wrap": (_P, [_V, _IP, _I, _I]),
     "tops_view": (_P, [_P, _IP, _I]),
@@ -142,6 +147,7 @@ SIGNATURES = {
     "tops_quantize_linear_axis_forward": (None, [_P, _P, _P, _P, _I]),
     "tops_dequantize_linear_axis_forward": (None, [_P, _P, _P, _P, _I]),
     "tops_conv2d_forward_noalloc": (None, [_P, _P, _P, _P, ctypes.POINTER(CConvParams)]),
+    "tops_conv2d_noalloc_prepare": (_I, []),
     "tops_conv2d_noalloc_limits": (_SZ, [ctypes.POINTER(_SZ), ctypes.POINTER(_SZ)]),
     "tops_gemm_qdq_forward": (_I, [_P, _P, _P, _P, _P, _P, _P, ctypes.c_float, ctypes.c_float, _I, _I]),
     "tops_conv2d_dqw_forward": (_I, [_P, _P, _P, _P, _P, ctypes.POINTER(CConvParams)]),

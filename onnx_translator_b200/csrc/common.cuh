@@ -40,6 +40,9 @@ const double* cos_lut_device();           // uploads on first use
 int*         device_status_word();        // device pointer to the host-visible status word (may be null)
 int*         device_status_word_if_created();   // as above, but never allocates (null until first created)
 void         poll_device_status();        // host: turn a raised status word into an error
+// Opt-in for more than 48 KB of dynamic shared memory.  The attribute belongs to the (kernel, device) pair, so
+// it is recorded per device: the first launch of `kernel` on each device sets it, with that device current.
+bool         ensure_dynamic_smem(const void* kernel, size_t bytes);
 
 #define TOPS_CUDA_OK(expr) ::tops::check_cuda((expr), #expr)
 #define TOPS_CHECK_LAUNCH(name) ::tops::check_cuda(cudaGetLastError(), name)

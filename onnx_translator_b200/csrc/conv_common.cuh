@@ -50,6 +50,8 @@ struct ShiftedGemm {
     int relu = 0;
     const float* residual = nullptr;          // float32, shape of Y: added to the result before the optional Relu
     LevelsOut lv;                             // result as levels for the next quantised convolution (Y may then be null)
+    int y_channels_last = 0;                  // Y is float32 [images][OH][OW][M] instead of NCHW
+    int residual_channels_last = 0;           // the residual is [images][OH][OW][M]
 };
 bool shifted_gemm_launch(const ShiftedGemm& g);
 // Whether the driver accepts the activation map of `g` (no launch): used to choose a layout before the filters are laid out.

@@ -8,8 +8,10 @@
 // operator.  For them this entry point does the same computation with scratch that already
 // exists: a file-scope device array that is part of the loaded library image.
 //
-// Cost of that choice: the array (kScratchBytes, 36 MiB) is reserved on EVERY GPU the library is
-// loaded on, from load until the process exits, whether or not this function is ever called.
+// Cost of that choice: the array (kScratchBytes, 36 MiB) is part of the library's device image, so
+// every GPU on which the library's device code gets loaded holds it until the process exits, whether
+// or not this function is ever called there.  (With CUDA's default lazy module loading that happens
+// at the first kernel launch or symbol lookup of this library on that GPU -- possibly this call.)
 //
 // Rules for callers
 //   * Size limit: the padded copy of X (N * Hp * Wp * C elements) must fit kInputBytes = 32 MiB and
@@ -20,7 +22,12 @@
 //     switch to another kernel here.
 //   * The first call on each device looks up the device address of the array (and, if nothing in
 //     the library ran on that device before, creates the library's stream).  Make that first call
-//     before starting any stream capture.
+//     before starting any stream capture -- or call tops_conv2d_noalloc_prepare() there, which does
+//     this set-up and nothing else.
+//   * A bounded wait that expires inside the kernel is reported (TOPS_ERR_DEVICE_TIMEOUT at the next
+//     tops_sync) through a word of pinned host memory.  This function never allocates it: it exists
+//     once tops_conv2d_noalloc_prepare() or any other tensor-core operator of the library has run.
+//     Without it an expired wait still ends the kernel, but nothing reports it.
 //   * All calls share the one array.  It still holds the previous call's data when the next call
 //     starts; every byte a call reads it first writes (padding included), so nothing needs
 //     clearing.  Two calls that overlap on the GPU (different streams, or different host threads)
@@ -78,14 +85,21 @@ TOPS_API void tops_conv2d_forward_noalloc(const Tensor* X, const Tensor* W, cons
         zero_fill(Y);
         return;
     }
-    if (!acquire_device()) return;
+    if (!acquire_device()) return;                         // no usable device: nothing can be written either
     unsigned char* scratch = scratch_for_current_device();
-    if (!scratch) return;                                  // the CUDA error is already recorded
+    if (!scratch) { zero_fill(Y); finish_op(); return; }   // the CUDA error is already recorded
     if (!conv_tc_run(X, W, B, Y, c, plan, scratch, scratch + kInputBytes, device_status_word_if_created())) {
         set_error(TOPS_ERR_CUDA, "%s: the kernels could not be launched", name);      // keeps an earlier, more specific error
         zero_fill(Y);
     }
     finish_op();
+}
+
+TOPS_API int tops_conv2d_noalloc_prepare(void) {
+    if (!acquire_device()) return tops_last_error();
+    if (!scratch_for_current_device()) return tops_last_error();
+    (void)device_status_word();                             // pinned host word for time-out reports (allocates once per process)
+    return TOPS_OK;
 }
 
 TOPS_API size_t tops_conv2d_noalloc_limits(size_t* input_bytes, size_t* filter_bytes) {

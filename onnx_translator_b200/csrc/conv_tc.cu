@@ -67,6 +67,73 @@ __global__ void __launch_bounds__(256) nchw_to_padded_nhwc(const E* __restrict__
     }
 }
 
+// The same copy for planes whose byte size is a multiple of 16 (so that every channel plane starts on a 16-byte
+// boundary): both sides move 16 bytes per thread.  One CTA takes 64 channels x kTilePos consecutive positions of one
+// image plane (flat h * W + w, contiguous in NCHW whatever the width); a thread loads 16 bytes ALONG THE PLANE of four
+// channels, the tile is transposed through shared memory, and a thread stores 16 bytes ALONG THE CHANNELS of one
+// position.  Only interior cells are written here; zero_padding_cells clears the border.
+template <typename E>
+__global__ void __launch_bounds__(256) nchw_to_padded_nhwc_vec(const E* __restrict__ x, E* __restrict__ xp,
+                                                                int C, int H, int W, int Hp, int Wp, int pt, int pl) {
+    constexpr int kVec = 16 / (int)sizeof(E);               // elements per 16 bytes
+    constexpr int kTilePos = 16 * kVec;                     // positions per tile: 16 vectors per channel row
+    constexpr int kPitchWords = 64 + 1;                     // 256 bytes of payload + one word: rows land on different banks
+    __shared__ uint32_t tile[64 * kPitchWords];             // [channel][position], 4-byte granules
+    const int plane = H * W;
+    const int p0 = blockIdx.x * kTilePos, n = blockIdx.y, c0 = blockIdx.z * 64;
+    {
+        const int v = threadIdx.x & 15, cc0 = threadIdx.x >> 4;
+        const int p = p0 + v * kVec;
+        uint4 val[4];
+        #pragma unroll
+        for (int i = 0; i < 4; i++) {
+            const int c = c0 + cc0 + 16 * i;
+            val[i] = (p < plane && c < C) ? __ldg(reinterpret_cast<const uint4*>(x + ((size_t)n * C + c) * plane + p)) : make_uint4(0, 0, 0, 0);
+        }
+        #pragma unroll
+        for (int i = 0; i < 4; i++) {
+            uint32_t* row = tile + (cc0 + 16 * i) * kPitchWords + v * 4;
+            row[0] = val[i].x; row[1] = val[i].y; row[2] = val[i].z; row[3] = val[i].w;
+        }
+    }
+    __syncthreads();
+    constexpr int kGroups = 64 / kVec;                      // 16-byte channel groups per position
+    constexpr int kPosPerPass = 256 / kGroups;
+    const int cg = threadIdx.x % kGroups, pos0 = threadIdx.x / kGroups;
+    const int c = c0 + cg * kVec;
+    if (c >= C) return;
+    const E* tile_e = reinterpret_cast<const E*>(tile);
+    #pragma unroll
+    for (int pass = 0; pass < kTilePos / kPosPerPass; pass++) {
+        const int pp = pos0 + pass * kPosPerPass, p = p0 + pp;
+        if (p >= plane) continue;
+        __align__(16) E out[kVec];
+        #pragma unroll
+        for (int j = 0; j < kVec; j++) out[j] = tile_e[(size_t)(cg * kVec + j) * (kPitchWords * 4 / sizeof(E)) + pp];
+        const int h = p / W, w = p - h * W;
+        *reinterpret_cast<uint4*>(xp + (((size_t)n * Hp + h + pt) * Wp + w + pl) * C + c) = *reinterpret_cast<const uint4*>(out);
+    }
+}
+
+// Clears the cells of a padded channels-last tensor [N][Hp][Wp][C] that lie outside the H x W interior placed at
+// (pt, pl): pt rows on top, Hp - pt - H rows at the bottom, and Wp - W cells in each interior row.  One thread per
+// 16 bytes (row_bytes = C * element size is a multiple of 16).
+__global__ void __launch_bounds__(256) zero_padding_cells(uint4* __restrict__ xp, int row_vecs, int H, int W, int Hp, int Wp, int pt, int pl) {
+    const int top = pt * Wp, bottom = (Hp - pt - H) * Wp, side = Wp - W;
+    const int cells = top + bottom + H * side;
+    const size_t total = (size_t)cells * row_vecs;
+    const int n = blockIdx.y;
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
+        int cell = (int)(i / row_vecs);
+        const int v = (int)(i - (size_t)cell * row_vecs);
+        int hp, wp;
+        if (cell < top) { hp = cell / Wp; wp = cell - hp * Wp; }
+        else if (cell < top + bottom) { cell -= top; hp = pt + H + cell / Wp; wp = cell % Wp; }
+        else { cell -= top + bottom; const int r = cell / side, k = cell - r * side; hp = pt + r; wp = k < pl ? k : W + k; }
+        xp[(((size_t)n * Hp + hp) * Wp + wp) * row_vecs + v] = make_uint4(0, 0, 0, 0);
+    }
+}
+
 // [M][C][KH*KW] -> [KH*KW][M][C]
 template <typename E>
 __global__ void __launch_bounds__(256) filters_to_tap_major(const E* __restrict__ w, E* __restrict__ wt, int M, int C, int taps) {
@@ -127,8 +194,22 @@ bool conv_tc_run(const Tensor* X, const Tensor* W, const Tensor* B, Tensor* Y, c
 
     const dim3 tgrid(c.N * Hp, (Wp + 63) / 64, (c.C + 63) / 64);
     const int wgrid = grid_for((size_t)c.M * c.C * taps, 256, st->sm_count, 4);
+    // planes that start on 16-byte boundaries take the copy that moves 16 bytes per thread on both sides
+    const bool vec_copy = ((size_t)c.H * c.W * es) % 16 == 0 && ((uintptr_t)X->data & 15) == 0 && ((uintptr_t)xp & 15) == 0 && c.N <= 65535;
+    if (vec_copy) {
+        const int tile_pos = 16 * (16 / es);
+        const dim3 vgrid((c.H * c.W + tile_pos - 1) / tile_pos, c.N, (c.C + 63) / 64);
+        const int row_vecs = c.C * es / 16;
+        const int pad_cells = Hp * Wp - c.H * c.W;
+        if (pad_cells > 0) {
+            const dim3 zgrid((unsigned)(((size_t)pad_cells * row_vecs + 255) / 256), c.N);
+            zero_padding_cells<<<zgrid, 256, 0, s>>>((uint4*)xp, row_vecs, c.H, c.W, Hp, Wp, c.pt, c.pl);
+        }
+        if (es == 2) nchw_to_padded_nhwc_vec<uint16_t><<<vgrid, 256, 0, s>>>((const uint16_t*)X->data, (uint16_t*)xp, c.C, c.H, c.W, Hp, Wp, c.pt, c.pl);
+        else         nchw_to_padded_nhwc_vec<uint8_t><<<vgrid, 256, 0, s>>>((const uint8_t*)X->data, (uint8_t*)xp, c.C, c.H, c.W, Hp, Wp, c.pt, c.pl);
+    }
     if (es == 2) {
-        nchw_to_padded_nhwc<uint16_t><<<tgrid, 256, 0, s>>>((const uint16_t*)X->data, (uint16_t*)xp, c.C, c.H, c.W, Hp, Wp, c.pt, c.pl);
+        if (!vec_copy) nchw_to_padded_nhwc<uint16_t><<<tgrid, 256, 0, s>>>((const uint16_t*)X->data, (uint16_t*)xp, c.C, c.H, c.W, Hp, Wp, c.pt, c.pl);
         if (dw == DTYPE_INT8 && dx == DTYPE_BFLOAT16)
             int8_filters_to_tap_major<true><<<wgrid, 256, 0, s>>>((const int8_t*)W->data, (uint16_t*)wt, c.M, c.C, taps);
         else if (dw == DTYPE_INT8)
@@ -136,7 +217,7 @@ bool conv_tc_run(const Tensor* X, const Tensor* W, const Tensor* B, Tensor* Y, c
         else
             filters_to_tap_major<uint16_t><<<wgrid, 256, 0, s>>>((const uint16_t*)W->data, (uint16_t*)wt, c.M, c.C, taps);
     } else {
-        nchw_to_padded_nhwc<uint8_t><<<tgrid, 256, 0, s>>>((const uint8_t*)X->data, (uint8_t*)xp, c.C, c.H, c.W, Hp, Wp, c.pt, c.pl);
+        if (!vec_copy) nchw_to_padded_nhwc<uint8_t><<<tgrid, 256, 0, s>>>((const uint8_t*)X->data, (uint8_t*)xp, c.C, c.H, c.W, Hp, Wp, c.pt, c.pl);
         filters_to_tap_major<uint8_t><<<wgrid, 256, 0, s>>>((const uint8_t*)W->data, (uint8_t*)wt, c.M, c.C, taps);
     }
     if (!TOPS_CHECK_LAUNCH("conv2d_forward (layout copies)")) return false;
@@ -211,6 +292,8 @@ bool shifted_gemm_launch(const ShiftedGemm& g) {
     p.relu = g.relu;
     p.residual = g.residual;
     p.lv = g.lv;
+    p.y_cl = g.y_channels_last;
+    p.res_cl = g.residual_channels_last;
     p.stage_tx = (uint32_t)(kTileABytes + n_cols * kRowBytes);
     const uint32_t idesc = umma::instr_desc(g.a_format, g.b_format, kBM, (uint32_t)n_cols);
     const int tiles = p.tiles_m * p.tiles_n;
@@ -219,11 +302,7 @@ bool shifted_gemm_launch(const ShiftedGemm& g) {
     if (g.fp8 && epi != kEpiPlain) return false;                     // the quantised extras exist for 16-bit operands only
 #define TOPS_CONV_LAUNCH(F8, E)                                                                                              \
     do {                                                                                                                     \
-        static bool attr = false;                                                                                            \
-        if (!attr) {                                                                                                         \
-            cudaFuncSetAttribute(tc_kernel<F8, kModeConv, E>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)tc_smem_bytes(kModeConv, E)); \
-            attr = true;                                                                                                     \
-        }                                                                                                                    \
+        if (!ensure_dynamic_smem((const void*)tc_kernel<F8, kModeConv, E>, tc_smem_bytes(kModeConv, E))) return false;          \
         tc_kernel<F8, kModeConv, E><<<grid, tc_threads(kModeConv, E), tc_smem_bytes(kModeConv, E), s>>>(map_a, map_b, p, idesc);   \
     } while (0)
     if (g.fp8) TOPS_CONV_LAUNCH(true, kEpiPlain);

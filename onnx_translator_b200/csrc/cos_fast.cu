@@ -108,14 +108,9 @@ bool cos_fast(const Tensor* x, Tensor* y, const double* lut) {
     if (!st) return true;
     const int smem = 4096 * (int)sizeof(double2);
     cudaStream_t s = current_stream();
-    static bool attr_done = false;
-    if (!attr_done) {
-        cudaFuncSetAttribute(cos_fast_kernel<DTYPE_FLOAT32>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
-        cudaFuncSetAttribute(cos_fast_kernel<DTYPE_FLOAT16>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
-        cudaFuncSetAttribute(cos_fast_kernel<DTYPE_BFLOAT16>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
-        cudaFuncSetAttribute(cos_selftest_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
-        attr_done = true;
-    }
+    const void* kernel = dt == DTYPE_FLOAT32 ? (const void*)cos_fast_kernel<DTYPE_FLOAT32>
+                       : dt == DTYPE_FLOAT16 ? (const void*)cos_fast_kernel<DTYPE_FLOAT16> : (const void*)cos_fast_kernel<DTYPE_BFLOAT16>;
+    if (!ensure_dynamic_smem(kernel, (size_t)smem)) return false;    // the general kernel computes the result; the error stays recorded
     if (x->size == 0) return true;
     const int vec_ok = aligned_to(x->data, 16) && aligned_to(y->data, 16);
     const int V = 16 / dtype_bytes(dt);
@@ -136,9 +131,7 @@ TOPS_API long long tops_selftest_cos(void) {
     DeviceState* st = acquire_device();
     const double* lut = cos_lut_device();
     if (!st || !lut) return -1;
-    Tensor dummy_x{}, dummy_y{};
-    dummy_x.dtype = dummy_y.dtype = DTYPE_FLOAT32;          // sets the shared-memory attribute once
-    cos_fast(&dummy_x, &dummy_y, lut);
+    if (!ensure_dynamic_smem((const void*)cos_selftest_kernel, 4096 * sizeof(double2))) return -1;
     unsigned long long* counter = nullptr;
     if (!TOPS_CUDA_OK(cudaMalloc(&counter, sizeof(*counter)))) return -1;
     cudaStream_t s = current_stream();

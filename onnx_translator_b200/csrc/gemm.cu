@@ -77,6 +77,67 @@ __global__ void __launch_bounds__(256) gemm_exact_kernel(const void* __restrict_
         }
 }
 
+// Few outputs, long reductions (a classifier layer on one image: 1 x 4096 times 4096 x 10): the 64 x 64 tiling
+// above would run one CTA that stops at two barriers every 16 steps of k.  Here a CTA owns 4 x 16 outputs; 192 of
+// its threads copy the next 128-deep slab of both operands into shared memory while the other 64 walk the current
+// slab, one output each, in increasing k -- the reference's summation order, so the result stays bit-identical.
+constexpr int kSkM = 4, kSkN = 16, kSkK = 128;
+
+template <bool EXACT_PRODUCTS>
+__global__ void __launch_bounds__(256) gemm_skinny_kernel(const void* __restrict__ A, const void* __restrict__ B,
+                                                           void* __restrict__ Y, int da, int db, int dy,
+                                                           GemmShape g, BiasView bias, double alpha, double beta, BatchStrides batch) {
+    const size_t a_base = (size_t)blockIdx.z * batch.a, b_base = (size_t)blockIdx.z * batch.b, y_base = (size_t)blockIdx.z * batch.y;
+    __shared__ double sa[2][kSkM][kSkK];
+    __shared__ double sb[2][kSkN][kSkK + 1];
+    const int m0 = blockIdx.y * kSkM, n0 = blockIdx.x * kSkN;
+    const bool computes = threadIdx.x < kSkM * kSkN;
+    const int i = threadIdx.x / kSkN, j = threadIdx.x % kSkN;
+    const int chunks = (g.K + kSkK - 1) / kSkK;
+    auto fill = [&](int chunk, int buf, int first, int step) {
+        const int k0 = chunk * kSkK;
+        for (int e = first; e < (kSkM + kSkN) * kSkK; e += step) {
+            const int row = e / kSkK, kk = e - row * kSkK, k = k0 + kk;
+            double v = 0.0;
+            if (row < kSkM) {
+                const int m = m0 + row;
+                if (m < g.M && k < g.K) v = load_f64_rt(A, da, a_base + (g.transA ? (size_t)k * g.lda + m : (size_t)m * g.lda + k));
+                sa[buf][row][kk] = v;
+            } else {
+                const int n = n0 + row - kSkM;
+                if (n < g.N && k < g.K) v = load_f64_rt(B, db, b_base + (g.transB ? (size_t)n * g.ldb + k : (size_t)k * g.ldb + n));
+                sb[buf][row - kSkM][kk] = v;
+            }
+        }
+    };
+    fill(0, 0, threadIdx.x, 256);
+    __syncthreads();
+    double acc = 0.0;
+    for (int c = 0; c < chunks; c++) {
+        if (computes) {
+            const double* pa = sa[c & 1][i];
+            const double* pb = sb[c & 1][j];
+            #pragma unroll 8
+            for (int kk = 0; kk < kSkK; kk++) {
+                if (EXACT_PRODUCTS) acc = fma(pa[kk], pb[kk], acc);
+                else acc = __dadd_rn(acc, __dmul_rn(pa[kk], pb[kk]));
+            }
+        } else if (c + 1 < chunks) {
+            fill(c + 1, (c + 1) & 1, threadIdx.x - kSkM * kSkN, 256 - kSkM * kSkN);
+        }
+        __syncthreads();
+    }
+    const int m = m0 + i, n = n0 + j;
+    if (!computes || m >= g.M || n >= g.N) return;
+    double r = __dmul_rn(alpha, acc);
+    if (bias.mode != kBiasNone) {
+        const long long ci = bias_index(bias, m, n);
+        const double cv = ci >= 0 ? load_f64_rt(bias.ptr, bias.dtype, (size_t)ci) : 0.0;
+        r = __dadd_rn(r, __dmul_rn(beta, cv));
+    }
+    store_f64_rt(Y, dy, y_base + (size_t)m * g.N + n, r);
+}
+
 BiasView make_bias_view(const Tensor* C, int M, int N) {
     BiasView b;
     b.ptr = nullptr; b.dtype = DTYPE_FLOAT32; b.mode = kBiasNone; b.rows = 1; b.cols = 1;
@@ -108,12 +169,22 @@ bool gemm_exact(const Tensor* A, const Tensor* B, Tensor* Y, const GemmShape& g,
     if (!st) return false;
     const bool exact = dtype_exact_in_f32((int)A->dtype) && dtype_exact_in_f32((int)B->dtype);
     const size_t ea = (size_t)dtype_bytes((int)A->dtype), eb = (size_t)dtype_bytes((int)B->dtype), ey = (size_t)dtype_bytes((int)Y->dtype);
+    // too few 64 x 64 tiles to fill the GPU and a reduction long enough to matter: the 4 x 16 tiling
+    const bool skinny = g.K >= 4 * kSkK && (size_t)((g.M + kTile - 1) / kTile) * ((g.N + kTile - 1) / kTile) * batches < (size_t)st->sm_count / 2;
     for (int first = 0; first < batches; first += 65535) {         // grid.z limit
         const int nb = batches - first < 65535 ? batches - first : 65535;
         dim3 grid((g.N + kTile - 1) / kTile, (g.M + kTile - 1) / kTile, nb);
         const void* a = (const char*)A->data + (size_t)first * batch.a * ea;
         const void* b = (const char*)B->data + (size_t)first * batch.b * eb;
         void* y = (char*)Y->data + (size_t)first * batch.y * ey;
+        if (skinny) {
+            const dim3 sgrid((g.N + kSkN - 1) / kSkN, (g.M + kSkM - 1) / kSkM, nb);
+            if (exact) gemm_skinny_kernel<true><<<sgrid, 256, 0, current_stream()>>>(a, b, y, (int)A->dtype, (int)B->dtype, (int)Y->dtype, g, bias,
+                                                                                     (double)alpha, (double)beta, batch);
+            else gemm_skinny_kernel<false><<<sgrid, 256, 0, current_stream()>>>(a, b, y, (int)A->dtype, (int)B->dtype, (int)Y->dtype, g, bias,
+                                                                                (double)alpha, (double)beta, batch);
+            continue;
+        }
         if (exact) gemm_exact_kernel<true><<<grid, 256, 0, current_stream()>>>(a, b, y, (int)A->dtype, (int)B->dtype, (int)Y->dtype, g, bias,
                                                                                (double)alpha, (double)beta, batch);
         else gemm_exact_kernel<false><<<grid, 256, 0, current_stream()>>>(a, b, y, (int)A->dtype, (int)B->dtype, (int)Y->dtype, g, bias,

@@ -124,10 +124,9 @@ static bool gemm_split_f32(const Tensor* A, const Tensor* B, Tensor* Y, const Ge
         const uint32_t idesc = umma::instr_desc(1u, 1u, kBM, kBN);
         const int tiles = p.tiles_m * p.tiles_n;
         const int grid = tiles < st->sm_count ? tiles : st->sm_count;
-        static bool attr = false;
-        if (!attr) { cudaFuncSetAttribute(tc_kernel<false, kModeSplit>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)tc_smem_bytes(kModeSplit)); attr = true; }
-        tc_kernel<false, kModeSplit><<<grid, tc_threads(kModeSplit), tc_smem_bytes(kModeSplit), s>>>(map_a, map_b, p, idesc);
-        ok = TOPS_CHECK_LAUNCH("gemm_forward (tensor cores, float32 split)");
+        ok = ensure_dynamic_smem((const void*)tc_kernel<false, kModeSplit>, tc_smem_bytes(kModeSplit));
+        if (ok) tc_kernel<false, kModeSplit><<<grid, tc_threads(kModeSplit), tc_smem_bytes(kModeSplit), s>>>(map_a, map_b, p, idesc);
+        ok = ok && TOPS_CHECK_LAUNCH("gemm_forward (tensor cores, float32 split)");
         if (ok) count_tensor_core_launch();
     }
     cudaFreeAsync(ap, s);
@@ -192,12 +191,10 @@ bool gemm_tensor_core(const Tensor* A, const Tensor* B, Tensor* Y, const GemmSha
     const int grid = tiles < st->sm_count ? tiles : st->sm_count;
     cudaStream_t s = current_stream();
     if (fp8) {
-        static bool attr = false;
-        if (!attr) { cudaFuncSetAttribute(tc_kernel<true, kModeGemm>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)tc_smem_bytes(kModeGemm)); attr = true; }
+        if (!ensure_dynamic_smem((const void*)tc_kernel<true, kModeGemm>, tc_smem_bytes(kModeGemm))) return true;    // error recorded
         tc_kernel<true, kModeGemm><<<grid, tc_threads(kModeGemm), tc_smem_bytes(kModeGemm), s>>>(map_a, map_b, p, idesc);
     } else {
-        static bool attr = false;
-        if (!attr) { cudaFuncSetAttribute(tc_kernel<false, kModeGemm>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)tc_smem_bytes(kModeGemm)); attr = true; }
+        if (!ensure_dynamic_smem((const void*)tc_kernel<false, kModeGemm>, tc_smem_bytes(kModeGemm))) return true;
         tc_kernel<false, kModeGemm><<<grid, tc_threads(kModeGemm), tc_smem_bytes(kModeGemm), s>>>(map_a, map_b, p, idesc);
     }
     TOPS_CHECK_LAUNCH("gemm_forward (tensor cores)");

@@ -152,6 +152,68 @@ __global__ void __launch_bounds__(256) activations_to_levels_few_channels(const 
     }
 }
 
+// The same from a channels-last source [N][H][W][C] (the float32 edges a fused graph keeps between its
+// quantised convolutions): source and destination both run along the channels, so there is nothing to
+// transpose.  A thread owns eight consecutive channels of one position: 32 bytes in, 16 bytes out.
+template <int XK, bool SIGNED>
+__global__ void __launch_bounds__(256) channels_last_to_levels(const void* __restrict__ x, uint16_t* __restrict__ z, QGeom g, int images,
+                                                               const float* __restrict__ scale_ptr, const void* __restrict__ zero_ptr) {
+    const int groups = (g.C + 7) >> 3, plane = g.H * g.W;
+    const size_t total = (size_t)images * plane * groups;
+    int zero = 0;
+    if (zero_ptr) zero = SIGNED ? (int)*(const int8_t*)zero_ptr : (int)*(const uint8_t*)zero_ptr;
+    const float zf = (float)zero;
+    float scale = 1.0f, inv = 1.0f;
+    if (XK == 0) { scale = __ldg(scale_ptr); inv = quantize_reciprocal(scale); }
+    const bool vec = (g.C & 7) == 0;
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
+        const int cg = (int)(i % groups);
+        const size_t t = i / groups;
+        const int p = (int)(t % plane), n = (int)(t / plane);
+        const int h = p / g.W, w = p - h * g.W;
+        size_t src_p = (size_t)p;
+        if (g.sub) src_p = (size_t)(2 * h) * g.srcW + 2 * w;
+        const size_t at = ((size_t)n * g.src_plane + src_p) * g.C + (size_t)cg * 8;
+        float v[8];
+        if (XK == 0) {
+            if (vec) {
+                const float4 a = __ldg((const float4*)((const float*)x + at)), b = __ldg((const float4*)((const float*)x + at + 4));
+                v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w; v[4] = b.x; v[5] = b.y; v[6] = b.z; v[7] = b.w;
+            } else {
+                #pragma unroll
+                for (int e = 0; e < 8; e++) v[e] = cg * 8 + e < g.C ? __ldg((const float*)x + at + e) : 0.0f;
+            }
+        } else {
+            #pragma unroll
+            for (int e = 0; e < 8; e++) {
+                const uint8_t code = cg * 8 + e < g.C ? ((const uint8_t*)x)[at + e] : (uint8_t)zero;
+                v[e] = (float)(SIGNED ? (int)(int8_t)code : (int)code);
+            }
+        }
+        uint32_t packed[4];
+        #pragma unroll
+        for (int e = 0; e < 8; e += 2) {
+            float level[2];
+            #pragma unroll
+            for (int k = 0; k < 2; k++) {
+                if (cg * 8 + e + k >= g.C) level[k] = 0.0f;
+                else if (XK == 0) level[k] = quantize_level_8bit<SIGNED ? DTYPE_INT8 : DTYPE_UINT8>(v[e + k], scale, inv, zf);
+                else level[k] = __fsub_rn(v[e + k], zf);
+            }
+            packed[e >> 1] = __byte_perm(__float_as_uint(level[0]), __float_as_uint(level[1]), 0x7632);
+        }
+        int A = h + g.pt, B = w + g.pl, slot = 0;
+        if (g.S == 2) { slot = ((A & 1) * 2 + (B & 1)) * g.C; A >>= 1; B >>= 1; }
+        uint16_t* dst = z + (((size_t)n * g.Hz + A) * g.Wz + B) * g.Cz + slot + cg * 8;
+        if (vec) {
+            *reinterpret_cast<uint4*>(dst) = make_uint4(packed[0], packed[1], packed[2], packed[3]);
+        } else {
+            #pragma unroll
+            for (int e = 0; e < 8; e++) if (cg * 8 + e < g.C) dst[e] = (uint16_t)(packed[e >> 1] >> ((e & 1) * 16));
+        }
+    }
+}
+
 // int8 filter codes [M][C][KH][KW] -> bfloat16 levels in the channel order of the activations:
 // [KHz*KWz][M][Cz], or with `merged` [KHz][M][KWz*Cz] (the taps of one filter row side by side, for
 // the layout in which one activation row covers KWz neighbouring cells)
@@ -220,8 +282,9 @@ static int qconv_run(const char* name, const QConvCall& q) {
     Tensor* Y = q.y;
     if (!X || !X->data || !Wq || !Wq->data || Wq->ndim != 4 || X->ndim != 4 || (!Y && !q.y_levels))
         return qconv_fail(name, TOPS_ERR_INVALID, "null argument, or tensors that are not 4-D, or no output given", Y);
-    const int N = q.x_levels ? q.x_shape[0] : X->shape[0], C = q.x_levels ? q.x_shape[1] : X->shape[1];
-    const int H = q.x_levels ? q.x_shape[2] : X->shape[2], W = q.x_levels ? q.x_shape[3] : X->shape[3];
+    const bool x_cl = !q.x_levels && q.x_channels_last;            // x is [N, H, W, C]
+    const int N = q.x_levels ? q.x_shape[0] : X->shape[0], C = q.x_levels ? q.x_shape[1] : X->shape[x_cl ? 3 : 1];
+    const int H = q.x_levels ? q.x_shape[2] : X->shape[x_cl ? 1 : 2], W = q.x_levels ? q.x_shape[3] : X->shape[x_cl ? 2 : 3];
     const int M = Wq->shape[0], KH = Wq->shape[2], KW = Wq->shape[3];
     QGeom g;
     int OH, OW, dil_h, dil_w;
@@ -248,7 +311,11 @@ static int qconv_run(const char* name, const QConvCall& q) {
         return qconv_fail(name, TOPS_ERR_UNSUPPORTED, "wants int8 filter codes, one float32 activation scale, one float32 scale per output channel, a float32 bias", Y);
     const size_t out_elems = (size_t)N * M * OH * OW;
     int dy = DTYPE_FLOAT32;
-    if (Y) {
+    if (Y && q.y_channels_last) {
+        dy = (int)Y->dtype;
+        if (!Y->data || Y->ndim != 4 || Y->shape[0] != N || Y->shape[1] != OH || Y->shape[2] != OW || Y->shape[3] != M || dy != DTYPE_FLOAT32)
+            return qconv_fail(name, TOPS_ERR_INVALID, "a channels-last Y must be float32 [N, OH, OW, M]", Y);
+    } else if (Y) {
         dy = (int)Y->dtype;
         if (!Y->data || Y->ndim != 4 || Y->shape[0] != N || Y->shape[1] != M || Y->shape[2] != OH || Y->shape[3] != OW ||
             (dy != DTYPE_FLOAT32 && dy != DTYPE_BFLOAT16 && dy != DTYPE_FLOAT16))
@@ -291,14 +358,20 @@ static int qconv_run(const char* name, const QConvCall& q) {
         if (cudaMallocAsync(&z, z_bytes + 128, s) != cudaSuccess) { cudaGetLastError(); return qconv_fail(name, TOPS_ERR_OOM, "scratch", nullptr); }
         // padding cells and padding channels are zero; a 1x1 convolution without padding over a channel
         // count that is a multiple of 8 has neither
-        const bool every_cell_written = g.S == 1 && g.Hz == H && g.Wz == W && g.Cz == C;
+        const bool every_cell_written = g.S == 1 && g.Hz == g.H && g.Wz == g.W && g.Cz == C;
         ok = every_cell_written || TOPS_CUDA_OK(cudaMemsetAsync(z, 0, z_bytes + 128, s));
         const dim3 grid((H * W + 63) / 64, N, (C + 63) / 64);
         const dim3 grid_few((H * W + 255) / 256, N);
         const void* zero_ptr = zero_given ? q.x_zero->data : nullptr;
         const float* scale_ptr = (const float*)q.x_scale->data;
         const bool is_signed = code_dt == DTYPE_INT8;
-        if (C <= 8) {
+        if (x_cl) {
+            const int cl_grid = grid_for((size_t)N * g.H * g.W * ((C + 7) / 8), 256, st->sm_count, 8);
+            if (x_is_float && is_signed)       channels_last_to_levels<0, true><<<cl_grid, 256, 0, s>>>(X->data, (uint16_t*)z, g, N, scale_ptr, zero_ptr);
+            else if (x_is_float)               channels_last_to_levels<0, false><<<cl_grid, 256, 0, s>>>(X->data, (uint16_t*)z, g, N, scale_ptr, zero_ptr);
+            else if (is_signed)                channels_last_to_levels<1, true><<<cl_grid, 256, 0, s>>>(X->data, (uint16_t*)z, g, N, scale_ptr, zero_ptr);
+            else                               channels_last_to_levels<1, false><<<cl_grid, 256, 0, s>>>(X->data, (uint16_t*)z, g, N, scale_ptr, zero_ptr);
+        } else if (C <= 8) {
             if (x_is_float && is_signed)       activations_to_levels_few_channels<0, true><<<grid_few, 256, 0, s>>>(X->data, (uint16_t*)z, g, scale_ptr, zero_ptr);
             else if (x_is_float)               activations_to_levels_few_channels<0, false><<<grid_few, 256, 0, s>>>(X->data, (uint16_t*)z, g, scale_ptr, zero_ptr);
             else if (is_signed)                activations_to_levels_few_channels<1, true><<<grid_few, 256, 0, s>>>(X->data, (uint16_t*)z, g, scale_ptr, zero_ptr);
@@ -371,6 +444,8 @@ static int qconv_run(const char* name, const QConvCall& q) {
         sg.relu = q.relu ? 1 : 0;
         sg.residual = (R && R->data) ? (const float*)R->data : nullptr;
         sg.lv = lv;
+        sg.y_channels_last = (Y && q.y_channels_last) ? 1 : 0;
+        sg.residual_channels_last = (sg.residual && q.residual_channels_last) ? 1 : 0;
         ok = shifted_gemm_launch(sg);
     }
     if (!q.x_levels) cudaFreeAsync(z, s);

@@ -82,6 +82,34 @@ DeviceState* acquire_device() {
 
 static int current_device_index() { return t_device >= 0 ? t_device : default_device(); }
 
+// (kernel, device) pairs whose dynamic shared-memory limit has been raised.  A flat table under the device
+// mutex: a few dozen kernels at most, looked up once per launch.
+struct SmemOptIn { const void* kernel; size_t bytes; unsigned device_mask; };
+static SmemOptIn g_smem_opt_in[128];
+static int       g_smem_opt_in_count = 0;
+
+bool ensure_dynamic_smem(const void* kernel, size_t bytes) {
+    const int dev = current_device_index();
+    if (dev < 0 || dev >= kMaxDevices) return false;
+    std::lock_guard<std::mutex> lock(g_device_mutex);
+    SmemOptIn* slot = nullptr;
+    for (int i = 0; i < g_smem_opt_in_count; i++)
+        if (g_smem_opt_in[i].kernel == kernel && g_smem_opt_in[i].bytes == bytes) { slot = &g_smem_opt_in[i]; break; }
+    if (slot && (slot->device_mask >> dev & 1u)) return true;
+    if (!TOPS_CUDA_OK(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bytes))) return false;
+    if (!slot && g_smem_opt_in_count < 128) { slot = &g_smem_opt_in[g_smem_opt_in_count++]; *slot = SmemOptIn{kernel, bytes, 0u}; }
+    if (slot) slot->device_mask |= 1u << dev;      // table full: the attribute is simply set again next time
+    return true;
+}
+
+// Host-only view of that bookkeeping for the tests: how many devices hold the opt-in of entry `index`
+// (-1 past the end).
+int smem_opt_in_devices(int index) {
+    std::lock_guard<std::mutex> lock(g_device_mutex);
+    if (index < 0 || index >= g_smem_opt_in_count) return -1;
+    return __builtin_popcount(g_smem_opt_in[index].device_mask);
+}
+
 cudaStream_t current_stream() {
     const int dev = current_device_index();
     if (dev < 0 || dev >= kMaxDevices) return nullptr;
@@ -378,6 +406,51 @@ TOPS_API int tops_sync(void) {
     return ok ? tops_last_error() : tops_last_error();
 }
 TOPS_API int tops_set_memory_mode(int managed) { g_managed.store(managed ? 1 : 0); return TOPS_OK; }
+
+// ---- stream capture: a fixed sequence of operator calls as one CUDA graph ---------------------------------------
+// Everything an operator enqueues (kernels, memsets, its stream-ordered scratch allocations and their releases)
+// lands on the current stream, so capturing that stream while the calls are repeated records the whole sequence;
+// launching the instantiated graph then costs one driver call instead of one per kernel.
+struct CapturedGraph { cudaGraphExec_t exec; int device; };
+
+TOPS_API int tops_capture_begin(void) {
+    if (!acquire_device()) return tops_last_error();
+    if (managed_mode()) { set_error(TOPS_ERR_UNSUPPORTED, "tops_capture_begin: managed-memory mode synchronises after every operator"); return tops_last_error(); }
+    return TOPS_CUDA_OK(cudaStreamBeginCapture(current_stream(), cudaStreamCaptureModeRelaxed)) ? TOPS_OK : tops_last_error();
+}
+
+TOPS_API void* tops_capture_end(void) {
+    if (!acquire_device()) return nullptr;
+    cudaGraph_t graph = nullptr;
+    const cudaError_t e = cudaStreamEndCapture(current_stream(), &graph);
+    if (e != cudaSuccess || !graph) {
+        cudaGetLastError();
+        set_error(TOPS_ERR_CUDA, "tops_capture_end: the sequence could not be captured (%s)", cudaGetErrorString(e));
+        return nullptr;
+    }
+    cudaGraphExec_t exec = nullptr;
+    const bool ok = TOPS_CUDA_OK(cudaGraphInstantiate(&exec, graph, 0));
+    cudaGraphDestroy(graph);
+    if (!ok) return nullptr;
+    CapturedGraph* out = new (std::nothrow) CapturedGraph{exec, current_device_index()};
+    if (!out) { cudaGraphExecDestroy(exec); set_error(TOPS_ERR_OOM, "tops_capture_end: host allocation failed"); }
+    return out;
+}
+
+TOPS_API int tops_capture_launch(void* captured) {
+    CapturedGraph* g = (CapturedGraph*)captured;
+    if (!g) { set_error(TOPS_ERR_INVALID, "tops_capture_launch: null graph"); return tops_last_error(); }
+    if (!acquire_device()) return tops_last_error();
+    if (g->device != current_device_index()) { set_error(TOPS_ERR_INVALID, "tops_capture_launch: captured on device %d", g->device); return tops_last_error(); }
+    return TOPS_CUDA_OK(cudaGraphLaunch(g->exec, current_stream())) ? TOPS_OK : tops_last_error();
+}
+
+TOPS_API void tops_capture_free(void* captured) {
+    CapturedGraph* g = (CapturedGraph*)captured;
+    if (!g) return;
+    cudaGraphExecDestroy(g->exec);
+    delete g;
+}
 
 TOPS_API Tensor* tops_create_uninit(const int* shape, int ndim, DataType dtype) { return allocate(shape, ndim, dtype, false); }
 

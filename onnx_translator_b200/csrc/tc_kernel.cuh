@@ -63,6 +63,8 @@ struct TcParams {
     int relu = 0;          // clamp the result at zero before it is stored (v > 0 ? v : 0)
     const float* residual = nullptr;   // convolution mode: float32 tensor of the output's shape added before the clamp
     LevelsOut lv;                      // convolution mode: also / instead write the result as levels for the next convolution
+    int y_cl = 0;                      // convolution mode: Y (float32) is stored channels-last [N][OH][OW][OC] instead of NCHW
+    int res_cl = 0;                    // convolution mode: the residual is stored channels-last
 };
 
 __device__ __forceinline__ void tile_coords(int tile, int tiles_m, int tiles_n, int& tm, int& tn) {
@@ -242,7 +244,7 @@ tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUt
             // convolution mode: where this lane's row goes in the NCHW output, and the residual values
             // of the first column chunk, requested before the accumulator is even complete
             bool conv_row = false;
-            size_t conv_base = 0, plane_out = 0;
+            size_t conv_base = 0, plane_out = 0, cl_base = 0;
             uint16_t* levels_row = nullptr;
             float res_next[kW];
             constexpr bool with_res = MODE == kModeConv && (EPI & kEpiResidual) != 0;
@@ -252,6 +254,8 @@ tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUt
                 conv_row = img < p.cv.images && oh < p.cv.OH && ow < p.cv.OW;
                 plane_out = (size_t)p.cv.OH * p.cv.OW;
                 conv_base = ((size_t)img * p.cv.OC + (size_t)tn * kBN) * plane_out + (size_t)oh * p.cv.OW + ow;
+                // the same element in a channels-last tensor: the row's channels are contiguous
+                cl_base = (((size_t)img * p.cv.OH + oh) * p.cv.OW + ow) * (size_t)p.cv.OC + (size_t)tn * kBN;
                 if constexpr ((EPI & kEpiLevels) != 0) {
                     // where this row's levels go: it is input pixel (oh, ow) of the next convolution -- worked out
                     // once per tile, not once per column chunk (two integer divisions per lane)
@@ -261,6 +265,21 @@ tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUt
                 }
             }
             auto fetch_residual = [&](int chunk, float (&dst)[kW]) {
+                if (p.res_cl) {                                    // kW consecutive floats of this row
+                    const float* src = p.residual + cl_base + chunk * kW;
+                    const int left = p.N - (tn * kBN + chunk * kW);
+                    if (conv_row && left >= kW && (p.N & 3) == 0) {
+                        #pragma unroll
+                        for (int j = 0; j < kW; j += 4) {
+                            const float4 v4 = __ldg((const float4*)(src + j));
+                            dst[j] = v4.x; dst[j + 1] = v4.y; dst[j + 2] = v4.z; dst[j + 3] = v4.w;
+                        }
+                    } else {
+                        #pragma unroll
+                        for (int j = 0; j < kW; j++) dst[j] = (conv_row && j < left) ? __ldg(src + j) : 0.0f;
+                    }
+                    return;
+                }
                 const float* src = p.residual + conv_base + (size_t)(chunk * kW) * plane_out;
                 #pragma unroll
                 for (int j = 0; j < kW; j++)
@@ -383,6 +402,15 @@ tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUt
                             }
                             if (p.Y == nullptr) {
                                 // levels only
+                            } else if (p.y_cl) {                       // float32, channels-last: kW consecutive floats of this row
+                                float* dst = (float*)p.Y + cl_base + c * kW;
+                                if (n0 + kW <= p.N && (p.N & 3) == 0) {
+                                    #pragma unroll
+                                    for (int j = 0; j < kW; j += 4) *(float4*)(dst + j) = make_float4(v[j], v[j + 1], v[j + 2], v[j + 3]);
+                                } else {
+                                    #pragma unroll
+                                    for (int j = 0; j < kW; j++) if (n0 + j < p.N) dst[j] = v[j];
+                                }
                             } else if (p.dy == DTYPE_FLOAT32) {
                                 float* dst = (float*)p.Y + base;
                                 #pragma unroll

@@ -57,15 +57,16 @@ class Tensor_:
 class Ops:
     """Base of every operator class; holds the library and the execution templates."""
     _lib = None
+    _recorder = None                         # set while a call plan is being recorded (nn/plan.py)
 
     @classmethod
     def _get_lib(cls):
-        if cls._lib is None:
+        if Ops._lib is None:
             lib = capi.load()                # raises when the CUDA library is not built
             lib.init_cos_lut()
             capi.check(lib)                  # raises when there is no usable CUDA device
-            cls._lib = lib
-        return cls._lib
+            Ops._lib = lib
+        return Ops._lib
 
     def __init__(self, inputs, outputs):
         self.inputs = inputs
@@ -78,7 +79,7 @@ class Ops:
     def lib(self):
         """The operator library, opened at the first use: a node can be constructed (and a graph built and
         inspected) on a machine without a GPU; running it there raises."""
-        return self._get_lib()
+        return Ops._recorder or self._get_lib()
 
     # -- marshalling ---------------------------------------------------------------------------
     def _numpy_to_ctensor(self, arr, dtype: str):
@@ -177,3 +178,4 @@ def synchronize() -> None:
 
 
 from .graph import Graph, qdq_resnet50, small_cnn  # noqa: E402  (the graph runner builds on the classes above)
+from .plan import GraphPlan  # noqa: E402

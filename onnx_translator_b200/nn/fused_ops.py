@@ -28,7 +28,10 @@ class QLinearConv(Ops):
     * ``levels_in``: x is the levels tensor the producing QLinearConv wrote for this convolution.
     * ``next_conv`` (dict with pads, strides, dilations, kernel): the result is handed to the next quantised
       convolution as integer levels (quantised with next_scale / next_zero) instead of as float32 -- or, with
-      ``also_float``, besides the float32 tensor (two outputs), when other nodes read the float32 values too."""
+      ``also_float``, besides the float32 tensor (two outputs), when other nodes read the float32 values too.
+    * ``x_channels_last`` / ``y_channels_last`` / ``residual_channels_last``: that float32 tensor is stored
+      [N, H, W, C] instead of the ABI's NCHW.  ``Graph.fused()`` sets these on edges that only fused convolutions
+      touch; such a ``Tensor`` carries ``channels_last = True`` and its NCHW shape in ``logical_shape``."""
 
     def __init__(self, inputs, outputs, pads, strides, dilations, relu, dtype="float32", from_float=False):
         super().__init__(inputs, outputs)
@@ -37,6 +40,7 @@ class QLinearConv(Ops):
         self.levels_in = False
         self.next_conv = None
         self.also_float = False       # with next_conv: outputs are (float32 tensor, levels tensor) instead of the levels alone
+        self.x_channels_last = self.y_channels_last = self.residual_channels_last = False
         # The filters in the layout the tensor cores read, made by the library on the first call and reused while
         # the node keeps seeing the same weight array (replace the array, or call drop_filter_cache(), after
         # changing weights in place).
@@ -70,16 +74,18 @@ class QLinearConv(Ops):
 
     def forward(self, x: Tensor, x_scale: Tensor, x_zero: Tensor, wq: Tensor, w_scale: Tensor, b: Tensor = None,
                 residual: Tensor = None, next_scale: Tensor = None, next_zero: Tensor = None) -> dict:
-        n, _, h, w = x.logical_shape if self.levels_in else x.data.shape
+        n, _, h, w = x.logical_shape if (self.levels_in or self.x_channels_last) else x.data.shape
         m, _, kh, kw = wq.data.shape
         out_shape = (n, m,
                      _pooled_extent(h, self.pads[0], self.pads[2], self.dilations[0], kh, self.strides[0]),
                      _pooled_extent(w, self.pads[1], self.pads[3], self.dilations[1], kw, self.strides[1]))
-        if residual is not None and tuple(residual.data.shape) != out_shape:
-            # a broadcasting Add is not what the fused epilogue does: run the three operators
+        if residual is not None and self.residual_channels_last and tuple(residual.logical_shape) != out_shape:
+            raise ValueError(f"{self.name}: the channels-last residual has shape {residual.logical_shape}, the convolution gives {out_shape}")
+        if residual is not None and not self.residual_channels_last and (tuple(residual.data.shape) != out_shape or residual.dtype != "float32"):
+            # a broadcasting or converting Add is not what the fused epilogue does: run the three operators
             from .Operators import ADD, RELU
             plain = QLinearConv([], [], self.pads, self.strides, self.dilations, False, self.dtype, self.from_float)
-            plain.levels_in = self.levels_in
+            plain.levels_in, plain.x_channels_last = self.levels_in, self.x_channels_last
             y = ADD([], [], dtype=self.dtype).forward(plain.forward(x, x_scale, x_zero, wq, w_scale, b)["tensor"], residual)["tensor"]
             return self._publish(RELU([], [], dtype=self.dtype).forward(y)["tensor"] if self.relu else y)
 
@@ -93,6 +99,7 @@ class QLinearConv(Ops):
             call.x_shape = (ctypes.c_int * 4)(*x.logical_shape)
         call.x_scale, call.x_zero, call.w_codes, call.w_scale = ptr(x_scale), ptr(x_zero), ptr(wq), ptr(w_scale)
         call.bias, call.residual = ptr(b), ptr(residual)
+        call.x_channels_last, call.residual_channels_last = int(self.x_channels_last), int(self.residual_channels_last and residual is not None)
         call.params, call.relu = ctypes.pointer(params), int(self.relu)
         key = (id(wq.data), tuple(wq.data.shape), bool(self.levels_in), tuple(self.pads), tuple(self.strides), tuple(self.dilations))
         if key != self._filter_cache_key:
@@ -107,9 +114,10 @@ class QLinearConv(Ops):
             call.next_scale, call.next_zero = ptr(next_scale), ptr(next_zero)
             call.next_params = ctypes.pointer(next_params)
             call.next_kernel = (ctypes.c_int * 2)(*self.next_conv["kernel"])
+        stored_shape = (out_shape[0], out_shape[2], out_shape[3], out_shape[1]) if self.y_channels_last else out_shape
         if self.next_conv is None or self.also_float:
-            y_handle = self._new_output(out_shape, self.dtype)
-            call.y = ctypes.cast(y_handle, ctypes.c_void_p)
+            y_handle = self._new_output(stored_shape, self.dtype)
+            call.y, call.y_channels_last = ctypes.cast(y_handle, ctypes.c_void_p), int(self.y_channels_last)
         rc = self.lib.tops_qconv_forward(ctypes.byref(call))
         for hdl in handles.values():
             self.lib.free_tensor(hdl)
@@ -117,7 +125,9 @@ class QLinearConv(Ops):
             if y_handle is not None:
                 self.lib.free_tensor(y_handle)
             capi.check(self.lib)
-        result = None if y_handle is None else self._finish([], y_handle, out_shape, self.dtype)
+        result = None if y_handle is None else self._finish([], y_handle, stored_shape, self.dtype)
+        if result is not None and self.y_channels_last:
+            result.channels_last, result.logical_shape = True, out_shape
         if levels is not None:
             out = Tensor(*levels.shape, dtype="bfloat16", data=levels)
             out.logical_shape = out_shape

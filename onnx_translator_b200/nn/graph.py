@@ -98,8 +98,15 @@ class Graph:
             w_codes, w_scale, w_zero = (self.initializers[e] for e in dq_w.inputs)
             strides, dil = list(conv.strides), list(conv.dilations)
             covered = conv.group == 1 and (strides == [1, 1] or (strides == [2, 2] and dil == [1, 1]))
-            if (not covered or w_codes.dtype != "int8" or w_scale.dtype != "float32" or np.any(w_zero.numpy() != 0)
-                    or w_scale.data_size != w_codes.size[0] or self.initializers[q.inputs[1]].data_size != 1):
+            m_out = int(w_codes.size[0])
+            # DequantizeLinear has no axis: its scale broadcasts over TRAILING dimensions, so only [M, 1, 1, 1] scales per
+            # output channel, which is what the fused node applies; a float16 DequantizeLinear would round each
+            # dequantised value, which the fused node does not
+            per_channel = tuple(w_scale.size) == (m_out, 1, 1, 1) and tuple(w_zero.size) == tuple(w_scale.size)
+            x_zero = self.initializers[q.inputs[2]]
+            if (not covered or not per_channel or w_codes.dtype != "int8" or w_scale.dtype != "float32" or np.any(w_zero.numpy() != 0)
+                    or (dq_x.dtype or "float32") != "float32" or (dq_w.dtype or "float32") != "float32" or x_zero.dtype != q.dtype
+                    or self.initializers[q.inputs[1]].data_size != 1 or x_zero.data_size != 1):
                 continue
             relu, out_edge = False, conv.outputs[0]
             if sole_consumer(out_edge):
@@ -183,6 +190,28 @@ class Graph:
                 producer_node.also_float = True
                 producer_node.outputs = [edge, edge + ".levels"]
                 consumer.inputs = [edge + ".levels"] + list(consumer.inputs[1:])
+        # fourth pass: a float32 edge that only fused convolutions touch (as activations to quantise, or as the
+        # residual) never meets the ABI's NCHW rule, so it is kept channels-last -- the order the tensor-core
+        # kernel produces and consumes (contiguous 64-byte pieces per pixel instead of one element per plane)
+        readers = {}
+        for op in kept:
+            for slot, e in enumerate(op.inputs):
+                if e:
+                    readers.setdefault(e, []).append((op, slot))
+        for op in kept:
+            if kind(op) != "QLinearConv" or op.dtype != "float32" or (op.next_conv is not None and not op.also_float):
+                continue
+            edge = op.outputs[0]
+            users = readers.get(edge, [])
+            fused_only = all(kind(u) == "QLinearConv" and ((slot == 0 and u.from_float and not u.levels_in) or slot == 6) for u, slot in users)
+            if not users or not fused_only or edge in self.output_name or self.initializers[op.inputs[3]].size[0] % 4:
+                continue
+            op.y_channels_last = True
+            for u, slot in users:
+                if slot == 0:
+                    u.x_channels_last = True
+                else:
+                    u.residual_channels_last = True
         g = Graph(kept, list(self.input_name), list(self.output_name), self.model_name, self.initializers)
         g._resident = self._resident
         if hasattr(self, "macs_per_image"):
@@ -195,6 +224,12 @@ class Graph:
             for t in self.initializers.values():
                 t.to_device()
             self._resident = True
+
+    def plan(self, *inputs):
+        """Records one forward pass on ``inputs`` as a list of library calls (``nn.plan.GraphPlan``): later runs
+        replay that list -- or, after ``capture()``, launch one CUDA graph -- instead of walking the nodes."""
+        from .plan import GraphPlan
+        return GraphPlan(self, inputs)
 
     def forward(self, *inputs):
         """Runs the graph on device-resident edges and returns the output tensor (or a tuple of

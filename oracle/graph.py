@@ -4,7 +4,8 @@ operator objects the device runner executes."""
 import numpy as np
 
 
-def run(graph, port, *inputs):
+def run(graph, port, *inputs, all_edges=False):
+    """Outputs of the graph; with ``all_edges`` also the dict of every edge (name -> array) for layer-by-layer checks."""
     edges = {name: (t.numpy(), t.dtype) for name, t in graph.initializers.items()}
     for name, t in zip(graph.input_name, inputs):
         edges[name] = (t.numpy(), t.dtype)
@@ -45,4 +46,7 @@ def run(graph, port, *inputs):
             raise NotImplementedError(kind)
         edges[op.outputs[0]] = (np.asarray(y), out_dt)
     outs = tuple(edges[e][0] for e in graph.output_name)
-    return outs[0] if len(outs) == 1 else outs
+    outs = outs[0] if len(outs) == 1 else outs
+    if all_edges:
+        return outs, {name: value for name, (value, _) in edges.items()}
+    return outs
