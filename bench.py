@@ -6,6 +6,7 @@ shape [1,512,1], [1024] and [64,512,1024] over seven dtype pairs, Relu/Abs on th
 the five A dtypes, Cos on float32.  One "step" is one pass over all 95 operator calls.
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+    python bench.py --case <operator> [--dtype ...] [--rows ...] ...      one operator case, for profilers (see run_case)
 
 Prints ONE JSON line.  `value` is algorithmic GB/s of the whole job with inputs resident in HBM,
 `e2e` the same metric through the C ABI with pinned HOST buffers (H2D of both operands and D2H of
@@ -395,13 +396,6 @@ def run_ours(args):
                 line["other_ops"] = other_ops(lib, stream, peak)
             except Exception as exc:                      # the headline numbers stand on their own
                 line["other_ops"] = {"error": str(exc)[:200]}
-        details = os.path.join(ROOT, "gpurun_out")
-        try:
-            os.makedirs(details, exist_ok=True)
-            with open(os.path.join(details, "bench_per_op.json"), "w") as f:
-                json.dump({"per_op_GBps": per_op, "per_launch_ms": [round(float(x), 5) for x in per_launch_ms]}, f, indent=1)
-        except OSError:
-            pass
         print(json.dumps(line), flush=True)
     for ptr in list(pinned.values()) + out_pinned:
         lib.tops_host_free(ptr)
@@ -563,51 +557,81 @@ def other_ops(lib, stream, hbm_peak):
 def qdq_cnn_throughput(lib, stream, world, local, batch=256):
     """Images per second of the QDQ ResNet-50-shaped graph (benchmark config 5: batch 256 per GPU, float32
     [N,3,224,224] input, int8 QDQ around every convolution), input resident, every rank its own batch
-    (batch sharding, no collective), time = max over ranks.  The graph runs through Graph.fused(): each
-    Q -> DQ -> Conv [-> Relu] chain is one tensor-core call; the other nodes are the plain operators."""
+    (batch sharding, no collective), time = max over ranks.  The graph runs through Graph.fused() (each
+    Q -> DQ -> Conv [-> Add] [-> Relu] chain is one tensor-core call) and Graph.plan(): the forward pass is
+    recorded once and replayed as one CUDA graph launch.  Host time per forward (the call that enqueues a
+    pass, no synchronisation) is reported beside the device time, with the spread over ranks."""
     import torch
     from onnx_translator_b200 import capi, nn
     graph, x = nn.qdq_resnet50(batch=batch, seed=0)
     fused = graph.fused()
     xd = x.to_device()
-    fused.forward(xd)                                   # warm-up: weights become resident, pools grow
-    fused.forward(xd)
-    lib.tops_sync()
-    iters = 3
-    ev = [torch.cuda.Event(enable_timing=True) for _ in range(iters + 1)]
     before = lib.tops_tensor_core_launches()
+    plan = fused.plan(xd)                               # the recording pass: weights become resident, filter caches fill
+    tc_launches = int(lib.tops_tensor_core_launches() - before)
+    plan.run()
+    captured = plan.capture()
+    plan.run()
+    lib.tops_sync()
+    capi.check(lib)
+    iters = 5
+    ev = [torch.cuda.Event(enable_timing=True) for _ in range(iters + 1)]
+    host = []
     ev[0].record(stream)
     for i in range(iters):
-        out = fused.forward(xd)
+        t0 = time.perf_counter()
+        out = plan.run()
+        host.append((time.perf_counter() - t0) * 1e3)
         ev[i + 1].record(stream)
     lib.tops_sync()
     torch.cuda.synchronize()
     capi.check(lib)
     ms = float(np.median([ev[i].elapsed_time(ev[i + 1]) for i in range(iters)]))
-    t = torch.tensor([ms], dtype=torch.float64, device=f"cuda:{local}")
+    host_ms = float(np.median(host))
+    # the node-by-node interpreter on the same graph, host side only (what a plan saves)
+    t0 = time.perf_counter()
+    fused.forward(xd)
+    walk_ms = (time.perf_counter() - t0) * 1e3
+    lib.tops_sync()
+    per_rank = torch.tensor([[ms, host_ms, walk_ms]], dtype=torch.float64, device=f"cuda:{local}")
     if world > 1:
         import torch.distributed as dist
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-    ms = float(t.cpu()[0])
+        gathered = [torch.zeros_like(per_rank) for _ in range(world)]
+        dist.all_gather(gathered, per_rank)
+        per_rank = torch.cat(gathered)
+    per_rank = per_rank.cpu().numpy()
+    ms = float(per_rank[:, 0].max())
     prob = out.numpy()
     flops = 2.0 * graph.macs_per_image * batch
     cpu = None
+    prob_diff = None
     if world == 1:
         # the same graph (unfused, as the reference would run it) on the host cores, one image
         import oracle
         from oracle import graph as oracle_graph
         kind = "reference" if oracle.available("ref") else "port"
-        host = oracle.HostOracle("ref" if kind == "reference" else "port")
+        host_oracle = oracle.HostOracle("ref" if kind == "reference" else "port")
         cores = oracle.use_all_host_threads()
         one = nn.Tensor(1, 3, 224, 224, dtype="float32", data=np.ascontiguousarray(x.numpy()[:1]))
         t0 = time.perf_counter()
-        oracle_graph.run(graph, host, one)
+        cpu_prob = oracle_graph.run(graph, host_oracle, one)
         dt = time.perf_counter() - t0
         cpu = {"images_per_s": round(1.0 / dt, 3), "cores": cores, "kind": kind, "sample": f"1 image, {dt:.1f} s, C functions node by node"}
+        prob_diff = float(np.abs(prob[0].astype(np.float64) - cpu_prob[0]).max())
+    n_calls = len(plan.calls)
+    plan.close()
     return {"cpu_baseline": cpu, "images_per_s": round(world * batch / (ms / 1e3), 1), "ms_per_batch": round(ms, 3), "batch_per_gpu": batch,
             "n_gpus": world, "TFLOPs_per_gpu": round(flops / 1e12 / (ms / 1e3), 1), "gflop_per_image": round(2.0 * graph.macs_per_image / 1e9, 2),
-            "tensor_core_launches_per_batch": int((lib.tops_tensor_core_launches() - before) // iters),
-            "nodes": len(fused.ops), "nodes_unfused": len(graph.ops),
+            "tensor_core_launches_per_batch": tc_launches,
+            "nodes": len(fused.ops), "nodes_unfused": len(graph.ops), "library_calls_per_forward": n_calls,
+            "cuda_graph": bool(captured),
+            "device_ms_per_rank": {"min": round(float(per_rank[:, 0].min()), 3), "max": round(float(per_rank[:, 0].max()), 3)},
+            "host_ms_per_forward": {"min": round(float(per_rank[:, 1].min()), 3), "max": round(float(per_rank[:, 1].max()), 3),
+                                    "what": "time for plan.run() to return (one CUDA graph launch when captured), no synchronisation"},
+            "host_ms_node_by_node": {"min": round(float(per_rank[:, 2].min()), 3), "max": round(float(per_rank[:, 2].max()), 3),
+                                     "what": "Graph.forward walking the fused nodes in Python, no synchronisation"},
+            "max_abs_prob_diff": prob_diff,
+            "max_abs_prob_diff_what": "image 0 of the batch: fused GPU graph against the unfused graph on the CPU (largest probability about 1e-3)" if prob_diff is not None else None,
             "softmax_rows_sum_to_one": bool(np.allclose(prob.sum(axis=1), 1.0, atol=1e-4))}
 
 
@@ -690,7 +714,232 @@ def run_reference(args):
     print(json.dumps(line), flush=True)
 
 
+# ---- single operator cases (profiler command lines) ------------------------------------------------------------
+CASE_ITEM = {"float32": 4, "float16": 2, "bfloat16": 2, "int32": 4, "int8": 1, "uint8": 1, "float64": 8,
+        "float8_e4m3": 1, "float8_e5m2": 1, "int16": 2, "int64": 8, "int4": 1}
+
+
+def _case_rand(rng, shape, dtype, lo=-100, hi=100):
+    from onnx_translator_b200 import capi
+    st = capi.DTYPE_TO_NUMPY[dtype]
+    if dtype in ("int8", "int4"):
+        return rng.integers(-7, 8, shape).astype(st)
+    if dtype in ("uint8", "float8_e4m3", "float8_e5m2"):
+        return rng.integers(0, 120, shape).astype(st)
+    if dtype in ("int16", "int32", "int64"):
+        return rng.integers(-1000, 1001, shape).astype(st)
+    v = rng.uniform(lo, hi, shape).astype(np.float32)
+    if dtype == "bfloat16":
+        u = v.view(np.uint32).astype(np.uint64)
+        return ((u + 0x7FFF + ((u >> 16) & 1)) >> 16).astype(np.uint16)
+    return v.astype(st)
+
+
+def _case_ints(vals):
+    arr = (ctypes.c_int * len(vals))(*vals)
+    return arr, ctypes.cast(arr, ctypes.POINTER(ctypes.c_int))
+
+
+def run_case(case, argv):
+    """One operator case a few times, event-timed: small self-contained command lines for profilers (one kernel,
+    few launches, bounded memory).  Elementwise cases use A[rows,512,1024] with B of shape [1,512,1] (row), [1024]
+    (vec) or full; quantize / dequantize X[rows,8192]; softmax X[rows,1000]; maxpool X[rows,64,112,112] k3 s2 p1;
+    qdq_resnet50 the fused benchmark graph on --batch images (replayed from its call plan)."""
+    import ctypes
+    from onnx_translator_b200 import capi
+    from onnx_translator_b200.device import DeviceArray
+    from onnx_translator_b200.capi import CConvParams, CPoolParams
+    ap = argparse.ArgumentParser(prog="bench.py --case " + case)
+    ap.add_argument("--dtype", default="float32")
+    ap.add_argument("--b-dtype", default=None)
+    ap.add_argument("--out", default=None)
+    ap.add_argument("--rows", type=int, default=16)
+    ap.add_argument("--b", default="row", choices=("row", "vec", "full"))
+    ap.add_argument("--iters", type=int, default=3)
+    ap.add_argument("--warmup", type=int, default=1)
+    ap.add_argument("--m", type=int, default=4096)
+    ap.add_argument("--n", type=int, default=4096)
+    ap.add_argument("--k", type=int, default=4096)
+    ap.add_argument("--batch", type=int, default=8)
+    ap.add_argument("--channels", type=int, default=256)
+    ap.add_argument("--hw", type=int, default=56)
+    ap.add_argument("--ksize", type=int, default=1)
+    args = ap.parse_args(argv)
+    args.op = case
+
+    lib = capi.load()
+    lib.init_cos_lut()
+    capi.check(lib)
+    rng = np.random.default_rng(0)
+    dt = args.dtype
+    out_dt = args.out or dt
+    flops = 0
+    keep = []
+    if args.op in ("add", "sub", "mul", "div"):
+        shape = (args.rows, 512, 1024)
+        bshape = {"row": (1, 512, 1), "vec": (1024,), "full": shape}[args.b]
+        bdt = args.b_dtype or dt
+        a = DeviceArray.from_numpy(_case_rand(rng, shape, dt), dt)
+        b = DeviceArray.from_numpy(_case_rand(rng, bshape, bdt, 0.5, 100), bdt)
+        o = DeviceArray.empty(shape, out_dt)
+        fn = getattr(lib, args.op + "_forward")
+        call = lambda: fn(a.handle, b.handle, o.handle)
+        n = a.size
+        nbytes = n * (CASE_ITEM[dt] + CASE_ITEM[out_dt]) + b.size * CASE_ITEM[bdt]
+    elif args.op in ("relu", "abs", "cos"):
+        shape = (args.rows, 512, 1024)
+        a = DeviceArray.from_numpy(_case_rand(rng, shape, dt, -10, 10), dt)
+        o = DeviceArray.empty(shape, out_dt)
+        fn = getattr(lib, args.op + "_forward")
+        call = lambda: fn(a.handle, o.handle)
+        nbytes = a.size * (CASE_ITEM[dt] + CASE_ITEM[out_dt])
+    elif args.op in ("exp", "log", "sqrt", "sigmoid", "tanh", "neg", "reciprocal", "ceil", "floor", "sin", "tan", "atan", "softplus", "softsign",
+                     "hard_swish", "acos", "asin", "cosh", "sinh", "asinh", "acosh", "atanh", "round", "erf", "gelu", "cast"):
+        shape = (args.rows, 512, 1024)
+        a = DeviceArray.from_numpy(_case_rand(rng, shape, dt, -3, 3), dt)
+        o = DeviceArray.empty(shape, out_dt)
+        fn = getattr(lib, args.op + "_forward")
+        call = lambda: fn(a.handle, o.handle)
+        nbytes = a.size * (CASE_ITEM[dt] + CASE_ITEM[out_dt])
+    elif args.op == "dynamic_quantize":
+        # range pass + quantise pass over float32 [rows, 8192]: x read twice, uint8 codes written once
+        shape = (args.rows, 8192)
+        x = DeviceArray.from_numpy(rng.standard_normal(shape).astype(np.float32), "float32")
+        o = DeviceArray.empty(shape, "uint8")
+        sc, zp = DeviceArray.empty((1,), "float32"), DeviceArray.empty((1,), "uint8")
+        call = lambda: lib.dynamic_quantize_linear_forward(x.handle, o.handle, sc.handle, zp.handle)
+        nbytes = x.size * 9
+        dt, out_dt = "float32", "uint8"
+    elif args.op == "batch_norm":
+        shape = (args.batch, args.channels, args.hw, args.hw)
+        x = DeviceArray.from_numpy(rng.standard_normal(shape).astype(np.float32), "float32")
+        o = DeviceArray.empty(shape, "float32")
+        ps = [DeviceArray.from_numpy(v.astype(np.float32), "float32") for v in (rng.normal(1, 0.1, args.channels), rng.normal(0, 0.1, args.channels),
+                                                                                rng.normal(0, 0.1, args.channels), rng.uniform(0.5, 2, args.channels))]
+        keep = ps
+        call = lambda: lib.batch_norm_forward(x.handle, ps[0].handle, ps[1].handle, ps[2].handle, ps[3].handle, o.handle, ctypes.c_float(1e-5))
+        nbytes = x.size * 8
+        dt = out_dt = "float32"
+    elif args.op == "global_average_pool":
+        shape = (args.batch, args.channels, args.hw, args.hw)
+        x = DeviceArray.from_numpy(rng.standard_normal(shape).astype(np.float32), "float32")
+        o = DeviceArray.empty(shape[:2] + (1, 1), "float32")
+        call = lambda: lib.global_average_pool_forward(x.handle, o.handle)
+        nbytes = x.size * 4
+        dt = out_dt = "float32"
+    elif args.op in ("quantize", "dequantize"):
+        shape = (args.rows, 8192)
+        if args.op == "quantize":
+            out_dt = args.out or "int8"
+            x = DeviceArray.from_numpy(rng.standard_normal(shape).astype(np.float32), "float32")
+            zdt = out_dt if out_dt in ("int8", "uint8") else "int8"
+        else:
+            dt = args.dtype if args.dtype != "float32" else "int8"
+            out_dt = args.out or "float32"
+            x = DeviceArray.from_numpy(_case_rand(rng, shape, dt), dt)
+            zdt = dt if dt in ("int8", "uint8") else "int8"
+        if args.b == "vec":
+            s = DeviceArray.from_numpy(rng.uniform(0.01, 0.05, (1, 8192)).astype(np.float32), "float32")
+            z = DeviceArray.from_numpy(rng.integers(0, 9, (1, 8192)).astype(capi.DTYPE_TO_NUMPY[zdt]), zdt)
+        else:
+            s = DeviceArray.from_numpy(np.array([0.02], np.float32), "float32")
+            z = DeviceArray.from_numpy(np.array([0]).astype(capi.DTYPE_TO_NUMPY[zdt]), zdt)
+        o = DeviceArray.empty(shape, out_dt)
+        fn = lib.quantize_linear_forward if args.op == "quantize" else lib.dequantize_linear_forward
+        call = lambda: fn(x.handle, s.handle, z.handle, o.handle)
+        nbytes = x.size * (CASE_ITEM[x.dtype_name] + CASE_ITEM[out_dt])
+    elif args.op == "softmax":
+        shape = (args.rows, 1000)
+        x = DeviceArray.from_numpy(_case_rand(rng, shape, dt, -10, 10), dt)
+        o = DeviceArray.empty(shape, out_dt)
+        call = lambda: lib.softmax_forward(x.handle, o.handle, 1)
+        nbytes = x.size * (CASE_ITEM[dt] + CASE_ITEM[out_dt])
+    elif args.op == "maxpool":
+        shape = (args.rows, 64, 112, 112)
+        x = DeviceArray.from_numpy(_case_rand(rng, shape, dt), dt)
+        o = DeviceArray.empty((args.rows, 64, 56, 56), out_dt)
+        keep = [_case_ints([1, 1, 1, 1]), _case_ints([2, 2]), _case_ints([1, 1]), _case_ints([3, 3])]
+        prm = CPoolParams(keep[0][1], keep[1][1], keep[2][1], keep[3][1])
+        call = lambda: lib.max_pool_forward(x.handle, o.handle, ctypes.byref(prm))
+        nbytes = x.size * CASE_ITEM[dt] + o.size * CASE_ITEM[out_dt]
+    elif args.op == "gemm":
+        a = DeviceArray.from_numpy(_case_rand(rng, (args.m, args.k), dt, -0.05, 0.05), dt)
+        b = DeviceArray.from_numpy(_case_rand(rng, (args.n, args.k), dt, -0.05, 0.05), dt)
+        c = DeviceArray.from_numpy(rng.standard_normal((1, args.n)).astype(np.float32), "float32")
+        o = DeviceArray.empty((args.m, args.n), out_dt)
+        call = lambda: lib.gemm_forward(a.handle, b.handle, c.handle, o.handle, 1.0, 1.0, 0, 1)
+        nbytes = a.size * CASE_ITEM[dt] + b.size * CASE_ITEM[dt] + o.size * CASE_ITEM[out_dt]
+        flops = 2.0 * args.m * args.n * args.k
+    elif args.op == "conv":
+        n_, c_, hw = args.batch, args.channels, args.hw
+        x = DeviceArray.from_numpy(_case_rand(rng, (n_, c_, hw, hw), dt, -1, 1), dt)
+        w = DeviceArray.from_numpy(_case_rand(rng, (c_, c_, 3, 3), dt, -0.05, 0.05), dt)
+        o = DeviceArray.empty((n_, c_, hw, hw), out_dt)
+        keep = [_case_ints([1, 1, 1, 1]), _case_ints([1, 1]), _case_ints([1, 1])]
+        prm = CConvParams(keep[0][1], keep[1][1], keep[2][1], 1)
+        call = lambda: lib.conv2d_forward(x.handle, w.handle, None, o.handle, ctypes.byref(prm))
+        nbytes = x.size * CASE_ITEM[dt] + w.size * CASE_ITEM[dt] + o.size * CASE_ITEM[out_dt]
+        flops = 2.0 * n_ * hw * hw * c_ * c_ * 9
+    elif args.op == "qconv":
+        # one Q -> DQ -> Conv(DQ(W)) -> Relu chain in one call: float32 [batch, channels, hw, hw] -> [batch, n, hw, hw],
+        # ksize x ksize filters (stride 1, "same" padding)
+        n_, c_, hw, ks, m_ = args.batch, args.channels, args.hw, args.ksize, args.n
+        x = DeviceArray.from_numpy(rng.standard_normal((n_, c_, hw, hw)).astype(np.float32), "float32")
+        wq = DeviceArray.from_numpy(rng.integers(-127, 128, (m_, c_, ks, ks)).astype(np.int8), "int8")
+        ws = DeviceArray.from_numpy(rng.uniform(0.005, 0.02, m_).astype(np.float32), "float32")
+        sx = DeviceArray.from_numpy(np.array([0.03], np.float32), "float32")
+        zx = DeviceArray.from_numpy(np.zeros(1, np.int8), "int8")
+        o = DeviceArray.empty((n_, m_, hw, hw), "float32")
+        pad = ks // 2
+        keep = [_case_ints([pad] * 4), _case_ints([1, 1]), _case_ints([1, 1])]
+        prm = CConvParams(keep[0][1], keep[1][1], keep[2][1], 1)
+        call = lambda: lib.tops_qdq_conv_forward(x.handle, sx.handle, zx.handle, wq.handle, ws.handle, None, None, o.handle,
+                                                 ctypes.byref(prm), 1)
+        nbytes = x.size * 4 + o.size * 4
+        flops = 2.0 * n_ * hw * hw * m_ * c_ * ks * ks
+        dt = out_dt = "float32"
+    elif args.op == "qdq_resnet50":
+        # the QDQ ResNet-50-shaped graph through Graph.fused(); --batch images of 224 x 224
+        from onnx_translator_b200 import nn
+        graph, x_host = nn.qdq_resnet50(batch=args.batch, seed=0)
+        fused = graph.fused()
+        xd = x_host.to_device()
+        plan = fused.plan(xd)
+        keep = [graph, fused, xd, plan]
+        call = lambda: plan.run()
+        nbytes = 0
+        flops = 2.0 * graph.macs_per_image * args.batch
+        dt = out_dt = "float32"
+    else:
+        raise SystemExit(f"unknown op {args.op}")
+
+    import torch
+    stream = torch.cuda.ExternalStream(lib.tops_get_stream())
+    for _ in range(args.warmup):
+        call()
+    lib.tops_sync()
+    capi.check(lib)
+    ev = [torch.cuda.Event(enable_timing=True) for _ in range(args.iters + 1)]
+    ev[0].record(stream)
+    for i in range(args.iters):
+        call()
+        ev[i + 1].record(stream)
+    lib.tops_sync()
+    torch.cuda.synchronize()
+    capi.check(lib)
+    ms = [ev[i].elapsed_time(ev[i + 1]) for i in range(args.iters)]
+    best = min(ms)
+    msg = f"{args.op} {dt}->{out_dt}: {best:.4f} ms best of {args.iters} ({np.mean(ms):.4f} mean), {nbytes / 1e9 / (best / 1e3):.1f} GB/s algorithmic"
+    if flops:
+        msg += f", {flops / 1e12 / (best / 1e3):.1f} TFLOP/s"
+    print(msg)
+
+
+
 def main():
+    if "--case" in sys.argv:
+        i = sys.argv.index("--case")
+        return run_case(sys.argv[i + 1], sys.argv[1:i] + sys.argv[i + 2:])
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=10)

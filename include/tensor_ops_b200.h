@@ -281,6 +281,25 @@ void tops_quantize_linear_axis_forward(const Tensor* X, const Tensor* Scale, con
 void tops_dequantize_linear_axis_forward(const Tensor* X, const Tensor* Scale, const Tensor* ZeroPoint,
                                          Tensor* Y, int axis);
 
+/* Quantize / Dequantize fused with their elementwise neighbours (no single counterpart in the reference: each call
+   replaces a chain of its operators, tensor_ops.c:999-1034 with :864-997 add_forward and :708-728 relu_forward in
+   between).  Results are bit-identical to the chain of separate calls.  Return TOPS_OK or the recorded error;
+   TOPS_ERR_UNSUPPORTED (outputs zero-filled) means the caller runs the separate operators instead.
+
+   tops_quantize_dequantize_forward:  Y = DequantizeLinear(QuantizeLinear(X, Scale, ZeroPoint), Scale, ZeroPoint)
+     X, Scale, Y float32; Scale / ZeroPoint broadcast against X (one value, or [1,C,1,1] for per-axis); the code type
+     is Codes->dtype (int8, uint8, float8) -- ZeroPoint has that type too, or int8 for float8 codes -- and, when
+     Codes is NULL, ZeroPoint's type.  Codes, when given, receives what QuantizeLinear would store.
+     Moves 8 bytes per element (9 with the codes) where the two operators move 10.
+
+   tops_dq_add_q_forward:  Y = QuantizeLinear([Relu](DequantizeLinear(A, a_scale, a_zero) + DequantizeLinear(B, b_scale, b_zero)),
+                                                y_scale, y_zero)
+     A, B, Y int8 / uint8 codes of one element count; one float32 scale and one zero point of the tensor's own code
+     type (NULL = 0) each.  Moves 3 bytes per element where the four or five operators move 27 or 35. */
+int tops_quantize_dequantize_forward(const Tensor* X, const Tensor* Scale, const Tensor* ZeroPoint, Tensor* Codes, Tensor* Y);
+int tops_dq_add_q_forward(const Tensor* A, const Tensor* a_scale, const Tensor* a_zero, const Tensor* B, const Tensor* b_scale,
+                          const Tensor* b_zero, const Tensor* y_scale, const Tensor* y_zero, Tensor* Y, int relu);
+
 /* Convolution for callers that must not let this library allocate GPU memory (no counterpart in
    the reference, whose library only ever uses the host heap).  conv2d_forward takes two scratch
    tensors from the CUDA memory pool on each call; a process that has given the whole device to its

@@ -146,6 +146,8 @@ SIGNATURES = {
     "tops_dynamic_quantize_apply": (ctypes.c_int, [_P, _P, _P, _P, _P]),
     "tops_quantize_linear_axis_forward": (None, [_P, _P, _P, _P, _I]),
     "tops_dequantize_linear_axis_forward": (None, [_P, _P, _P, _P, _I]),
+    "tops_quantize_dequantize_forward": (_I, [_P, _P, _P, _P, _P]),
+    "tops_dq_add_q_forward": (_I, [_P, _P, _P, _P, _P, _P, _P, _P, _P, _I]),
     "tops_conv2d_forward_noalloc": (None, [_P, _P, _P, _P, ctypes.POINTER(CConvParams)]),
     "tops_conv2d_noalloc_prepare": (_I, []),
     "tops_conv2d_noalloc_limits": (_SZ, [ctypes.POINTER(_SZ), ctypes.POINTER(_SZ)]),

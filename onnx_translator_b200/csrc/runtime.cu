@@ -183,8 +183,8 @@ static Tensor* allocate(const int* shape, int ndim, DataType dtype, bool zero) {
     if (managed_mode()) {
         impl->kind = kManaged;
         e = cudaMallocManaged(&impl->pub.data, bytes);
-        if (e == cudaSuccess && zero) e = cudaMemset(impl->pub.data, 0, bytes);
-        if (e == cudaSuccess) e = cudaStreamSynchronize(s);
+        if (e == cudaSuccess && zero) e = cudaMemsetAsync(impl->pub.data, 0, bytes, s);     // on the stream that is synchronised next:
+        if (e == cudaSuccess) e = cudaStreamSynchronize(s);                                 // the host may write into it right away
     } else {
         e = cudaMallocAsync(&impl->pub.data, bytes, s);
         if (e == cudaSuccess && zero) e = cudaMemsetAsync(impl->pub.data, 0, bytes, s);

@@ -133,3 +133,88 @@ class QLinearConv(Ops):
             out.logical_shape = out_shape
             result = out if result is None else (result, out)
         return self._publish(result)
+
+
+class QuantizeDequantize(Ops):
+    """QuantizeLinear followed by DequantizeLinear with the same scale and zero point, in one pass over the tensor
+    (replaces nn/Operators.py:427-450 and :452-473; C: tensor_ops.c:999-1034).  ``outputs`` is [dequantised] or
+    [dequantised, codes] when something else reads the codes.  Falls back to the two operators for what the fused
+    call does not cover (other dtypes than float32, broadcast patterns it cannot collapse)."""
+
+    def __init__(self, inputs, outputs, axis=1, code_dtype="int8", dtype="float32", with_codes=False):
+        super().__init__(inputs, outputs)
+        self.axis, self.code_dtype, self.dtype, self.with_codes = axis, code_dtype, dtype, bool(with_codes)
+
+    def _two_operators(self, x, scale, zero):
+        from .Operators import DequantizeLinear, QuantizeLinear
+        codes = QuantizeLinear([], [], axis=self.axis, dtype=self.code_dtype).forward(x, scale, zero)["tensor"]
+        s, z = scale, zero
+        if scale.data.ndim == 1 and x.data.ndim > 1:         # DequantizeLinear has no axis: hand it the reshaped operands
+            shape = [1] * x.data.ndim
+            shape[self.axis if self.axis >= 0 else self.axis + x.data.ndim] = scale.data.size
+            s = Tensor(*shape, dtype=scale.dtype, data=scale.data.reshape(shape))
+            z = Tensor(*shape, dtype=zero.dtype, data=zero.data.reshape(shape))
+        y = DequantizeLinear([], [], dtype=self.dtype).forward(codes, s, z)["tensor"]
+        return self._publish((y, codes) if self.with_codes else y)
+
+    def forward(self, x: Tensor, scale: Tensor, zero: Tensor) -> dict:
+        if x.dtype != "float32" or self.dtype != "float32" or scale.dtype != "float32":
+            return self._two_operators(x, scale, zero)
+        shape = tuple(x.data.shape)
+        s_data, z_data = scale.data, zero.data
+        if s_data.ndim == 1 and len(shape) > 1:                # a 1-D scale sits on ``axis`` (nn/Operators.py:439-445)
+            bshape = [1] * len(shape)
+            bshape[self.axis if self.axis >= 0 else self.axis + len(shape)] = s_data.size
+            s_data, z_data = s_data.reshape(bshape), z_data.reshape(bshape)
+        handles = [self._numpy_to_ctensor(x.data, x.dtype), self._numpy_to_ctensor(s_data, scale.dtype), self._numpy_to_ctensor(z_data, zero.dtype)]
+        y = self._new_output(shape, "float32")
+        codes = self._new_output(shape, self.code_dtype) if self.with_codes else None
+        rc = self.lib.tops_quantize_dequantize_forward(handles[0], handles[1], handles[2], codes, y)
+        if rc:
+            for h in handles + [y] + ([codes] if codes else []):
+                self.lib.free_tensor(h)
+            code = self.lib.tops_last_error()
+            self.lib.tops_clear_error()
+            if code != 5:                                       # anything but "unsupported" is a real error
+                raise capi.TensorOpsError(f"tops_quantize_dequantize_forward failed with code {code}")
+            return self._two_operators(x, scale, zero)
+        code_tensor = self._finish([], codes, shape, self.code_dtype) if codes else None
+        out = self._finish(handles, y, shape, "float32")
+        return self._publish((out, code_tensor) if self.with_codes else out)
+
+
+class DequantAddQuant(Ops):
+    """QuantizeLinear([Relu](DequantizeLinear(a) + DequantizeLinear(b))) in one pass: the tail of a quantised
+    residual block (replaces nn/Operators.py:452-473 twice, :170-200, :32-80 and :427-450).
+    inputs: [a, a_scale, a_zero, b, b_scale, b_zero, y_scale, y_zero]."""
+
+    def __init__(self, inputs, outputs, relu=False, dtype="int8"):
+        super().__init__(inputs, outputs)
+        self.relu, self.dtype = bool(relu), dtype
+
+    def _five_operators(self, a, a_s, a_z, b, b_s, b_z, y_s, y_z):
+        from .Operators import ADD, RELU, DequantizeLinear, QuantizeLinear
+        da = DequantizeLinear([], [], dtype="float32").forward(a, a_s, a_z)["tensor"]
+        db = DequantizeLinear([], [], dtype="float32").forward(b, b_s, b_z)["tensor"]
+        t = ADD([], [], dtype="float32").forward(da, db)["tensor"]
+        if self.relu:
+            t = RELU([], [], dtype="float32").forward(t)["tensor"]
+        return self._publish(QuantizeLinear([], [], axis=1, dtype=self.dtype).forward(t, y_s, y_z)["tensor"])
+
+    def forward(self, a, a_s, a_z, b, b_s, b_z, y_s, y_z) -> dict:
+        shape = tuple(a.data.shape)
+        if tuple(b.data.shape) != shape:
+            return self._five_operators(a, a_s, a_z, b, b_s, b_z, y_s, y_z)
+        operands = (a, a_s, a_z, b, b_s, b_z, y_s, y_z)
+        handles = [self._numpy_to_ctensor(t.data, t.dtype) for t in operands]
+        y = self._new_output(shape, self.dtype)
+        rc = self.lib.tops_dq_add_q_forward(*handles, y, int(self.relu))
+        if rc:
+            for h in handles + [y]:
+                self.lib.free_tensor(h)
+            code = self.lib.tops_last_error()
+            self.lib.tops_clear_error()
+            if code != 5:
+                raise capi.TensorOpsError(f"tops_dq_add_q_forward failed with code {code}")
+            return self._five_operators(*operands)
+        return self._publish(self._finish(handles, y, shape, self.dtype))

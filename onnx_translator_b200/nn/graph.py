@@ -60,7 +60,7 @@ class Graph:
             if edge not in produced:
                 raise ValueError(f"graph output {edge!r} is not produced by any node")
 
-    def fused(self) -> "Graph":
+    def fused(self, channels_last: bool = True) -> "Graph":
         """A graph computing the same function with every
 
             QuantizeLinear -> DequantizeLinear -> Conv(weights = DequantizeLinear(initializers)) [-> Relu]
@@ -72,7 +72,8 @@ class Graph:
         other readers, besides) a float32 tensor.
         A chain is taken only when nothing else reads its inner edges, the weight zero points are all
         zero and the convolution is one the fused kernel covers (group 1; stride 1, or stride 2 with
-        dilation 1); everything else is left as it is.  Initializers are shared with this graph."""
+        dilation 1); everything else is left as it is.  Initializers are shared with this graph.
+        ``channels_last=False`` keeps every float32 edge NCHW (the fourth pass below is skipped)."""
         from .fused_ops import QLinearConv
         nodes = list(self.ops.values())
         producer = {e: op for op in nodes for e in op.outputs}
@@ -198,7 +199,7 @@ class Graph:
             for slot, e in enumerate(op.inputs):
                 if e:
                     readers.setdefault(e, []).append((op, slot))
-        for op in kept:
+        for op in kept if channels_last else ():
             if kind(op) != "QLinearConv" or op.dtype != "float32" or (op.next_conv is not None and not op.also_float):
                 continue
             edge = op.outputs[0]
@@ -212,11 +213,80 @@ class Graph:
                     u.x_channels_last = True
                 else:
                     u.residual_channels_last = True
+        kept = self._fuse_elementwise_qdq(kept)
         g = Graph(kept, list(self.input_name), list(self.output_name), self.model_name, self.initializers)
         g._resident = self._resident
         if hasattr(self, "macs_per_image"):
             g.macs_per_image = self.macs_per_image
         return g
+
+    def _fuse_elementwise_qdq(self, nodes):
+        """Q/DQ chains that no convolution absorbed, fused with their elementwise neighbours:
+
+            DequantizeLinear(a), DequantizeLinear(b) -> Add [-> Relu] -> QuantizeLinear      one DequantAddQuant node
+            QuantizeLinear -> DequantizeLinear (same scale and zero point)                   one QuantizeDequantize node
+
+        A chain is taken only when its inner edges have no other reader and are not graph outputs (the codes of a
+        Q -> DQ pair may have other readers: the fused node then writes them as a second output)."""
+        from .fused_ops import DequantAddQuant, QuantizeDequantize
+        kind = lambda op: type(op).__name__
+        made_by = {e: op for op in nodes for e in op.outputs}
+        readers: Dict[str, list] = {}
+        for op in nodes:
+            for e in op.inputs:
+                if e:
+                    readers.setdefault(e, []).append(op)
+        inner = lambda e: len(readers.get(e, [])) == 1 and e not in self.output_name
+        one = lambda name: name in self.initializers and self.initializers[name].data_size == 1
+        gone, replaced = set(), {}
+        for add in nodes:
+            if kind(add) != "ADD" or (add.dtype or "float32") != "float32" or len(add.inputs) != 2 or add.inputs[0] == add.inputs[1]:
+                continue
+            dqs = [made_by.get(e) for e in add.inputs]
+            if not all(d is not None and kind(d) == "DequantizeLinear" and (d.dtype or "float32") == "float32" and inner(d.outputs[0])
+                       and d.name not in gone and all(one(n) for n in d.inputs[1:3]) for d in dqs):
+                continue
+            tail, relu = add, False
+            if not inner(add.outputs[0]):
+                continue
+            nxt = readers[add.outputs[0]][0]
+            if kind(nxt) == "RELU" and (nxt.dtype or "float32") == "float32" and inner(nxt.outputs[0]):
+                tail, relu, nxt = nxt, True, readers[nxt.outputs[0]][0]
+            if kind(nxt) != "QuantizeLinear" or nxt.dtype not in ("int8", "uint8") or not all(one(n) for n in nxt.inputs[1:3]):
+                continue
+            if any(self.initializers[d.inputs[2]].dtype not in ("int8", "uint8") for d in dqs) or self.initializers[nxt.inputs[2]].dtype != nxt.dtype:
+                continue
+            node = DequantAddQuant(list(dqs[0].inputs[:3]) + list(dqs[1].inputs[:3]) + list(nxt.inputs[1:3]), [nxt.outputs[0]], relu, nxt.dtype)
+            node.name = add.name + ".fused"
+            gone.update(d.name for d in dqs)
+            gone.update((add.name, nxt.name))
+            if relu:
+                gone.add(tail.name)
+            replaced[nxt.name] = node                       # the fused node sits where the chain ended
+        for q in nodes:
+            if kind(q) != "QuantizeLinear" or q.name in gone or q.dtype not in ("int8", "uint8", "float8_e4m3", "float8_e5m2"):
+                continue
+            dq = next((r for r in readers.get(q.outputs[0], []) if kind(r) == "DequantizeLinear" and r.inputs[0] == q.outputs[0]
+                       and r.inputs[1:3] == q.inputs[1:3] and (r.dtype or "float32") == "float32" and r.name not in gone), None)
+            if dq is None:
+                continue
+            scale = self.initializers.get(q.inputs[1])
+            # DequantizeLinear has no axis: the pair is the same function for every element only when the scale is one
+            # value or already shaped for plain broadcasting
+            if scale is None or not (scale.data_size == 1 or len(scale.size) != 1):
+                continue
+            shared = not inner(q.outputs[0])
+            node = QuantizeDequantize(list(q.inputs[:3]), [dq.outputs[0]] + ([q.outputs[0]] if shared else []), q.axis, q.dtype, "float32", shared)
+            node.name = q.name + ".fused"
+            gone.update((q.name, dq.name))
+            replaced[q.name] = node                         # where the QuantizeLinear stood: before every reader of the codes
+        out = []
+        for op in nodes:
+            if op.name in replaced:
+                out.append(replaced[op.name])
+            elif op.name not in gone:
+                out.append(op)
+        return out
 
     def make_resident(self) -> None:
         """Upload every initializer once; later calls of ``forward`` reuse the device copies."""

@@ -42,6 +42,8 @@ class _Recorder:
         self._lib = lib
         self.calls: List[tuple] = []
         self.held: List[object] = []          # tensor handles this recording holds a reference to
+        self.recording = True                 # afterwards every call passes straight through (tensors made while
+                                              # recording keep this object as their library handle)
 
     def _hold(self, handle) -> None:
         if handle:
@@ -61,6 +63,8 @@ class _Recorder:
 
     def __getattr__(self, name):
         fn = getattr(self._lib, name)
+        if not self.recording:
+            return fn
         if name in _REFUSED:
             def refused(*args):
                 raise capi.TensorOpsError(f"{name} was called while a call plan was being recorded: this graph reads tensors "
@@ -97,6 +101,7 @@ class GraphPlan:
             outs = graph.forward(*self.inputs)
         finally:
             Ops._recorder = None
+            recorder.recording = False
         capi.check(self.lib)
         self._recorder = recorder
         self.outputs = outs

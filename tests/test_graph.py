@@ -200,8 +200,67 @@ def test_fusion_pass_leaves_what_it_must_not_touch():
     # non-zero weight zero points, grouped or stride-3 convolutions are not what the fused kernel computes
     for bad in (dict(weight_zero=3), dict(group=2), dict(stride=3)):
         kinds = [type(op).__name__ for op in _hand_built_qdq_block(**bad).fused().ops.values()]
-        assert kinds[:5] == ["QuantizeLinear", "DequantizeLinear", "DequantizeLinear", "Conv", "RELU"], bad
+        # (the Q -> DQ pair in front of the untouched convolution still becomes one round-trip node)
+        assert kinds[:4] == ["QuantizeDequantize", "DequantizeLinear", "Conv", "RELU"], bad
         assert kinds.count("QLinearConv") == 1                                   # the second chain is still taken
+
+
+def test_fusion_conditions_on_scale_shape_and_dtypes():
+    """DequantizeLinear has no axis: only a weight scale shaped [M, 1, 1, 1] scales per output channel.  A flat [M]
+    scale, a float16 DequantizeLinear or a zero point of another type than the codes leave the chain unfused."""
+    from onnx_translator_b200 import nn
+    T = lambda a, dt: nn.Tensor(*np.asarray(a).shape, dtype=dt, data=np.asarray(a))
+    def conv_kinds(mutate):
+        g = _hand_built_qdq_block()
+        mutate(g)
+        return [type(op).__name__ for op in Graph(list(g.ops.values()), "x", ["y"], "block", g.initializers).fused().ops.values()]
+    def flat_scale(g):
+        g.initializers["w1s"] = T(np.full(8, 0.01, np.float32), "float32")
+        g.initializers["w1z"] = T(np.zeros(8, np.int8), "int8")
+    def half_dq(g):
+        list(g.ops.values())[2].dtype = "float16"
+    def zero_type(g):
+        g.initializers["z"] = T(np.zeros(1, np.uint8), "uint8")
+    assert conv_kinds(lambda g: None).count("Conv") == 0
+    for mutate in (flat_scale, half_dq, zero_type):
+        assert conv_kinds(mutate).count("Conv") >= 1, mutate.__name__
+
+
+def _hand_built_quantised_add(relu=True, second_reader=False):
+    """a, b int8 codes -> DQ, DQ -> Add [-> Relu] -> Q -> DQ -> (output), and x -> Q -> DQ beside it."""
+    from onnx_translator_b200 import nn
+    from onnx_translator_b200.nn import Operators as ops
+    f32 = "float32"
+    T = lambda a, dt: nn.Tensor(*np.asarray(a).shape, dtype=dt, data=np.asarray(a))
+    init = {"sa": T(np.array([0.05], np.float32), f32), "za": T(np.array([3], np.int8), "int8"),
+            "sb": T(np.array([0.02], np.float32), f32), "zb": T(np.array([100], np.uint8), "uint8"),
+            "sy": T(np.array([0.04], np.float32), f32), "zy": T(np.array([-5], np.int8), "int8")}
+    nodes = [ops.DequantizeLinear(["a", "sa", "za"], ["da"], dtype=f32),
+             ops.DequantizeLinear(["b", "sb", "zb"], ["db"], dtype=f32),
+             ops.ADD(["da", "db"], ["sum"], dtype=f32)]
+    edge = "sum"
+    if relu:
+        nodes.append(ops.RELU(["sum"], ["act"], dtype=f32))
+        edge = "act"
+    nodes += [ops.QuantizeLinear([edge, "sy", "zy"], ["yq"], axis=1, dtype="int8"),
+              ops.DequantizeLinear(["yq", "sy", "zy"], ["y"], dtype=f32),
+              ops.QuantizeLinear(["x", "sy", "zy"], ["xq"], axis=1, dtype="int8"),
+              ops.DequantizeLinear(["xq", "sy", "zy"], ["xr"], dtype=f32)]
+    outputs = ["y", "xr"] + (["sum"] if second_reader else [])
+    return Graph(nodes, ["a", "b", "x"], outputs, "qadd", init)
+
+
+def test_elementwise_qdq_fusion_pass_without_a_gpu():
+    fused = _hand_built_quantised_add().fused()
+    kinds = [type(op).__name__ for op in fused.ops.values()]
+    assert kinds == ["DequantAddQuant", "DequantizeLinear", "QuantizeDequantize"]
+    first, _, third = fused.ops.values()
+    assert first.relu and first.inputs == ["a", "sa", "za", "b", "sb", "zb", "sy", "zy"] and first.outputs == ["yq"]
+    assert third.inputs == ["x", "sy", "zy"] and third.outputs == ["xr"] and not third.with_codes
+    assert not list(_hand_built_quantised_add(relu=False).fused().ops.values())[0].relu
+    # the float32 sum is a graph output too: the chain must stay as it is
+    kinds = [type(op).__name__ for op in _hand_built_quantised_add(second_reader=True).fused().ops.values()]
+    assert kinds[:3] == ["DequantizeLinear", "DequantizeLinear", "ADD"] and "DequantAddQuant" not in kinds
 
 
 @pytest.mark.gpu
@@ -215,7 +274,7 @@ def test_levels_edges_do_not_change_the_fused_graph_result():
     # conv2 and conv3 of each of the five blocks, plus the first convolution reading each later block's input
     assert sum(getattr(op, "levels_in", False) for op in with_levels.ops.values()) == 2 * 5 + 4
     assert sum(getattr(op, "also_float", False) for op in with_levels.ops.values()) == 4
-    plain = graph.fused()
+    plain = graph.fused(channels_last=False)
     for op in plain.ops.values():
         if type(op).__name__ == "QLinearConv":
             if op.next_conv is not None:

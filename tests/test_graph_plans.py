@@ -116,10 +116,8 @@ def test_channels_last_edges_do_not_change_the_fused_graph_result():
     assert n_cl == (6 - 1) + 4
     assert sum(getattr(op, "residual_channels_last", False) for op in with_cl.ops.values()) == 6
     assert sum(getattr(op, "x_channels_last", False) for op in with_cl.ops.values()) >= 3      # stride-2 shortcuts read the block input as float32
-    nchw = graph.fused()
-    for op in nchw.ops.values():
-        if type(op).__name__ == "QLinearConv":
-            op.x_channels_last = op.y_channels_last = op.residual_channels_last = False
+    nchw = graph.fused(channels_last=False)
+    assert not any(getattr(op, "y_channels_last", False) for op in nchw.ops.values())
     a = with_cl.forward(x).numpy()
     b = nchw.forward(x).numpy()
     assert np.array_equal(a.view(np.uint32), b.view(np.uint32))
