@@ -347,6 +347,10 @@ def run_ours(args):
                 raise                            # the ranks must stay in step
             qdq_cnn = {"error": str(exc)[:300]}
 
+    sharded = None
+    if world > 1 and not args.no_extra:
+        sharded = sharded_leg(lib, stream, world, rank, local)
+
     if rank == 0:
         peak, peak_kind = peaks()
         binary_idx = [i for i, it in enumerate(plan) if it["kind"] == "binary"]
@@ -391,6 +395,13 @@ def run_ours(args):
         line["cpu_baseline"] = cpu_baseline(budget_s=20.0) if world == 1 else None
         if qdq_cnn is not None:
             line["qdq_cnn"] = qdq_cnn
+        if sharded is not None:
+            line["sharded"] = sharded
+        if world == 1 and not args.no_extra:
+            try:
+                line["small_cnn"] = small_cnn_latency(lib, stream)
+            except Exception as exc:
+                line["small_cnn"] = {"error": str(exc)[:200]}
         if world == 1 and not args.no_extra:
             try:
                 line["other_ops"] = other_ops(lib, stream, peak)
@@ -451,6 +462,11 @@ def other_ops(lib, stream, hbm_peak):
         q = DeviceArray.empty((8192, 8192), dt)
         mem(f"quantize_f32_to_{label}", n * 5, lambda: lib.quantize_linear_forward(x.handle, sc.handle, zp.handle, q.handle))
         mem(f"dequantize_{label}_to_f32", n * 5, lambda: lib.dequantize_linear_forward(q.handle, sc.handle, zp.handle, back.handle))
+        # config 3 as what it is, a round trip: Q -> DQ in one pass (8 bytes per element), against the two calls above (10)
+        codes = None if zp.dtype_name == dt else q.handle       # float8 codes with an int8 zero point: the code type comes from a codes tensor
+        mem(f"qdq_roundtrip_f32_{label}", n * 8, lambda: lib.tops_quantize_dequantize_forward(x.handle, sc.handle, zp.handle, codes, back.handle))
+        if codes is not None:
+            out[f"qdq_roundtrip_f32_{label}"]["note"] = "the codes are stored too (9 bytes per element moved, 8 counted)"
         del q
     # the range-driven quantiser: x is read twice (range, then codes), the codes written once
     dq = DeviceArray.empty((8192, 8192), "uint8")
@@ -498,7 +514,8 @@ def other_ops(lib, stream, hbm_peak):
     bias = DeviceArray.from_numpy(rng.standard_normal((1, m)).astype(np.float32), "float32")
     flops = 2.0 * m * m * m
     import ml_dtypes
-    variants = (("bf16_in_f32_out", "bfloat16", bf16, "float32"), ("bf16_in_bf16_out", "bfloat16", bf16, "bfloat16"),
+    variants = (("f32_in_f32_out", "float32", lambda v: v, "float32"),
+                ("bf16_in_f32_out", "bfloat16", bf16, "float32"), ("bf16_in_bf16_out", "bfloat16", bf16, "bfloat16"),
                 ("fp16_in_fp16_out", "float16", lambda v: v.astype(np.float16), "float16"),
                 ("fp8_e4m3_in_bf16_out", "float8_e4m3", lambda v: (v * 16).astype(ml_dtypes.float8_e4m3fn).view(np.uint8), "bfloat16"))
     for label, dt, conv, odt in variants:
@@ -509,6 +526,8 @@ def other_ops(lib, stream, hbm_peak):
         ms = timed(lambda: lib.gemm_forward(a.handle, b.handle, bias.handle, y.handle, 1.0, 1.0, 0, 1))
         out[f"gemm_8192_{label}"] = {"TFLOPs": round(flops / 1e12 / (ms / 1e3), 1), "ms": round(ms, 4),
                                      "tensor_core_path": lib.tops_tensor_core_launches() > before}
+        if label == "f32_in_f32_out":
+            out[f"gemm_8192_{label}"]["how"] = "three bfloat16 planes per operand, six plane products accumulated in float32 (judged against the bf16 peak / 6)"
         if label == "fp8_e4m3_in_bf16_out":
             # the DQ -> Gemm -> Q chain of config 4 in one call: per-tensor operand scales, e4m3 result
             sa = DeviceArray.from_numpy(np.array([1 / 16], np.float32), "float32")
@@ -551,7 +570,188 @@ def other_ops(lib, stream, hbm_peak):
     ms = timed(lambda: lib.tops_conv2d_dqw_forward(cx.handle, wq.handle, ws.handle, None, cy.handle, ctypes.byref(cprm)), iters=3)
     out["conv_256x256x56x56_k3_bf16_int8_qdq_weights"] = {"TFLOPs": round(2.0 * 256 * 56 * 56 * 256 * 2304 / 1e12 / (ms / 1e3), 1),
                                                           "ms": round(ms, 4), "tensor_core_path": lib.tops_tensor_core_launches() > before}
+    del cx, cw, cy, wq, ws
+    out["cpu_slabs"] = cpu_slab_baselines()
     return out
+
+
+def cpu_slab_baselines():
+    """The reference C library on this machine's cores for the two contractions of config 4, timed on a slab and
+    scaled (rows of a Gemm and images of a convolution are independent: tensor_ops.c:1174-1176, 1064-1066):
+    Gemm float32 M = 32 of 8192 rows x 256; Conv float32 1 of 256 images x 256."""
+    import oracle
+    kind = "reference" if oracle.available("ref") else "port"
+    host = oracle.HostOracle("ref" if kind == "reference" else "port")
+    cores = oracle.use_all_host_threads()
+    rng = np.random.default_rng(1)
+    f32 = "float32"
+    res = {}
+    a = rng.normal(0, 0.02, (32, 8192)).astype(np.float32)
+    b = rng.normal(0, 0.02, (8192, 8192)).astype(np.float32)
+    c = rng.standard_normal(8192).astype(np.float32)
+    t0 = time.perf_counter()
+    host.gemm(a, f32, b, f32, c, f32, f32, 1.0, 1.0, 0, 1)
+    dt = time.perf_counter() - t0
+    res["gemm_8192_f32"] = {"slab": "M = 32 of 8192 rows", "slab_s": round(dt, 3), "factor": 256, "full_problem_s": round(dt * 256, 1),
+                            "GFLOPs": round(2.0 * 32 * 8192 * 8192 / 1e9 / dt, 2), "cores": cores, "kind": kind}
+    del a, b, c
+    x = rng.standard_normal((1, 256, 56, 56)).astype(np.float32)
+    w = rng.normal(0, 0.02, (256, 256, 3, 3)).astype(np.float32)
+    t0 = time.perf_counter()
+    host.conv2d(x, f32, w, f32, None, f32, f32, (1, 1, 1, 1), (1, 1), (1, 1), 1)
+    dt = time.perf_counter() - t0
+    res["conv_256x256x56x56_k3_f32"] = {"slab": "1 of 256 images", "slab_s": round(dt, 3), "factor": 256, "full_problem_s": round(dt * 256, 1),
+                                       "GFLOPs": round(2.0 * 56 * 56 * 256 * 2304 / 1e9 / dt, 2), "cores": cores, "kind": kind}
+    return res
+
+
+def sharded_leg(lib, stream, world, rank, local):
+    """Strong scaling of two fixed-size problems over the ranks (N > 1), results gathered ON THE DEVICE with NCCL:
+    the bf16 Gemm 8192^3 of config 4 sharded along N (each rank a block of rows of B and of the bias, A replicated;
+    tensor_ops.c:1174-1176 makes rows independent) followed by the all-gather of column blocks, and one float32
+    broadcast Add of config 2 sharded by rows followed by the all-gather of row blocks.  Rank 0 also computes both
+    problems whole and compares the gathered results bit for bit.  Times are device-measured, max over ranks."""
+    import torch
+    import torch.distributed as dist
+    from onnx_translator_b200 import capi, shard
+    from onnx_translator_b200.device import DeviceArray
+    rng = np.random.default_rng(7)                       # the same operands on every rank
+
+    def bf16(a):
+        u = np.ascontiguousarray(a, dtype=np.float32).view(np.uint32).astype(np.uint64)
+        return ((u + 0x7FFF + ((u >> 16) & 1)) >> 16).astype(np.uint16)
+
+    def timed(call, iters=5):
+        call()
+        lib.tops_sync()
+        torch.cuda.synchronize()
+        dist.barrier()
+        ev = [torch.cuda.Event(enable_timing=True) for _ in range(iters + 1)]
+        with torch.cuda.stream(stream):
+            ev[0].record(stream)
+            for i in range(iters):
+                call()
+                ev[i + 1].record(stream)
+        lib.tops_sync()
+        torch.cuda.synchronize()
+        ms = float(np.median([ev[i].elapsed_time(ev[i + 1]) for i in range(iters)]))
+        t = torch.tensor([ms], dtype=torch.float64, device=f"cuda:{local}")
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.cpu()[0])
+
+    out = {}
+    # -- Gemm sharded along N --------------------------------------------------------------------------
+    m = 8192
+    a_host = bf16(rng.normal(0, 0.02, (m, m)).astype(np.float32))
+    b_host = bf16(rng.normal(0, 0.02, (m, m)).astype(np.float32))
+    bias_host = rng.standard_normal((1, m)).astype(np.float32)
+    b_blk, bias_blk, (n0, n1) = shard.gemm_shard(b_host, bias_host, world, rank)
+    a = DeviceArray.from_numpy(a_host, "bfloat16")
+    b = DeviceArray.from_numpy(np.ascontiguousarray(b_blk), "bfloat16")
+    bias = DeviceArray.from_numpy(np.ascontiguousarray(bias_blk), "float32")
+    y = DeviceArray.empty((m, n1 - n0), "bfloat16")
+    gathered = {}
+
+    def gemm_compute():
+        lib.gemm_forward(a.handle, b.handle, bias.handle, y.handle, 1.0, 1.0, 0, 1)
+
+    def gemm_gather():
+        with torch.cuda.stream(stream):
+            gathered["y"] = shard.gather_columns(y.as_torch(), m)
+
+    compute_ms = timed(gemm_compute)
+    gather_ms = timed(gemm_gather)
+    same = None
+    if rank == 0:
+        b_full = DeviceArray.from_numpy(b_host, "bfloat16")
+        bias_full = DeviceArray.from_numpy(bias_host, "float32")
+        y_full = DeviceArray.empty((m, m), "bfloat16")
+        lib.gemm_forward(a.handle, b_full.handle, bias_full.handle, y_full.handle, 1.0, 1.0, 0, 1)
+        lib.tops_sync()
+        same = bool(torch.equal(gathered["y"].view(torch.int16), y_full.as_torch().view(torch.int16)))
+        del b_full, bias_full, y_full
+    out["gemm_8192_bf16_sharded_along_N"] = {
+        "compute_ms": round(compute_ms, 4), "gather_ms": round(gather_ms, 4), "TFLOPs_compute": round(2.0 * m ** 3 / 1e12 / (compute_ms / 1e3), 1),
+        "TFLOPs_with_gather": round(2.0 * m ** 3 / 1e12 / ((compute_ms + gather_ms) / 1e3), 1),
+        "collective": "NCCL all-gather of [N/g, M] row blocks of the transposed result + transposes", "collective_share": round(gather_ms / (compute_ms + gather_ms), 3),
+        "gathered_equals_single_gpu_result": same}
+    del a, b, bias, y
+    gathered.clear()
+    # -- broadcast Add sharded by rows ------------------------------------------------------------------------
+    a_host = rng.uniform(-100, 100, (FULL_ROWS, MID, INNER)).astype(np.float32)
+    b_host = rng.uniform(-100, 100, (1, MID, 1)).astype(np.float32)
+    mine = np.ascontiguousarray(shard.split_rows(a_host, world, rank))
+    a = DeviceArray.from_numpy(mine, "float32")
+    b = DeviceArray.from_numpy(b_host, "float32")
+    o = DeviceArray.empty(mine.shape, "float32")
+
+    def add_compute():
+        lib.add_forward(a.handle, b.handle, o.handle)
+
+    def add_gather():
+        with torch.cuda.stream(stream):
+            gathered["o"] = shard.gather_rows(o.as_torch(), FULL_ROWS)
+
+    compute_ms = timed(add_compute)
+    gather_ms = timed(add_gather)
+    same = None
+    if rank == 0:
+        a_full = DeviceArray.from_numpy(a_host, "float32")
+        o_full = DeviceArray.empty(a_host.shape, "float32")
+        lib.add_forward(a_full.handle, b.handle, o_full.handle)
+        lib.tops_sync()
+        same = bool(torch.equal(gathered["o"].view(torch.int32), o_full.as_torch().view(torch.int32)))
+    nbytes = a_host.nbytes * 2
+    out["add_f32_A64x512x1024_row_sharded"] = {
+        "compute_ms": round(compute_ms, 4), "gather_ms": round(gather_ms, 4), "GBps_compute": round(nbytes / 1e9 / (compute_ms / 1e3), 1),
+        "collective": "NCCL all-gather of row blocks", "collective_share": round(gather_ms / (compute_ms + gather_ms), 3),
+        "gathered_equals_single_gpu_result": same}
+    capi.check(lib)
+    return out
+
+
+def small_cnn_latency(lib, stream):
+    """Config 1: microseconds per forward pass of the small CNN (12 nodes), replayed from its call plan as one
+    CUDA graph, with the reference C library running the same nodes on the host beside it."""
+    import torch
+    import oracle
+    from oracle import graph as oracle_graph
+    from onnx_translator_b200 import capi, nn
+    graph, x = nn.small_cnn(seed=0)
+    plan = graph.plan(x)
+    plan.run()
+    captured = plan.capture()
+    iters = 200
+    for _ in range(20):
+        plan.run()
+    lib.tops_sync()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record(stream)
+    for _ in range(iters):
+        plan.run()
+    e1.record(stream)
+    lib.tops_sync()
+    torch.cuda.synchronize()
+    device_us = e0.elapsed_time(e1) * 1e3 / iters
+    t0 = time.perf_counter()
+    for _ in range(50):                                  # latency a caller sees: enqueue one pass and wait for it
+        plan.run()
+        lib.tops_sync()
+    wall_us = (time.perf_counter() - t0) * 1e6 / 50
+    capi.check(lib)
+    kind = "reference" if oracle.available("ref") else "port"
+    host = oracle.HostOracle("ref" if kind == "reference" else "port")
+    cores = oracle.use_all_host_threads()
+    oracle_graph.run(graph, host, x)
+    t0 = time.perf_counter()
+    for _ in range(20):
+        oracle_graph.run(graph, host, x)
+    cpu_us = (time.perf_counter() - t0) * 1e6 / 20
+    n_calls = len(plan.calls)
+    plan.close()
+    return {"us_per_graph_device": round(device_us, 2), "us_per_graph_enqueue_and_wait": round(wall_us, 1), "cuda_graph": bool(captured),
+            "library_calls_per_forward": n_calls,
+            "cpu_baseline": {"us_per_graph": round(cpu_us, 1), "cores": cores, "kind": kind, "sample": "20 passes, C functions node by node"}}
 
 
 def qdq_cnn_throughput(lib, stream, world, local, batch=256):
@@ -656,13 +856,30 @@ def cpu_sweep(rows, steps, warmup):
     plan = sweep_plan(rows)
     full = (rows, MID, INNER)
     prepared = []
+    wrapped_a, wrapped_b, wrapped_o = {}, {}, {}            # one host copy per distinct operand, shared by the calls that use it
+
+    def a_of(item):
+        key = "cos" if item["op"] == "cos" else item["a"]
+        if key not in wrapped_a:
+            wrapped_a[key] = oracle._Wrapped(a_cos_host if key == "cos" else a_host[key], item["a"])
+        return wrapped_a[key]
+
+    def b_of(item):
+        key = (item["bname"], item["b"], item["divisor"])
+        if key not in wrapped_b:
+            wrapped_b[key] = oracle._Wrapped(np.ascontiguousarray(np.broadcast_to(b_host[key], full)), item["b"])
+        return wrapped_b[key]
+
+    def o_of(item):
+        if item["o"] not in wrapped_o:
+            wrapped_o[item["o"]] = oracle._out(full, item["o"])
+        return wrapped_o[item["o"]]
+
     for item in plan:
-        a = a_cos_host if item["op"] == "cos" else a_host[item["a"]]
-        wa = oracle._Wrapped(a, item["a"])
-        wo = oracle._out(full, item["o"])
+        wa, wo = a_of(item), o_of(item)
         if item["kind"] == "binary":
-            b = np.ascontiguousarray(np.broadcast_to(b_host[(item["bname"], item["b"], item["divisor"])], full))
-            prepared.append((host._fn[item["op"]], (wa.ref, oracle._Wrapped(b, item["b"]).ref, wo.ref), (wa, b, wo)))
+            wb = b_of(item)
+            prepared.append((host._fn[item["op"]], (wa.ref, wb.ref, wo.ref), (wa, wb, wo)))
         else:
             prepared.append((host._fn[item["op"]], (wa.ref, wo.ref), (wa, wo)))
     bytes_step = sum(item["bytes"] for item in plan)
@@ -695,8 +912,16 @@ def run_reference(args):
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return
-    rows = 8
-    steps, warmup = max(1, args.steps), max(0, min(args.warmup, 1))
+    # the full workload of our arm (A[64,512,1024], about 4 GB of host operands) when the host has the memory for it
+    rows = FULL_ROWS
+    try:
+        with open("/proc/meminfo") as f:
+            avail_kb = next(int(line.split()[1]) for line in f if line.startswith("MemAvailable"))
+        if avail_kb < 12 * 1024 * 1024:
+            rows = 16
+    except Exception:
+        rows = 16
+    steps, warmup = max(1, min(args.steps, 20)), max(0, min(args.warmup, 1))
     gbs, dt, kind, cores = cpu_sweep(rows, steps, warmup)
     world = int(os.environ.get("WORLD_SIZE", "1"))
     line = {
@@ -705,7 +930,8 @@ def run_reference(args):
         "value": round(gbs, 3), "unit": "GB/s", "n_gpus": world, "steps": steps, "warmup": warmup,
         "ms_per_step": round(dt * 1e3, 2), "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
         "dtype": "f64 arithmetic over f32/f16/bf16/i32/i8 storage", "data": "synthetic",
-        "config": {"workload": f"config 2 sweep, bounded sample: A[{rows},512,1024] ({rows}/{FULL_ROWS} of the rows), 95 calls per step",
+        "config": {"workload": ("config 2: broadcast elementwise sweep, A[64,512,1024] x B{[1,512,1],[1024],full} x 7 dtype pairs x Add/Sub/Mul/Div + Relu/Abs x 5 dtypes + Cos f32 (95 calls per step), operands pre-broadcast on the host as the reference's ABI requires"
+                                if rows == FULL_ROWS else f"config 2 sweep, bounded sample: A[{rows},512,1024] ({rows}/{FULL_ROWS} of the rows), 95 calls per step"),
                    "parallelism": f"OpenMP, {cores} host threads"},
         "cpu_baseline": {"value": round(gbs, 3), "unit": "GB/s", "cores": cores, "kind": kind,
                          "sample": f"{steps} timed passes of the sweep on A[{rows},512,1024], C functions only, operands pre-broadcast"},

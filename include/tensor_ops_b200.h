@@ -421,6 +421,12 @@ long long tops_selftest_encoder(DataType dtype);
    the reference.  Returns the number of disagreements, or -1 on error. */
 long long tops_selftest_cos(void);
 
+/* Device-side check of the bounded waits: one thread waits on a barrier that nothing arms, with a budget of
+   `budget_microseconds` (1 .. 100000).  Returns 1 when the wait gave up as it must (0 if it claims to have succeeded,
+   -1 on error); the expiry is also recorded like a real one, so the next tops_sync reports TOPS_ERR_DEVICE_TIMEOUT
+   until tops_clear_error.  The kernel returns normally: nothing faults and the context stays usable. */
+int tops_selftest_wait_timeout(int budget_microseconds);
+
 /* Number of tensor-core (tcgen05) kernels launched so far by Gemm / Conv2d in this process: lets a
    caller tell that a call took the tensor-core path rather than the exact double-accumulating one. */
 long long tops_tensor_core_launches(void);

@@ -161,6 +161,7 @@ SIGNATURES = {
     "tops_selftest_encoder": (ctypes.c_longlong, [_I]),
     "tops_tensor_core_launches": (ctypes.c_longlong, []),
     "tops_selftest_cos": (ctypes.c_longlong, []),
+    "tops_selftest_wait_timeout": (_I, [_I]),
     "tops_debug_plan_broadcast": (_I, [_IP, _I, _IP, _I, _IP, ctypes.POINTER(ctypes.c_uint), _IP, _IP]),
     "tops_version": (ctypes.c_char_p, []),
 }

@@ -182,6 +182,31 @@ ConvTcPlan conv_tc_plan(const Tensor* X, const Tensor* W, const Tensor* Y, const
     return plan;
 }
 
+// The layout copy of images [n0, n0 + count) of X into the padded channels-last scratch, on `stream`.
+static void conv_tc_layout(const Tensor* X, void* xp, const ConvGeom& c, const ConvTcPlan& plan, int n0, int count, cudaStream_t stream) {
+    const int es = plan.es, Hp = plan.Hp, Wp = plan.Wp;
+    const char* x = (const char*)X->data + (size_t)n0 * c.C * c.H * c.W * es;
+    char* dst = (char*)xp + (size_t)n0 * Hp * Wp * c.C * es;
+    // planes that start on 16-byte boundaries take the copy that moves 16 bytes per thread on both sides
+    const bool vec_copy = ((size_t)c.H * c.W * es) % 16 == 0 && ((uintptr_t)x & 15) == 0 && ((uintptr_t)dst & 15) == 0 && count <= 65535;
+    if (vec_copy) {
+        const int tile_pos = 16 * (16 / es);
+        const dim3 vgrid((c.H * c.W + tile_pos - 1) / tile_pos, count, (c.C + 63) / 64);
+        const int row_vecs = c.C * es / 16;
+        const int pad_cells = Hp * Wp - c.H * c.W;
+        if (pad_cells > 0) {
+            const dim3 zgrid((unsigned)(((size_t)pad_cells * row_vecs + 255) / 256), count);
+            zero_padding_cells<<<zgrid, 256, 0, stream>>>((uint4*)dst, row_vecs, c.H, c.W, Hp, Wp, c.pt, c.pl);
+        }
+        if (es == 2) nchw_to_padded_nhwc_vec<uint16_t><<<vgrid, 256, 0, stream>>>((const uint16_t*)x, (uint16_t*)dst, c.C, c.H, c.W, Hp, Wp, c.pt, c.pl);
+        else         nchw_to_padded_nhwc_vec<uint8_t><<<vgrid, 256, 0, stream>>>((const uint8_t*)x, (uint8_t*)dst, c.C, c.H, c.W, Hp, Wp, c.pt, c.pl);
+        return;
+    }
+    const dim3 tgrid(count * Hp, (Wp + 63) / 64, (c.C + 63) / 64);
+    if (es == 2) nchw_to_padded_nhwc<uint16_t><<<tgrid, 256, 0, stream>>>((const uint16_t*)x, (uint16_t*)dst, c.C, c.H, c.W, Hp, Wp, c.pt, c.pl);
+    else         nchw_to_padded_nhwc<uint8_t><<<tgrid, 256, 0, stream>>>((const uint8_t*)x, (uint8_t*)dst, c.C, c.H, c.W, Hp, Wp, c.pt, c.pl);
+}
+
 bool conv_tc_run(const Tensor* X, const Tensor* W, const Tensor* B, Tensor* Y, const ConvGeom& c, const ConvTcPlan& plan,
                  void* xp, void* wt, int* status, const float* w_scale) {
     DeviceState* st = acquire_device();
@@ -190,26 +215,9 @@ bool conv_tc_run(const Tensor* X, const Tensor* W, const Tensor* B, Tensor* Y, c
     const int dx = (int)X->dtype, dw = (int)W->dtype, dy = (int)Y->dtype;
     const int es = plan.es, Hp = plan.Hp, Wp = plan.Wp, taps = plan.taps;
     const bool fp8 = plan.fp8;
-    const size_t rows = plan.rows;
 
-    const dim3 tgrid(c.N * Hp, (Wp + 63) / 64, (c.C + 63) / 64);
     const int wgrid = grid_for((size_t)c.M * c.C * taps, 256, st->sm_count, 4);
-    // planes that start on 16-byte boundaries take the copy that moves 16 bytes per thread on both sides
-    const bool vec_copy = ((size_t)c.H * c.W * es) % 16 == 0 && ((uintptr_t)X->data & 15) == 0 && ((uintptr_t)xp & 15) == 0 && c.N <= 65535;
-    if (vec_copy) {
-        const int tile_pos = 16 * (16 / es);
-        const dim3 vgrid((c.H * c.W + tile_pos - 1) / tile_pos, c.N, (c.C + 63) / 64);
-        const int row_vecs = c.C * es / 16;
-        const int pad_cells = Hp * Wp - c.H * c.W;
-        if (pad_cells > 0) {
-            const dim3 zgrid((unsigned)(((size_t)pad_cells * row_vecs + 255) / 256), c.N);
-            zero_padding_cells<<<zgrid, 256, 0, s>>>((uint4*)xp, row_vecs, c.H, c.W, Hp, Wp, c.pt, c.pl);
-        }
-        if (es == 2) nchw_to_padded_nhwc_vec<uint16_t><<<vgrid, 256, 0, s>>>((const uint16_t*)X->data, (uint16_t*)xp, c.C, c.H, c.W, Hp, Wp, c.pt, c.pl);
-        else         nchw_to_padded_nhwc_vec<uint8_t><<<vgrid, 256, 0, s>>>((const uint8_t*)X->data, (uint8_t*)xp, c.C, c.H, c.W, Hp, Wp, c.pt, c.pl);
-    }
     if (es == 2) {
-        if (!vec_copy) nchw_to_padded_nhwc<uint16_t><<<tgrid, 256, 0, s>>>((const uint16_t*)X->data, (uint16_t*)xp, c.C, c.H, c.W, Hp, Wp, c.pt, c.pl);
         if (dw == DTYPE_INT8 && dx == DTYPE_BFLOAT16)
             int8_filters_to_tap_major<true><<<wgrid, 256, 0, s>>>((const int8_t*)W->data, (uint16_t*)wt, c.M, c.C, taps);
         else if (dw == DTYPE_INT8)
@@ -217,22 +225,26 @@ bool conv_tc_run(const Tensor* X, const Tensor* W, const Tensor* B, Tensor* Y, c
         else
             filters_to_tap_major<uint16_t><<<wgrid, 256, 0, s>>>((const uint16_t*)W->data, (uint16_t*)wt, c.M, c.C, taps);
     } else {
-        if (!vec_copy) nchw_to_padded_nhwc<uint8_t><<<tgrid, 256, 0, s>>>((const uint8_t*)X->data, (uint8_t*)xp, c.C, c.H, c.W, Hp, Wp, c.pt, c.pl);
         filters_to_tap_major<uint8_t><<<wgrid, 256, 0, s>>>((const uint8_t*)W->data, (uint8_t*)wt, c.M, c.C, taps);
     }
-    if (!TOPS_CHECK_LAUNCH("conv2d_forward (layout copies)")) return false;
 
     ShiftedGemm sg;
-    sg.xp = xp; sg.wt = wt; sg.es = es; sg.fp8 = fp8;
+    sg.wt = wt; sg.es = es; sg.fp8 = fp8;
     sg.a_format = fp8 ? (dx == DTYPE_FLOAT8_E5M2 ? 1u : 0u) : (dx == DTYPE_BFLOAT16 ? 1u : 0u);
     sg.b_format = fp8 ? (dw == DTYPE_FLOAT8_E5M2 ? 1u : 0u) : (dw == DTYPE_INT8 ? sg.a_format : (dw == DTYPE_BFLOAT16 ? 1u : 0u));
-    sg.images = c.N; sg.Hp = Hp; sg.Wp = Wp; sg.C = c.C; sg.M = c.M; sg.KH = c.KH; sg.KW = c.KW; sg.dil_h = c.dh; sg.dil_w = c.dw;
+    sg.Hp = Hp; sg.Wp = Wp; sg.C = c.C; sg.M = c.M; sg.KH = c.KH; sg.KW = c.KW; sg.dil_h = c.dh; sg.dil_w = c.dw;
     sg.OH = c.OH; sg.OW = c.OW;
-    sg.Y = Y->data; sg.dy = dy;
+    sg.dy = dy;
     sg.bias = (B && B->data) ? B->data : nullptr;
     sg.bias_dtype = sg.bias ? (int)B->dtype : DTYPE_FLOAT32;
     sg.status = status;
     if (w_scale) { sg.fs.b_scale = w_scale; sg.fs.b_per_column = 1; }
+
+    conv_tc_layout(X, xp, c, plan, 0, c.N, s);
+    if (!TOPS_CHECK_LAUNCH("conv2d_forward (layout copies)")) return false;
+    sg.xp = xp;
+    sg.Y = Y->data;
+    sg.images = c.N;
     return shifted_gemm_launch(sg);
 }
 
@@ -298,18 +310,37 @@ bool shifted_gemm_launch(const ShiftedGemm& g) {
     const uint32_t idesc = umma::instr_desc(g.a_format, g.b_format, kBM, (uint32_t)n_cols);
     const int tiles = p.tiles_m * p.tiles_n;
     const int grid = tiles < st->sm_count ? tiles : st->sm_count;
-    const int epi = (g.residual ? kEpiResidual : 0) | (g.lv.z ? kEpiLevels : 0);
+    int epi = (g.residual ? kEpiResidual : 0) | (g.lv.z ? kEpiLevels : 0);
     if (g.fp8 && epi != kEpiPlain) return false;                     // the quantised extras exist for 16-bit operands only
+    // Row-linear epilogue: the GEMM row is the output pixel (no padded rows to drop) and every float32 tensor the
+    // epilogue touches is channels-last, so residual, output and levels are [rows][M] matrices the copy engine moves.
+    EpilogueMaps em{};
+    const bool rows_linear = !g.fp8 && taps == 1 && g.Hp == g.OH && g.Wp == g.OW && (g.M % 16) == 0 &&
+        (g.Y != nullptr || g.lv.z != nullptr) && (g.Y == nullptr || (g.y_channels_last && g.dy == DTYPE_FLOAT32)) &&
+        (g.residual == nullptr || g.residual_channels_last) && (!g.bias || g.bias_dtype == DTYPE_FLOAT32) &&
+        (g.lv.z == nullptr || (g.lv.S == 1 && g.lv.pt == 0 && g.lv.pl == 0 && g.lv.Hz == g.OH && g.lv.Wz == g.OW && g.lv.Cz == g.M)) &&
+        !getenv("TOPS_NO_ROW_EPILOGUE");
+    if (rows_linear) {
+        bool maps_ok = true;
+        if (g.Y) maps_ok = maps_ok && make_row_box_map(&em.y, g.Y, 4, rows, (uint64_t)g.M, 32, 16);
+        if (g.residual) maps_ok = maps_ok && make_row_box_map(&em.res, g.residual, 4, rows, (uint64_t)g.M, 32, 16);
+        if (g.lv.z) maps_ok = maps_ok && make_row_box_map(&em.lv, g.lv.z, 2, rows, (uint64_t)g.M, 32, 16);
+        if (maps_ok) epi |= kEpiRows;
+    }
 #define TOPS_CONV_LAUNCH(F8, E)                                                                                              \
     do {                                                                                                                     \
         if (!ensure_dynamic_smem((const void*)tc_kernel<F8, kModeConv, E>, tc_smem_bytes(kModeConv, E))) return false;          \
-        tc_kernel<F8, kModeConv, E><<<grid, tc_threads(kModeConv, E), tc_smem_bytes(kModeConv, E), s>>>(map_a, map_b, p, idesc);   \
+        tc_kernel<F8, kModeConv, E><<<grid, tc_threads(kModeConv, E), tc_smem_bytes(kModeConv, E), s>>>(map_a, map_b, p, idesc, em);   \
     } while (0)
     if (g.fp8) TOPS_CONV_LAUNCH(true, kEpiPlain);
     else if (epi == kEpiPlain) TOPS_CONV_LAUNCH(false, kEpiPlain);
     else if (epi == kEpiResidual) TOPS_CONV_LAUNCH(false, kEpiResidual);
     else if (epi == kEpiLevels) TOPS_CONV_LAUNCH(false, kEpiLevels);
-    else TOPS_CONV_LAUNCH(false, kEpiResidual | kEpiLevels);
+    else if (epi == (kEpiResidual | kEpiLevels)) TOPS_CONV_LAUNCH(false, kEpiResidual | kEpiLevels);
+    else if (epi == kEpiRows) TOPS_CONV_LAUNCH(false, kEpiRows);
+    else if (epi == (kEpiRows | kEpiResidual)) TOPS_CONV_LAUNCH(false, kEpiRows | kEpiResidual);
+    else if (epi == (kEpiRows | kEpiLevels)) TOPS_CONV_LAUNCH(false, kEpiRows | kEpiLevels);
+    else TOPS_CONV_LAUNCH(false, kEpiRows | kEpiResidual | kEpiLevels);
 #undef TOPS_CONV_LAUNCH
     if (!TOPS_CHECK_LAUNCH("conv2d_forward (tensor cores)")) return false;
     count_tensor_core_launch();

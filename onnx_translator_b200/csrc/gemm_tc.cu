@@ -56,6 +56,20 @@ bool make_tensor_map(CUtensorMap* out, const void* base, int elem_bytes, bool is
     return r == CUDA_SUCCESS;
 }
 
+bool make_row_box_map(CUtensorMap* out, const void* base, int elem_bytes, uint64_t rows, uint64_t cols, uint32_t box_rows, uint32_t box_cols) {
+    EncodeTiledFn fn = encode_tiled_fn();
+    if (!fn) return false;
+    const uint32_t row_bytes = box_cols * (uint32_t)elem_bytes;
+    if ((row_bytes != 32 && row_bytes != 64) || (elem_bytes != 2 && elem_bytes != 4)) return false;
+    const cuuint64_t gdim[2] = {cols, rows}, gstride[1] = {cols * (uint64_t)elem_bytes};
+    const cuuint32_t bdim[2] = {box_cols, box_rows}, estride[2] = {1, 1};
+    const CUresult r = fn(out, elem_bytes == 4 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32 : CU_TENSOR_MAP_DATA_TYPE_UINT16, 2, const_cast<void*>(base),
+                          gdim, gstride, bdim, estride, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                          row_bytes == 64 ? CU_TENSOR_MAP_SWIZZLE_64B : CU_TENSOR_MAP_SWIZZLE_32B,
+                          CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    return r == CUDA_SUCCESS;
+}
+
 // ---- host --------------------------------------------------------------------------------------------------------
 static bool is_fp8(int dt) { return dt == DTYPE_FLOAT8_E4M3 || dt == DTYPE_FLOAT8_E5M2; }
 
@@ -125,7 +139,7 @@ static bool gemm_split_f32(const Tensor* A, const Tensor* B, Tensor* Y, const Ge
         const int tiles = p.tiles_m * p.tiles_n;
         const int grid = tiles < st->sm_count ? tiles : st->sm_count;
         ok = ensure_dynamic_smem((const void*)tc_kernel<false, kModeSplit>, tc_smem_bytes(kModeSplit));
-        if (ok) tc_kernel<false, kModeSplit><<<grid, tc_threads(kModeSplit), tc_smem_bytes(kModeSplit), s>>>(map_a, map_b, p, idesc);
+        if (ok) tc_kernel<false, kModeSplit><<<grid, tc_threads(kModeSplit), tc_smem_bytes(kModeSplit), s>>>(map_a, map_b, p, idesc, EpilogueMaps{});
         ok = ok && TOPS_CHECK_LAUNCH("gemm_forward (tensor cores, float32 split)");
         if (ok) count_tensor_core_launch();
     }
@@ -192,10 +206,10 @@ bool gemm_tensor_core(const Tensor* A, const Tensor* B, Tensor* Y, const GemmSha
     cudaStream_t s = current_stream();
     if (fp8) {
         if (!ensure_dynamic_smem((const void*)tc_kernel<true, kModeGemm>, tc_smem_bytes(kModeGemm))) return true;    // error recorded
-        tc_kernel<true, kModeGemm><<<grid, tc_threads(kModeGemm), tc_smem_bytes(kModeGemm), s>>>(map_a, map_b, p, idesc);
+        tc_kernel<true, kModeGemm><<<grid, tc_threads(kModeGemm), tc_smem_bytes(kModeGemm), s>>>(map_a, map_b, p, idesc, EpilogueMaps{});
     } else {
         if (!ensure_dynamic_smem((const void*)tc_kernel<false, kModeGemm>, tc_smem_bytes(kModeGemm))) return true;
-        tc_kernel<false, kModeGemm><<<grid, tc_threads(kModeGemm), tc_smem_bytes(kModeGemm), s>>>(map_a, map_b, p, idesc);
+        tc_kernel<false, kModeGemm><<<grid, tc_threads(kModeGemm), tc_smem_bytes(kModeGemm), s>>>(map_a, map_b, p, idesc, EpilogueMaps{});
     }
     TOPS_CHECK_LAUNCH("gemm_forward (tensor cores)");
     count_tensor_core_launch();

@@ -145,45 +145,60 @@ __global__ void __launch_bounds__(256) max_pool_stride2_strips(const typename St
     const S* src = x + (size_t)plane * (size_t)(H * W) + 4u * q;
     S* dst = y + (size_t)plane * (size_t)(OH * OW) + 2u * q;
 
-    // horizontal maxima of one input row for this thread's two output columns
-    auto row_maxima = [&](int ih, bool on, float& m0, float& m1) {
-        float v[4];
-        pool_load4<DT>(src + ih * W, on, v);
+    // Phase 1: every input row of the strip is requested before any is used (2 * STRIP rows, plus the row above for the
+    // 3x3 pool), so a thread has all of its loads in flight at once.
+    constexpr int kRows = 2 * STRIP + (K == 3 ? 1 : 0);
+    const int first_row = 2 * oh0 - (K == 3 ? 1 : 0);
+    float v[kRows][4];
+    float left_edge[kRows];                                           // column 4q - 1 for lane 0 of a warp that starts inside a row
+    bool on[kRows];
+    #pragma unroll
+    for (int r = 0; r < kRows; r++) {
+        const int ih = first_row + r;
+        // the row above the strip exists for every strip but the first; rows 2 * oh and 2 * oh + 1 exist when output row oh does
+        const int rr = K == 3 ? (r - 1) >> 1 : r >> 1;
+        on[r] = (K == 3 && r == 0) ? (live && oh0 > 0 && oh0 < OH) : (live && oh0 + rr < OH);
+        pool_load4<DT>(src + ih * W, on[r], v[r]);
+        left_edge[r] = -INFINITY;
+        if constexpr (K == 3) if (lane == 0 && q != 0 && on[r]) left_edge[r] = to_f32<DT>(src[ih * W - 1]);
+    }
+    // Phase 2: horizontal maxima of each row for this thread's two output columns, then down the columns.  The tap
+    // order of the reference (row by row, left to right, strict '>') is kept.
+    auto row_maxima = [&](int r, float& m0, float& m1) {
         m0 = -INFINITY; m1 = -INFINITY;
         if constexpr (K == 3) {
-            float left = __shfl_up_sync(0xFFFFFFFFu, v[3], 1);        // column 4q - 1 lives in the lane to the left
+            float left = __shfl_up_sync(0xFFFFFFFFu, v[r][3], 1);     // column 4q - 1 lives in the lane to the left
             if (q == 0) left = -INFINITY;                             // padding column
-            else if (lane == 0 && on) left = to_f32<DT>(src[ih * W - 1]);
+            else if (lane == 0) left = left_edge[r];
             if (left > m0) m0 = left;
-            if (v[0] > m0) m0 = v[0];
-            if (v[1] > m0) m0 = v[1];
-            if (v[1] > m1) m1 = v[1];
-            if (v[2] > m1) m1 = v[2];
-            if (v[3] > m1) m1 = v[3];
+            if (v[r][0] > m0) m0 = v[r][0];
+            if (v[r][1] > m0) m0 = v[r][1];
+            if (v[r][1] > m1) m1 = v[r][1];
+            if (v[r][2] > m1) m1 = v[r][2];
+            if (v[r][3] > m1) m1 = v[r][3];
         } else {
-            if (v[0] > m0) m0 = v[0];
-            if (v[1] > m0) m0 = v[1];
-            if (v[2] > m1) m1 = v[2];
-            if (v[3] > m1) m1 = v[3];
+            if (v[r][0] > m0) m0 = v[r][0];
+            if (v[r][1] > m0) m0 = v[r][1];
+            if (v[r][2] > m1) m1 = v[r][2];
+            if (v[r][3] > m1) m1 = v[r][3];
         }
     };
-
     float carry0 = -INFINITY, carry1 = -INFINITY;                     // the row above the strip (3x3 only)
-    if constexpr (K == 3) row_maxima(2 * oh0 - 1, live && oh0 > 0 && oh0 < OH, carry0, carry1);
+    if constexpr (K == 3) row_maxima(0, carry0, carry1);
     #pragma unroll
-    for (int r = 0; r < STRIP; r++) {                                 // unrolled: the loads of the whole strip are in flight together
+    for (int r = 0; r < STRIP; r++) {
         const int oh = oh0 + r;
-        const bool on = live && oh < OH;
+        const bool row_on = live && oh < OH;
         float a0, a1, b0, b1;
-        row_maxima(2 * oh, on, a0, a1);
-        row_maxima(2 * oh + 1, on, b0, b1);
+        row_maxima(2 * r + (K == 3 ? 1 : 0), a0, a1);
+        row_maxima(2 * r + 1 + (K == 3 ? 1 : 0), b0, b1);
         float o0 = carry0, o1 = carry1;                               // -Inf for the 2x2 pool
         if (a0 > o0) o0 = a0;
         if (a1 > o1) o1 = a1;
         if (b0 > o0) o0 = b0;
         if (b1 > o1) o1 = b1;
         if constexpr (K == 3) { carry0 = b0; carry1 = b1; }
-        if (on) {
+        if (row_on) {
             S out[2];
             if constexpr (dtype_is_int(DT)) { out[0] = from_f64<DT>((double)o0); out[1] = from_f64<DT>((double)o1); }
             else { out[0] = from_f32<DT>(o0); out[1] = from_f32<DT>(o1); }
@@ -203,7 +218,7 @@ static bool launch_stride2(const Tensor* X, Tensor* Y, const PoolGeom& p, Device
     if ((uintptr_t)X->data % (4 * sizeof(S)) || (uintptr_t)Y->data % (2 * sizeof(S))) return false;
     const size_t planes = (size_t)X->shape[0] * X->shape[1];
     const uint32_t quads = (uint32_t)(p.W / 4);
-    int strip = 8;                                                    // output rows per thread
+    int strip = 4;                                                    // output rows per thread (all of a strip's input rows are loaded up front)
     while (strip > 1 && planes * quads * (size_t)((p.OH + strip - 1) / strip) < (size_t)st->sm_count * 4096) strip /= 2;
     const uint32_t strips = (uint32_t)((p.OH + strip - 1) / strip);
     const size_t total = planes * quads * strips;

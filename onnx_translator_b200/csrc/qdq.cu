@@ -49,6 +49,9 @@ static bool qdq_typed(const char* name, const Geometry& geom, Operand* ops, Tens
     });
 }
 
+bool qdq_fast(const char* name, bool quantize, const Tensor* x, const Tensor* s, const Tensor* z, Tensor* y, const ShapeView& s_shape,
+              const ShapeView& z_shape);     // qdq_fast.cu
+
 // axis >= 0: Scale / ZeroPoint are 1-D of length Y.shape[axis]; axis < -64: plain broadcasting.
 constexpr int kNoAxis = -1000;
 
@@ -88,7 +91,8 @@ static void qdq_forward(const char* name, const Tensor* x, const Tensor* s, cons
     }
     ops[0].ptr = x->data; ops[1].ptr = s->data; ops[2].ptr = z->data;
 
-    bool done = false;
+    // float32 against 8-bit codes with one scale, or one per element of the last dimension: the dedicated loops
+    bool done = qdq_fast(name, QUANTIZE, x, s, z, y, sv, zv);
 #define TOPS_Q(X, Z, O) if (!done && dx == X && ds == DTYPE_FLOAT32 && dz == Z && dout == O) { \
         qdq_typed<QuantizeBody, true, X, DTYPE_FLOAT32, Z, O>(name, geom, ops, y); done = true; }
 #define TOPS_DQ(X, Z, O) if (!done && dx == X && ds == DTYPE_FLOAT32 && dz == Z && dout == O) { \

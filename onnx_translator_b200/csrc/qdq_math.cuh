@@ -70,4 +70,13 @@ __device__ __forceinline__ float quantize_level_8bit(float x, float s, float inv
     return __fsub_rn(fminf(fmaxf(__fadd_rn(r, zf), lo), hi), zf);
 }
 
+// The same level by the reference's double division alone, kept OUT of line: the tensor-core epilogues call it only
+// for the rare values their fast rounding cannot decide, and inlining sixteen double divisions into an epilogue that
+// a handful of warps run would triple its code size for nothing.
+static __device__ __noinline__ float quantize_level_exact(float x, float s, float zf, int is_signed) {
+    const int code = is_signed ? (int)quantize_exact<DTYPE_INT8>((double)x, (double)s, (double)zf)
+                               : (int)quantize_exact<DTYPE_UINT8>((double)x, (double)s, (double)zf);
+    return (float)code - zf;
+}
+
 }  // namespace tops

@@ -3,6 +3,7 @@
 // reference encoder; disagreements are counted.  NaN inputs are skipped for bfloat16 only where
 // both produce a NaN code.
 #include "common.cuh"
+#include "umma.cuh"
 
 namespace tops {
 
@@ -28,9 +29,45 @@ __global__ void encoder_selftest_kernel(unsigned long long* mismatches, uint32_t
     if (bad) atomicAdd(mismatches, bad);
 }
 
+// One thread waits, with a short clock budget, on a barrier that nothing ever arms: the wait must give up, raise the
+// abort flag and return, and the kernel must report through the status word -- the path every tensor-core kernel of
+// the library takes when one of its waits expires.  Nothing here spins without a limit.
+__global__ void wait_timeout_selftest_kernel(int* status, long long budget_cycles, int* gave_up) {
+    __shared__ uint64_t bar;
+    __shared__ int abort_flag;
+    if (threadIdx.x == 0) {
+        umma::mbar_init(&bar, 1);
+        abort_flag = 0;
+        umma::mbar_fence_init();
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        const bool done = umma::mbar_wait(&bar, 0, &abort_flag, budget_cycles);
+        *gave_up = done ? 0 : 1;
+    }
+    __syncthreads();
+    if (threadIdx.x == 0 && abort_flag && status) atomicExch(status, 1);
+}
+
 }  // namespace tops
 
 using namespace tops;
+
+TOPS_API int tops_selftest_wait_timeout(int budget_microseconds) {
+    if (!acquire_device()) return -1;
+    if (budget_microseconds < 1 || budget_microseconds > 100000) { set_error(TOPS_ERR_INVALID, "tops_selftest_wait_timeout: budget outside 1 .. 100000 us"); return -1; }
+    int* gave_up = nullptr;
+    if (!TOPS_CUDA_OK(cudaMalloc(&gave_up, sizeof(int)))) return -1;
+    cudaStream_t s = current_stream();
+    cudaMemsetAsync(gave_up, 0, sizeof(int), s);
+    wait_timeout_selftest_kernel<<<1, 32, 0, s>>>(device_status_word(), (long long)budget_microseconds * 2000, gave_up);     // about 2 cycles per ns
+    int host = 0;
+    const bool ok = TOPS_CHECK_LAUNCH("tops_selftest_wait_timeout") &&
+                    TOPS_CUDA_OK(cudaMemcpyAsync(&host, gave_up, sizeof(host), cudaMemcpyDeviceToHost, s)) &&
+                    TOPS_CUDA_OK(cudaStreamSynchronize(s));
+    cudaFree(gave_up);
+    return ok ? host : -1;
+}
 
 TOPS_API long long tops_selftest_encoder(DataType dtype) {
     if (!acquire_device()) return -1;

@@ -19,16 +19,24 @@ constexpr int kStageRowWords = 36;                 // 32 words of payload + 4 of
 // stage for more epilogue warps -- more loads and stores in flight per SM.  A warp may only read the quarter of
 // tensor memory given by its index modulo 4, so the warps that share a quarter take alternate column chunks.
 constexpr int kModeGemm = 0, kModeConv = 1, kModeSplit = 2;
-__host__ __device__ constexpr int tc_stages(int mode) { return mode == kModeConv ? 3 : kStages; }
+// The plain convolution epilogue (no residual, no levels) leaves room for the fourth stage: its layers are the ones with
+// long K loops (a 3 x 3 convolution over 256 channels has 36 K blocks per tile), where the copy latency is what the
+// multiplier waits for.
+__host__ __device__ constexpr int tc_stages(int mode, int epi = 0) { return mode == kModeConv && epi != 0 ? 3 : kStages; }
 // Epilogue warps: 4 for the Gemm modes.  Convolution mode is bound by its epilogue (short K loops, strided NCHW
 // stores, residual loads, quantisation to levels), so it handles 16 accumulator columns at a time -- half the
 // registers per thread -- and runs 16 epilogue warps, or 12 where the residual is compiled in (its prefetch
 // registers do not fit the 96-register budget of 18 warps without spilling; measured slower).
-__host__ __device__ constexpr int tc_epilogue_warps(int mode, int epi = 0) { return mode != kModeConv ? 4 : ((epi & 1) ? 12 : 16); }
+__host__ __device__ constexpr int tc_epilogue_warps(int mode, int epi = 0) { return mode != kModeConv ? 4 : ((epi & 4) ? 16 : (epi & 1) ? 12 : 16); }
+// Row-linear epilogue (EPI bit 2): bytes of shared memory each epilogue warp stages its tiles in -- 32 rows x 64 bytes of
+// float32 output, the same of residual input, 32 rows x 32 bytes of levels -- and where the warps' barriers live.
+constexpr int kRowsOutBytes = 2048, kRowsResBytes = 2048, kRowsLevBytes = 1024, kRowsWarpBytes = 5120, kRowsBarBytes = 1024;
 __host__ __device__ constexpr int tc_chunk_columns(int mode) { return mode == kModeConv ? 16 : 32; }
 __host__ __device__ constexpr int tc_threads(int mode, int epi = 0) { return 64 + 32 * tc_epilogue_warps(mode, epi); }
 __host__ __device__ constexpr size_t tc_smem_bytes(int mode, int epi = 0) {
-    return (size_t)tc_stages(mode) * kStageBytes + 1024 /*alignment slack*/ + 128 /*barriers*/ +
+    if (mode == kModeConv && (epi & 4))
+        return (size_t)tc_stages(mode, epi) * kStageBytes + 1024 /*alignment slack*/ + kRowsBarBytes + (size_t)tc_epilogue_warps(mode, epi) * kRowsWarpBytes;
+    return (size_t)tc_stages(mode, epi) * kStageBytes + 1024 /*alignment slack*/ + 128 /*barriers*/ +
            (size_t)tc_epilogue_warps(mode, epi) * kBN * 4 /*bias*/ + (size_t)tc_epilogue_warps(mode, epi) * kBN * 4 /*column scales*/ +
            (mode == kModeConv ? 0 : 4 * 32 * kStageRowWords * 4) /*output staging (row-major outputs only)*/;
 }
@@ -82,13 +90,19 @@ __device__ __forceinline__ void tile_coords(int tile, int tiles_m, int tiles_n, 
 
 // EPI (convolution mode only) selects the epilogue extras that are compiled in, so that a kernel
 // carries registers only for what it uses: bit 0 = residual operand, bit 1 = levels output.
-constexpr int kEpiPlain = 0, kEpiResidual = 1, kEpiLevels = 2;
+// Bit 2 (convolutions whose GEMM row IS the output pixel: 1 x 1, no padding, and everything float32 channels-last):
+// the epilogue moves its tiles with the copy engine -- residual in, float32 and levels out -- through per-warp
+// staging in shared memory, so no thread issues a global load or store of its own.
+constexpr int kEpiPlain = 0, kEpiResidual = 1, kEpiLevels = 2, kEpiRows = 4;
+
+// Tensor maps of the row-linear epilogue (unused by every other variant): [rows][OC] matrices in boxes of 32 rows x 16 columns.
+struct EpilogueMaps { CUtensorMap y, res, lv; };
 
 template <bool FP8, int MODE, int EPI = kEpiPlain>
 __global__ void __launch_bounds__(tc_threads(MODE, EPI), 1)
 tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, const TcParams p,
-               const uint32_t idesc) {
-    constexpr int kSt = tc_stages(MODE), kEpi = tc_epilogue_warps(MODE, EPI);
+               const uint32_t idesc, const __grid_constant__ EpilogueMaps em) {
+    constexpr int kSt = tc_stages(MODE, EPI), kEpi = tc_epilogue_warps(MODE, EPI);
     // Sixteen epilogue warps work as two groups of eight, one per accumulator buffer: consecutive tiles of the CTA
     // are finished by different groups, so the latency chain of one tile's epilogue (accumulator ready -> tensor
     // memory load -> arithmetic -> stores) overlaps the next tile's instead of following it.
@@ -105,6 +119,10 @@ tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUt
     float* bias_stage = (float*)(bars + 16);                   // kEpi warps x kBN floats
     float* scale_stage = bias_stage + kEpi * kBN;              // kEpi warps x kBN floats
     uint32_t* out_stage = (uint32_t*)(scale_stage + kEpi * kBN);   // 4 warps x 32 rows x kStageRowWords (not in convolution mode)
+    constexpr bool kRows = MODE == kModeConv && (EPI & kEpiRows) != 0;
+    // row-linear epilogue: [barrier block of 1 KB: pipeline barriers, then one residual barrier per epilogue warp][per-warp staging]
+    uint64_t* res_bars = bars + 32;
+    uint8_t* rows_stage = (uint8_t*)bars + kRowsBarBytes;
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int tiles_per_batch = p.tiles_m * p.tiles_n;
@@ -113,6 +131,7 @@ tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUt
     if (threadIdx.x == 0) {
         for (int s = 0; s < kSt; s++) { umma::mbar_init(&full[s], 1); umma::mbar_init(&empty[s], 1); }
         for (int b = 0; b < 2; b++) { umma::mbar_init(&acc_full[b], 1); umma::mbar_init(&acc_empty[b], kEpiG); }
+        if constexpr (kRows) for (int w = 0; w < kEpi; w++) umma::mbar_init(&res_bars[w], 1);
         *abort_flag = 0;
         umma::mbar_fence_init();
         umma::tma_prefetch_desc(&map_a);
@@ -191,6 +210,142 @@ tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUt
         constexpr int kW = tc_chunk_columns(MODE);                  // accumulator columns a warp handles at a time
         const int first_chunk = eg >> 2;
         uint32_t local = 0;
+        if constexpr (kRows) {
+            // ---- row-linear epilogue: every global access is a tile copy ------------------------------------------------
+            constexpr bool with_res = (EPI & kEpiResidual) != 0, with_lv = (EPI & kEpiLevels) != 0;
+            uint8_t* st_out = rows_stage + (size_t)epi * kRowsWarpBytes;
+            uint8_t* st_res = st_out + kRowsOutBytes;
+            uint8_t* st_lv = st_res + kRowsResBytes;
+            uint64_t* res_bar = &res_bars[epi];
+            uint32_t res_phase = 0;
+            float alpha = p.alpha;
+            if (p.fs.a_scale) alpha = __fmul_rn(alpha, __ldg(p.fs.a_scale));
+            float lv_scale = 0.0f, lv_inv = 0.0f, lv_zero = 0.0f;
+            if constexpr (with_lv) {
+                lv_scale = __ldg(p.lv.scale);
+                lv_inv = quantize_reciprocal(lv_scale);
+                if (p.lv.zero) lv_zero = p.lv.zero_signed ? (float)*(const int8_t*)p.lv.zero : (float)*(const uint8_t*)p.lv.zero;
+            }
+            const float lo = p.lv.zero_signed ? -128.0f : 0.0f, hi = p.lv.zero_signed ? 127.0f : 255.0f;
+            const float lo_z = __fsub_rn(lo, lv_zero), hi_z = __fsub_rn(hi, lv_zero);
+            // this lane's 16-byte chunks inside the staged boxes (row = lane)
+            uint32_t off64[4], off32[2];
+            #pragma unroll
+            for (int j = 0; j < 4; j++) off64[j] = umma::swizzled_chunk<64>((uint32_t)lane, (uint32_t)j);
+            #pragma unroll
+            for (int j = 0; j < 2; j++) off32[j] = umma::swizzled_chunk<32>((uint32_t)lane, (uint32_t)j);
+            bool alive = true;
+            for (int tile = blockIdx.x; tile < total_tiles && alive; tile += gridDim.x, local++) {
+                const uint32_t buf = local & 1u, use = (local >> 1) & 1u;
+                if (kEpiGroups == 2 && (int)buf != group) continue;
+                int tm, tn;
+                tile_coords(tile, p.tiles_m, p.tiles_n, tm, tn);
+                const int row0 = tm * kBM + quarter * 32;             // first of this warp's 32 rows = output pixels
+                if constexpr (with_res) {                              // the first chunk's residual travels while the tensor core works
+                    if (lane == 0 && tn * kBN + first_chunk * kW < p.N) {
+                        umma::mbar_expect_tx(res_bar, kRowsResBytes);
+                        umma::tma_load_2d(st_res, &em.res, res_bar, tn * kBN + first_chunk * kW, row0);
+                    }
+                }
+                if (!umma::mbar_wait(&acc_full[buf], use, abort_flag)) break;
+                umma::fence_after_sync();
+                const uint32_t t_row = tmem_base + ((uint32_t)(quarter * 32) << 16) + buf * kBN;
+                #pragma unroll 1
+                for (int c = first_chunk; c < kBN / kW; c += kChunkStep) {
+                    const int n0 = tn * kBN + c * kW;
+                    if (n0 >= p.N) break;                              // p.N is a multiple of kW here
+                    uint32_t r[kW];
+                    umma::tmem_load_chunk<kW>(t_row + (uint32_t)(c * kW), r);
+                    float v[kW];
+                    // per-channel scale and bias straight from global memory: every lane reads the same 64 bytes
+                    float sc[kW];
+                    #pragma unroll
+                    for (int j = 0; j < kW; j += 4) {
+                        const float4 s4 = p.fs.b_per_column ? __ldg((const float4*)(p.fs.b_scale + n0 + j)) : make_float4(1.0f, 1.0f, 1.0f, 1.0f);
+                        sc[j] = s4.x; sc[j + 1] = s4.y; sc[j + 2] = s4.z; sc[j + 3] = s4.w;
+                    }
+                    float bs[kW];
+                    #pragma unroll
+                    for (int j = 0; j < kW; j += 4) {
+                        const float4 b4 = p.bias.mode == kBiasPerColumn ? __ldg((const float4*)((const float*)p.bias.ptr + n0 + j)) : make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+                        bs[j] = b4.x; bs[j + 1] = b4.y; bs[j + 2] = b4.z; bs[j + 3] = b4.w;
+                    }
+                    umma::tmem_load_wait();
+                    #pragma unroll
+                    for (int j = 0; j < kW; j++) {
+                        const float scale = p.fs.b_per_column ? __fmul_rn(alpha, sc[j]) : alpha;
+                        v[j] = __fmul_rn(scale, __uint_as_float(r[j]));
+                        if (p.bias.mode == kBiasPerColumn) v[j] = __fadd_rn(v[j], __fmul_rn(p.beta, bs[j]));
+                    }
+                    if constexpr (with_res) {
+                        if (!umma::mbar_wait(res_bar, res_phase, abort_flag)) { alive = false; break; }
+                        res_phase ^= 1u;
+                        #pragma unroll
+                        for (int j = 0; j < kW; j += 4) {
+                            const float4 r4 = *(const float4*)(st_res + off64[j >> 2]);
+                            v[j] = __fadd_rn(v[j], r4.x); v[j + 1] = __fadd_rn(v[j + 1], r4.y);
+                            v[j + 2] = __fadd_rn(v[j + 2], r4.z); v[j + 3] = __fadd_rn(v[j + 3], r4.w);
+                        }
+                        __syncwarp();                                  // every lane has read its row: the buffer may be refilled
+                        const int c_next = c + kChunkStep;
+                        if (lane == 0 && c_next < kBN / kW && tn * kBN + c_next * kW < p.N) {
+                            umma::mbar_expect_tx(res_bar, kRowsResBytes);
+                            umma::tma_load_2d(st_res, &em.res, res_bar, tn * kBN + c_next * kW, row0);
+                        }
+                    }
+                    if (p.relu) {
+                        #pragma unroll
+                        for (int j = 0; j < kW; j++) v[j] = fmaxf(v[j], 0.0f);
+                    }
+                    uint32_t packed[kW / 2];
+                    if constexpr (with_lv) {
+                        #pragma unroll
+                        for (int j0 = 0; j0 < kW; j0 += 8) {
+                            float level[8];
+                            bool decided = true;
+                            #pragma unroll
+                            for (int e = 0; e < 8; e++) {
+                                const float q = __fmul_rn(v[j0 + e], lv_inv);
+                                const float rq = __fsub_rn(__fadd_rn(q, 12582912.0f), 12582912.0f);
+                                decided = decided & (fmaf(fabsf(q), 1.9073486e-6f, fabsf(__fsub_rn(q, rq))) < 0.5f);
+                                level[e] = fminf(fmaxf(rq, lo_z), hi_z);
+                            }
+                            if (!decided) {
+                                #pragma unroll
+                                for (int e = 0; e < 8; e++)
+                                    level[e] = quantize_level_exact(v[j0 + e], lv_scale, lv_zero, p.lv.zero_signed);
+                            }
+                            #pragma unroll
+                            for (int e = 0; e < 8; e += 2)
+                                packed[(j0 + e) >> 1] = __byte_perm(__float_as_uint(level[e]), __float_as_uint(level[e + 1]), 0x7632);
+                        }
+                    }
+                    // the previous chunk's stores must have read the staging buffers before they are overwritten
+                    if (lane == 0) umma::bulk_wait_read();
+                    __syncwarp();
+                    if (p.Y != nullptr) {
+                        #pragma unroll
+                        for (int j = 0; j < kW; j += 4) *(float4*)(st_out + off64[j >> 2]) = make_float4(v[j], v[j + 1], v[j + 2], v[j + 3]);
+                    }
+                    if constexpr (with_lv) {
+                        #pragma unroll
+                        for (int j = 0; j < kW / 8; j++)
+                            *(uint4*)(st_lv + off32[j]) = make_uint4(packed[4 * j], packed[4 * j + 1], packed[4 * j + 2], packed[4 * j + 3]);
+                    }
+                    umma::fence_proxy_async_smem();
+                    __syncwarp();
+                    if (lane == 0) {
+                        if (p.Y != nullptr) umma::tma_store_2d(&em.y, st_out, n0, row0);
+                        if constexpr (with_lv) umma::tma_store_2d(&em.lv, st_lv, n0, row0);
+                        umma::bulk_commit();
+                    }
+                }
+                umma::fence_before_sync();
+                __syncwarp();
+                if (lane == 0) umma::mbar_arrive(&acc_empty[buf]);
+            }
+            if (lane == 0) umma::bulk_wait_all();                   // the staging buffers outlive every store that reads them
+        } else {
         float* my_bias = bias_stage + epi * kBN;                     // this warp's private copy: no cross-warp sync
         uint32_t* my_stage = out_stage + quarter * 32 * kStageRowWords;
         float* my_scale = scale_stage + epi * kBN;
@@ -384,8 +539,7 @@ tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUt
                                     if (!decided) {
                                         #pragma unroll
                                         for (int e = 0; e < 8; e++)
-                                            level[e] = p.lv.zero_signed ? quantize_level_8bit<DTYPE_INT8>(v[j0 + e], ls, linv, zf)
-                                                                        : quantize_level_8bit<DTYPE_UINT8>(v[j0 + e], ls, linv, zf);
+                                            level[e] = quantize_level_exact(v[j0 + e], ls, zf, p.lv.zero_signed);
                                     }
                                     #pragma unroll
                                     for (int e = 0; e < 8; e += 2)
@@ -441,20 +595,40 @@ tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUt
                             *(uint4*)(my_rows + (j >> 1)) = make_uint4(encode_bf16x2(v[j], v[j + 1]), encode_bf16x2(v[j + 2], v[j + 3]),
                                                                         encode_bf16x2(v[j + 4], v[j + 5]), encode_bf16x2(v[j + 6], v[j + 7]));
                     } else if (dtype_bytes(p.dy) == 1) {
-                        // 8-bit outputs: QuantizeLinear when a result scale was given, a plain store otherwise
+                        // 8-bit outputs: QuantizeLinear when a result scale was given, a plain store otherwise.  All of it
+                        // stays on the float32 / integer pipes (the float64 pipe is narrow and this runs once per element):
+                        // integers through a saturating pack -- NaN, Inf and |q| >= 2^63 become the most negative value
+                        // first, as the reference's float -> int64 conversion makes them -- and integer-valued float8
+                        // results through the paired hardware convert, which agrees with the reference's encoder on them.
                         #pragma unroll
                         for (int j = 0; j < 32; j += 4) {
-                            uint32_t word = 0;
+                            float q[4];
                             #pragma unroll
                             for (int e = 0; e < 4; e++) {
-                                float q = v[j + e];
-                                if (p.fs.y_scale) q = rintf(__fmul_rn(q, y_inv));
-                                uint32_t code;
-                                if (p.dy == DTYPE_FLOAT8_E4M3) code = encode_e4m3(q);
-                                else if (p.dy == DTYPE_FLOAT8_E5M2) code = encode_e5m2(q);
-                                else if (p.dy == DTYPE_INT8) code = (uint8_t)from_f64<DTYPE_INT8>((double)q);
-                                else code = from_f64<DTYPE_UINT8>((double)q);
-                                word |= code << (8 * e);
+                                q[e] = v[j + e];
+                                if (p.fs.y_scale) q[e] = rintf(__fmul_rn(q[e], y_inv));
+                            }
+                            uint32_t word = 0;
+                            if (p.dy == DTYPE_INT8 || p.dy == DTYPE_UINT8) {
+                                int iv[4];
+                                #pragma unroll
+                                for (int e = 0; e < 4; e++) iv[e] = fabsf(q[e]) < 9.2e18f ? __float2int_rn(q[e]) : (int)0x80000000;
+                                word = p.dy == DTYPE_INT8 ? pack_sat_s8x4(iv[0], iv[1], iv[2], iv[3]) : pack_sat_u8x4(iv[0], iv[1], iv[2], iv[3]);
+                            } else if (p.fs.y_scale && p.dy == DTYPE_FLOAT8_E4M3) {
+                                const uint32_t lo2 = __nv_cvt_float2_to_fp8x2(make_float2(q[0], q[1]), __NV_SATFINITE, __NV_E4M3);
+                                const uint32_t hi2 = __nv_cvt_float2_to_fp8x2(make_float2(q[2], q[3]), __NV_SATFINITE, __NV_E4M3);
+                                word = lo2 | (hi2 << 16);
+                            } else if (p.fs.y_scale && p.dy == DTYPE_FLOAT8_E5M2) {
+                                const uint32_t lo2 = __nv_cvt_float2_to_fp8x2(make_float2(q[0], q[1]), __NV_SATFINITE, __NV_E5M2);
+                                const uint32_t hi2 = __nv_cvt_float2_to_fp8x2(make_float2(q[2], q[3]), __NV_SATFINITE, __NV_E5M2);
+                                word = lo2 | (hi2 << 16);
+                                #pragma unroll
+                                for (int e = 0; e < 4; e++)          // the reference overflows to infinity where the hardware saturates
+                                    if (fabsf(q[e]) >= 61440.0f) word = (word & ~(0xFFu << (8 * e))) | ((q[e] < 0.0f ? 0xFCu : 0x7Cu) << (8 * e));
+                            } else {
+                                #pragma unroll
+                                for (int e = 0; e < 4; e++)
+                                    word |= (uint32_t)(p.dy == DTYPE_FLOAT8_E4M3 ? encode_e4m3(q[e]) : encode_e5m2(q[e])) << (8 * e);
                             }
                             my_rows[j >> 2] = word;
                         }
@@ -497,6 +671,7 @@ tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUt
             __syncwarp();
             if (lane == 0) umma::mbar_arrive(&acc_empty[buf]);
         }
+        }   // not the row-linear epilogue
     }
 
     umma::fence_before_sync();

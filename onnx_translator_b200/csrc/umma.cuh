@@ -37,14 +37,14 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
 }
 // Waits for the phase with the given parity.  Returns false when the budget ran out or another
 // role already raised `*abort_flag` (shared memory); the caller then leaves its loop.
-__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag) {
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag, long long budget_cycles = kWaitBudgetCycles) {
     if (mbar_try_wait(bar, parity)) return true;
     const long long t0 = clock64();
     for (;;) {
         #pragma unroll 1
         for (int i = 0; i < 64; i++) if (mbar_try_wait(bar, parity)) return true;
         if (*abort_flag) return false;
-        if (clock64() - t0 > kWaitBudgetCycles) { *abort_flag = 1; return false; }
+        if (clock64() - t0 > budget_cycles) { *abort_flag = 1; return false; }
     }
 }
 
@@ -76,6 +76,19 @@ __device__ __forceinline__ void tma_load_4d(void* smem, const CUtensorMap* map, 
         ::"r"(smem_u32(smem)), "l"(reinterpret_cast<uint64_t>(map)), "r"(smem_u32(bar)), "r"(c0), "r"(c1), "r"(c2), "r"(c3)
         : "memory");
 }
+
+// Tile stores shared -> global (bulk async group of the issuing thread).  The shared-memory source must have been
+// made visible to the async proxy (fence_proxy_async_smem after the generic-proxy writes) and must not be
+// overwritten until bulk_wait_read says the copy engine has read it.
+__device__ __forceinline__ void tma_store_2d(const CUtensorMap* map, const void* smem, int c0, int c1) {
+    asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%2, %3}], [%1];"
+                 ::"l"(reinterpret_cast<uint64_t>(map)), "r"(smem_u32(smem)), "r"(c0), "r"(c1) : "memory");
+}
+__device__ __forceinline__ void bulk_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
+// All of this thread's committed bulk stores have finished READING shared memory (the buffers may be reused).
+__device__ __forceinline__ void bulk_wait_read() { asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory"); }
+// All of this thread's committed bulk stores have completed.
+__device__ __forceinline__ void bulk_wait_all() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
 
 // ---- tcgen05 ------------------------------------------------------------------------------------------------
 __device__ __forceinline__ void tmem_alloc(uint32_t* smem_slot, uint32_t columns) {     // one full warp
@@ -148,6 +161,17 @@ __host__ __device__ constexpr uint32_t instr_desc(uint32_t a_format, uint32_t b_
     return (1u << 4) | (a_format << 7) | (b_format << 10) | ((n >> 3) << 17) | ((m >> 4) << 24);
 }
 
+// Byte offset of 16-byte chunk `chunk` of row `row` inside a box whose rows are ROW_BYTES (32 or 64) wide, as the
+// copy engine lays it out with the swizzle of that width: the chunk index is XORed with address bits 7 and up
+// (one bit for 32-byte rows, two for 64-byte rows).  The box base must be aligned to 1024 bytes.
+template <int ROW_BYTES>
+__device__ __forceinline__ uint32_t swizzled_chunk(uint32_t row, uint32_t chunk) {
+    static_assert(ROW_BYTES == 32 || ROW_BYTES == 64, "row width");
+    const uint32_t linear = row * ROW_BYTES;
+    const uint32_t mask = ROW_BYTES == 64 ? 3u : 1u;
+    return linear + ((chunk ^ ((linear >> 7) & mask)) << 4);
+}
+
 }  // namespace umma
 
 // Host: encode a tiled tensor map (rank <= 4) with the 128-byte swizzle and zero fill.
@@ -155,5 +179,9 @@ __host__ __device__ constexpr uint32_t instr_desc(uint32_t a_format, uint32_t b_
 bool make_tensor_map(CUtensorMap* out, const void* base, int elem_bytes, bool is_fp8, bool is_fp16, int rank,
                      const uint64_t* dims, const uint64_t* strides_bytes, const uint32_t* box,
                      const uint32_t* elem_strides);
+// Host: a row-major matrix [rows][cols] of float32 (elem_bytes 4) or 16-bit (elem_bytes 2) elements seen as boxes of
+// box_rows x box_cols whose rows are 32 or 64 bytes wide; the shared-memory image uses the swizzle of that width
+// (16-byte chunk index XOR address bits 7.., see swizzled_chunk).
+bool make_row_box_map(CUtensorMap* out, const void* base, int elem_bytes, uint64_t rows, uint64_t cols, uint32_t box_rows, uint32_t box_cols);
 
 }  // namespace tops

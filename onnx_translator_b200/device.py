@@ -79,6 +79,28 @@ class DeviceArray:
     def data_ptr(self) -> int:
         return self.handle.contents.data or 0
 
+    # -- zero-copy hand-over to frameworks ---------------------------------------------------------------
+    _TYPESTR = {"float32": "<f4", "float64": "<f8", "float16": "<f2", "int8": "|i1", "uint8": "|u1", "int4": "|i1", "int16": "<i2",
+                "int32": "<i4", "int64": "<i8", "bfloat16": "<u2", "float8_e4m3": "|u1", "float8_e5m2": "|u1", "bool": "|u1"}
+
+    @property
+    def __cuda_array_interface__(self):
+        """The CUDA array interface (version 2): lets torch / cupy / numba view the memory without a copy.  Types numpy
+        has no name for travel as their storage codes (bfloat16 as uint16, float8 as uint8)."""
+        return {"shape": self.shape, "typestr": self._TYPESTR[self.dtype_name], "data": (self.data_ptr, False), "version": 2}
+
+    def as_torch(self):
+        """A torch tensor over the same device memory (no copy); it keeps this array alive.  Work enqueued on the
+        library's stream must be ordered before torch touches it: run torch under
+        ``torch.cuda.ExternalStream(lib.tops_get_stream())`` or call ``tops_sync`` first."""
+        import torch
+        device = self._lib.tops_get_device()
+        t = torch.as_tensor(self, device=torch.device("cuda", device))
+        if self.dtype_name == "bfloat16":
+            t = t.view(torch.bfloat16)                 # the interface carried the codes as 16-bit integers
+        t._tops_owner = self
+        return t
+
     def reshape(self, *shape) -> "DeviceArray":
         """Zero-copy view with a new shape (one -1 allowed)."""
         if len(shape) == 1 and isinstance(shape[0], (tuple, list)):

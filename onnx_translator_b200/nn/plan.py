@@ -14,8 +14,8 @@ work is the same every time, and at eight ranks per host it is what the GPUs end
 
 ``GraphPlan.run`` replays the list: one ctypes call per recorded operator call, nothing else.
 ``GraphPlan.capture`` replays it once more inside ``tops_capture_begin`` / ``tops_capture_end``; from
-then on ``run`` is a single ``tops_capture_launch``.  Outputs are the tensors of the recording pass,
-overwritten by every run.  A plan is valid for the input shapes and dtypes it was recorded with, and
+then on ``run`` is a single ``tops_capture_launch``.  Inputs are copied (device to device) into buffers the
+plan owns; outputs are the tensors of the recording pass, overwritten by every run.  A plan is valid for the input shapes and dtypes it was recorded with, and
 for graphs whose control flow does not depend on tensor contents (a node that reads a tensor back
 to the host while recording is refused).
 """
@@ -93,7 +93,16 @@ class GraphPlan:
         self.graph = graph                    # keeps nodes, attribute arrays and initializers alive
         self.lib = Ops._get_lib()
         graph.make_resident()
-        self.inputs = [t.to_device() for t in inputs]
+        # the plan's own input buffers (copies of the example inputs): a caller's tensor is never aliased, so a later
+        # run(other) cannot overwrite it
+        from . import Tensor
+        from ..device import DeviceArray
+        self.inputs = []
+        for t in inputs:
+            src = t.to_device()
+            mine = DeviceArray.empty(tuple(src.data.shape), src.dtype, lib=self.lib)
+            self.lib.flatten_forward(src.data.handle, mine.handle)
+            self.inputs.append(Tensor(*src.size, dtype=src.dtype, data=mine))
         self._captured = None
         recorder = _Recorder(self.lib)
         Ops._recorder = recorder
@@ -113,7 +122,7 @@ class GraphPlan:
             raise ValueError(f"plan takes {len(self.inputs)} inputs, got {len(inputs)}")
         for mine, given in zip(self.inputs, inputs):
             if given is mine or given.data is mine.data:
-                continue
+                continue                      # the caller wrote into the plan's own buffer
             src = given.to_device()
             if tuple(src.data.shape) != tuple(mine.data.shape) or src.dtype != mine.dtype:
                 raise ValueError(f"plan was recorded for input {tuple(mine.data.shape)} {mine.dtype}, got {tuple(src.data.shape)} {src.dtype}")

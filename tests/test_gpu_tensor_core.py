@@ -200,29 +200,49 @@ def test_fused_fp8_gemm_with_operand_scales(port, case):
     _gate(to_f64(got, out_dt), want, s_mag, out_dt, "fused fp8 gemm")
 
 
-def test_fused_fp8_gemm_quantised_result(port):
-    """DQ -> Gemm -> Q(e4m3): every code lies between the codes the oracle's QuantizeLinear gives
-    for the float64 result minus and plus the accumulation tolerance."""
+@pytest.mark.parametrize("out_dt", ["float8_e4m3", "float8_e5m2", "int8", "uint8"])
+def test_fused_fp8_gemm_quantised_result(port, out_dt):
+    """DQ -> Gemm -> Q: every code lies between the codes the oracle's QuantizeLinear gives for the float64 result
+    minus and plus the accumulation tolerance -- for each 8-bit result type, with results beyond the type's range
+    (saturation for e4m3 and the integers, infinity for e5m2) and a NaN row among them."""
     from onnx_translator_b200 import fused
     m, n, k = 384, 512, 1024
     rng = np.random.default_rng(5)
-    sa, sb, sy = np.float32(1 / 1024), np.float32(1 / 2048), np.float32(1 / 16)
+    sa, sb = np.float32(1 / 1024), np.float32(1 / 2048)
+    sy = np.float32({"float8_e4m3": 1 / 16, "float8_e5m2": 1 / 4096, "int8": 1 / 8, "uint8": 1 / 8}[out_dt])
     a = from_f64(rng.normal(0, 40, (m, k)), "float8_e4m3")
     b = from_f64(rng.normal(0, 90, (n, k)), "float8_e4m3")
+    a[7, :] = 0x7F                                                    # a NaN operand row: the whole result row is NaN
     bias = rng.normal(0, 1, n).astype(np.float32)
-    zero = np.zeros(1, np.uint8)
-    a_dq = port.dequantize(a, "float8_e4m3", np.array([sa]), "float32", zero, "float8_e4m3", "float32").astype(np.float64)
-    b_dq = port.dequantize(b, "float8_e4m3", np.array([sb]), "float32", zero, "float8_e4m3", "float32").astype(np.float64)
-    y = a_dq @ b_dq.T + bias.astype(np.float64)
-    tol = 1e-6 * (np.abs(a_dq) @ np.abs(b_dq).T + np.abs(bias)) + 2.0 ** -23 * np.abs(y)
-    lo = np.nextafter((y - tol).astype(np.float32), np.float32(-np.inf))
-    hi = np.nextafter((y + tol).astype(np.float32), np.float32(np.inf))
-    q = lambda v: to_f64(port.quantize(v, "float32", np.array([sy]), "float32", zero, "float8_e4m3", "float8_e4m3"), "float8_e4m3")
+    bias[::37] = 1e9 if out_dt != "float8_e5m2" else 3e4             # far beyond the range / past e5m2's overflow threshold after scaling
+    bias[5::41] = -1e9 if out_dt != "float8_e5m2" else -3e4
+    zero_dt = out_dt if out_dt in ("int8", "uint8") else "float8_e4m3"
+    zero = np.zeros(1, np.int8 if zero_dt == "int8" else np.uint8)
+    e4_zero = np.zeros(1, np.uint8)
+    a_dq = port.dequantize(a, "float8_e4m3", np.array([sa]), "float32", e4_zero, "float8_e4m3", "float32").astype(np.float64)
+    b_dq = port.dequantize(b, "float8_e4m3", np.array([sb]), "float32", e4_zero, "float8_e4m3", "float32").astype(np.float64)
+    with np.errstate(invalid="ignore"):
+        y = a_dq @ b_dq.T + bias.astype(np.float64)
+        tol = 1e-6 * (np.abs(a_dq) @ np.abs(b_dq).T + np.abs(bias)) + 2.0 ** -23 * np.abs(y)
+    finite = np.isfinite(y)
+    lo = np.nextafter(np.where(finite, y - tol, 0).astype(np.float32), np.float32(-np.inf))
+    hi = np.nextafter(np.where(finite, y + tol, 0).astype(np.float32), np.float32(np.inf))
+    q = lambda v: to_f64(port.quantize(v, "float32", np.array([sy]), "float32", zero, zero_dt, out_dt), out_dt)
     q_lo, q_hi = q(lo), q(hi)
-    got = to_f64(fused.gemm_qdq(a, sa, b, sb, bias.reshape(1, n), y_scale=sy, out_dtype="float8_e4m3").numpy(), "float8_e4m3")
-    assert np.all((got >= q_lo) & (got <= q_hi)), int(((got < q_lo) | (got > q_hi)).sum())
-    assert np.mean(got == q(y.astype(np.float32))) > 0.999
-    assert np.unique(got).size > 20                                   # a real spread of codes, not a saturated output
+    got_codes = fused.gemm_qdq(a, sa, b, sb, bias.reshape(1, n), y_scale=sy, out_dtype=out_dt).numpy()
+    got = to_f64(got_codes, out_dt)
+    inside = (got >= q_lo) & (got <= q_hi)
+    assert np.all(inside[finite]), int((~inside[finite]).sum())
+    want_nan_row = port.quantize(np.full(n, np.nan, np.float32), "float32", np.array([sy]), "float32", zero, zero_dt, out_dt)
+    if out_dt in ("int8", "uint8"):
+        assert np.array_equal(got_codes[7], want_nan_row)            # the x86 float -> integer conversion of NaN: the most negative value
+    else:
+        assert np.all(np.isnan(got[7]))
+    rows = np.arange(m) != 7
+    assert np.mean(got[rows] == q(y.astype(np.float32))[rows]) > 0.999
+    assert np.unique(got[rows]).size > 20                             # a real spread of codes, not a saturated output
+    if out_dt == "float8_e5m2":
+        assert np.isinf(got[rows][:, ::37]).all() and np.isinf(got[rows][:, 5::41]).all()
 
 
 @pytest.mark.parametrize("x_dt", ["bfloat16", "float16"])

@@ -19,7 +19,8 @@ def _worker(rank, world, port, ret):
     import torch.distributed as dist
     import oracle
     from onnx_translator_b200 import shard
-    dist.init_process_group("gloo", rank=rank, world_size=world)
+    import datetime
+    dist.init_process_group("gloo", rank=rank, world_size=world, timeout=datetime.timedelta(seconds=120))
     try:
         port_lib = oracle.HostOracle("port")
         rng = np.random.default_rng(123)                       # same data on every rank
@@ -80,9 +81,17 @@ def test_two_ranks_reproduce_the_single_process_result():
     procs = [ctx.Process(target=_worker, args=(r, 2, port, ret)) for r in range(2)]
     for p in procs:
         p.start()
-    for p in procs:
-        p.join(timeout=180)
-        assert p.exitcode == 0
+    try:
+        for p in procs:
+            p.join(timeout=180)
+    finally:
+        for p in procs:                                  # a rank stuck in a collective after its peer died is ended here
+            if p.is_alive():
+                p.terminate()
+                p.join(10)
+                if p.is_alive():
+                    p.kill()
+    assert [p.exitcode for p in procs] == [0, 0]
     assert dict(ret) == {0: (True,) * 6, 1: (True,) * 6}
 
 
