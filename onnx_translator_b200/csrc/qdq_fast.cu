@@ -3,10 +3,11 @@
 //   * one scale and one zero point for the whole tensor, or
 //   * one per element of the innermost dimension (per-axis on the last axis).
 // Everything that does not depend on the element -- reciprocal of the scale, zero point folded into the rounding
-// constant -- is computed once per thread instead of once per run, and a thread moves 16 elements per step
-// (64 bytes of float32, 16 bytes of codes).  The arithmetic is that of the general bodies (qdq_math.cuh): rounding by
-// adding 1.5 * 2^23, a tie margin test, the reference's double division for the rare undecided run.
-// For the per-axis form the grid is sized so that a thread meets the same 16 columns on every step.
+// constant -- is computed once per thread instead of once per run, and a thread moves 16 elements per step, as four
+// groups of four that interleave with the other lanes' groups so that each instruction of the warp is one contiguous
+// span.  The arithmetic is that of the general bodies (qdq_math.cuh): rounding by adding 1.5 * 2^23, a tie margin test,
+// the reference's double division for the rare undecided group.
+// For the per-axis form the grid is sized so that a warp meets the same 128 columns on every step.
 #include "elementwise.cuh"
 #include "qdq_math.cuh"
 
@@ -33,172 +34,204 @@ template <int DO, int DZ> __device__ __forceinline__ float zero_point_term(const
     else return z;
 }
 
-// 16 values -> 16 codes.  `inv`, `zf` (zero_point_term): per element when PER_COLUMN, else entry 0 serves all.
-template <int DO, bool PER_COLUMN>
-__device__ __forceinline__ bool quantize16(const float (&x)[16], const float* inv, const float* zf, uint32_t (&words)[4]) {
+// A warp works on tiles; inside a tile lane l owns the groups of four consecutive elements l, l + 32, l + 64, l + 96, so
+// every load and every store instruction of the warp covers one contiguous span (512 bytes of float32, 128 bytes of
+// codes) -- a thread that walked 16 consecutive elements would write each 32-byte sector in two halves.
+
+// Four values -> four codes in one word.  Returns false when the fast rounding could not decide some element.
+template <int DO>
+__device__ __forceinline__ bool quantize4(const float4 x, const float (&inv)[4], const float (&zt)[4], uint32_t& word) {
     constexpr bool kFp8 = DO == DTYPE_FLOAT8_E4M3 || DO == DTYPE_FLOAT8_E5M2;
+    const float v[4] = {x.x, x.y, x.z, x.w};
     bool all_ok = true;
     if constexpr (kFp8) {
-        float fr[16];
+        float fr[4];
         #pragma unroll
-        for (int j = 0; j < 16; j++) {
-            const float q = __fmul_rn(x[j], inv[PER_COLUMN ? j : 0]);
+        for (int j = 0; j < 4; j++) {
+            const float q = __fmul_rn(v[j], inv[j]);
             const float rq = __fsub_rn(__fadd_rn(q, 12582912.0f), 12582912.0f);
             all_ok = all_ok & (fmaf(fabsf(q), 1.9073486e-6f, fabsf(__fsub_rn(q, rq))) < 0.5f);
             if constexpr (DO == DTYPE_FLOAT8_E5M2) all_ok = all_ok & (fabsf(q) < 57000.0f);     // beyond: the reference overflows to infinity
-            fr[j] = __fadd_rn(rq, zf[PER_COLUMN ? j : 0]);
+            fr[j] = __fadd_rn(rq, zt[j]);
         }
-        #pragma unroll
-        for (int j = 0; j < 16; j += 4) {
-            const uint32_t lo = __nv_cvt_float2_to_fp8x2(make_float2(fr[j], fr[j + 1]), __NV_SATFINITE, DO == DTYPE_FLOAT8_E4M3 ? __NV_E4M3 : __NV_E5M2);
-            const uint32_t hi = __nv_cvt_float2_to_fp8x2(make_float2(fr[j + 2], fr[j + 3]), __NV_SATFINITE, DO == DTYPE_FLOAT8_E4M3 ? __NV_E4M3 : __NV_E5M2);
-            words[j >> 2] = lo | (hi << 16);
-        }
+        const uint32_t lo = __nv_cvt_float2_to_fp8x2(make_float2(fr[0], fr[1]), __NV_SATFINITE, DO == DTYPE_FLOAT8_E4M3 ? __NV_E4M3 : __NV_E5M2);
+        const uint32_t hi = __nv_cvt_float2_to_fp8x2(make_float2(fr[2], fr[3]), __NV_SATFINITE, DO == DTYPE_FLOAT8_E4M3 ? __NV_E4M3 : __NV_E5M2);
+        word = lo | (hi << 16);
     } else {
-        int v[16];
+        int c[4];
         #pragma unroll
-        for (int j = 0; j < 16; j++) {
-            const float q = __fmul_rn(x[j], inv[PER_COLUMN ? j : 0]);
+        for (int j = 0; j < 4; j++) {
+            const float q = __fmul_rn(v[j], inv[j]);
             const float t = __fadd_rn(q, 12582912.0f);
             const float d = __fsub_rn(q, __fsub_rn(t, 12582912.0f));
             all_ok = all_ok & (fmaf(fabsf(q), 1.9073486e-6f, fabsf(d)) < 0.5f);
-            v[j] = __float_as_int(t) + __float_as_int(zf[PER_COLUMN ? j : 0]);
+            c[j] = __float_as_int(t) + __float_as_int(zt[j]);
         }
-        #pragma unroll
-        for (int j = 0; j < 16; j += 4)
-            words[j >> 2] = DO == DTYPE_INT8 ? pack_sat_s8x4(v[j], v[j + 1], v[j + 2], v[j + 3]) : pack_sat_u8x4(v[j], v[j + 1], v[j + 2], v[j + 3]);
+        word = DO == DTYPE_INT8 ? pack_sat_s8x4(c[0], c[1], c[2], c[3]) : pack_sat_u8x4(c[0], c[1], c[2], c[3]);
     }
     return all_ok;
 }
 
-// One step of 16 elements at `first`; `col` is the first column's index into scale / zero (0 for the per-tensor form).
-template <int DO, int DZ, bool PER_COLUMN>
-__device__ __forceinline__ void quantize_step(const float* __restrict__ x, uint8_t* __restrict__ y, const float* __restrict__ scale,
-                                              const void* __restrict__ zero, size_t first, size_t col, const float* inv, const float* zf) {
-    float v[16];
+// Quantise four groups of four elements (16-byte aligned, at first[k]; `on[k]` false skips a group).  All four loads are
+// issued before the first value is used.  `col`: index of a group's first scale / zero point, `col_step` 1 when the
+// scales differ per column, 0 when one scale serves all.
+template <int DO, int DZ>
+__device__ __forceinline__ void quantize_groups(const float* __restrict__ x, uint8_t* __restrict__ y, const float* __restrict__ scale,
+                                                const void* __restrict__ zero, const size_t (&first)[4], const bool (&on)[4], size_t col,
+                                                size_t col_step, const float (&inv)[4], const float (&zt)[4]) {
+    float4 v[4];
+    #pragma unroll
+    for (int k = 0; k < 4; k++) v[k] = on[k] ? __ldcs(reinterpret_cast<const float4*>(x + first[k])) : make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+    uint32_t word[4];
+    bool ok[4];
+    #pragma unroll
+    for (int k = 0; k < 4; k++) ok[k] = quantize4<DO>(v[k], inv, zt, word[k]);
     #pragma unroll
     for (int k = 0; k < 4; k++) {
-        const float4 f = __ldcs(reinterpret_cast<const float4*>(x + first) + k);
-        v[4 * k] = f.x; v[4 * k + 1] = f.y; v[4 * k + 2] = f.z; v[4 * k + 3] = f.w;
-    }
-    uint32_t words[4];
-    if (!quantize16<DO, PER_COLUMN>(v, inv, zf, words)) {          // rare: some element sits on a rounding tie, is huge or not finite
-        #pragma unroll
-        for (int j = 0; j < 16; j++) {
-            const size_t c = PER_COLUMN ? col + j : 0;
-            const uint32_t code = quantize_exact_code<DO>(v[j], scale[c], zero_point_value<DZ>(zero, c));
-            if ((j & 3) == 0) words[j >> 2] = code;
-            else words[j >> 2] |= code << (8 * (j & 3));
+        if (!on[k]) continue;
+        if (!ok[k]) {                                                // rare: a rounding tie, a huge or a non-finite value
+            const float e[4] = {v[k].x, v[k].y, v[k].z, v[k].w};
+            word[k] = 0;
+            #pragma unroll
+            for (int j = 0; j < 4; j++) {
+                const size_t c = col + j * col_step;
+                word[k] |= quantize_exact_code<DO>(e[j], scale[c], zero_point_value<DZ>(zero, c)) << (8 * j);
+            }
         }
+        __stcs(reinterpret_cast<uint32_t*>(y + first[k]), word[k]);
     }
-    __stcs(reinterpret_cast<uint4*>(y + first), make_uint4(words[0], words[1], words[2], words[3]));
 }
+
+constexpr int kTileElems = 512;          // per warp and step: 4 groups of 4 elements per lane
 
 template <int DO, int DZ>
 __global__ void __launch_bounds__(256) quantize_per_tensor_kernel(const float* __restrict__ x, uint8_t* __restrict__ y, const float* __restrict__ scale,
                                                                   const void* __restrict__ zero, size_t n) {
     wait_for_previous_kernel();
-    float inv[1] = {quantize_reciprocal(__ldg(scale))};
-    float zf[1] = {zero_point_term<DO, DZ>(zero, 0)};
-    const size_t runs = n / 16, step = (size_t)gridDim.x * blockDim.x;
-    for (size_t r = (size_t)blockIdx.x * blockDim.x + threadIdx.x; r < runs; r += step)
-        quantize_step<DO, DZ, false>(x, y, scale, zero, r * 16, 0, inv, zf);
-    if (blockIdx.x == 0 && threadIdx.x == 0)                             // the last, incomplete run
-        for (size_t i = runs * 16; i < n; i++) {
-            const typename Storage<DO>::type code = quantize_exact<DO>((double)x[i], (double)scale[0], (double)zero_point_value<DZ>(zero, 0));
-            y[i] = *reinterpret_cast<const uint8_t*>(&code);
-        }
+    const float inv1 = quantize_reciprocal(__ldg(scale)), zt1 = zero_point_term<DO, DZ>(zero, 0);
+    const float inv[4] = {inv1, inv1, inv1, inv1}, zt[4] = {zt1, zt1, zt1, zt1};
+    const size_t lane = threadIdx.x & 31, warp = ((size_t)blockIdx.x * blockDim.x + threadIdx.x) >> 5, warps = ((size_t)gridDim.x * blockDim.x) >> 5;
+    const size_t tiles = n / kTileElems;
+    const bool on[4] = {true, true, true, true};
+    for (size_t t = warp; t < tiles; t += warps) {
+        const size_t base = t * kTileElems + lane * 4;
+        const size_t first[4] = {base, base + 128, base + 256, base + 384};
+        quantize_groups<DO, DZ>(x, y, scale, zero, first, on, 0, 0, inv, zt);
+    }
+    if (warp == 0)                                                   // what does not fill a tile: element by element, the reference's way
+        for (size_t i = tiles * kTileElems + lane; i < n; i += 32) y[i] = (uint8_t)quantize_exact_code<DO>(x[i], scale[0], zero_point_value<DZ>(zero, 0));
 }
 
-// rows x cols, scale / zero of length cols; cols is a multiple of 16 and the thread count a multiple of cols / 16.
+// rows x cols with scale / zero of length cols; cols is a multiple of 128.  A warp owns one tile of 128 columns (lane l
+// the columns 4l .. 4l + 3 of it, whose reciprocals and zero points it keeps) and walks down the rows four at a time;
+// the warp count is a multiple of the number of column tiles.
 template <int DO, int DZ>
 __global__ void __launch_bounds__(256) quantize_per_column_kernel(const float* __restrict__ x, uint8_t* __restrict__ y, const float* __restrict__ scale,
                                                                   const void* __restrict__ zero, size_t rows, uint32_t cols) {
     wait_for_previous_kernel();
-    const uint32_t groups = cols / 16;
-    const size_t tid = (size_t)blockIdx.x * blockDim.x + threadIdx.x, threads = (size_t)gridDim.x * blockDim.x;
-    const uint32_t col = (uint32_t)(tid % groups) * 16;
-    float inv[16], zf[16];
+    const uint32_t col_tiles = cols / 128;
+    const size_t lane = threadIdx.x & 31, warp = ((size_t)blockIdx.x * blockDim.x + threadIdx.x) >> 5, warps = ((size_t)gridDim.x * blockDim.x) >> 5;
+    const size_t col = (warp % col_tiles) * 128 + lane * 4;
+    float inv[4], zt[4];
     #pragma unroll
-    for (int j = 0; j < 16; j++) { inv[j] = quantize_reciprocal(__ldg(scale + col + j)); zf[j] = zero_point_term<DO, DZ>(zero, col + j); }
-    for (size_t row = tid / groups; row < rows; row += threads / groups)
-        quantize_step<DO, DZ, true>(x, y, scale, zero, row * cols + col, col, inv, zf);
+    for (int j = 0; j < 4; j++) { inv[j] = quantize_reciprocal(__ldg(scale + col + j)); zt[j] = zero_point_term<DO, DZ>(zero, col + j); }
+    for (size_t row = (warp / col_tiles) * 4; row < rows; row += (warps / col_tiles) * 4) {
+        const size_t base = row * cols + col;
+        const size_t first[4] = {base, base + cols, base + 2 * (size_t)cols, base + 3 * (size_t)cols};
+        const bool on[4] = {true, row + 1 < rows, row + 2 < rows, row + 3 < rows};
+        quantize_groups<DO, DZ>(x, y, scale, zero, first, on, col, 1, inv, zt);
+    }
 }
 
-// ---- Dequantize: 16 codes -> 16 float32 -------------------------------------------------------------------------------
-template <int DX, bool PER_COLUMN>
-__device__ __forceinline__ void dequantize_step(const uint8_t* __restrict__ x, float* __restrict__ y, size_t first, const float* s, const float* zf) {
-    const uint4 raw = __ldcs(reinterpret_cast<const uint4*>(x + first));
-    const uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
-    float f[16];
-    #pragma unroll
-    for (int k = 0; k < 4; k++) {
-        if constexpr (DX == DTYPE_INT8 || DX == DTYPE_UINT8) {
-            // the byte becomes the low mantissa byte of 2^23 (signed bytes biased by 128 first); the bias leaves with the zero point
-            const uint32_t word = DX == DTYPE_INT8 ? (w[k] ^ 0x80808080u) : w[k];
-            const float bias = DX == DTYPE_INT8 ? 8388736.0f : 8388608.0f;
-            f[4 * k]     = __fsub_rn(__uint_as_float(__byte_perm(word, 0x4B000000u, 0x7540)), bias);
-            f[4 * k + 1] = __fsub_rn(__uint_as_float(__byte_perm(word, 0x4B000000u, 0x7541)), bias);
-            f[4 * k + 2] = __fsub_rn(__uint_as_float(__byte_perm(word, 0x4B000000u, 0x7542)), bias);
-            f[4 * k + 3] = __fsub_rn(__uint_as_float(__byte_perm(word, 0x4B000000u, 0x7543)), bias);
-        } else {
-            #pragma unroll
-            for (int h = 0; h < 2; h++) {                        // two float8 codes per hardware convert
-                const uint16_t two = (uint16_t)(w[k] >> (16 * h));
-                uint32_t half2_bits;
-                if constexpr (DX == DTYPE_FLOAT8_E4M3) {
-                    const __half2_raw hr = __nv_cvt_fp8x2_to_halfraw2(two, __NV_E4M3);
-                    half2_bits = (uint32_t)hr.x | ((uint32_t)hr.y << 16);
-                } else {
-                    half2_bits = __byte_perm((uint32_t)two, 0u, 0x1404);       // an e5m2 code is the upper byte of a float16
-                }
-                const float2 p = __half22float2(*reinterpret_cast<const __half2*>(&half2_bits));
-                f[4 * k + 2 * h] = p.x; f[4 * k + 2 * h + 1] = p.y;
+// ---- Dequantize: four codes (one word) -> four float32 ---------------------------------------------------------------------
+template <int DX>
+__device__ __forceinline__ void dequantize_word(uint32_t w, float* __restrict__ dst, const float (&s)[4], const float (&zf)[4]) {
+    float f[4];
+    if constexpr (DX == DTYPE_INT8 || DX == DTYPE_UINT8) {
+        // the byte becomes the low mantissa byte of 2^23 (signed bytes biased by 128 first), then the bias is subtracted
+        const uint32_t word = DX == DTYPE_INT8 ? (w ^ 0x80808080u) : w;
+        const float bias = DX == DTYPE_INT8 ? 8388736.0f : 8388608.0f;
+        f[0] = __fsub_rn(__uint_as_float(__byte_perm(word, 0x4B000000u, 0x7540)), bias);
+        f[1] = __fsub_rn(__uint_as_float(__byte_perm(word, 0x4B000000u, 0x7541)), bias);
+        f[2] = __fsub_rn(__uint_as_float(__byte_perm(word, 0x4B000000u, 0x7542)), bias);
+        f[3] = __fsub_rn(__uint_as_float(__byte_perm(word, 0x4B000000u, 0x7543)), bias);
+    } else {
+        #pragma unroll
+        for (int h = 0; h < 2; h++) {                                // two float8 codes per hardware convert
+            const uint16_t two = (uint16_t)(w >> (16 * h));
+            uint32_t half2_bits;
+            if constexpr (DX == DTYPE_FLOAT8_E4M3) {
+                const __half2_raw hr = __nv_cvt_fp8x2_to_halfraw2(two, __NV_E4M3);
+                half2_bits = (uint32_t)hr.x | ((uint32_t)hr.y << 16);
+            } else {
+                half2_bits = __byte_perm((uint32_t)two, 0u, 0x1404);   // an e5m2 code is the upper byte of a float16
             }
+            const float2 p = __half22float2(*reinterpret_cast<const __half2*>(&half2_bits));
+            f[2 * h] = p.x; f[2 * h + 1] = p.y;
         }
     }
+    float4 out;
+    out.x = __fmul_rn(__fsub_rn(f[0], zf[0]), s[0]);
+    out.y = __fmul_rn(__fsub_rn(f[1], zf[1]), s[1]);
+    out.z = __fmul_rn(__fsub_rn(f[2], zf[2]), s[2]);
+    out.w = __fmul_rn(__fsub_rn(f[3], zf[3]), s[3]);
+    __stcs(reinterpret_cast<float4*>(dst), out);
+}
+
+// Four groups of four codes (one word each, at first[k]); all four loads are issued before the first is used.
+template <int DX>
+__device__ __forceinline__ void dequantize_groups(const uint8_t* __restrict__ x, float* __restrict__ y, const size_t (&first)[4], const bool (&on)[4],
+                                                  const float (&s)[4], const float (&zf)[4]) {
+    uint32_t w[4];
     #pragma unroll
-    for (int k = 0; k < 4; k++) {
-        float4 out;
-        out.x = __fmul_rn(__fsub_rn(f[4 * k], zf[PER_COLUMN ? 4 * k : 0]), s[PER_COLUMN ? 4 * k : 0]);
-        out.y = __fmul_rn(__fsub_rn(f[4 * k + 1], zf[PER_COLUMN ? 4 * k + 1 : 0]), s[PER_COLUMN ? 4 * k + 1 : 0]);
-        out.z = __fmul_rn(__fsub_rn(f[4 * k + 2], zf[PER_COLUMN ? 4 * k + 2 : 0]), s[PER_COLUMN ? 4 * k + 2 : 0]);
-        out.w = __fmul_rn(__fsub_rn(f[4 * k + 3], zf[PER_COLUMN ? 4 * k + 3 : 0]), s[PER_COLUMN ? 4 * k + 3 : 0]);
-        __stcs(reinterpret_cast<float4*>(y + first) + k, out);
-    }
+    for (int k = 0; k < 4; k++) w[k] = on[k] ? __ldcs(reinterpret_cast<const uint32_t*>(x + first[k])) : 0u;
+    #pragma unroll
+    for (int k = 0; k < 4; k++) if (on[k]) dequantize_word<DX>(w[k], y + first[k], s, zf);
 }
 
 template <int DX, int DZ>
 __global__ void __launch_bounds__(256) dequantize_per_tensor_kernel(const uint8_t* __restrict__ x, float* __restrict__ y, const float* __restrict__ scale,
                                                                     const void* __restrict__ zero, size_t n) {
     wait_for_previous_kernel();
-    float s[1] = {__ldg(scale)};
-    float zf[1] = {zero_point_value<DZ>(zero, 0)};
-    const size_t runs = n / 16, step = (size_t)gridDim.x * blockDim.x;
-    for (size_t r = (size_t)blockIdx.x * blockDim.x + threadIdx.x; r < runs; r += step) dequantize_step<DX, false>(x, y, r * 16, s, zf);
-    if (blockIdx.x == 0 && threadIdx.x == 0)
-        for (size_t i = runs * 16; i < n; i++) y[i] = __fmul_rn(__fsub_rn(to_f32<DX>(((const typename Storage<DX>::type*)x)[i]), zf[0]), s[0]);
+    const float s1 = __ldg(scale), z1 = zero_point_value<DZ>(zero, 0);
+    const float s[4] = {s1, s1, s1, s1}, zf[4] = {z1, z1, z1, z1};
+    const size_t lane = threadIdx.x & 31, warp = ((size_t)blockIdx.x * blockDim.x + threadIdx.x) >> 5, warps = ((size_t)gridDim.x * blockDim.x) >> 5;
+    const size_t tiles = n / kTileElems;
+    const bool on[4] = {true, true, true, true};
+    for (size_t t = warp; t < tiles; t += warps) {
+        const size_t base = t * kTileElems + lane * 4;
+        const size_t first[4] = {base, base + 128, base + 256, base + 384};
+        dequantize_groups<DX>(x, y, first, on, s, zf);
+    }
+    if (warp == 0)
+        for (size_t i = tiles * kTileElems + lane; i < n; i += 32)
+            y[i] = __fmul_rn(__fsub_rn(to_f32<DX>(((const typename Storage<DX>::type*)x)[i]), z1), s1);
 }
 
 template <int DX, int DZ>
 __global__ void __launch_bounds__(256) dequantize_per_column_kernel(const uint8_t* __restrict__ x, float* __restrict__ y, const float* __restrict__ scale,
                                                                     const void* __restrict__ zero, size_t rows, uint32_t cols) {
     wait_for_previous_kernel();
-    const uint32_t groups = cols / 16;
-    const size_t tid = (size_t)blockIdx.x * blockDim.x + threadIdx.x, threads = (size_t)gridDim.x * blockDim.x;
-    const uint32_t col = (uint32_t)(tid % groups) * 16;
-    float s[16], zf[16];
+    const uint32_t col_tiles = cols / 128;
+    const size_t lane = threadIdx.x & 31, warp = ((size_t)blockIdx.x * blockDim.x + threadIdx.x) >> 5, warps = ((size_t)gridDim.x * blockDim.x) >> 5;
+    const size_t col = (warp % col_tiles) * 128 + lane * 4;
+    float s[4], zf[4];
     #pragma unroll
-    for (int j = 0; j < 16; j++) { s[j] = __ldg(scale + col + j); zf[j] = zero_point_value<DZ>(zero, col + j); }
-    for (size_t row = tid / groups; row < rows; row += threads / groups) dequantize_step<DX, true>(x, y, row * cols + col, s, zf);
+    for (int j = 0; j < 4; j++) { s[j] = __ldg(scale + col + j); zf[j] = zero_point_value<DZ>(zero, col + j); }
+    for (size_t row = (warp / col_tiles) * 4; row < rows; row += (warps / col_tiles) * 4) {
+        const size_t base = row * cols + col;
+        const size_t first[4] = {base, base + cols, base + 2 * (size_t)cols, base + 3 * (size_t)cols};
+        const bool on[4] = {true, row + 1 < rows, row + 2 < rows, row + 3 < rows};
+        dequantize_groups<DX>(x, y, first, on, s, zf);
+    }
 }
 
 // ---- host ---------------------------------------------------------------------------------------------------------------
-// Thread blocks of 256 such that the thread count is a multiple of `groups` (0 when that takes more than the GPU holds).
+// Thread blocks of 256 (8 warps) such that the warp count is a multiple of `groups` (0 when that takes more than the GPU holds).
 static int grid_multiple_of(uint32_t groups, size_t work_items, int sm_count) {
-    uint64_t a = groups, b = 256;
+    uint64_t a = groups, b = 8;
     while (b) { const uint64_t t = a % b; a = b; b = t; }
-    const uint64_t unit = (uint64_t)groups / a;                    // blocks per period: lcm(groups, 256) / 256
+    const uint64_t unit = (uint64_t)groups / a;                    // blocks per period: lcm(groups, 8) / 8
     const uint64_t limit = (uint64_t)sm_count * kEwCtasPerSm;
     if (unit > limit) return 0;
     uint64_t want = (work_items + 255) / 256;
@@ -233,7 +266,7 @@ static int scale_form(const Tensor* t, const ShapeView& s, const ShapeView& z) {
     auto inner_vector = [&](const ShapeView& v) {                 // size == cols with the last dimension == cols: every other dimension is 1
         return v.size == cols && v.ndim >= 1 && v.ndim <= t->ndim && (size_t)v.shape[v.ndim - 1] == cols;
     };
-    if (cols >= 16 && cols % 16 == 0 && cols <= 0x7FFFFFF0ull && inner_vector(s) && inner_vector(z)) return 2;
+    if (cols >= 128 && cols % 128 == 0 && cols <= 0x7FFFFF80ull && inner_vector(s) && inner_vector(z)) return 2;
     return 0;
 }
 
@@ -255,7 +288,7 @@ bool qdq_fast(const char* name, bool quantize, const Tensor* x, const Tensor* s,
     const float* scale = (const float*)s->data;
     bool ok = true;
     if (form == 1) {
-        const int grid = grid_for((n + 15) / 16, 256, st->sm_count, kEwCtasPerSm);
+        const int grid = grid_for((n + 15) / 16, 256, st->sm_count, kEwCtasPerSm);       // 16 elements per thread and step
 #define TOPS_FAST(DC, DZ)                                                                                                                  \
         if (dc == DC && dz == DZ) {                                                                                                        \
             ok = quantize ? launch_pdl(name, quantize_per_tensor_kernel<DC, DZ>, grid, (const float*)x->data, (uint8_t*)y->data, scale, (const void*)z->data, n) \
@@ -266,7 +299,7 @@ bool qdq_fast(const char* name, bool quantize, const Tensor* x, const Tensor* s,
     } else {
         const uint32_t cols = (uint32_t)y->shape[y->ndim - 1];
         const size_t rows = n / cols;
-        const int grid = grid_multiple_of(cols / 16, n / 16, st->sm_count);
+        const int grid = grid_multiple_of(cols / 128, n / 16, st->sm_count);
         if (grid == 0) return false;
 #define TOPS_FAST(DC, DZ)                                                                                                                  \
         if (dc == DC && dz == DZ) {                                                                                                        \

@@ -545,7 +545,11 @@ tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUt
                                     for (int e = 0; e < 8; e += 2)
                                         packed[(j0 + e) >> 1] = __byte_perm(__float_as_uint(level[e]), __float_as_uint(level[e + 1]), 0x7632);
                                 }
-                                if (n0 + kW <= p.N) {                  // kW contiguous channels of this pixel
+                                if (n0 + kW <= p.N && kW == 16 && ((p.lv.Cz | p.lv.C) & 15) == 0) {
+                                    // kW contiguous channels of this pixel = one 32-byte sector, written by ONE instruction: two
+                                    // 16-byte stores per lane would leave every sector half-written between them
+                                    umma::store_global_32B(zdst, packed);
+                                } else if (n0 + kW <= p.N) {
                                     #pragma unroll
                                     for (int q4 = 0; q4 < kW / 8; q4++)
                                         *reinterpret_cast<uint4*>(zdst + 8 * q4) = make_uint4(packed[4 * q4], packed[4 * q4 + 1], packed[4 * q4 + 2], packed[4 * q4 + 3]);

@@ -50,7 +50,7 @@ def test_per_tensor_forms(port, codes, shape):
 
 
 @pytest.mark.parametrize("codes", CODES, ids=lambda c: c[0])
-@pytest.mark.parametrize("shape", [(37, 64), (5, 3, 48), (300, 16), (2, 8192)], ids=str)
+@pytest.mark.parametrize("shape", [(37, 128), (5, 3, 256), (300, 16), (2, 8192), (9, 64)], ids=str)
 def test_one_scale_per_element_of_the_last_dimension(port, codes, shape):
     code_dt, zero_dt = codes
     cols = shape[-1]
