@@ -298,6 +298,8 @@ bool shifted_gemm_launch(const ShiftedGemm& g) {
     p.status = g.status;
     p.vec_store = 0;
     p.cv.Wp = g.Wp; p.cv.plane = g.Hp * g.Wp;
+    p.cv.by_plane.set((uint32_t)(g.Hp * g.Wp));
+    p.cv.by_Wp.set((uint32_t)g.Wp);
     p.cv.images = g.images; p.cv.OH = g.OH; p.cv.OW = g.OW; p.cv.OC = g.M;
     p.cv.KW = g.KW; p.cv.dil_h = g.dil_h; p.cv.dil_w = g.dil_w;
     p.fs = g.fs;
@@ -307,6 +309,7 @@ bool shifted_gemm_launch(const ShiftedGemm& g) {
     p.y_cl = g.y_channels_last;
     p.res_cl = g.residual_channels_last;
     p.stage_tx = (uint32_t)(kTileABytes + n_cols * kRowBytes);
+    p.acc_buffers = (n_cols <= 128 && !getenv("TOPS_TWO_ACC_BUFFERS")) ? 4 : 2;
     const uint32_t idesc = umma::instr_desc(g.a_format, g.b_format, kBM, (uint32_t)n_cols);
     const int tiles = p.tiles_m * p.tiles_n;
     const int grid = tiles < st->sm_count ? tiles : st->sm_count;
@@ -326,6 +329,14 @@ bool shifted_gemm_launch(const ShiftedGemm& g) {
         if (g.residual) maps_ok = maps_ok && make_row_box_map(&em.res, g.residual, 4, rows, (uint64_t)g.M, 32, 16);
         if (g.lv.z) maps_ok = maps_ok && make_row_box_map(&em.lv, g.lv.z, 2, rows, (uint64_t)g.M, 32, 16);
         if (maps_ok) epi |= kEpiRows;
+    }
+    // a narrow filter box leaves room for more, smaller pipeline stages in the shared memory the variant reserves
+    {
+        const uint32_t bytes = (uint32_t)(kTileABytes + n_cols * kRowBytes);
+        const int room = tc_stages(kModeConv, epi) * kStageBytes;
+        int st = room / (int)bytes;
+        if (st > 8) st = 8;
+        if (n_cols < kBN && !getenv("TOPS_FIXED_STAGES")) { p.stages = st; p.stage_bytes = bytes; }
     }
 #define TOPS_CONV_LAUNCH(F8, E)                                                                                              \
     do {                                                                                                                     \

@@ -36,7 +36,7 @@ __host__ __device__ constexpr int tc_threads(int mode, int epi = 0) { return 64 
 __host__ __device__ constexpr size_t tc_smem_bytes(int mode, int epi = 0) {
     if (mode == kModeConv && (epi & 4))
         return (size_t)tc_stages(mode, epi) * kStageBytes + 1024 /*alignment slack*/ + kRowsBarBytes + (size_t)tc_epilogue_warps(mode, epi) * kRowsWarpBytes;
-    return (size_t)tc_stages(mode, epi) * kStageBytes + 1024 /*alignment slack*/ + 128 /*barriers*/ +
+    return (size_t)tc_stages(mode, epi) * kStageBytes + 1024 /*alignment slack*/ + 256 /*barriers*/ +
            (size_t)tc_epilogue_warps(mode, epi) * kBN * 4 /*bias*/ + (size_t)tc_epilogue_warps(mode, epi) * kBN * 4 /*column scales*/ +
            (mode == kModeConv ? 0 : 4 * 32 * kStageRowWords * 4) /*output staging (row-major outputs only)*/;
 }
@@ -50,6 +50,7 @@ struct ConvView {
     int images, OH, OW, OC;
     int c_blocks;          // K blocks per filter tap
     int KW, dil_h, dil_w;
+    FastDiv by_plane, by_Wp;   // row index -> (image, padded row, padded column) without integer divisions
 };
 
 struct TcParams {
@@ -64,6 +65,8 @@ struct TcParams {
     int* status;           // device-visible word, set non-zero when a wait gave up
     int vec_store;         // Y base and row pitch are 16-byte aligned
     uint32_t stage_tx = kStageBytes;   // bytes the two copies of a pipeline stage deliver (less when the B box is narrower than kBN)
+    int stages = 0;                    // pipeline stages in use (0: as many as the kernel variant reserves room for) ...
+    uint32_t stage_bytes = kStageBytes;   // ... of this many bytes each: a narrower B box leaves room for more, smaller stages
     int batches = 1;       // Gemm mode: independent problems of one shape; the tensor maps are then 3-D
                            // (K, rows, batch) and Y holds the results back to back
     ConvView cv;           // convolution mode only
@@ -71,12 +74,14 @@ struct TcParams {
     int relu = 0;          // clamp the result at zero before it is stored (v > 0 ? v : 0)
     const float* residual = nullptr;   // convolution mode: float32 tensor of the output's shape added before the clamp
     LevelsOut lv;                      // convolution mode: also / instead write the result as levels for the next convolution
+    int acc_buffers = 2;               // accumulator buffers in tensor memory: 2 x 256 columns, or 4 x 128 (N <= 128, 16 epilogue warps)
     int y_cl = 0;                      // convolution mode: Y (float32) is stored channels-last [N][OH][OW][OC] instead of NCHW
     int res_cl = 0;                    // convolution mode: the residual is stored channels-last
 };
 
 __device__ __forceinline__ void tile_coords(int tile, int tiles_m, int tiles_n, int& tm, int& tn) {
     // groups of 16 row blocks sweep all column blocks: concurrently running CTAs share A and B tiles in L2
+    if (tiles_n == 1) { tm = tile; tn = 0; return; }              // one column block: no integer divisions
     constexpr int kGroup = 16;
     const int per_group = kGroup * tiles_n;
     const int g = tile / per_group, r = tile - g * per_group;
@@ -103,20 +108,31 @@ __global__ void __launch_bounds__(tc_threads(MODE, EPI), 1)
 tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, const TcParams p,
                const uint32_t idesc, const __grid_constant__ EpilogueMaps em) {
     constexpr int kSt = tc_stages(MODE, EPI), kEpi = tc_epilogue_warps(MODE, EPI);
-    // Sixteen epilogue warps work as two groups of eight, one per accumulator buffer: consecutive tiles of the CTA
-    // are finished by different groups, so the latency chain of one tile's epilogue (accumulator ready -> tensor
-    // memory load -> arithmetic -> stores) overlaps the next tile's instead of following it.
-    constexpr int kEpiGroups = kEpi >= 16 ? 2 : 1, kEpiG = kEpi / kEpiGroups;
+    // Sixteen epilogue warps work as groups, one per accumulator buffer: consecutive tiles of the CTA are finished by
+    // different groups, so the latency chain of one tile's epilogue (accumulator ready -> tensor memory load ->
+    // arithmetic -> stores) overlaps the next tiles' instead of following it.  Two buffers of 256 columns and two
+    // groups of eight warps normally; layers with at most 128 output channels get FOUR buffers of 128 columns and four
+    // groups of four warps (one per quarter of the tile's rows): twice as many tiles in flight, and a warp meets each
+    // tile's fixed work (row decode, barrier hand-offs) once per four column chunks instead of once per two.
+    const int n_buf = kEpi >= 16 ? p.acc_buffers : 2;
+    const int epi_groups = kEpi >= 16 ? n_buf : 1, epi_per_group = kEpi / epi_groups;
+    const uint32_t acc_stride = n_buf == 4 ? 128u : (uint32_t)kBN;
+    const uint32_t buf_mask = (uint32_t)n_buf - 1u, buf_shift = n_buf == 4 ? 2u : 1u;     // tile counter -> (buffer, phase) without a division
     extern __shared__ uint8_t smem_raw[];
     uint8_t* tiles = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
     uint64_t* bars = (uint64_t*)(tiles + (size_t)kSt * kStageBytes);
-    uint64_t* full = bars;                    // [kSt]  TMA -> MMA
-    uint64_t* empty = bars + kSt;             // [kSt]  MMA -> TMA
-    uint64_t* acc_full = bars + 2 * kSt;      // [2]    MMA -> epilogue
-    uint64_t* acc_empty = acc_full + 2;       // [2]    epilogue -> MMA
-    uint32_t* tmem_slot = (uint32_t*)(acc_empty + 2);
+    // Stages: the variant reserves kSt * kStageBytes; a layer whose filter box is narrow cuts that room into more, smaller
+    // stages (short K loops wait on the copy latency, and more stages in flight hide more of it).
+    constexpr int kMaxStages = 8;
+    const uint32_t n_st = p.stages > 0 ? (uint32_t)p.stages : (uint32_t)kSt;
+    const uint32_t stage_bytes = p.stages > 0 ? p.stage_bytes : (uint32_t)kStageBytes;
+    uint64_t* full = bars;                    // [kMaxStages]  TMA -> MMA
+    uint64_t* empty = bars + kMaxStages;      // [kMaxStages]  MMA -> TMA
+    uint64_t* acc_full = bars + 2 * kMaxStages;   // [4]    MMA -> epilogue
+    uint64_t* acc_empty = acc_full + 4;       // [4]    epilogue -> MMA
+    uint32_t* tmem_slot = (uint32_t*)(acc_empty + 4);
     volatile int* abort_flag = (volatile int*)(tmem_slot + 1);
-    float* bias_stage = (float*)(bars + 16);                   // kEpi warps x kBN floats
+    float* bias_stage = (float*)(bars + 26);                   // kEpi warps x kBN floats
     float* scale_stage = bias_stage + kEpi * kBN;              // kEpi warps x kBN floats
     uint32_t* out_stage = (uint32_t*)(scale_stage + kEpi * kBN);   // 4 warps x 32 rows x kStageRowWords (not in convolution mode)
     constexpr bool kRows = MODE == kModeConv && (EPI & kEpiRows) != 0;
@@ -129,8 +145,8 @@ tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUt
     const int total_tiles = MODE == kModeGemm ? tiles_per_batch * p.batches : tiles_per_batch;
 
     if (threadIdx.x == 0) {
-        for (int s = 0; s < kSt; s++) { umma::mbar_init(&full[s], 1); umma::mbar_init(&empty[s], 1); }
-        for (int b = 0; b < 2; b++) { umma::mbar_init(&acc_full[b], 1); umma::mbar_init(&acc_empty[b], kEpiG); }
+        for (uint32_t s = 0; s < n_st; s++) { umma::mbar_init(&full[s], 1); umma::mbar_init(&empty[s], 1); }
+        for (int b = 0; b < 4; b++) { umma::mbar_init(&acc_full[b], 1); umma::mbar_init(&acc_empty[b], (uint32_t)epi_per_group); }
         if constexpr (kRows) for (int w = 0; w < kEpi; w++) umma::mbar_init(&res_bars[w], 1);
         *abort_flag = 0;
         umma::mbar_fence_init();
@@ -145,26 +161,26 @@ tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUt
 
     if (warp == 0) {
         if (lane == 0) {
-            uint32_t it = 0;
+            // One thread feeds the whole pipeline, so every instruction of this loop is on the critical path of a K
+            // block: stage index, phase and filter tap are carried as counters -- an integer division by a run-time
+            // value costs this thread more than the multiplies of a short K block take.
+            uint32_t s = 0, ph = 0;
             for (int tile = blockIdx.x; tile < total_tiles && !*abort_flag; tile += gridDim.x) {
                 int tm, tn;
-                const int bt = MODE == kModeGemm ? tile / tiles_per_batch : 0;
+                const int bt = (MODE == kModeGemm && p.batches > 1) ? tile / tiles_per_batch : 0;
                 tile_coords(tile - bt * tiles_per_batch, p.tiles_m, p.tiles_n, tm, tn);
-                for (int kb = 0; kb < p.k_blocks; kb++, it++) {
-                    const uint32_t s = it % kSt, ph = (it / kSt) & 1u;
+                int cb = 0, tap = 0, kw = 0, shift = 0;             // channel block inside the tap / plane pair, tap, its column, its row shift
+                for (int kb = 0; kb < p.k_blocks; kb++) {
                     if (!umma::mbar_wait(&empty[s], ph ^ 1u, abort_flag)) break;
-                    uint8_t* a_tile = tiles + (size_t)s * kStageBytes;
+                    uint8_t* a_tile = tiles + (size_t)s * stage_bytes;
                     umma::mbar_expect_tx(&full[s], p.stage_tx);
                     if constexpr (MODE == kModeSplit) {
                         // smallest products first: (a3 b1) (a2 b2) (a1 b3) (a2 b1) (a1 b2) (a1 b1)
-                        const int seg = kb / p.cv.c_blocks, cb = kb - seg * p.cv.c_blocks;
+                        const int seg = tap;
                         const int plane_a = (0x001012 >> (4 * seg)) & 0xF, plane_b = (0x010210 >> (4 * seg)) & 0xF;
                         umma::tma_load_3d(a_tile, &map_a, &full[s], cb * p.k_step, tm * kBM, plane_a);
                         umma::tma_load_3d(a_tile + kTileABytes, &map_b, &full[s], cb * p.k_step, tn * kBN, plane_b);
                     } else if constexpr (MODE == kModeConv) {
-                        const int tap = kb / p.cv.c_blocks, cb = kb - tap * p.cv.c_blocks;
-                        const int kh = tap / p.cv.KW, kw = tap - kh * p.cv.KW;
-                        const int shift = kh * p.cv.dil_h * p.cv.Wp + kw * p.cv.dil_w;
                         umma::tma_load_2d(a_tile, &map_a, &full[s], cb * p.k_step, tm * kBM + shift);
                         umma::tma_load_3d(a_tile + kTileABytes, &map_b, &full[s], cb * p.k_step, tn * kBN, tap);
                     } else if (p.batches > 1) {
@@ -174,29 +190,39 @@ tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUt
                         umma::tma_load_2d(a_tile, &map_a, &full[s], kb * p.k_step, tm * kBM);
                         umma::tma_load_2d(a_tile + kTileABytes, &map_b, &full[s], kb * p.k_step, tn * kBN);
                     }
+                    if constexpr (MODE != kModeGemm) {
+                        if (++cb == p.cv.c_blocks) {                // next filter tap (next plane pair in split mode)
+                            cb = 0; tap++;
+                            if constexpr (MODE == kModeConv) {
+                                shift += p.cv.dil_w;
+                                if (++kw == p.cv.KW) { kw = 0; shift += p.cv.dil_h * p.cv.Wp - p.cv.KW * p.cv.dil_w; }
+                            }
+                        }
+                    }
+                    if (++s == n_st) { s = 0; ph ^= 1u; }
                 }
             }
         }
     } else if (warp == 1) {
         if (lane == 0) {
-            uint32_t it = 0, local = 0;
+            uint32_t s = 0, ph = 0, local = 0;
             for (int tile = blockIdx.x; tile < total_tiles && !*abort_flag; tile += gridDim.x, local++) {
-                const uint32_t buf = local & 1u, use = (local >> 1) & 1u;
+                const uint32_t buf = local & buf_mask, use = (local >> buf_shift) & 1u;
                 if (!umma::mbar_wait(&acc_empty[buf], use ^ 1u, abort_flag)) break;
                 umma::fence_after_sync();
-                const uint32_t d_tmem = tmem_base + buf * kBN;
+                const uint32_t d_tmem = tmem_base + buf * acc_stride;
                 bool ok = true;
-                for (int kb = 0; kb < p.k_blocks; kb++, it++) {
-                    const uint32_t s = it % kSt, ph = (it / kSt) & 1u;
+                for (int kb = 0; kb < p.k_blocks; kb++) {
                     if (!umma::mbar_wait(&full[s], ph, abort_flag)) { ok = false; break; }
                     umma::fence_after_sync();
-                    const uint8_t* a_tile = tiles + (size_t)s * kStageBytes;
+                    const uint8_t* a_tile = tiles + (size_t)s * stage_bytes;
                     const uint64_t da = umma::smem_desc_k_major_sw128(a_tile);
                     const uint64_t db = umma::smem_desc_k_major_sw128(a_tile + kTileABytes);
                     #pragma unroll
                     for (int k = 0; k < kRowBytes / 32; k++)      // 32 bytes of K per instruction
                         umma::mma_ss<FP8>(d_tmem, da + (uint64_t)(k * 2), db + (uint64_t)(k * 2), idesc, (kb | k) != 0);
                     umma::mma_commit(&empty[s]);                    // the stage is free once these MMAs retire
+                    if (++s == n_st) { s = 0; ph ^= 1u; }
                 }
                 if (!ok) break;
                 umma::mma_commit(&acc_full[buf]);
@@ -205,8 +231,8 @@ tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUt
     } else {
         const int quarter = warp & 3;                               // TMEM lanes this warp may read
         const int epi = warp - 2;                                   // 0 .. kEpi-1
-        const int group = epi / kEpiG, eg = epi - group * kEpiG;     // group: which accumulator buffer's tiles this warp finishes
-        constexpr int kChunkStep = kEpiG / 4;                       // warps of a group that share a quarter alternate chunks
+        const int group = epi / epi_per_group, eg = epi - group * epi_per_group;     // group: which accumulator buffer's tiles this warp finishes
+        const int kChunkStep = epi_per_group / 4;                   // warps of a group that share a quarter alternate chunks
         constexpr int kW = tc_chunk_columns(MODE);                  // accumulator columns a warp handles at a time
         const int first_chunk = eg >> 2;
         uint32_t local = 0;
@@ -236,8 +262,8 @@ tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUt
             for (int j = 0; j < 2; j++) off32[j] = umma::swizzled_chunk<32>((uint32_t)lane, (uint32_t)j);
             bool alive = true;
             for (int tile = blockIdx.x; tile < total_tiles && alive; tile += gridDim.x, local++) {
-                const uint32_t buf = local & 1u, use = (local >> 1) & 1u;
-                if (kEpiGroups == 2 && (int)buf != group) continue;
+                const uint32_t buf = local & buf_mask, use = (local >> buf_shift) & 1u;
+                if (epi_groups > 1 && (int)buf != group) continue;
                 int tm, tn;
                 tile_coords(tile, p.tiles_m, p.tiles_n, tm, tn);
                 const int row0 = tm * kBM + quarter * 32;             // first of this warp's 32 rows = output pixels
@@ -249,7 +275,7 @@ tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUt
                 }
                 if (!umma::mbar_wait(&acc_full[buf], use, abort_flag)) break;
                 umma::fence_after_sync();
-                const uint32_t t_row = tmem_base + ((uint32_t)(quarter * 32) << 16) + buf * kBN;
+                const uint32_t t_row = tmem_base + ((uint32_t)(quarter * 32) << 16) + buf * acc_stride;
                 #pragma unroll 1
                 for (int c = first_chunk; c < kBN / kW; c += kChunkStep) {
                     const int n0 = tn * kBN + c * kW;
@@ -364,10 +390,10 @@ tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUt
             if (p.lv.zero) lv_zero = p.lv.zero_signed ? (float)*(const int8_t*)p.lv.zero : (float)*(const uint8_t*)p.lv.zero;
         }
         for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x, local++) {
-            const uint32_t buf = local & 1u, use = (local >> 1) & 1u;
-            if (kEpiGroups == 2 && (int)buf != group) continue;      // the other group's tile
+            const uint32_t buf = local & buf_mask, use = (local >> buf_shift) & 1u;
+            if (epi_groups > 1 && (int)buf != group) continue;       // another group's tile
             int tm, tn;
-            const int bt = MODE == kModeGemm ? tile / tiles_per_batch : 0;
+            const int bt = (MODE == kModeGemm && p.batches > 1) ? tile / tiles_per_batch : 0;
             tile_coords(tile - bt * tiles_per_batch, p.tiles_m, p.tiles_n, tm, tn);
             const int m = tm * kBM + quarter * 32 + lane;
             // beta * C for this tile, fetched while the tensor core is still working on it
@@ -404,8 +430,8 @@ tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUt
             float res_next[kW];
             constexpr bool with_res = MODE == kModeConv && (EPI & kEpiResidual) != 0;
             if constexpr (MODE == kModeConv) {
-                const int img = m / p.cv.plane, rem = m - img * p.cv.plane;
-                const int oh = rem / p.cv.Wp, ow = rem - oh * p.cv.Wp;
+                const int img = (int)p.cv.by_plane.div((uint32_t)m), rem = m - img * p.cv.plane;
+                const int oh = (int)p.cv.by_Wp.div((uint32_t)rem), ow = rem - oh * p.cv.Wp;
                 conv_row = img < p.cv.images && oh < p.cv.OH && ow < p.cv.OW;
                 plane_out = (size_t)p.cv.OH * p.cv.OW;
                 conv_base = ((size_t)img * p.cv.OC + (size_t)tn * kBN) * plane_out + (size_t)oh * p.cv.OW + ow;
@@ -443,7 +469,7 @@ tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUt
             if constexpr (with_res) fetch_residual(first_chunk, res_next);
             if (!umma::mbar_wait(&acc_full[buf], use, abort_flag)) break;
             umma::fence_after_sync();
-            const uint32_t t_row = tmem_base + ((uint32_t)(quarter * 32) << 16) + buf * kBN;
+            const uint32_t t_row = tmem_base + ((uint32_t)(quarter * 32) << 16) + buf * acc_stride;
             #pragma unroll 1
             for (int c = first_chunk; c < kBN / kW; c += kChunkStep) {
                 const int n0 = tn * kBN + c * kW;
