@@ -309,7 +309,11 @@ bool shifted_gemm_launch(const ShiftedGemm& g) {
     p.y_cl = g.y_channels_last;
     p.res_cl = g.residual_channels_last;
     p.stage_tx = (uint32_t)(kTileABytes + n_cols * kRowBytes);
-    p.acc_buffers = (n_cols <= 128 && !getenv("TOPS_TWO_ACC_BUFFERS")) ? 4 : 2;
+    // accumulator buffers and epilogue groups: always more buffers than groups where tensor memory has the columns
+    p.acc_buffers = n_cols <= 64 ? 8 : n_cols <= 128 ? 4 : 2;
+    p.epilogue_groups = n_cols <= 64 ? 4 : n_cols <= 128 ? 2 : (getenv("TOPS_ONE_EPILOGUE_GROUP") ? 1 : 2);
+    if (getenv("TOPS_ACC_BUFFERS")) p.acc_buffers = atoi(getenv("TOPS_ACC_BUFFERS"));           // measurement switches
+    if (getenv("TOPS_EPILOGUE_GROUPS")) p.epilogue_groups = atoi(getenv("TOPS_EPILOGUE_GROUPS"));
     const uint32_t idesc = umma::instr_desc(g.a_format, g.b_format, kBM, (uint32_t)n_cols);
     const int tiles = p.tiles_m * p.tiles_n;
     const int grid = tiles < st->sm_count ? tiles : st->sm_count;

@@ -36,7 +36,7 @@ __host__ __device__ constexpr int tc_threads(int mode, int epi = 0) { return 64 
 __host__ __device__ constexpr size_t tc_smem_bytes(int mode, int epi = 0) {
     if (mode == kModeConv && (epi & 4))
         return (size_t)tc_stages(mode, epi) * kStageBytes + 1024 /*alignment slack*/ + kRowsBarBytes + (size_t)tc_epilogue_warps(mode, epi) * kRowsWarpBytes;
-    return (size_t)tc_stages(mode, epi) * kStageBytes + 1024 /*alignment slack*/ + 256 /*barriers*/ +
+    return (size_t)tc_stages(mode, epi) * kStageBytes + 1024 /*alignment slack*/ + 384 /*barriers*/ +
            (size_t)tc_epilogue_warps(mode, epi) * kBN * 4 /*bias*/ + (size_t)tc_epilogue_warps(mode, epi) * kBN * 4 /*column scales*/ +
            (mode == kModeConv ? 0 : 4 * 32 * kStageRowWords * 4) /*output staging (row-major outputs only)*/;
 }
@@ -74,7 +74,8 @@ struct TcParams {
     int relu = 0;          // clamp the result at zero before it is stored (v > 0 ? v : 0)
     const float* residual = nullptr;   // convolution mode: float32 tensor of the output's shape added before the clamp
     LevelsOut lv;                      // convolution mode: also / instead write the result as levels for the next convolution
-    int acc_buffers = 2;               // accumulator buffers in tensor memory: 2 x 256 columns, or 4 x 128 (N <= 128, 16 epilogue warps)
+    int acc_buffers = 2;               // accumulator buffers in tensor memory: 2 x 256 columns, 4 x 128 (N <= 128) or 8 x 64 (N <= 64)
+    int epilogue_groups = 2;           // sixteen epilogue warps: how many tiles they finish at a time (1, 2 or 4 groups)
     int y_cl = 0;                      // convolution mode: Y (float32) is stored channels-last [N][OH][OW][OC] instead of NCHW
     int res_cl = 0;                    // convolution mode: the residual is stored channels-last
 };
@@ -114,10 +115,13 @@ tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUt
     // groups of eight warps normally; layers with at most 128 output channels get FOUR buffers of 128 columns and four
     // groups of four warps (one per quarter of the tile's rows): twice as many tiles in flight, and a warp meets each
     // tile's fixed work (row decode, barrier hand-offs) once per four column chunks instead of once per two.
-    const int n_buf = kEpi >= 16 ? p.acc_buffers : 2;
-    const int epi_groups = kEpi >= 16 ? n_buf : 1, epi_per_group = kEpi / epi_groups;
-    const uint32_t acc_stride = n_buf == 4 ? 128u : (uint32_t)kBN;
-    const uint32_t buf_mask = (uint32_t)n_buf - 1u, buf_shift = n_buf == 4 ? 2u : 1u;     // tile counter -> (buffer, phase) without a division
+    // More buffers than groups matter as much as the groups: a group that has finished a tile finds the next accumulator
+    // already complete instead of waiting for the copy and multiply roles to refill the buffer it has just released.
+    const int n_buf = kEpi >= 16 ? p.acc_buffers : 2;                    // 2, 4 or 8 buffers of 256, 128 or 64 columns
+    const int epi_groups = kEpi >= 16 ? p.epilogue_groups : 1, epi_per_group = kEpi / epi_groups;
+    const uint32_t acc_stride = 512u / (uint32_t)n_buf;
+    // tile counter -> (buffer, phase, group) without a division
+    const uint32_t buf_mask = (uint32_t)n_buf - 1u, buf_shift = n_buf == 8 ? 3u : n_buf == 4 ? 2u : 1u, group_mask = (uint32_t)epi_groups - 1u;
     extern __shared__ uint8_t smem_raw[];
     uint8_t* tiles = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
     uint64_t* bars = (uint64_t*)(tiles + (size_t)kSt * kStageBytes);
@@ -128,16 +132,16 @@ tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUt
     const uint32_t stage_bytes = p.stages > 0 ? p.stage_bytes : (uint32_t)kStageBytes;
     uint64_t* full = bars;                    // [kMaxStages]  TMA -> MMA
     uint64_t* empty = bars + kMaxStages;      // [kMaxStages]  MMA -> TMA
-    uint64_t* acc_full = bars + 2 * kMaxStages;   // [4]    MMA -> epilogue
-    uint64_t* acc_empty = acc_full + 4;       // [4]    epilogue -> MMA
-    uint32_t* tmem_slot = (uint32_t*)(acc_empty + 4);
+    uint64_t* acc_full = bars + 2 * kMaxStages;   // [8]    MMA -> epilogue
+    uint64_t* acc_empty = acc_full + 8;       // [8]    epilogue -> MMA
+    uint32_t* tmem_slot = (uint32_t*)(acc_empty + 8);
     volatile int* abort_flag = (volatile int*)(tmem_slot + 1);
-    float* bias_stage = (float*)(bars + 26);                   // kEpi warps x kBN floats
+    float* bias_stage = (float*)(bars + 34);                   // kEpi warps x kBN floats
     float* scale_stage = bias_stage + kEpi * kBN;              // kEpi warps x kBN floats
     uint32_t* out_stage = (uint32_t*)(scale_stage + kEpi * kBN);   // 4 warps x 32 rows x kStageRowWords (not in convolution mode)
     constexpr bool kRows = MODE == kModeConv && (EPI & kEpiRows) != 0;
     // row-linear epilogue: [barrier block of 1 KB: pipeline barriers, then one residual barrier per epilogue warp][per-warp staging]
-    uint64_t* res_bars = bars + 32;
+    uint64_t* res_bars = bars + 40;
     uint8_t* rows_stage = (uint8_t*)bars + kRowsBarBytes;
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -146,7 +150,7 @@ tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUt
 
     if (threadIdx.x == 0) {
         for (uint32_t s = 0; s < n_st; s++) { umma::mbar_init(&full[s], 1); umma::mbar_init(&empty[s], 1); }
-        for (int b = 0; b < 4; b++) { umma::mbar_init(&acc_full[b], 1); umma::mbar_init(&acc_empty[b], (uint32_t)epi_per_group); }
+        for (int b = 0; b < 8; b++) { umma::mbar_init(&acc_full[b], 1); umma::mbar_init(&acc_empty[b], (uint32_t)epi_per_group); }
         if constexpr (kRows) for (int w = 0; w < kEpi; w++) umma::mbar_init(&res_bars[w], 1);
         *abort_flag = 0;
         umma::mbar_fence_init();
@@ -263,7 +267,7 @@ tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUt
             bool alive = true;
             for (int tile = blockIdx.x; tile < total_tiles && alive; tile += gridDim.x, local++) {
                 const uint32_t buf = local & buf_mask, use = (local >> buf_shift) & 1u;
-                if (epi_groups > 1 && (int)buf != group) continue;
+                if ((int)(local & group_mask) != group) continue;
                 int tm, tn;
                 tile_coords(tile, p.tiles_m, p.tiles_n, tm, tn);
                 const int row0 = tm * kBM + quarter * 32;             // first of this warp's 32 rows = output pixels
@@ -336,10 +340,14 @@ tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUt
                                 decided = decided & (fmaf(fabsf(q), 1.9073486e-6f, fabsf(__fsub_rn(q, rq))) < 0.5f);
                                 level[e] = fminf(fmaxf(rq, lo_z), hi_z);
                             }
-                            if (!decided) {
+                            if (!decided) {                             // rare: redo only the values the fast rounding could not decide
                                 #pragma unroll
-                                for (int e = 0; e < 8; e++)
-                                    level[e] = quantize_level_exact(v[j0 + e], lv_scale, lv_zero, p.lv.zero_signed);
+                                for (int e = 0; e < 8; e++) {
+                                    const float q = __fmul_rn(v[j0 + e], lv_inv);
+                                    const float rq = __fsub_rn(__fadd_rn(q, 12582912.0f), 12582912.0f);
+                                    if (!(fmaf(fabsf(q), 1.9073486e-6f, fabsf(__fsub_rn(q, rq))) < 0.5f))
+                                        level[e] = quantize_level_exact(v[j0 + e], lv_scale, lv_zero, p.lv.zero_signed);
+                                }
                             }
                             #pragma unroll
                             for (int e = 0; e < 8; e += 2)
@@ -391,7 +399,7 @@ tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUt
         }
         for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x, local++) {
             const uint32_t buf = local & buf_mask, use = (local >> buf_shift) & 1u;
-            if (epi_groups > 1 && (int)buf != group) continue;       // another group's tile
+            if ((int)(local & group_mask) != group) continue;       // another group's tile
             int tm, tn;
             const int bt = (MODE == kModeGemm && p.batches > 1) ? tile / tiles_per_batch : 0;
             tile_coords(tile - bt * tiles_per_batch, p.tiles_m, p.tiles_n, tm, tn);
@@ -525,7 +533,10 @@ tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUt
                         #pragma unroll
                         for (int j = 0; j < kW; j++) v[j] = __fmaf_rn(p.beta, cv[j], v[j]);
                     }
-                    if (p.relu && !with_res) {
+                    // levels alone: Relu is part of the clamp below (a negative value quantises to a level <= 0, and 0 lies inside
+                    // [lo - z, hi - z]), one instruction per value less
+                    const bool relu_in_clamp = MODE == kModeConv && (EPI & kEpiLevels) != 0 && !with_res && p.relu && p.Y == nullptr;
+                    if (p.relu && !with_res && !relu_in_clamp) {
                         #pragma unroll
                         for (int j = 0; j < kW; j++) v[j] = fmaxf(v[j], 0.0f);      // same results as v > 0 ? v : 0, NaN and -0 included
                     }
@@ -549,7 +560,7 @@ tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUt
                                 // closer than 2^-19 |q|, which also catches |q| >= 2^18 and NaN -- is redone with the
                                 // reference's double division
                                 const float lo = p.lv.zero_signed ? -128.0f : 0.0f, hi = p.lv.zero_signed ? 127.0f : 255.0f;
-                                const float lo_z = __fsub_rn(lo, zf), hi_z = __fsub_rn(hi, zf);
+                                const float lo_z = relu_in_clamp ? fmaxf(__fsub_rn(lo, zf), 0.0f) : __fsub_rn(lo, zf), hi_z = __fsub_rn(hi, zf);
                                 uint32_t packed[kW / 2];
                                 #pragma unroll
                                 for (int j0 = 0; j0 < kW; j0 += 8) {
@@ -562,10 +573,14 @@ tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUt
                                         decided = decided & (fmaf(fabsf(q), 1.9073486e-6f, fabsf(__fsub_rn(q, rq))) < 0.5f);
                                         level[e] = fminf(fmaxf(rq, lo_z), hi_z);              // clamp(rq + z, lo, hi) - z, all small integers
                                     }
-                                    if (!decided) {
+                                    if (!decided) {                     // rare: redo only the values the fast rounding could not decide
                                         #pragma unroll
-                                        for (int e = 0; e < 8; e++)
-                                            level[e] = quantize_level_exact(v[j0 + e], ls, zf, p.lv.zero_signed);
+                                        for (int e = 0; e < 8; e++) {
+                                            const float q = __fmul_rn(v[j0 + e], linv);
+                                            const float rq = __fsub_rn(__fadd_rn(q, 12582912.0f), 12582912.0f);
+                                            if (!(fmaf(fabsf(q), 1.9073486e-6f, fabsf(__fsub_rn(q, rq))) < 0.5f))
+                                                level[e] = quantize_level_exact(relu_in_clamp ? fmaxf(v[j0 + e], 0.0f) : v[j0 + e], ls, zf, p.lv.zero_signed);
+                                        }
                                     }
                                     #pragma unroll
                                     for (int e = 0; e < 8; e += 2)
