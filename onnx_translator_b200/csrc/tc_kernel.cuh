@@ -99,6 +99,13 @@ __device__ __forceinline__ void tile_coords(int tile, int tiles_m, int tiles_n, 
 // Bit 2 (convolutions whose GEMM row IS the output pixel: 1 x 1, no padding, and everything float32 channels-last):
 // the epilogue moves its tiles with the copy engine -- residual in, float32 and levels out -- through per-warp
 // staging in shared memory, so no thread issues a global load or store of its own.
+// Requantisation to levels in the epilogues: q = v * (1 / s) with the CORRECTLY ROUNDED reciprocal is within 2^-23 |q| of
+// v / s (two roundings of 2^-24 each), so rounding q decides rint(v / s) for every value further than that from a
+// tie; the margin tested is twice the bound.  (The elementwise kernels use the approximate reciprocal and 2^-19.)
+constexpr float kLevelsTieMargin = 2.3841858e-7f;      // 2^-22
+__device__ __forceinline__ float levels_reciprocal(float s) {
+    return fabsf(s) < 8.5e37f ? __frcp_rn(s) : __int_as_float(0x7FC00000);      // NaN: every value takes the exact division
+}
 constexpr int kEpiPlain = 0, kEpiResidual = 1, kEpiLevels = 2, kEpiRows = 4;
 
 // Tensor maps of the row-linear epilogue (unused by every other variant): [rows][OC] matrices in boxes of 32 rows x 16 columns.
@@ -253,7 +260,7 @@ tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUt
             float lv_scale = 0.0f, lv_inv = 0.0f, lv_zero = 0.0f;
             if constexpr (with_lv) {
                 lv_scale = __ldg(p.lv.scale);
-                lv_inv = quantize_reciprocal(lv_scale);
+                lv_inv = levels_reciprocal(lv_scale);
                 if (p.lv.zero) lv_zero = p.lv.zero_signed ? (float)*(const int8_t*)p.lv.zero : (float)*(const uint8_t*)p.lv.zero;
             }
             const float lo = p.lv.zero_signed ? -128.0f : 0.0f, hi = p.lv.zero_signed ? 127.0f : 255.0f;
@@ -337,7 +344,7 @@ tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUt
                             for (int e = 0; e < 8; e++) {
                                 const float q = __fmul_rn(v[j0 + e], lv_inv);
                                 const float rq = __fsub_rn(__fadd_rn(q, 12582912.0f), 12582912.0f);
-                                decided = decided & (fmaf(fabsf(q), 1.9073486e-6f, fabsf(__fsub_rn(q, rq))) < 0.5f);
+                                decided = decided & (fmaf(fabsf(q), kLevelsTieMargin, fabsf(__fsub_rn(q, rq))) < 0.5f);
                                 level[e] = fminf(fmaxf(rq, lo_z), hi_z);
                             }
                             if (!decided) {                             // rare: redo only the values the fast rounding could not decide
@@ -345,7 +352,7 @@ tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUt
                                 for (int e = 0; e < 8; e++) {
                                     const float q = __fmul_rn(v[j0 + e], lv_inv);
                                     const float rq = __fsub_rn(__fadd_rn(q, 12582912.0f), 12582912.0f);
-                                    if (!(fmaf(fabsf(q), 1.9073486e-6f, fabsf(__fsub_rn(q, rq))) < 0.5f))
+                                    if (!(fmaf(fabsf(q), kLevelsTieMargin, fabsf(__fsub_rn(q, rq))) < 0.5f))
                                         level[e] = quantize_level_exact(v[j0 + e], lv_scale, lv_zero, p.lv.zero_signed);
                                 }
                             }
@@ -394,7 +401,7 @@ tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUt
         float lv_scale = 0.0f, lv_inv = 0.0f, lv_zero = 0.0f;
         if constexpr (MODE == kModeConv && (EPI & kEpiLevels) != 0) {
             lv_scale = __ldg(p.lv.scale);
-            lv_inv = quantize_reciprocal(lv_scale);
+            lv_inv = levels_reciprocal(lv_scale);
             if (p.lv.zero) lv_zero = p.lv.zero_signed ? (float)*(const int8_t*)p.lv.zero : (float)*(const uint8_t*)p.lv.zero;
         }
         for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x, local++) {
@@ -557,7 +564,7 @@ tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUt
                                 const float ls = lv_scale, linv = lv_inv, zf = lv_zero;
                                 // eight values at a time on the fast path without branches (their dependency chains
                                 // interleave); a group in which the fast rounding could not decide some value -- a tie
-                                // closer than 2^-19 |q|, which also catches |q| >= 2^18 and NaN -- is redone with the
+                                // closer than 2^-22 |q|, which also catches |q| >= 2^21 and NaN -- is redone with the
                                 // reference's double division
                                 const float lo = p.lv.zero_signed ? -128.0f : 0.0f, hi = p.lv.zero_signed ? 127.0f : 255.0f;
                                 const float lo_z = relu_in_clamp ? fmaxf(__fsub_rn(lo, zf), 0.0f) : __fsub_rn(lo, zf), hi_z = __fsub_rn(hi, zf);
@@ -570,7 +577,7 @@ tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUt
                                     for (int e = 0; e < 8; e++) {
                                         const float q = __fmul_rn(v[j0 + e], linv);
                                         const float rq = __fsub_rn(__fadd_rn(q, 12582912.0f), 12582912.0f);
-                                        decided = decided & (fmaf(fabsf(q), 1.9073486e-6f, fabsf(__fsub_rn(q, rq))) < 0.5f);
+                                        decided = decided & (fmaf(fabsf(q), kLevelsTieMargin, fabsf(__fsub_rn(q, rq))) < 0.5f);
                                         level[e] = fminf(fmaxf(rq, lo_z), hi_z);              // clamp(rq + z, lo, hi) - z, all small integers
                                     }
                                     if (!decided) {                     // rare: redo only the values the fast rounding could not decide
@@ -578,7 +585,7 @@ tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUt
                                         for (int e = 0; e < 8; e++) {
                                             const float q = __fmul_rn(v[j0 + e], linv);
                                             const float rq = __fsub_rn(__fadd_rn(q, 12582912.0f), 12582912.0f);
-                                            if (!(fmaf(fabsf(q), 1.9073486e-6f, fabsf(__fsub_rn(q, rq))) < 0.5f))
+                                            if (!(fmaf(fabsf(q), kLevelsTieMargin, fabsf(__fsub_rn(q, rq))) < 0.5f))
                                                 level[e] = quantize_level_exact(relu_in_clamp ? fmaxf(v[j0 + e], 0.0f) : v[j0 + e], ls, zf, p.lv.zero_signed);
                                         }
                                     }
