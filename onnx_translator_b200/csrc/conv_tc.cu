@@ -312,8 +312,16 @@ bool shifted_gemm_launch(const ShiftedGemm& g) {
     // accumulator buffers and epilogue groups: always more buffers than groups where tensor memory has the columns
     p.acc_buffers = n_cols <= 64 ? 8 : n_cols <= 128 ? 4 : 2;
     p.epilogue_groups = n_cols <= 64 ? 4 : n_cols <= 128 ? 2 : (getenv("TOPS_ONE_EPILOGUE_GROUP") ? 1 : 2);
-    if (getenv("TOPS_ACC_BUFFERS")) p.acc_buffers = atoi(getenv("TOPS_ACC_BUFFERS"));           // measurement switches
-    if (getenv("TOPS_EPILOGUE_GROUPS")) p.epilogue_groups = atoi(getenv("TOPS_EPILOGUE_GROUPS"));
+    // measurement switches; anything tensor memory (512 columns) or the warp layout cannot hold is ignored
+    if (const char* e = getenv("TOPS_ACC_BUFFERS")) {
+        const int b = atoi(e);
+        if ((b == 2 || b == 4 || b == 8) && b * n_cols <= 512) p.acc_buffers = b;
+    }
+    if (const char* e = getenv("TOPS_EPILOGUE_GROUPS")) {
+        const int gr = atoi(e);
+        if (gr == 1 || gr == 2 || gr == 4) p.epilogue_groups = gr;
+    }
+    if (p.epilogue_groups > p.acc_buffers) p.epilogue_groups = p.acc_buffers;
     const uint32_t idesc = umma::instr_desc(g.a_format, g.b_format, kBM, (uint32_t)n_cols);
     const int tiles = p.tiles_m * p.tiles_n;
     const int grid = tiles < st->sm_count ? tiles : st->sm_count;
@@ -338,9 +346,12 @@ bool shifted_gemm_launch(const ShiftedGemm& g) {
     {
         const uint32_t bytes = (uint32_t)(kTileABytes + n_cols * kRowBytes);
         const int room = tc_stages(kModeConv, epi) * kStageBytes;
-        int st = room / (int)bytes;
+        // At most 128 output channels: the multiplies of a K block take less time than the barrier round trip of the two
+        // single-thread roles, so two K blocks travel per stage.
+        const int per_stage = (n_cols <= 128 && p.k_blocks >= 2 && !getenv("TOPS_ONE_K_BLOCK_PER_STAGE")) ? 2 : 1;
+        int st = room / ((int)bytes * per_stage);
         if (st > 8) st = 8;
-        if (n_cols < kBN && !getenv("TOPS_FIXED_STAGES")) { p.stages = st; p.stage_bytes = bytes; }
+        if (n_cols < kBN && !getenv("TOPS_FIXED_STAGES")) { p.stages = st; p.stage_bytes = bytes * (uint32_t)per_stage; p.kb_per_stage = per_stage; }
     }
 #define TOPS_CONV_LAUNCH(F8, E)                                                                                              \
     do {                                                                                                                     \

@@ -67,6 +67,7 @@ struct TcParams {
     uint32_t stage_tx = kStageBytes;   // bytes the two copies of a pipeline stage deliver (less when the B box is narrower than kBN)
     int stages = 0;                    // pipeline stages in use (0: as many as the kernel variant reserves room for) ...
     uint32_t stage_bytes = kStageBytes;   // ... of this many bytes each: a narrower B box leaves room for more, smaller stages
+    int kb_per_stage = 1;              // K blocks (of stage_tx bytes each, back to back) that share one stage and its pair of barriers
     int batches = 1;       // Gemm mode: independent problems of one shape; the tensor maps are then 3-D
                            // (K, rows, batch) and Y holds the results back to back
     ConvView cv;           // convolution mode only
@@ -181,25 +182,23 @@ tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUt
                 const int bt = (MODE == kModeGemm && p.batches > 1) ? tile / tiles_per_batch : 0;
                 tile_coords(tile - bt * tiles_per_batch, p.tiles_m, p.tiles_n, tm, tn);
                 int cb = 0, tap = 0, kw = 0, shift = 0;             // channel block inside the tap / plane pair, tap, its column, its row shift
-                for (int kb = 0; kb < p.k_blocks; kb++) {
-                    if (!umma::mbar_wait(&empty[s], ph ^ 1u, abort_flag)) break;
-                    uint8_t* a_tile = tiles + (size_t)s * stage_bytes;
-                    umma::mbar_expect_tx(&full[s], p.stage_tx);
+                // the two copies of K block kb, into the stage memory at a_tile, completing on bar
+                auto copy_k_block = [&](int kb, uint8_t* a_tile, uint64_t* bar) {
                     if constexpr (MODE == kModeSplit) {
                         // smallest products first: (a3 b1) (a2 b2) (a1 b3) (a2 b1) (a1 b2) (a1 b1)
                         const int seg = tap;
                         const int plane_a = (0x001012 >> (4 * seg)) & 0xF, plane_b = (0x010210 >> (4 * seg)) & 0xF;
-                        umma::tma_load_3d(a_tile, &map_a, &full[s], cb * p.k_step, tm * kBM, plane_a);
-                        umma::tma_load_3d(a_tile + kTileABytes, &map_b, &full[s], cb * p.k_step, tn * kBN, plane_b);
+                        umma::tma_load_3d(a_tile, &map_a, bar, cb * p.k_step, tm * kBM, plane_a);
+                        umma::tma_load_3d(a_tile + kTileABytes, &map_b, bar, cb * p.k_step, tn * kBN, plane_b);
                     } else if constexpr (MODE == kModeConv) {
-                        umma::tma_load_2d(a_tile, &map_a, &full[s], cb * p.k_step, tm * kBM + shift);
-                        umma::tma_load_3d(a_tile + kTileABytes, &map_b, &full[s], cb * p.k_step, tn * kBN, tap);
+                        umma::tma_load_2d(a_tile, &map_a, bar, cb * p.k_step, tm * kBM + shift);
+                        umma::tma_load_3d(a_tile + kTileABytes, &map_b, bar, cb * p.k_step, tn * kBN, tap);
                     } else if (p.batches > 1) {
-                        umma::tma_load_3d(a_tile, &map_a, &full[s], kb * p.k_step, tm * kBM, bt);
-                        umma::tma_load_3d(a_tile + kTileABytes, &map_b, &full[s], kb * p.k_step, tn * kBN, bt);
+                        umma::tma_load_3d(a_tile, &map_a, bar, kb * p.k_step, tm * kBM, bt);
+                        umma::tma_load_3d(a_tile + kTileABytes, &map_b, bar, kb * p.k_step, tn * kBN, bt);
                     } else {
-                        umma::tma_load_2d(a_tile, &map_a, &full[s], kb * p.k_step, tm * kBM);
-                        umma::tma_load_2d(a_tile + kTileABytes, &map_b, &full[s], kb * p.k_step, tn * kBN);
+                        umma::tma_load_2d(a_tile, &map_a, bar, kb * p.k_step, tm * kBM);
+                        umma::tma_load_2d(a_tile + kTileABytes, &map_b, bar, kb * p.k_step, tn * kBN);
                     }
                     if constexpr (MODE != kModeGemm) {
                         if (++cb == p.cv.c_blocks) {                // next filter tap (next plane pair in split mode)
@@ -210,6 +209,24 @@ tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUt
                             }
                         }
                     }
+                };
+                int kb = 0;
+                if (MODE == kModeConv && p.kb_per_stage == 2) {
+                    // narrow layers: two K blocks share a stage and its pair of barriers (one round trip for both)
+                    for (; kb + 2 <= p.k_blocks; kb += 2) {
+                        if (!umma::mbar_wait(&empty[s], ph ^ 1u, abort_flag)) break;
+                        uint8_t* a_tile = tiles + (size_t)s * stage_bytes;
+                        umma::mbar_expect_tx(&full[s], 2u * p.stage_tx);
+                        copy_k_block(kb, a_tile, &full[s]);
+                        copy_k_block(kb + 1, a_tile + p.stage_tx, &full[s]);
+                        if (++s == n_st) { s = 0; ph ^= 1u; }
+                    }
+                }
+                for (; kb < p.k_blocks; kb++) {
+                    if (!umma::mbar_wait(&empty[s], ph ^ 1u, abort_flag)) break;
+                    uint8_t* a_tile = tiles + (size_t)s * stage_bytes;
+                    umma::mbar_expect_tx(&full[s], p.stage_tx);
+                    copy_k_block(kb, a_tile, &full[s]);
                     if (++s == n_st) { s = 0; ph ^= 1u; }
                 }
             }
@@ -223,15 +240,29 @@ tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUt
                 umma::fence_after_sync();
                 const uint32_t d_tmem = tmem_base + buf * acc_stride;
                 bool ok = true;
-                for (int kb = 0; kb < p.k_blocks; kb++) {
-                    if (!umma::mbar_wait(&full[s], ph, abort_flag)) { ok = false; break; }
-                    umma::fence_after_sync();
-                    const uint8_t* a_tile = tiles + (size_t)s * stage_bytes;
+                auto multiply_k_block = [&](const uint8_t* a_tile, uint32_t accumulate) {
                     const uint64_t da = umma::smem_desc_k_major_sw128(a_tile);
                     const uint64_t db = umma::smem_desc_k_major_sw128(a_tile + kTileABytes);
                     #pragma unroll
-                    for (int k = 0; k < kRowBytes / 32; k++)      // 32 bytes of K per instruction
-                        umma::mma_ss<FP8>(d_tmem, da + (uint64_t)(k * 2), db + (uint64_t)(k * 2), idesc, (kb | k) != 0);
+                    for (int k = 0; k < kRowBytes / 32; k++)          // 32 bytes of K per instruction
+                        umma::mma_ss<FP8>(d_tmem, da + (uint64_t)(k * 2), db + (uint64_t)(k * 2), idesc, accumulate | (uint32_t)k);
+                };
+                int kb = 0;
+                if (MODE == kModeConv && p.kb_per_stage == 2) {
+                    for (; kb + 2 <= p.k_blocks; kb += 2) {
+                        if (!umma::mbar_wait(&full[s], ph, abort_flag)) { ok = false; break; }
+                        umma::fence_after_sync();
+                        const uint8_t* a_tile = tiles + (size_t)s * stage_bytes;
+                        multiply_k_block(a_tile, (uint32_t)kb);
+                        multiply_k_block(a_tile + p.stage_tx, 1u);
+                        umma::mma_commit(&empty[s]);                // the stage is free once these MMAs retire
+                        if (++s == n_st) { s = 0; ph ^= 1u; }
+                    }
+                }
+                for (; ok && kb < p.k_blocks; kb++) {
+                    if (!umma::mbar_wait(&full[s], ph, abort_flag)) { ok = false; break; }
+                    umma::fence_after_sync();
+                    multiply_k_block(tiles + (size_t)s * stage_bytes, (uint32_t)kb);
                     umma::mma_commit(&empty[s]);                    // the stage is free once these MMAs retire
                     if (++s == n_st) { s = 0; ph ^= 1u; }
                 }
