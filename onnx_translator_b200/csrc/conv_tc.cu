@@ -330,7 +330,7 @@ bool shifted_gemm_launch(const ShiftedGemm& g) {
     // Row-linear epilogue: the GEMM row is the output pixel (no padded rows to drop) and every float32 tensor the
     // epilogue touches is channels-last, so residual, output and levels are [rows][M] matrices the copy engine moves.
     EpilogueMaps em{};
-    const bool rows_linear = !g.fp8 && taps == 1 && g.Hp == g.OH && g.Wp == g.OW && (g.M % 16) == 0 &&
+    const bool rows_linear = !g.fp8 && taps == 1 && g.Hp == g.OH && g.Wp == g.OW && (g.M % 16) == 0 && g.M <= kRowsMaxChannels &&
         (g.Y != nullptr || g.lv.z != nullptr) && (g.Y == nullptr || (g.y_channels_last && g.dy == DTYPE_FLOAT32)) &&
         (g.residual == nullptr || g.residual_channels_last) && (!g.bias || g.bias_dtype == DTYPE_FLOAT32) &&
         (g.lv.z == nullptr || (g.lv.S == 1 && g.lv.pt == 0 && g.lv.pl == 0 && g.lv.Hz == g.OH && g.lv.Wz == g.OW && g.lv.Cz == g.M)) &&

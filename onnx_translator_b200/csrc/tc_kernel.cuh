@@ -22,7 +22,9 @@ constexpr int kModeGemm = 0, kModeConv = 1, kModeSplit = 2;
 // The plain convolution epilogue (no residual, no levels) leaves room for the fourth stage: its layers are the ones with
 // long K loops (a 3 x 3 convolution over 256 channels has 36 K blocks per tile), where the copy latency is what the
 // multiplier waits for.
-__host__ __device__ constexpr int tc_stages(int mode, int epi = 0) { return mode == kModeConv && epi != 0 ? 3 : kStages; }
+// The row-linear epilogue (EPI bit 2) with residual AND levels keeps two stages: its layers have short K loops and are
+// bound by the epilogue, and the third stage's room holds staging and the per-channel constants instead.
+__host__ __device__ constexpr int tc_stages(int mode, int epi = 0) { return mode != kModeConv || epi == 0 ? kStages : (epi & 7) == 7 ? 2 : 3; }
 // Epilogue warps: 4 for the Gemm modes.  Convolution mode is bound by its epilogue (short K loops, strided NCHW
 // stores, residual loads, quantisation to levels), so it handles 16 accumulator columns at a time -- half the
 // registers per thread -- and runs 16 epilogue warps, or 12 where the residual is compiled in (its prefetch
@@ -30,12 +32,16 @@ __host__ __device__ constexpr int tc_stages(int mode, int epi = 0) { return mode
 __host__ __device__ constexpr int tc_epilogue_warps(int mode, int epi = 0) { return mode != kModeConv ? 4 : ((epi & 4) ? 16 : (epi & 1) ? 12 : 16); }
 // Row-linear epilogue (EPI bit 2): bytes of shared memory each epilogue warp stages its tiles in -- 32 rows x 64 bytes of
 // float32 output, the same of residual input, 32 rows x 32 bytes of levels -- and where the warps' barriers live.
-constexpr int kRowsOutBytes = 2048, kRowsResBytes = 2048, kRowsLevBytes = 1024, kRowsWarpBytes = 5120, kRowsBarBytes = 1024;
+constexpr int kRowsOutBytes = 2048, kRowsResBytes = 2048, kRowsLevBytes = 1024, kRowsBarBytes = 1024;
+__host__ __device__ constexpr int rows_warp_bytes(int epi) { return kRowsOutBytes + ((epi & 1) ? kRowsResBytes : 0) + ((epi & 2) ? kRowsLevBytes : 0); }
+// ... and of the per-channel constants it keeps there for the whole launch: x_scale * w_scale[n] and beta * bias[n] of up
+// to kRowsMaxChannels output channels, computed once per CTA instead of once per value.
+constexpr int kRowsMaxChannels = 2048, kRowsColumnBytes = 2 * kRowsMaxChannels * 4;
 __host__ __device__ constexpr int tc_chunk_columns(int mode) { return mode == kModeConv ? 16 : 32; }
 __host__ __device__ constexpr int tc_threads(int mode, int epi = 0) { return 64 + 32 * tc_epilogue_warps(mode, epi); }
 __host__ __device__ constexpr size_t tc_smem_bytes(int mode, int epi = 0) {
     if (mode == kModeConv && (epi & 4))
-        return (size_t)tc_stages(mode, epi) * kStageBytes + 1024 /*alignment slack*/ + kRowsBarBytes + (size_t)tc_epilogue_warps(mode, epi) * kRowsWarpBytes;
+        return (size_t)tc_stages(mode, epi) * kStageBytes + 1024 /*alignment slack*/ + kRowsBarBytes + kRowsColumnBytes + (size_t)tc_epilogue_warps(mode, epi) * rows_warp_bytes(epi);
     return (size_t)tc_stages(mode, epi) * kStageBytes + 1024 /*alignment slack*/ + 384 /*barriers*/ +
            (size_t)tc_epilogue_warps(mode, epi) * kBN * 4 /*bias*/ + (size_t)tc_epilogue_warps(mode, epi) * kBN * 4 /*column scales*/ +
            (mode == kModeConv ? 0 : 4 * 32 * kStageRowWords * 4) /*output staging (row-major outputs only)*/;
@@ -150,7 +156,9 @@ tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUt
     constexpr bool kRows = MODE == kModeConv && (EPI & kEpiRows) != 0;
     // row-linear epilogue: [barrier block of 1 KB: pipeline barriers, then one residual barrier per epilogue warp][per-warp staging]
     uint64_t* res_bars = bars + 40;
-    uint8_t* rows_stage = (uint8_t*)bars + kRowsBarBytes;
+    float* col_scale = (float*)((uint8_t*)bars + kRowsBarBytes);    // [kRowsMaxChannels], then the biases
+    float* col_bias = col_scale + kRowsMaxChannels;
+    uint8_t* rows_stage = (uint8_t*)bars + kRowsBarBytes + kRowsColumnBytes;
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int tiles_per_batch = p.tiles_m * p.tiles_n;
@@ -166,6 +174,14 @@ tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUt
         umma::tma_prefetch_desc(&map_b);
     }
     if (warp == 1) umma::tmem_alloc(tmem_slot, 512);
+    if constexpr (kRows) {
+        float alpha = p.alpha;
+        if (p.fs.a_scale) alpha = __fmul_rn(alpha, __ldg(p.fs.a_scale));
+        for (int n = threadIdx.x; n < p.N; n += blockDim.x) {
+            col_scale[n] = p.fs.b_per_column ? __fmul_rn(alpha, __ldg(p.fs.b_scale + n)) : alpha;
+            col_bias[n] = p.bias.mode == kBiasPerColumn ? __fmul_rn(p.beta, __ldg((const float*)p.bias.ptr + n)) : 0.0f;
+        }
+    }
     umma::fence_before_sync();
     __syncthreads();
     umma::fence_after_sync();
@@ -281,13 +297,11 @@ tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUt
         if constexpr (kRows) {
             // ---- row-linear epilogue: every global access is a tile copy ------------------------------------------------
             constexpr bool with_res = (EPI & kEpiResidual) != 0, with_lv = (EPI & kEpiLevels) != 0;
-            uint8_t* st_out = rows_stage + (size_t)epi * kRowsWarpBytes;
+            uint8_t* st_out = rows_stage + (size_t)epi * rows_warp_bytes(EPI);
             uint8_t* st_res = st_out + kRowsOutBytes;
-            uint8_t* st_lv = st_res + kRowsResBytes;
+            uint8_t* st_lv = st_res + (with_res ? kRowsResBytes : 0);
             uint64_t* res_bar = &res_bars[epi];
             uint32_t res_phase = 0;
-            float alpha = p.alpha;
-            if (p.fs.a_scale) alpha = __fmul_rn(alpha, __ldg(p.fs.a_scale));
             float lv_scale = 0.0f, lv_inv = 0.0f, lv_zero = 0.0f;
             if constexpr (with_lv) {
                 lv_scale = __ldg(p.lv.scale);
@@ -325,25 +339,21 @@ tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUt
                     uint32_t r[kW];
                     umma::tmem_load_chunk<kW>(t_row + (uint32_t)(c * kW), r);
                     float v[kW];
-                    // per-channel scale and bias straight from global memory: every lane reads the same 64 bytes
-                    float sc[kW];
-                    #pragma unroll
-                    for (int j = 0; j < kW; j += 4) {
-                        const float4 s4 = p.fs.b_per_column ? __ldg((const float4*)(p.fs.b_scale + n0 + j)) : make_float4(1.0f, 1.0f, 1.0f, 1.0f);
-                        sc[j] = s4.x; sc[j + 1] = s4.y; sc[j + 2] = s4.z; sc[j + 3] = s4.w;
-                    }
-                    float bs[kW];
-                    #pragma unroll
-                    for (int j = 0; j < kW; j += 4) {
-                        const float4 b4 = p.bias.mode == kBiasPerColumn ? __ldg((const float4*)((const float*)p.bias.ptr + n0 + j)) : make_float4(0.0f, 0.0f, 0.0f, 0.0f);
-                        bs[j] = b4.x; bs[j + 1] = b4.y; bs[j + 2] = b4.z; bs[j + 3] = b4.w;
-                    }
                     umma::tmem_load_wait();
+                    // per-channel constants from shared memory (every lane reads the same 16 bytes: a broadcast)
                     #pragma unroll
-                    for (int j = 0; j < kW; j++) {
-                        const float scale = p.fs.b_per_column ? __fmul_rn(alpha, sc[j]) : alpha;
-                        v[j] = __fmul_rn(scale, __uint_as_float(r[j]));
-                        if (p.bias.mode == kBiasPerColumn) v[j] = __fadd_rn(v[j], __fmul_rn(p.beta, bs[j]));
+                    for (int j = 0; j < kW; j += 4) {
+                        const float4 s4 = *(const float4*)(col_scale + n0 + j);
+                        v[j] = __fmul_rn(s4.x, __uint_as_float(r[j]));         v[j + 1] = __fmul_rn(s4.y, __uint_as_float(r[j + 1]));
+                        v[j + 2] = __fmul_rn(s4.z, __uint_as_float(r[j + 2])); v[j + 3] = __fmul_rn(s4.w, __uint_as_float(r[j + 3]));
+                    }
+                    if (p.bias.mode == kBiasPerColumn) {
+                        #pragma unroll
+                        for (int j = 0; j < kW; j += 4) {
+                            const float4 b4 = *(const float4*)(col_bias + n0 + j);
+                            v[j] = __fadd_rn(v[j], b4.x); v[j + 1] = __fadd_rn(v[j + 1], b4.y);
+                            v[j + 2] = __fadd_rn(v[j + 2], b4.z); v[j + 3] = __fadd_rn(v[j + 3], b4.w);
+                        }
                     }
                     if constexpr (with_res) {
                         if (!umma::mbar_wait(res_bar, res_phase, abort_flag)) { alive = false; break; }
