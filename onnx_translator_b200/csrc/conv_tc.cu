@@ -353,10 +353,18 @@ bool shifted_gemm_launch(const ShiftedGemm& g) {
         if (st > 8) st = 8;
         if (n_cols < kBN && !getenv("TOPS_FIXED_STAGES")) { p.stages = st; p.stage_bytes = bytes * (uint32_t)per_stage; p.kb_per_stage = per_stage; }
     }
+    // programmatic stream serialisation: the kernel waits for its predecessor itself (first statement); TOPS_PDL=0 switches it off
+    static const bool pdl = [] { const char* e = getenv("TOPS_PDL"); return !(e && e[0] == '0'); }();
+    cudaLaunchAttribute pdl_attr[1];
+    pdl_attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    pdl_attr[0].val.programmaticStreamSerializationAllowed = 1;
 #define TOPS_CONV_LAUNCH(F8, E)                                                                                              \
     do {                                                                                                                     \
         if (!ensure_dynamic_smem((const void*)tc_kernel<F8, kModeConv, E>, tc_smem_bytes(kModeConv, E))) return false;          \
-        tc_kernel<F8, kModeConv, E><<<grid, tc_threads(kModeConv, E), tc_smem_bytes(kModeConv, E), s>>>(map_a, map_b, p, idesc, em);   \
+        cudaLaunchConfig_t cfg = {};                                                                                         \
+        cfg.gridDim = dim3(grid); cfg.blockDim = dim3(tc_threads(kModeConv, E)); cfg.dynamicSmemBytes = tc_smem_bytes(kModeConv, E); \
+        cfg.stream = s; cfg.attrs = pdl_attr; cfg.numAttrs = pdl ? 1 : 0;                                                    \
+        check_cuda(cudaLaunchKernelEx(&cfg, tc_kernel<F8, kModeConv, E>, map_a, map_b, p, idesc, em), "conv2d_forward (tensor cores)"); \
     } while (0)
     if (g.fp8) TOPS_CONV_LAUNCH(true, kEpiPlain);
     else if (epi == kEpiPlain) TOPS_CONV_LAUNCH(false, kEpiPlain);

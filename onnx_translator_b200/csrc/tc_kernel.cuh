@@ -122,6 +122,10 @@ template <bool FP8, int MODE, int EPI = kEpiPlain>
 __global__ void __launch_bounds__(tc_threads(MODE, EPI), 1)
 tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, const TcParams p,
                const uint32_t idesc, const __grid_constant__ EpilogueMaps em) {
+    // Launched with programmatic stream serialisation the CTAs are scheduled while the previous kernel of the stream drains
+    // (one SM at a time, as its CTAs leave); nothing here touches memory before that kernel has completed.
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     constexpr int kSt = tc_stages(MODE, EPI), kEpi = tc_epilogue_warps(MODE, EPI);
     // Sixteen epilogue warps work as groups, one per accumulator buffer: consecutive tiles of the CTA are finished by
     // different groups, so the latency chain of one tile's epilogue (accumulator ready -> tensor memory load ->
