@@ -38,6 +38,8 @@ struct QGeom {
     int KH, KW, KHz, KWz;  // original and space-to-depth filter extents
     int M;
     int sub, srcW, src_plane;   // sub = 1: the layout pass reads every second row and column of a srcW-wide source plane
+    FastDiv by_W, by_plane, by_groups, by_Wz;   // the layout passes' index arithmetic: W, H * W, ceil(C / 8), Wz (set by set_divisors)
+    void set_divisors() { by_W.set((uint32_t)W); by_plane.set((uint32_t)(H * W)); by_groups.set((uint32_t)((C + 7) >> 3)); by_Wz.set((uint32_t)Wz); }
 };
 
 __device__ __forceinline__ uint16_t level_bits(int v) {        // small integer -> bfloat16 bits (exact for |v| <= 256)
@@ -67,21 +69,32 @@ __global__ void __launch_bounds__(256) activations_to_levels(const void* __restr
         const int p = p0 + pp;
         if (p < plane) {
             size_t src_p = (size_t)p;
-            if (g.sub) { const int hs = p / g.W; src_p = (size_t)(2 * hs) * g.srcW + 2 * (p - hs * g.W); }
+            if (g.sub) { const int hs = (int)g.by_W.div((uint32_t)p); src_p = (size_t)(2 * hs) * g.srcW + 2 * (p - hs * g.W); }
             // this thread's 16 values (8 channel pairs) first, so that all loads are in flight together
             float v[16];
-            #pragma unroll
-            for (int i = 0; i < 8; i++) {
+            const size_t cs = (size_t)g.src_plane;                      // distance between channels
+            const size_t first = ((size_t)n * g.C + c0 + 2 * cq) * cs + src_p;    // channel c0 + 2 cq of this position
+            if (XK == 0 && c0 + 64 <= g.C) {                             // a full tile of float32 values: one address, constant steps
+                const float* src = (const float*)x + first;
                 #pragma unroll
-                for (int e = 0; e < 2; e++) {
-                    const int c = c0 + 2 * (cq + 4 * i) + e;
-                    float value = 0.0f;
-                    if (c < g.C) {
-                        const size_t at = ((size_t)n * g.C + c) * (size_t)g.src_plane + src_p;
-                        if (XK == 0) value = __ldg((const float*)x + at);
-                        else { const uint8_t code = ((const uint8_t*)x)[at]; value = (float)(SIGNED ? (int)(int8_t)code : (int)code); }
+                for (int i = 0; i < 8; i++) {
+                    v[2 * i] = __ldg(src + (size_t)(8 * i) * cs);
+                    v[2 * i + 1] = __ldg(src + (size_t)(8 * i + 1) * cs);
+                }
+            } else {
+                #pragma unroll
+                for (int i = 0; i < 8; i++) {
+                    #pragma unroll
+                    for (int e = 0; e < 2; e++) {
+                        const int c = c0 + 2 * (cq + 4 * i) + e;
+                        float value = 0.0f;
+                        if (c < g.C) {
+                            const size_t at = first + (size_t)(8 * i + e) * cs;
+                            if (XK == 0) value = __ldg((const float*)x + at);
+                            else { const uint8_t code = ((const uint8_t*)x)[at]; value = (float)(SIGNED ? (int)(int8_t)code : (int)code); }
+                        }
+                        v[2 * i + e] = value;
                     }
-                    v[2 * i + e] = value;
                 }
             }
             const float zf = (float)zero;
@@ -111,7 +124,7 @@ __global__ void __launch_bounds__(256) activations_to_levels(const void* __restr
     for (int pass = 0; pass < 2; pass++) {
         const int pp = pos0 + pass * 32, p = p0 + pp;
         if (p >= plane) continue;
-        const int h = p / g.W, w = p - h * g.W;
+        const int h = (int)g.by_W.div((uint32_t)p), w = p - h * g.W;
         int A = h + g.pt, B = w + g.pl, slot = 0;
         if (g.S == 2) { slot = ((A & 1) * 2 + (B & 1)) * g.C; A >>= 1; B >>= 1; }
         uint16_t* dst = z + (((size_t)n * g.Hz + A) * g.Wz + B) * g.Cz + slot + c;
@@ -127,28 +140,51 @@ __global__ void __launch_bounds__(256) activations_to_levels(const void* __restr
 }
 
 // The same for few input channels (C <= 8, e.g. the RGB stem): the 64-channel tiles above would be almost
-// empty, so here a thread owns one plane position and all of its channels.
-template <int XK, bool SIGNED>
-__global__ void __launch_bounds__(256) activations_to_levels_few_channels(const void* __restrict__ x, uint16_t* __restrict__ z, QGeom g,
-                                                                          const float* __restrict__ scale_ptr, const void* __restrict__ zero_ptr) {
-    const int plane = g.H * g.W, n = blockIdx.y;
-    const int p = blockIdx.x * blockDim.x + threadIdx.x;
-    if (p >= plane) return;
+// empty.  Here a thread owns one CELL of the levels tensor -- for stride 2 the 2 x 2 input positions
+// that fold into it, all channels -- and writes it whole, padding channels and cells outside the image
+// included (zeros), 16 bytes at a time: every cell is written, so the tensor needs no clearing, and no
+// store is narrower than a sector's half.  (One thread per input position wrote its C levels as C
+// separate 2-byte stores.)
+// CC: the channel count when it is 1, 3 or 4 (the cell's levels then stay in registers), 0 for any other.
+template <int XK, bool SIGNED, int CC>
+__global__ void __launch_bounds__(256) cells_from_few_channels(const void* __restrict__ x, uint16_t* __restrict__ z, QGeom g,
+                                                               const float* __restrict__ scale_ptr, const void* __restrict__ zero_ptr) {
+    const int cells = g.Hz * g.Wz, n = blockIdx.y;
+    const int q = blockIdx.x * blockDim.x + threadIdx.x;
+    if (q >= cells) return;
     int zero = 0;
     if (zero_ptr) zero = SIGNED ? (int)*(const int8_t*)zero_ptr : (int)*(const uint8_t*)zero_ptr;
     const float zf = (float)zero;
     float scale = 1.0f, inv = 1.0f;
     if (XK == 0) { scale = __ldg(scale_ptr); inv = quantize_reciprocal(scale); }
-    const int h = p / g.W, w = p - h * g.W;
-    int A = h + g.pt, B = w + g.pl, slot = 0;
-    if (g.S == 2) { slot = ((A & 1) * 2 + (B & 1)) * g.C; A >>= 1; B >>= 1; }
-    uint16_t* dst = z + (((size_t)n * g.Hz + A) * g.Wz + B) * g.Cz + slot;
-    for (int c = 0; c < g.C; c++) {
-        const size_t at = ((size_t)n * g.C + c) * (size_t)plane + (size_t)p;
-        float level;
-        if (XK == 0) level = quantize_level_8bit<SIGNED ? DTYPE_INT8 : DTYPE_UINT8>(__ldg((const float*)x + at), scale, inv, zf);
-        else { const uint8_t code = ((const uint8_t*)x)[at]; level = __fsub_rn((float)(SIGNED ? (int)(int8_t)code : (int)code), zf); }
-        dst[c] = (uint16_t)(__float_as_uint(level) >> 16);
+    const int a = (int)g.by_Wz.div((uint32_t)q), b = q - a * g.Wz;
+    const size_t plane = (size_t)g.H * g.W;
+    const int C = CC ? CC : g.C;
+    uint16_t level[32];                                           // S * S * C <= 32 channels of the cell, then the padding
+    #pragma unroll
+    for (int k = 0; k < 32; k++) level[k] = 0;
+    #pragma unroll
+    for (int rs = 0; rs < 4; rs++) {
+        if (rs >= g.S * g.S) break;
+        const int r = g.S == 2 ? rs >> 1 : 0, sx = g.S == 2 ? rs & 1 : 0;
+        const int h = g.S * a + r - g.pt, w = g.S * b + sx - g.pl;
+        if (h < 0 || h >= g.H || w < 0 || w >= g.W) continue;     // a padding position: its levels stay zero
+        const size_t at = (size_t)n * C * plane + (size_t)h * g.W + w;
+        #pragma unroll
+        for (int c = 0; c < 8; c++) {
+            if (c >= C) break;
+            float lv;
+            if (XK == 0) lv = quantize_level_8bit<SIGNED ? DTYPE_INT8 : DTYPE_UINT8>(__ldg((const float*)x + at + (size_t)c * plane), scale, inv, zf);
+            else { const uint8_t code = ((const uint8_t*)x)[at + (size_t)c * plane]; lv = __fsub_rn((float)(SIGNED ? (int)(int8_t)code : (int)code), zf); }
+            level[rs * C + c] = (uint16_t)(__float_as_uint(lv) >> 16);
+        }
+    }
+    uint4* dst = (uint4*)(z + ((size_t)n * cells + q) * g.Cz);      // Cz is a multiple of 8: 16-byte pieces
+    #pragma unroll
+    for (int k = 0; k < 4; k++) {
+        if (8 * k >= g.Cz) break;
+        dst[k] = make_uint4(level[8 * k] | (uint32_t)level[8 * k + 1] << 16, level[8 * k + 2] | (uint32_t)level[8 * k + 3] << 16,
+                            level[8 * k + 4] | (uint32_t)level[8 * k + 5] << 16, level[8 * k + 6] | (uint32_t)level[8 * k + 7] << 16);
     }
 }
 
@@ -167,10 +203,14 @@ __global__ void __launch_bounds__(256) channels_last_to_levels(const void* __res
     if (XK == 0) { scale = __ldg(scale_ptr); inv = quantize_reciprocal(scale); }
     const bool vec = (g.C & 7) == 0;
     for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
-        const int cg = (int)(i % groups);
-        const size_t t = i / groups;
-        const int p = (int)(t % plane), n = (int)(t / plane);
-        const int h = p / g.W, w = p - h * g.W;
+        // (image, position, channel group) of item i: three divisions by run-time values, by multiply-high while i fits
+        // 31 bits (positions always do: the caller refuses more than 2^31 of them)
+        int cg;
+        uint32_t t;
+        if (i < 0x80000000ull) { t = g.by_groups.div((uint32_t)i); cg = (int)((uint32_t)i - t * (uint32_t)groups); }
+        else { t = (uint32_t)(i / groups); cg = (int)(i - (size_t)t * groups); }
+        const int n = (int)g.by_plane.div(t), p = (int)(t - (uint32_t)n * (uint32_t)plane);
+        const int h = (int)g.by_W.div((uint32_t)p), w = p - h * g.W;
         size_t src_p = (size_t)p;
         if (g.sub) src_p = (size_t)(2 * h) * g.srcW + 2 * w;
         const size_t at = ((size_t)n * g.src_plane + src_p) * g.C + (size_t)cg * 8;
@@ -297,6 +337,7 @@ static int qconv_run(const char* name, const QConvCall& q) {
         g.H = OH; g.W = OW; g.S = 1; g.pt = g.pl = 0; g.Hz = OH; g.Wz = OW; g.Cz = (C + 7) & ~7;
         g.sub = 1; g.srcW = W; g.src_plane = H * W;
     }
+    g.set_divisors();
     const bool zero_given = q.x_zero && q.x_zero->data;
     const bool x_is_float = !q.x_levels && X->dtype == DTYPE_FLOAT32;
     const int code_dt = q.x_levels ? DTYPE_INT8 : x_is_float ? (zero_given ? (int)q.x_zero->dtype : DTYPE_INT8) : (int)X->dtype;
@@ -358,10 +399,12 @@ static int qconv_run(const char* name, const QConvCall& q) {
         if (cudaMallocAsync(&z, z_bytes + 128, s) != cudaSuccess) { cudaGetLastError(); return qconv_fail(name, TOPS_ERR_OOM, "scratch", nullptr); }
         // padding cells and padding channels are zero; a 1x1 convolution without padding over a channel
         // count that is a multiple of 8 has neither
-        const bool every_cell_written = g.S == 1 && g.Hz == g.H && g.Wz == g.W && g.Cz == C;
-        ok = every_cell_written || TOPS_CUDA_OK(cudaMemsetAsync(z, 0, z_bytes + 128, s));
+        const bool few = !x_cl && C <= 8;                          // the per-cell kernel writes every cell and padding channel itself
+        const bool every_cell_written = few || (g.S == 1 && g.Hz == g.H && g.Wz == g.W && g.Cz == C);
+        ok = every_cell_written ? (!few || TOPS_CUDA_OK(cudaMemsetAsync((char*)z + z_bytes, 0, 128, s)))
+                                : TOPS_CUDA_OK(cudaMemsetAsync(z, 0, z_bytes + 128, s));
         const dim3 grid((H * W + 63) / 64, N, (C + 63) / 64);
-        const dim3 grid_few((H * W + 255) / 256, N);
+        const dim3 grid_few((g.Hz * g.Wz + 255) / 256, N);
         const void* zero_ptr = zero_given ? q.x_zero->data : nullptr;
         const float* scale_ptr = (const float*)q.x_scale->data;
         const bool is_signed = code_dt == DTYPE_INT8;
@@ -372,10 +415,18 @@ static int qconv_run(const char* name, const QConvCall& q) {
             else if (is_signed)                channels_last_to_levels<1, true><<<cl_grid, 256, 0, s>>>(X->data, (uint16_t*)z, g, N, scale_ptr, zero_ptr);
             else                               channels_last_to_levels<1, false><<<cl_grid, 256, 0, s>>>(X->data, (uint16_t*)z, g, N, scale_ptr, zero_ptr);
         } else if (C <= 8) {
-            if (x_is_float && is_signed)       activations_to_levels_few_channels<0, true><<<grid_few, 256, 0, s>>>(X->data, (uint16_t*)z, g, scale_ptr, zero_ptr);
-            else if (x_is_float)               activations_to_levels_few_channels<0, false><<<grid_few, 256, 0, s>>>(X->data, (uint16_t*)z, g, scale_ptr, zero_ptr);
-            else if (is_signed)                activations_to_levels_few_channels<1, true><<<grid_few, 256, 0, s>>>(X->data, (uint16_t*)z, g, scale_ptr, zero_ptr);
-            else                               activations_to_levels_few_channels<1, false><<<grid_few, 256, 0, s>>>(X->data, (uint16_t*)z, g, scale_ptr, zero_ptr);
+#define TOPS_FEW(XK, SG)                                                                                                        \
+            do {                                                                                                                \
+                if (C == 1)      cells_from_few_channels<XK, SG, 1><<<grid_few, 256, 0, s>>>(X->data, (uint16_t*)z, g, scale_ptr, zero_ptr); \
+                else if (C == 3) cells_from_few_channels<XK, SG, 3><<<grid_few, 256, 0, s>>>(X->data, (uint16_t*)z, g, scale_ptr, zero_ptr); \
+                else if (C == 4) cells_from_few_channels<XK, SG, 4><<<grid_few, 256, 0, s>>>(X->data, (uint16_t*)z, g, scale_ptr, zero_ptr); \
+                else             cells_from_few_channels<XK, SG, 0><<<grid_few, 256, 0, s>>>(X->data, (uint16_t*)z, g, scale_ptr, zero_ptr); \
+            } while (0)
+            if (x_is_float && is_signed) TOPS_FEW(0, true);
+            else if (x_is_float)         TOPS_FEW(0, false);
+            else if (is_signed)          TOPS_FEW(1, true);
+            else                         TOPS_FEW(1, false);
+#undef TOPS_FEW
         } else if (x_is_float) {
             if (is_signed) activations_to_levels<0, true><<<grid, 256, 0, s>>>(X->data, (uint16_t*)z, g, scale_ptr, zero_ptr);
             else           activations_to_levels<0, false><<<grid, 256, 0, s>>>(X->data, (uint16_t*)z, g, scale_ptr, zero_ptr);
