@@ -287,6 +287,9 @@ QCONV_CASES = [  # N, C, H, W, M, k, pad, stride, x_dt, zero, relu, bias
     (2, 16, 20, 20, 40, 3, 1, 1, "uint8", 7, False, True),
     (3, 8, 18, 18, 24, 5, 2, 1, "int8", 1, True, False),
     (2, 5, 33, 31, 16, 7, 3, 2, "int8", -4, True, True),
+    (2, 1, 21, 23, 16, 3, 1, 2, "uint8", 9, True, True),           # one channel (its own instance of the per-cell layout kernel)
+    (2, 4, 18, 18, 24, 3, 1, 1, "int8", -2, False, True),          # four channels (likewise)
+    (1, 2, 16, 20, 16, 5, 2, 2, "int8", 3, True, False),           # two channels, stride 2: the generic instance
 ]
 
 
