@@ -366,6 +366,9 @@ def run_ours(args):
         for i, it in enumerate(plan):
             per_op[it["label"]] = round(it["bytes"] / 1e9 / (per_launch_ms[i] / 1e3), 1)
         worst = sorted(per_op.items(), key=lambda kv: kv[1])[:5]
+        if os.environ.get("BENCH_ALL_OPS"):                         # every launch of the sweep, slowest first, on stderr
+            for label, gbps in sorted(per_op.items(), key=lambda kv: kv[1]):
+                print(f"{gbps:8.1f} GB/s  {label}", file=sys.stderr)
         line = {
             "metric": "per-op GB/s (aggregate over the broadcast elementwise sweep)",
             "value": round(world * bytes_step / 1e9 / (step_ms_max / 1e3), 2),
