@@ -360,6 +360,7 @@ bool shifted_gemm_launch(const ShiftedGemm& g) {
     pdl_attr[0].val.programmaticStreamSerializationAllowed = 1;
 #define TOPS_CONV_LAUNCH(F8, E)                                                                                              \
     do {                                                                                                                     \
+        static_assert(tc_smem_bytes(kModeConv, E) <= 227 * 1024, "the variant's shared memory exceeds what a CTA can have");    \
         if (!ensure_dynamic_smem((const void*)tc_kernel<F8, kModeConv, E>, tc_smem_bytes(kModeConv, E))) return false;          \
         cudaLaunchConfig_t cfg = {};                                                                                         \
         cfg.gridDim = dim3(grid); cfg.blockDim = dim3(tc_threads(kModeConv, E)); cfg.dynamicSmemBytes = tc_smem_bytes(kModeConv, E); \

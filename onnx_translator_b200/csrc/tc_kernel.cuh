@@ -19,12 +19,14 @@ constexpr int kStageRowWords = 36;                 // 32 words of payload + 4 of
 // stage for more epilogue warps -- more loads and stores in flight per SM.  A warp may only read the quarter of
 // tensor memory given by its index modulo 4, so the warps that share a quarter take alternate column chunks.
 constexpr int kModeGemm = 0, kModeConv = 1, kModeSplit = 2;
-// The plain convolution epilogue (no residual, no levels) leaves room for the fourth stage: its layers are the ones with
-// long K loops (a 3 x 3 convolution over 256 channels has 36 K blocks per tile), where the copy latency is what the
-// multiplier waits for.
+// The plain and the levels-only epilogue stage nothing but their per-channel constants and have room for four stages
+// (a 3 x 3 convolution over 256 channels has 36 K blocks per tile, and the copy latency is what the multiplier waits
+// for: the levels-only layers of a ResNet-50-shaped graph gained 6-14 % from the fourth stage); the residual variant
+// was measured slower with four (76 -> 86 us for its one layer there) and the row-linear epilogue (EPI bit 2) stages
+// its tiles in shared memory: three.
 // The row-linear epilogue (EPI bit 2) with residual AND levels keeps two stages: its layers have short K loops and are
 // bound by the epilogue, and the third stage's room holds staging and the per-channel constants instead.
-__host__ __device__ constexpr int tc_stages(int mode, int epi = 0) { return mode != kModeConv || epi == 0 ? kStages : (epi & 7) == 7 ? 2 : 3; }
+__host__ __device__ constexpr int tc_stages(int mode, int epi = 0) { return mode != kModeConv || (epi & 5) == 0 ? kStages : (epi & 7) == 7 ? 2 : 3; }
 // Epilogue warps: 4 for the Gemm modes.  Convolution mode is bound by its epilogue (short K loops, strided NCHW
 // stores, residual loads, quantisation to levels), so it handles 16 accumulator columns at a time -- half the
 // registers per thread -- and runs 16 epilogue warps, or 12 where the residual is compiled in (its prefetch
