@@ -26,13 +26,17 @@ __device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
 __device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
     asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
 }
+// One attempt: returns at once when the phase is complete; otherwise the thread may be SUSPENDED until it completes or
+// until the time hint runs out (nanoseconds) -- a suspended warp issues nothing, where a short system-chosen limit makes
+// every waiting warp a polling loop that shares its scheduler's issue slots with the warps that have work.
+constexpr uint32_t kSuspendHintNs = 200000u;
 __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
     uint32_t ok;
     asm volatile(
         "{\n\t.reg .pred p;\n\t"
-        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
         "selp.b32 %0, 1, 0, p;\n\t}"
-        : "=r"(ok) : "r"(smem_u32(bar)), "r"(parity) : "memory");
+        : "=r"(ok) : "r"(smem_u32(bar)), "r"(parity), "r"(kSuspendHintNs) : "memory");
     return ok != 0;
 }
 // Waits for the phase with the given parity.  Returns false when the budget ran out or another
@@ -42,7 +46,7 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volati
     const long long t0 = clock64();
     for (;;) {
         #pragma unroll 1
-        for (int i = 0; i < 64; i++) if (mbar_try_wait(bar, parity)) return true;
+        for (int i = 0; i < 8; i++) if (mbar_try_wait(bar, parity)) return true;
         if (*abort_flag) return false;
         if (clock64() - t0 > budget_cycles) { *abort_flag = 1; return false; }
     }
