@@ -83,7 +83,11 @@ __global__ void __launch_bounds__(256) gemm_exact_kernel(const void* __restrict_
 // slab, one output each, in increasing k -- the reference's summation order, so the result stays bit-identical.
 constexpr int kSkM = 4, kSkN = 16, kSkK = 128;
 
-template <bool EXACT_PRODUCTS>
+// F32_IN: both operands are float32 -- the copy threads then issue all of their loads before they use any (with the
+// run-time dtype switch every load waited for the one before it, and a slab took several memory latencies to arrive:
+// the K = 4096 classifier of the small CNN went from about 90 to 60 us; what is left is the chain of 4096 dependent
+// double-precision additions the reference's summation order imposes -- copying further ahead changed nothing).
+template <bool EXACT_PRODUCTS, bool F32_IN>
 __global__ void __launch_bounds__(256) gemm_skinny_kernel(const void* __restrict__ A, const void* __restrict__ B,
                                                            void* __restrict__ Y, int da, int db, int dy,
                                                            GemmShape g, BiasView bias, double alpha, double beta, BatchStrides batch) {
@@ -96,6 +100,32 @@ __global__ void __launch_bounds__(256) gemm_skinny_kernel(const void* __restrict
     const int chunks = (g.K + kSkK - 1) / kSkK;
     auto fill = [&](int chunk, int buf, int first, int step) {
         const int k0 = chunk * kSkK;
+        if constexpr (F32_IN) {
+            constexpr int kTotal = (kSkM + kSkN) * kSkK, kMost = (kTotal + 191) / 192;      // elements per copy thread at most
+            float v[kMost];
+            #pragma unroll
+            for (int t = 0; t < kMost; t++) {
+                const int e = first + t * step, row = e / kSkK, kk = e - row * kSkK, k = k0 + kk;
+                v[t] = 0.0f;
+                if (e < kTotal && k < g.K) {
+                    if (row < kSkM) {
+                        const int m = m0 + row;
+                        if (m < g.M) v[t] = __ldg((const float*)A + a_base + (g.transA ? (size_t)k * g.lda + m : (size_t)m * g.lda + k));
+                    } else {
+                        const int n = n0 + row - kSkM;
+                        if (n < g.N) v[t] = __ldg((const float*)B + b_base + (g.transB ? (size_t)n * g.ldb + k : (size_t)k * g.ldb + n));
+                    }
+                }
+            }
+            #pragma unroll
+            for (int t = 0; t < kMost; t++) {
+                const int e = first + t * step, row = e / kSkK, kk = e - row * kSkK;
+                if (e >= kTotal) break;
+                if (row < kSkM) sa[buf][row][kk] = (double)v[t];
+                else sb[buf][row - kSkM][kk] = (double)v[t];
+            }
+            return;
+        }
         for (int e = first; e < (kSkM + kSkN) * kSkK; e += step) {
             const int row = e / kSkK, kk = e - row * kSkK, k = k0 + kk;
             double v = 0.0;
@@ -179,10 +209,14 @@ bool gemm_exact(const Tensor* A, const Tensor* B, Tensor* Y, const GemmShape& g,
         void* y = (char*)Y->data + (size_t)first * batch.y * ey;
         if (skinny) {
             const dim3 sgrid((g.N + kSkN - 1) / kSkN, (g.M + kSkM - 1) / kSkM, nb);
-            if (exact) gemm_skinny_kernel<true><<<sgrid, 256, 0, current_stream()>>>(a, b, y, (int)A->dtype, (int)B->dtype, (int)Y->dtype, g, bias,
-                                                                                     (double)alpha, (double)beta, batch);
-            else gemm_skinny_kernel<false><<<sgrid, 256, 0, current_stream()>>>(a, b, y, (int)A->dtype, (int)B->dtype, (int)Y->dtype, g, bias,
-                                                                                (double)alpha, (double)beta, batch);
+            const bool f32 = A->dtype == DTYPE_FLOAT32 && B->dtype == DTYPE_FLOAT32;
+#define TOPS_SKINNY(EX, F) gemm_skinny_kernel<EX, F><<<sgrid, 256, 0, current_stream()>>>(a, b, y, (int)A->dtype, (int)B->dtype, (int)Y->dtype, g, bias, \
+                                                                                       (double)alpha, (double)beta, batch)
+            if (exact && f32) TOPS_SKINNY(true, true);
+            else if (exact)   TOPS_SKINNY(true, false);
+            else if (f32)     TOPS_SKINNY(false, true);
+            else              TOPS_SKINNY(false, false);
+#undef TOPS_SKINNY
             continue;
         }
         if (exact) gemm_exact_kernel<true><<<grid, 256, 0, current_stream()>>>(a, b, y, (int)A->dtype, (int)B->dtype, (int)Y->dtype, g, bias,
