@@ -204,13 +204,19 @@ bool gemm_tensor_core(const Tensor* A, const Tensor* B, Tensor* Y, const GemmSha
     const int tiles = p.tiles_m * p.tiles_n * batches;
     const int grid = tiles < st->sm_count ? tiles : st->sm_count;
     cudaStream_t s = current_stream();
-    if (fp8) {
-        if (!ensure_dynamic_smem((const void*)tc_kernel<true, kModeGemm>, tc_smem_bytes(kModeGemm))) return true;    // error recorded
-        tc_kernel<true, kModeGemm><<<grid, tc_threads(kModeGemm), tc_smem_bytes(kModeGemm), s>>>(map_a, map_b, p, idesc, EpilogueMaps{});
-    } else {
-        if (!ensure_dynamic_smem((const void*)tc_kernel<false, kModeGemm>, tc_smem_bytes(kModeGemm))) return true;
-        tc_kernel<false, kModeGemm><<<grid, tc_threads(kModeGemm), tc_smem_bytes(kModeGemm), s>>>(map_a, map_b, p, idesc, EpilogueMaps{});
-    }
+    // few K blocks per tile: the epilogue is what the launch waits for, so it gets eight warps instead of four
+    const bool short_k = p.k_blocks <= 8 && !getenv("TOPS_NO_SHORT_K_GEMM");
+#define TOPS_GEMM_LAUNCH(F8, E)                                                                                                   \
+    do {                                                                                                                          \
+        static_assert(tc_smem_bytes(kModeGemm, E) <= 227 * 1024, "the variant's shared memory exceeds what a CTA can have");      \
+        if (!ensure_dynamic_smem((const void*)tc_kernel<F8, kModeGemm, E>, tc_smem_bytes(kModeGemm, E))) return true;  /* error recorded */ \
+        tc_kernel<F8, kModeGemm, E><<<grid, tc_threads(kModeGemm, E), tc_smem_bytes(kModeGemm, E), s>>>(map_a, map_b, p, idesc, EpilogueMaps{}); \
+    } while (0)
+    if (fp8 && short_k) TOPS_GEMM_LAUNCH(true, kEpiShortK);
+    else if (fp8)       TOPS_GEMM_LAUNCH(true, kEpiPlain);
+    else if (short_k)   TOPS_GEMM_LAUNCH(false, kEpiShortK);
+    else                TOPS_GEMM_LAUNCH(false, kEpiPlain);
+#undef TOPS_GEMM_LAUNCH
     TOPS_CHECK_LAUNCH("gemm_forward (tensor cores)");
     count_tensor_core_launch();
     return true;

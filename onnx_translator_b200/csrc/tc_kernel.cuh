@@ -26,12 +26,17 @@ constexpr int kModeGemm = 0, kModeConv = 1, kModeSplit = 2;
 // its tiles in shared memory: three.
 // The row-linear epilogue (EPI bit 2) with residual AND levels keeps two stages: its layers have short K loops and are
 // bound by the epilogue, and the third stage's room holds staging and the per-channel constants instead.
-__host__ __device__ constexpr int tc_stages(int mode, int epi = 0) { return mode != kModeConv || (epi & 5) == 0 ? kStages : (epi & 7) == 7 ? 2 : 3; }
+// Gemm mode, EPI bit 3 (short reductions: a handful of K blocks per tile): the epilogue bounds such a launch -- four warps
+// carry every output of a 128 x 256 tile through scale, convert and store -- so that variant runs eight epilogue warps
+// (two per quarter of the tile's rows, alternate column chunks) and gives one pipeline stage for their staging.
+__host__ __device__ constexpr int tc_stages(int mode, int epi = 0) {
+    return mode != kModeConv ? ((epi & 8) ? 3 : kStages) : (epi & 5) == 0 ? kStages : (epi & 7) == 7 ? 2 : 3;
+}
 // Epilogue warps: 4 for the Gemm modes.  Convolution mode is bound by its epilogue (short K loops, strided NCHW
 // stores, residual loads, quantisation to levels), so it handles 16 accumulator columns at a time -- half the
 // registers per thread -- and runs 16 epilogue warps, or 12 where the residual is compiled in (its prefetch
 // registers do not fit the 96-register budget of 18 warps without spilling; measured slower).
-__host__ __device__ constexpr int tc_epilogue_warps(int mode, int epi = 0) { return mode != kModeConv ? 4 : ((epi & 4) ? 16 : (epi & 1) ? 12 : 16); }
+__host__ __device__ constexpr int tc_epilogue_warps(int mode, int epi = 0) { return mode != kModeConv ? ((epi & 8) ? 8 : 4) : ((epi & 4) ? 16 : (epi & 1) ? 12 : 16); }
 // Row-linear epilogue (EPI bit 2): bytes of shared memory each epilogue warp stages its tiles in -- 32 rows x 64 bytes of
 // float32 output, the same of residual input, 32 rows x 32 bytes of levels -- and where the warps' barriers live.
 constexpr int kRowsOutBytes = 2048, kRowsResBytes = 2048, kRowsLevBytes = 1024, kRowsBarBytes = 1024;
@@ -46,7 +51,7 @@ __host__ __device__ constexpr size_t tc_smem_bytes(int mode, int epi = 0) {
         return (size_t)tc_stages(mode, epi) * kStageBytes + 1024 /*alignment slack*/ + kRowsBarBytes + kRowsColumnBytes + (size_t)tc_epilogue_warps(mode, epi) * rows_warp_bytes(epi);
     return (size_t)tc_stages(mode, epi) * kStageBytes + 1024 /*alignment slack*/ + 384 /*barriers*/ +
            (size_t)tc_epilogue_warps(mode, epi) * kBN * 4 /*bias*/ + (size_t)tc_epilogue_warps(mode, epi) * kBN * 4 /*column scales*/ +
-           (mode == kModeConv ? 0 : 4 * 32 * kStageRowWords * 4) /*output staging (row-major outputs only)*/;
+           (mode == kModeConv ? 0 : tc_epilogue_warps(mode, epi) * 32 * kStageRowWords * 4) /*output staging (row-major outputs only)*/;
 }
 
 // Convolution as shifted GEMMs over a zero-padded channels-last copy of the input: row q of the
@@ -115,7 +120,7 @@ constexpr float kLevelsTieMargin = 2.3841858e-7f;      // 2^-22
 __device__ __forceinline__ float levels_reciprocal(float s) {
     return fabsf(s) < 8.5e37f ? __frcp_rn(s) : __int_as_float(0x7FC00000);      // NaN: every value takes the exact division
 }
-constexpr int kEpiPlain = 0, kEpiResidual = 1, kEpiLevels = 2, kEpiRows = 4;
+constexpr int kEpiPlain = 0, kEpiResidual = 1, kEpiLevels = 2, kEpiRows = 4, kEpiShortK = 8;     // the last: Gemm mode only
 
 // Tensor maps of the row-linear epilogue (unused by every other variant): [rows][OC] matrices in boxes of 32 rows x 16 columns.
 struct EpilogueMaps { CUtensorMap y, res, lv; };
@@ -435,7 +440,7 @@ tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUt
             if (lane == 0) umma::bulk_wait_all();                   // the staging buffers outlive every store that reads them
         } else {
         float* my_bias = bias_stage + epi * kBN;                     // this warp's private copy: no cross-warp sync
-        uint32_t* my_stage = out_stage + quarter * 32 * kStageRowWords;
+        uint32_t* my_stage = out_stage + epi * 32 * kStageRowWords;       // one staging area per epilogue warp
         float* my_scale = scale_stage + epi * kBN;
         int staged_tn = -1;
         float alpha = p.alpha;

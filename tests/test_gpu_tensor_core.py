@@ -49,6 +49,9 @@ GEMM_CASES = [  # M, N, K, a_dt, b_dt, out_dt, bias
     (512, 768, 1024, "float32", "float32", "float32", "col"),           # float32 inputs: three-way bfloat16 split
     (1024, 1024, 256, "float32", "float32", "float32", None),
     (640, 520, 2048, "float32", "float32", "bfloat16", "row"),
+    (1024, 1024, 128, "bfloat16", "bfloat16", "bfloat16", "col"),      # few K blocks: the variant with eight epilogue warps
+    (300, 700, 512, "float16", "float16", "float16", "matrix"),
+    (512, 520, 1024, "float8_e4m3", "float8_e5m2", "bfloat16", "row"),
 ]
 
 
